@@ -1,0 +1,9 @@
+"""decidra_b200: B200-native (sm_100a) state-once question path behind the reference's Engine API.
+
+The compute lives in ``libdecidra_b200.so`` (hand-written CUDA, see ``csrc/``); this package is the
+thin host mirror of the reference interface. There is no CPU fallback.
+"""
+from .config import ModelConfig, Options, d3_config, make_config, tiny_config
+from .engine import Engine, EngineError, HostStateCache, StateCache
+
+__all__ = ["ModelConfig", "Options", "d3_config", "make_config", "tiny_config", "Engine", "EngineError", "HostStateCache", "StateCache"]

@@ -1,0 +1,103 @@
+"""ctypes loader of ``libdecidra_b200.so``. There is no fallback: if the CUDA library is missing or
+cannot be loaded, importing the engine fails with an explicit error."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from .config import ModelConfig, Options
+
+LIB_PATH = Path(__file__).resolve().parent / "libdecidra_b200.so"
+
+OK, E_INVALID, E_OOM, E_UNSUPPORTED, E_CUDA, E_TIMEOUT = 0, 1, 2, 3, 4, 5
+PROF_NAMES = ("gemm", "attn", "gdn", "elementwise", "readout")
+
+
+class Info(C.Structure):
+    _fields_ = [
+        ("device", C.c_int32), ("sm_count", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+        ("device_name", C.c_char * 128), ("hidden", C.c_int32), ("num_layers", C.c_int32), ("readout_rows", C.c_int32),
+        ("supports_vision", C.c_int32), ("weight_bytes", C.c_uint64), ("workspace_bytes", C.c_uint64),
+    ]
+
+
+class ProfEntry(C.Structure):
+    _fields_ = [("ms", C.c_double), ("work", C.c_double), ("launches", C.c_int64)]
+
+
+# name -> (restype, argtypes); every symbol declared in include/decidra_b200.h
+P, I, F, SZ = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+I32P, U32P, FP = C.POINTER(C.c_int32), C.POINTER(C.c_uint32), C.POINTER(C.c_float)
+SIGNATURES = {
+    "dcd_engine_create": (I, [C.POINTER(ModelConfig), C.POINTER(Options), I, C.POINTER(P)]),
+    "dcd_engine_destroy": (None, [P]),
+    "dcd_last_error": (C.c_char_p, [P]),
+    "dcd_engine_info": (I, [P, C.POINTER(Info)]),
+    "dcd_engine_init_random": (I, [P, C.c_uint64]),
+    "dcd_engine_load_tensor": (I, [P, I, I, FP, SZ]),
+    "dcd_engine_read_tensor": (I, [P, I, I, FP, SZ]),
+    "dcd_rebind_blas": (I, [P]),
+    "dcd_capture_state": (I, [P, U32P, SZ, P, C.POINTER(P)]),
+    "dcd_readout_state_once_batch": (I, [P, P, C.POINTER(U32P), C.POINTER(SZ), SZ, FP]),
+    "dcd_readout_state_once_flat": (I, [P, P, U32P, U32P, SZ, FP]),
+    "dcd_readout_state_once_device": (I, [P, P, P, P, SZ, SZ, SZ, P]),
+    "dcd_capture_state_device": (I, [P, P, SZ, C.POINTER(P)]),
+    "dcd_decision_logits_split": (I, [P, U32P, SZ, SZ, FP]),
+    "dcd_state_free": (None, [P, P]),
+    "dcd_state_tokens": (SZ, [P]),
+    "dcd_state_pos_end": (SZ, [P]),
+    "dcd_state_bytes": (SZ, [P]),
+    "dcd_state_offload": (I, [P, P, C.POINTER(P)]),
+    "dcd_state_restore": (I, [P, P, C.POINTER(P)]),
+    "dcd_host_state_free": (None, [P]),
+    "dcd_state_zero_gdn_state": (I, [P, P, I]),
+    "dcd_state_zero_gdn_hist": (I, [P, P, I]),
+    "dcd_state_read_tensor": (I, [P, P, I, I, FP, C.POINTER(SZ)]),
+    "dcd_trim_pools": (I, [P]),
+    "dcd_mem_info": (I, [P, C.POINTER(SZ), C.POINTER(SZ)]),
+    "dcd_timer_begin": (I, [P]),
+    "dcd_timer_end": (I, [P]),
+    "dcd_timer_seconds": (C.c_double, [P]),
+    "dcd_vision_encode": (I, [P, P, SZ]),
+    "dcd_engine_sync": (I, [P]),
+    "dcd_profile_enable": (I, [P, I]),
+    "dcd_profile_read": (I, [P, C.POINTER(ProfEntry)]),
+    "dcd_launch_count": (C.c_int64, [P]),
+    "dcd_debug_layer_outputs": (I, [P, FP, SZ]),
+    "dcd_block_cascade_mask": (I, [SZ, SZ, C.POINTER(C.c_uint8)]),
+    "dcd_plan_chunks": (I, [C.POINTER(SZ), SZ, SZ, SZ, SZ, SZ, I32P, I32P, I32P]),
+    "dcd_decode_answer": (I, [FP, I, F, I, FP, FP]),
+    "dcd_pack": (I, [P, I32P, SZ, C.c_int32, I32P, I32P, I32P, I32P]),
+    "dcd_k_gemm_bf16_tc": (I, [P, P, P, I, I, I, I, I, I, P, P]),
+    "dcd_k_gemm_fma": (I, [P, P, P, I, I, I, I, P]),
+    "dcd_k_rmsnorm": (I, [P, P, P, I, I, F, I, I, P]),
+    "dcd_k_add_rmsnorm": (I, [P, P, P, P, P, I, I, F, I, P]),
+    "dcd_k_rmsnorm_gated": (I, [P, P, I, P, P, I, I, I, F, I, P]),
+    "dcd_k_silu_mul": (I, [P, P, P, SZ, I, P]),
+    "dcd_k_add": (I, [P, P, P, SZ, I, P]),
+    "dcd_k_conv1d_silu": (I, [P, I, P, P, P, P, P, I, I, I, P]),
+    "dcd_k_gdn_prepare": (I, [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, P]),
+    "dcd_k_gdn_recurrent": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
+    "dcd_k_qk_norm_rope": (I, [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F, P, I, P]),
+    "dcd_k_attention": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I, P]),
+    "dcd_k_readout": (I, [P, P, P, I, I, I, P]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the CUDA library; raise if it is absent (build it with ``python -m decidra_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m decidra_b200.build`. "
+                "decidra_b200 has no CPU or PyTorch fallback.")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib

@@ -1,0 +1,66 @@
+// Shared device helpers: storage-type traits (f32 / bf16), rounding, warp reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+
+// Device error word codes (written with atomicCAS so the first error wins).
+enum : int {
+  DERR_NONE = 0,
+  DERR_TOKEN_RANGE = 1,   // token id >= vocab
+  DERR_EMPTY_ITEM = 2,    // a packed sequence has length <= 0
+  DERR_GEMM_TIMEOUT = 3,  // a bounded mbarrier wait gave up in the tcgen05 GEMM
+  DERR_ATTN_TIMEOUT = 4,
+  DERR_POSITION_RANGE = 5 // RoPE position beyond the table
+};
+
+__device__ __forceinline__ void set_err(int* err, int code) {
+  if (err) atomicCAS(err, 0, code);
+}
+
+template <typename T> struct Ty;
+template <> struct Ty<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float rnd(float v) { return v; }
+};
+template <> struct Ty<bf16> {
+  static __device__ __forceinline__ float ld(const bf16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024 (multiple of 32). `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float sigmoid_f(float g) { return 1.0f / (1.0f + expf(-g)); }
+
+#define CUDA_TRY(expr)                          \
+  do {                                          \
+    cudaError_t _e = (expr);                    \
+    if (_e != cudaSuccess) return _e;           \
+  } while (0)

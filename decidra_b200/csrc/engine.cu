@@ -1,0 +1,1148 @@
+// Host orchestration and C ABI of the state-once question path.
+//
+// Mirrors, in C++ behind include/decidra_b200.h, what juanqui/decidra's Engine does for this
+// path: Engine::capture_state_mm (native/src/engine.rs:4616-4763),
+// Engine::state_once_batch_rows(_inner) (:4866-4987), run_layer_batch (:1725-1788),
+// full_attention_batch (:1790-2142), gdn_batch (:2144-2591), mlp (:2794-2885),
+// decision_logits_split (:4585-4601) and StateCache offload/restore (:559-648).
+// Differences by design: one fused projection GEMM per mixer (q|gate|k|v, and
+// qkv|z|b|a), SwiGLU folded into the gate/up GEMM epilogue, no K/V concatenation copies
+// (attention reads the cached state and the question's own rows in place), no host round
+// trip before the readout, packing metadata built on the device.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/decidra_b200.h"
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+#include "host_logic.h"
+#include "kernels.h"
+
+namespace {
+
+thread_local std::string g_create_error;
+
+struct Prof {
+  struct Pair { cudaEvent_t a, b; int kind; double work; };
+  std::vector<Pair> pairs;
+  std::vector<cudaEvent_t> pool;
+  bool on = false;
+  dcd_prof_entry acc[DCD_PROF_COUNT] = {};
+};
+
+struct LayerW {
+  bool full = false;
+  void *input_norm = nullptr, *post_norm = nullptr, *w_gu = nullptr, *w_down = nullptr;
+  void *w_qkv = nullptr, *w_o = nullptr, *qnorm = nullptr, *knorm = nullptr;
+  void *w_gin = nullptr, *w_out = nullptr, *conv = nullptr, *gnorm = nullptr;
+  float *A_log = nullptr, *dt_bias = nullptr;
+  TcTensorMap tm_gu, tm_down, tm_qkv, tm_o, tm_gin, tm_out;
+};
+
+}  // namespace
+
+struct dcd_state {
+  size_t state_len = 0, pos_end = 0, bytes = 0;
+  void* block = nullptr;
+  std::vector<void*> k, v, hist;
+  std::vector<float*> gstate;
+};
+
+struct dcd_host_state {
+  size_t state_len = 0, pos_end = 0, bytes = 0;
+  void* block = nullptr;  // pinned host copy of the device block
+};
+
+struct dcd_engine {
+  dcd_model_config c;
+  dcd_options o;
+  int device = 0, sm_count = 0, cc_major = 0, cc_minor = 0;
+  char device_name[128] = {};
+  bool bf = false;
+  size_t esz = 4;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  int64_t launches = 0;
+
+  // derived sizes
+  int H = 0, I = 0, qcols = 0, kvcols = 0, qkv_n = 0, conv_dim = 0, vd = 0, gin_n = 0, gu_rows = 0, rhalf = 0;
+  int Tm = 0;  // workspace rows
+
+  // weights
+  std::vector<void*> allocs;
+  std::vector<LayerW> layers;
+  void *embed = nullptr, *final_norm = nullptr;
+  float* readout = nullptr;
+  void *cos_t = nullptr, *sin_t = nullptr;
+  size_t weight_bytes = 0, workspace_bytes = 0;
+  bool weights_ready = false;
+
+  // workspace
+  void *x = nullptr, *h = nullptr, *x1 = nullptr, *mix = nullptr, *big = nullptr, *q = nullptr, *kown = nullptr;
+  void *bufA = nullptr, *bufB = nullptr, *conv = nullptr, *act = nullptr;
+  float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
+  uint32_t* d_ids = nullptr;
+  int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr;
+  int* d_err = nullptr;
+  int max_batch = 0;
+
+  // pinned staging
+  uint32_t* h_ids = nullptr;
+  int32_t* h_lens = nullptr;
+  float* h_logits = nullptr;
+  int* h_err = nullptr;
+
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  Prof prof;
+  float* tap_sink = nullptr;
+  size_t tap_cap = 0;
+};
+
+namespace {
+
+int fail(dcd_engine* e, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (e) e->err = buf; else g_create_error = buf;
+  return code;
+}
+int cuda_fail(dcd_engine* e, cudaError_t ce, const char* what) {
+  if (ce == cudaErrorMemoryAllocation) return fail(e, DCD_E_OOM, "%s: CUDA out of memory", what);
+  return fail(e, DCD_E_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+}
+#define CK(e, expr, what)                              \
+  do {                                                 \
+    cudaError_t _ce = (expr);                          \
+    if (_ce != cudaSuccess) return cuda_fail(e, _ce, what); \
+  } while (0)
+
+const double IH8_STD = 53509.919921;  // sqrt(8 * (65536^2 - 1) / 12)
+struct GenSpec { int dist; float p0, p1; bool round_bf; };
+GenSpec spec_for(int kind, bool bf) {
+  switch (kind) {
+    case DCD_T_READOUT: return {0, 0.02f, 0.f, false};
+    case DCD_T_A_LOG: return {1, 0.0f, 2.7725887f, false};
+    case DCD_T_DT_BIAS: return {1, -6.9f, -2.3f, false};
+    case DCD_T_CONV: return {1, -0.5f, 0.5f, bf};
+    case DCD_T_GNORM: return {0, 0.02f, 1.0f, bf};
+    default: return {0, 0.02f, 0.f, bf};
+  }
+}
+
+// Where a logical tensor lives: base pointer of the (possibly fused) destination, its logical
+// shape, the row mapping into the destination and whether it is stored as f32.
+struct Loc { void* base; size_t rows, cols; int mode, row_offset, dst_stride; bool f32; };
+
+bool locate(dcd_engine* e, int layer, int kind, Loc* out) {
+  const dcd_model_config& c = e->c;
+  const size_t H = e->H;
+  auto L = [&](void* b, size_t r, size_t cc, int mode, int ro, int ds, bool f) { *out = Loc{b, r, cc, mode, ro, ds, f}; return b != nullptr; };
+  if (layer < 0) {
+    switch (kind) {
+      case DCD_T_EMBED: return L(e->embed, c.vocab, H, 0, 0, (int)H, false);
+      case DCD_T_FINAL_NORM: return L(e->final_norm, 1, H, 0, 0, (int)H, false);
+      case DCD_T_READOUT: return L(e->readout, c.readout_rows, H, 0, 0, (int)H, true);
+      default: return false;
+    }
+  }
+  if (layer >= c.num_layers) return false;
+  LayerW& w = e->layers[layer];
+  const int hd = c.head_dim;
+  switch (kind) {
+    case DCD_T_INPUT_NORM: return L(w.input_norm, 1, H, 0, 0, (int)H, false);
+    case DCD_T_POST_NORM: return L(w.post_norm, 1, H, 0, 0, (int)H, false);
+    case DCD_T_GATE: return L(w.w_gu, e->I, H, 1, 0, (int)H, false);
+    case DCD_T_UP: return L(w.w_gu, e->I, H, 2, 0, (int)H, false);
+    case DCD_T_DOWN: return L(w.w_down, H, e->I, 0, 0, e->I, false);
+  }
+  if (w.full) {
+    switch (kind) {
+      case DCD_T_Q: return L(w.w_qkv, e->qcols, H, 0, 0, (int)H, false);
+      case DCD_T_K: return L(w.w_qkv, e->kvcols, H, 0, e->qcols, (int)H, false);
+      case DCD_T_V: return L(w.w_qkv, e->kvcols, H, 0, e->qcols + e->kvcols, (int)H, false);
+      case DCD_T_O: return L(w.w_o, H, (size_t)c.heads * hd, 0, 0, c.heads * hd, false);
+      case DCD_T_QNORM: return L(w.qnorm, 1, hd, 0, 0, hd, false);
+      case DCD_T_KNORM: return L(w.knorm, 1, hd, 0, 0, hd, false);
+      default: return false;
+    }
+  }
+  switch (kind) {
+    case DCD_T_IN_QKV: return L(w.w_gin, e->conv_dim, H, 0, 0, (int)H, false);
+    case DCD_T_IN_Z: return L(w.w_gin, e->vd, H, 0, e->conv_dim, (int)H, false);
+    case DCD_T_IN_B: return L(w.w_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd, (int)H, false);
+    case DCD_T_IN_A: return L(w.w_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd + c.gdn_v_heads, (int)H, false);
+    case DCD_T_OUT: return L(w.w_out, H, e->vd, 0, 0, e->vd, false);
+    case DCD_T_CONV: return L(w.conv, e->conv_dim, 4, 0, 0, 4, false);
+    case DCD_T_A_LOG: return L(w.A_log, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
+    case DCD_T_DT_BIAS: return L(w.dt_bias, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
+    case DCD_T_GNORM: return L(w.gnorm, 1, c.gdn_dv, 0, 0, c.gdn_dv, false);
+    default: return false;
+  }
+}
+
+int dev_alloc(dcd_engine* e, void** p, size_t bytes, bool zero, size_t* tally) {
+  bytes = (bytes + 255) & ~(size_t)255;
+  cudaError_t ce = cudaMalloc(p, bytes ? bytes : 256);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "cudaMalloc");
+  e->allocs.push_back(*p);
+  if (zero) CK(e, cudaMemsetAsync(*p, 0, bytes, e->stream), "memset");
+  if (tally) *tally += bytes;
+  return DCD_OK;
+}
+#define ALLOC(e, ptr, bytes, zero, tally)                                             \
+  do {                                                                                \
+    int _rc = dev_alloc(e, reinterpret_cast<void**>(&(ptr)), (bytes), (zero), (tally)); \
+    if (_rc) return _rc;                                                              \
+  } while (0)
+
+uint16_t host_bf16(float x) {
+  uint32_t u;
+  memcpy(&u, &x, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+// ---- profiling -----------------------------------------------------------------
+struct Scope {
+  dcd_engine* e;
+  int idx = -1;
+  Scope(dcd_engine* e_, int kind, double work, int n_launch) : e(e_) {
+    e->launches += n_launch;
+    if (!e->prof.on) return;
+    cudaEvent_t a, b;
+    auto get = [&](cudaEvent_t* ev) {
+      if (!e->prof.pool.empty()) { *ev = e->prof.pool.back(); e->prof.pool.pop_back(); }
+      else cudaEventCreate(ev);
+    };
+    get(&a);
+    get(&b);
+    cudaEventRecord(a, e->stream);
+    e->prof.pairs.push_back({a, b, kind, work});
+    idx = (int)e->prof.pairs.size() - 1;
+  }
+  ~Scope() {
+    if (idx >= 0) cudaEventRecord(e->prof.pairs[idx].b, e->stream);
+  }
+};
+
+// ---- GEMM dispatch -------------------------------------------------------------
+// C[M,N] = X[M,K] . W[N,K]^T. tcgen05 path for the bf16 engine, plain FMA otherwise.
+template <typename T>
+int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, void* C, int M, int N, int K,
+         int ldc, int epi) {
+  Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
+  if (e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K)) {
+    CK(e, tc_gemm_launch(tmA, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream), "tcgen05 gemm");
+    return DCD_OK;
+  }
+  if (epi != 0) return fail(e, DCD_E_INVALID, "internal: fused epilogue without tensor-core path");
+  CK(e, launch_gemm_fma<T>((const T*)X, (const T*)W, (T*)C, M, N, K, ldc, e->stream), "fma gemm");
+  return DCD_OK;
+}
+
+struct Pass {
+  int mode;  // 0 capture, 1 state-once question pass, 2 per-row reference
+  int T, B, max_len;
+  const dcd_state* cache = nullptr;
+  dcd_state* cap = nullptr;
+  int split = 0;
+};
+
+template <typename T>
+int run_layers(dcd_engine* e, const Pass& p) {
+  const dcd_model_config& c = e->c;
+  const int T_ = p.T, H = e->H, heads = c.heads, kv = c.kv_heads, hd = c.head_dim;
+  const int nk = c.gdn_k_heads, nv = c.gdn_v_heads, dk = c.gdn_dk, dv = c.gdn_dv;
+  cudaStream_t s = e->stream;
+  const bool tc = e->bf && e->o.gemm_path == 0;
+  TcTensorMap tm_h, tm_A, tm_B, tm_act;
+  if (tc) {
+    if (tc_make_tmap_a(&tm_h, e->h, T_, H) || tc_make_tmap_a(&tm_A, e->bufA, T_, heads * hd) ||
+        tc_make_tmap_a(&tm_B, e->bufB, T_, e->vd) || tc_make_tmap_a(&tm_act, e->act, T_, e->I))
+      return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an activation operand");
+  }
+  const size_t xbytes = (size_t)T_ * H * e->esz;
+  for (int li = 0; li < c.num_layers; ++li) {
+    LayerW& w = e->layers[li];
+    if (li == 0) {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 2.0 * xbytes, 1);
+      CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
+    }
+    if (w.full) {
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
+      if (rc) return rc;
+      T* big = (T*)e->big;
+      T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
+      {
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * (heads + kv) * hd * e->esz * 2.0, 1);
+        CK(e, launch_qk_norm_rope<T>(big, e->qkv_n, big + e->qcols, e->qkv_n, (const T*)w.qnorm, (const T*)w.knorm, (const T*)e->cos_t,
+                                     (const T*)e->sin_t, e->d_tokpos, 0, e->o.max_positions, (T*)e->q, kdst, kv * hd, T_, heads, kv, hd,
+                                     c.rotary_dim, c.rms_eps, e->d_err, s), "qk_norm_rope");
+      }
+      const T* vsrc = big + e->qcols + e->kvcols;
+      if (p.mode == 0) {
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * kv * hd * e->esz * 2.0, 1);
+        CK(e, launch_copy_rows<T>(vsrc, e->qkv_n, (T*)p.cap->v[li], kv * hd, T_, kv * hd, s), "copy V");
+      }
+      {
+        const int n_state = p.mode == 1 ? (int)p.cache->state_len : 0;
+        double keys = 0;  // sum over rows of visible keys
+        if (p.mode == 1) keys = (double)T_ * n_state + (double)T_ * p.max_len;  // upper bound on own keys
+        else if (p.mode == 0) keys = (double)T_ * T_;
+        else keys = (double)p.split * p.split + (double)(T_ - p.split) * T_;
+        Scope sc(e, DCD_PROF_ATTN, 4.0 * heads * hd * keys, 1);
+        CK(e, launch_attn_fma<T>((const T*)e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? (const T*)p.cache->k[li] : nullptr,
+                                 p.mode == 1 ? (const T*)p.cache->v[li] : nullptr, n_state, big, e->qkv_n, (T*)e->bufA, e->d_cu,
+                                 e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
+      }
+      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, e->mix, T_, H, heads * hd, H, 0);
+      if (rc) return rc;
+    } else {
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
+      if (rc) return rc;
+      T* big = (T*)e->big;
+      if (p.mode == 0) {
+        // last three pre-convolution rows, left-zero-padded (native/src/engine.rs:3348-3361)
+        CK(e, cudaMemsetAsync(p.cap->hist[li], 0, (size_t)3 * e->conv_dim * e->esz, s), "memset hist");
+        const int keep = T_ < 3 ? T_ : 3;
+        Scope sc(e, DCD_PROF_ELEMENTWISE, 0, 1);
+        CK(e, launch_copy_rows<T>(big + (size_t)(T_ - keep) * e->gin_n, e->gin_n, (T*)p.cap->hist[li] + (size_t)(3 - keep) * e->conv_dim,
+                                  e->conv_dim, keep, e->conv_dim, s), "copy conv tail");
+      }
+      {
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->conv_dim * e->esz * 2.0, 1);
+        CK(e, launch_conv1d_silu<T>(big, e->gin_n, p.mode == 1 ? (const T*)p.cache->hist[li] : nullptr, (const T*)w.conv, (T*)e->conv,
+                                    e->d_cu, e->d_tokq, T_, e->conv_dim, s), "conv1d");
+      }
+      {
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * nk * dk * (2.0 * e->esz + 8.0), 1);
+        const T* bsrc = big + e->conv_dim + e->vd;
+        CK(e, launch_gdn_prepare<T>((const T*)e->conv, e->conv_dim, bsrc, bsrc + nv, e->gin_n, w.A_log, w.dt_bias, e->qf, e->kf, e->g,
+                                    e->beta, T_, nk, nv, dk, s), "gdn_prepare");
+      }
+      {
+        Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
+        CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta,
+                                      p.mode == 1 ? p.cache->gstate[li] : nullptr, p.mode == 0 ? p.cap->gstate[li] : nullptr, (T*)e->bufA,
+                                      e->d_cu, p.B, nk, nv, dk, dv, p.B < 8, s), "gdn_recurrent");
+      }
+      {
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->vd * e->esz * 3.0, 1);
+        CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
+                                      c.rms_eps, s), "rmsnorm_gated");
+      }
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, e->mix, T_, H, e->vd, H, 0);
+      if (rc) return rc;
+    }
+    {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
+      CK(e, launch_add_rmsnorm<T>((const T*)e->x, (const T*)e->mix, (const T*)w.post_norm, (T*)e->x1, (T*)e->h, T_, H, c.rms_eps, s),
+         "add_rmsnorm");
+    }
+    if (tc) {
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, e->act, T_, e->gu_rows, H, e->I, 1);
+      if (rc) return rc;
+    } else {
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
+      if (rc) return rc;
+      Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->I * e->esz * 3.0, 1);
+      CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
+    }
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, e->mix, T_, H, e->I, H, 0);
+    if (rc) return rc;
+    if (li + 1 < c.num_layers) {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
+      CK(e, launch_add_rmsnorm<T>((const T*)e->x1, (const T*)e->mix, (const T*)e->layers[li + 1].input_norm, (T*)e->x, (T*)e->h, T_, H,
+                                  c.rms_eps, s), "add_rmsnorm");
+    } else {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 3.0 * xbytes, 1);
+      CK(e, launch_add<T>((const T*)e->x1, (const T*)e->mix, (T*)e->x, (size_t)T_ * H, s), "add");
+    }
+    if (e->tap_sink && (size_t)(li + 1) * T_ * H <= e->tap_cap) {
+      CK(e, launch_to_f32<T>((const T*)e->x, e->tap_dev, (size_t)T_ * H, s), "tap");
+      CK(e, cudaMemcpyAsync(e->tap_sink + (size_t)li * T_ * H, e->tap_dev, (size_t)T_ * H * 4, cudaMemcpyDeviceToHost, s), "tap copy");
+      CK(e, cudaStreamSynchronize(s), "tap sync");
+    }
+  }
+  return DCD_OK;
+}
+
+// Pack + embed + layers (+ final norm of last rows + readout unless capturing).
+template <typename T>
+int run_pass(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t* d_lens, int pos_start, float* d_out) {
+  cudaStream_t s = e->stream;
+  {
+    Scope sc(e, DCD_PROF_ELEMENTWISE, 12.0 * p.T, 2);
+    CK(e, launch_pack(d_lens, p.B, p.T, pos_start, e->d_cu, e->d_last, e->d_tokq, e->d_tokpos, e->d_err, s), "pack");
+  }
+  {
+    Scope sc(e, DCD_PROF_ELEMENTWISE, 2.0 * p.T * e->H * e->esz, 1);
+    CK(e, launch_embed<T>((const T*)e->embed, d_ids, (T*)e->x, p.T, e->H, e->c.vocab, e->d_err, s), "embed");
+  }
+  int rc = run_layers<T>(e, p);
+  if (rc) return rc;
+  if (p.mode != 0) {
+    {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, (double)p.B * e->H * (e->esz + 4.0), 1);
+      CK(e, launch_final_norm_rows<T>((const T*)e->x, (const T*)e->final_norm, e->hid, e->d_last, p.B, e->H, e->c.rms_eps, s), "final norm");
+    }
+    Scope sc(e, DCD_PROF_READOUT, 2.0 * p.B * e->H * e->c.readout_rows, 1);
+    CK(e, launch_readout(e->hid, e->readout, d_out, p.B, e->H, e->c.readout_rows, s), "readout");
+  }
+  return DCD_OK;
+}
+
+int run_pass_any(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t* d_lens, int pos_start, float* d_out) {
+  return e->bf ? run_pass<bf16>(e, p, d_ids, d_lens, pos_start, d_out) : run_pass<float>(e, p, d_ids, d_lens, pos_start, d_out);
+}
+
+int check_device_error(dcd_engine* e) {
+  // caller has synchronised the stream after copying d_err into h_err
+  const int code = *e->h_err;
+  if (code == DERR_NONE) return DCD_OK;
+  cudaMemsetAsync(e->d_err, 0, sizeof(int), e->stream);
+  cudaStreamSynchronize(e->stream);
+  switch (code) {
+    case DERR_TOKEN_RANGE: return fail(e, DCD_E_INVALID, "token id out of range for vocabulary %d", e->c.vocab);
+    case DERR_EMPTY_ITEM: return fail(e, DCD_E_INVALID, "batch item has no tokens");
+    case DERR_POSITION_RANGE: return fail(e, DCD_E_INVALID, "position beyond the RoPE table (%d)", e->o.max_positions);
+    case DERR_GEMM_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 GEMM: a bounded barrier wait gave up");
+    default: return fail(e, DCD_E_CUDA, "device error word %d", code);
+  }
+}
+
+int sync_and_check(dcd_engine* e) {
+  CK(e, cudaMemcpyAsync(e->h_err, e->d_err, sizeof(int), cudaMemcpyDeviceToHost, e->stream), "err copy");
+  CK(e, cudaStreamSynchronize(e->stream), "stream sync");
+  return check_device_error(e);
+}
+
+size_t state_bytes_for(const dcd_engine* e, size_t S) {
+  const dcd_model_config& c = e->c;
+  size_t b = 0;
+  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  for (int i = 0; i < c.num_layers; ++i) {
+    if (c.layer_is_full[i]) b += 2 * al(S * c.kv_heads * c.head_dim * e->esz);
+    else b += al((size_t)c.gdn_v_heads * c.gdn_dk * c.gdn_dv * 4) + al((size_t)3 * e->conv_dim * e->esz);
+  }
+  return b;
+}
+
+void carve_state(const dcd_engine* e, dcd_state* st) {
+  const dcd_model_config& c = e->c;
+  const int L = c.num_layers;
+  st->k.assign(L, nullptr); st->v.assign(L, nullptr); st->hist.assign(L, nullptr); st->gstate.assign(L, nullptr);
+  char* p = (char*)st->block;
+  auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  for (int i = 0; i < L; ++i) {
+    if (c.layer_is_full[i]) {
+      const size_t n = al(st->state_len * c.kv_heads * c.head_dim * e->esz);
+      st->k[i] = p; p += n;
+      st->v[i] = p; p += n;
+    } else {
+      st->gstate[i] = (float*)p; p += al((size_t)c.gdn_v_heads * c.gdn_dk * c.gdn_dv * 4);
+      st->hist[i] = p; p += al((size_t)3 * e->conv_dim * e->esz);
+    }
+  }
+}
+
+int new_state(dcd_engine* e, size_t S, dcd_state** out) {
+  dcd_state* st = new dcd_state();
+  st->state_len = S;
+  st->pos_end = S;
+  st->bytes = state_bytes_for(e, S);
+  cudaError_t ce = cudaMallocAsync(&st->block, st->bytes, e->stream);
+  if (ce != cudaSuccess) {
+    delete st;
+    cudaGetLastError();
+    return cuda_fail(e, ce, "state cache allocation");
+  }
+  carve_state(e, st);
+  *out = st;
+  return DCD_OK;
+}
+
+}  // namespace
+
+// =================================================================================
+// C ABI
+// =================================================================================
+extern "C" {
+
+const char* dcd_last_error(const dcd_engine* e) { return e ? e->err.c_str() : g_create_error.c_str(); }
+
+int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int device, dcd_engine** out) {
+  if (!out) return DCD_E_INVALID;
+  *out = nullptr;
+  if (!cfg) return fail(nullptr, DCD_E_INVALID, "null config");
+  const dcd_model_config& c = *cfg;
+  if (c.num_layers <= 0 || c.num_layers > 256 || c.hidden <= 0 || c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads ||
+      c.intermediate <= 0 || c.vocab <= 0 || c.readout_rows <= 0)
+    return fail(nullptr, DCD_E_INVALID, "invalid model config");
+  if (c.conv_kernel != 4) return fail(nullptr, DCD_E_UNSUPPORTED, "conv kernel %d unsupported (4 only)", c.conv_kernel);
+  if (c.head_dim != 64 && c.head_dim != 128 && c.head_dim != 256) return fail(nullptr, DCD_E_UNSUPPORTED, "head_dim %d unsupported", c.head_dim);
+  if ((c.gdn_dk != 64 && c.gdn_dk != 128) || c.gdn_dv % 16 || c.gdn_v_heads % c.gdn_k_heads)
+    return fail(nullptr, DCD_E_UNSUPPORTED, "GDN dims unsupported");
+  if (c.rotary_dim % 2 || c.rotary_dim > c.head_dim) return fail(nullptr, DCD_E_INVALID, "rotary_dim invalid");
+  if (c.dtype != 0 && c.dtype != 1) return fail(nullptr, DCD_E_INVALID, "dtype must be 0 (f32) or 1 (bf16)");
+  dcd_options o = {};
+  if (opt) o = *opt;
+  if (o.precision != 0) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (bf16/f32 only)", o.precision);
+  if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
+  if (o.max_rows <= 0) o.max_rows = 256;
+  if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
+  if (o.max_scores <= 0) o.max_scores = (int64_t)1 << 33;
+  if (o.max_positions <= 0) o.max_positions = 65536;
+
+  int ndev = 0;
+  cudaError_t ce = cudaGetDeviceCount(&ndev);
+  if (ce != cudaSuccess || ndev == 0) {
+    cudaGetLastError();
+    return fail(nullptr, DCD_E_CUDA, "no CUDA device: %s", ce == cudaSuccess ? "count is 0" : cudaGetErrorString(ce));
+  }
+  if (device < 0 || device >= ndev) return fail(nullptr, DCD_E_INVALID, "device %d out of range (%d devices)", device, ndev);
+  ce = cudaSetDevice(device);
+  if (ce != cudaSuccess) return fail(nullptr, DCD_E_CUDA, "cudaSetDevice: %s", cudaGetErrorString(ce));
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, device);
+  if (prop.major != 10) return fail(nullptr, DCD_E_UNSUPPORTED, "device %s is sm_%d%d; this library is built for sm_100a only", prop.name, prop.major, prop.minor);
+
+  dcd_engine* e = new dcd_engine();
+  e->c = c;
+  e->o = o;
+  e->device = device;
+  e->sm_count = prop.multiProcessorCount;
+  e->cc_major = prop.major;
+  e->cc_minor = prop.minor;
+  snprintf(e->device_name, sizeof e->device_name, "%s", prop.name);
+  e->bf = c.dtype == 1;
+  e->esz = e->bf ? 2 : 4;
+  e->H = c.hidden;
+  e->I = c.intermediate;
+  e->qcols = c.heads * 2 * c.head_dim;
+  e->kvcols = c.kv_heads * c.head_dim;
+  e->qkv_n = e->qcols + 2 * e->kvcols;
+  e->conv_dim = 2 * c.gdn_k_heads * c.gdn_dk + c.gdn_v_heads * c.gdn_dv;
+  e->vd = c.gdn_v_heads * c.gdn_dv;
+  e->gin_n = (e->conv_dim + e->vd + 2 * c.gdn_v_heads + 7) & ~7;
+  e->gu_rows = ((e->I + 127) / 128) * 256;
+  e->rhalf = c.rotary_dim / 2;
+  e->Tm = o.max_pass_tokens;
+  e->max_batch = o.max_pass_tokens;  // a question has >= 1 token
+  if ((e->H * e->esz) % 16 || (e->conv_dim % 8) || (e->qkv_n % 8)) {
+    delete e;
+    return fail(nullptr, DCD_E_UNSUPPORTED, "hidden/projection widths must keep rows 16-byte aligned");
+  }
+
+#define CRE(expr, what)                                            \
+  do {                                                             \
+    cudaError_t _ce = (expr);                                      \
+    if (_ce != cudaSuccess) {                                      \
+      int _rc = cuda_fail(nullptr, _ce, what);                     \
+      dcd_engine_destroy(e);                                       \
+      return _rc;                                                  \
+    }                                                              \
+  } while (0)
+#define CRA(ptr, bytes, zero, tally)                                                   \
+  do {                                                                                 \
+    int _rc = dev_alloc(e, reinterpret_cast<void**>(&(ptr)), (bytes), (zero), (tally)); \
+    if (_rc) { g_create_error = e->err; dcd_engine_destroy(e); return _rc; }           \
+  } while (0)
+
+  CRE(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream");
+  CRE(cudaEventCreate(&e->t0), "event");
+  CRE(cudaEventCreate(&e->t1), "event");
+  if (e->bf) CRE(tc_gemm_prepare_device(), "tcgen05 GEMM shared-memory attribute");
+
+  const size_t es = e->esz, H = e->H;
+  // ---- weights
+  e->layers.resize(c.num_layers);
+  CRA(e->embed, (size_t)c.vocab * H * es, false, &e->weight_bytes);
+  CRA(e->final_norm, H * es, true, &e->weight_bytes);
+  CRA(e->readout, (size_t)c.readout_rows * H * 4, true, &e->weight_bytes);
+  for (int i = 0; i < c.num_layers; ++i) {
+    LayerW& w = e->layers[i];
+    w.full = c.layer_is_full[i] != 0;
+    CRA(w.input_norm, H * es, true, &e->weight_bytes);
+    CRA(w.post_norm, H * es, true, &e->weight_bytes);
+    CRA(w.w_gu, (size_t)e->gu_rows * H * es, true, &e->weight_bytes);
+    CRA(w.w_down, H * (size_t)e->I * es, true, &e->weight_bytes);
+    if (w.full) {
+      CRA(w.w_qkv, (size_t)e->qkv_n * H * es, true, &e->weight_bytes);
+      CRA(w.w_o, H * (size_t)c.heads * c.head_dim * es, true, &e->weight_bytes);
+      CRA(w.qnorm, c.head_dim * es, true, &e->weight_bytes);
+      CRA(w.knorm, c.head_dim * es, true, &e->weight_bytes);
+    } else {
+      CRA(w.w_gin, (size_t)e->gin_n * H * es, true, &e->weight_bytes);
+      CRA(w.w_out, H * (size_t)e->vd * es, true, &e->weight_bytes);
+      CRA(w.conv, (size_t)e->conv_dim * 4 * es, true, &e->weight_bytes);
+      CRA(w.gnorm, c.gdn_dv * es, true, &e->weight_bytes);
+      CRA(w.A_log, c.gdn_v_heads * 4, true, &e->weight_bytes);
+      CRA(w.dt_bias, c.gdn_v_heads * 4, true, &e->weight_bytes);
+    }
+    if (e->bf) {
+      int bad = tc_make_tmap_b(&w.tm_gu, w.w_gu, e->gu_rows, H) | tc_make_tmap_b(&w.tm_down, w.w_down, H, e->I);
+      if (w.full) bad |= tc_make_tmap_b(&w.tm_qkv, w.w_qkv, e->qkv_n, H) | tc_make_tmap_b(&w.tm_o, w.w_o, H, (uint64_t)c.heads * c.head_dim);
+      else bad |= tc_make_tmap_b(&w.tm_gin, w.w_gin, e->gin_n, H) | tc_make_tmap_b(&w.tm_out, w.w_out, H, e->vd);
+      if (bad && o.gemm_path == 0) {
+        dcd_engine_destroy(e);
+        return fail(nullptr, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for a weight operand (layer %d)", i);
+      }
+    }
+  }
+  // ---- RoPE tables, built on the host exactly as Engine::rope_tables_positions does
+  // (native/src/engine.rs:1619-1643), once for every position.
+  {
+    const int half = e->rhalf, P = o.max_positions;
+    std::vector<float> inv(half > 0 ? half : 1);
+    for (int i = 0; i < half; ++i) inv[i] = 1.0f / powf(c.rope_theta, (float)(2 * i) / (float)c.rotary_dim);
+    const size_t n = (size_t)P * (half > 0 ? half : 1);
+    std::vector<unsigned char> cs(n * es), sn(n * es);
+    for (int p = 0; p < P && half > 0; ++p)
+      for (int i = 0; i < half; ++i) {
+        const float ang = (float)p * inv[i];
+        const float cv = cosf(ang), sv = sinf(ang);
+        const size_t at = (size_t)p * half + i;
+        if (e->bf) { ((uint16_t*)cs.data())[at] = host_bf16(cv); ((uint16_t*)sn.data())[at] = host_bf16(sv); }
+        else { ((float*)cs.data())[at] = cv; ((float*)sn.data())[at] = sv; }
+      }
+    CRA(e->cos_t, n * es, false, &e->weight_bytes);
+    CRA(e->sin_t, n * es, false, &e->weight_bytes);
+    CRE(cudaMemcpyAsync(e->cos_t, cs.data(), n * es, cudaMemcpyHostToDevice, e->stream), "rope upload");
+    CRE(cudaMemcpyAsync(e->sin_t, sn.data(), n * es, cudaMemcpyHostToDevice, e->stream), "rope upload");
+    CRE(cudaStreamSynchronize(e->stream), "rope upload");
+  }
+  // ---- workspace
+  const size_t Tm = e->Tm;
+  size_t bigw = e->qkv_n;
+  if ((size_t)e->gin_n > bigw) bigw = e->gin_n;
+  if ((size_t)e->gu_rows > bigw) bigw = e->gu_rows;
+  size_t aw = (size_t)c.heads * c.head_dim;
+  if ((size_t)e->vd > aw) aw = e->vd;
+  size_t* ws = &e->workspace_bytes;
+  CRA(e->x, Tm * H * es, false, ws);
+  CRA(e->h, Tm * H * es, false, ws);
+  CRA(e->x1, Tm * H * es, false, ws);
+  CRA(e->mix, Tm * H * es, false, ws);
+  CRA(e->big, Tm * bigw * es, false, ws);
+  CRA(e->q, Tm * (size_t)c.heads * c.head_dim * es, false, ws);
+  CRA(e->kown, Tm * (size_t)e->kvcols * es, false, ws);
+  CRA(e->bufA, Tm * aw * es, false, ws);
+  CRA(e->bufB, Tm * aw * es, false, ws);
+  CRA(e->conv, Tm * (size_t)e->conv_dim * es, false, ws);
+  CRA(e->act, Tm * (size_t)e->I * es, false, ws);
+  CRA(e->qf, Tm * (size_t)c.gdn_k_heads * c.gdn_dk * 4, false, ws);
+  CRA(e->kf, Tm * (size_t)c.gdn_k_heads * c.gdn_dk * 4, false, ws);
+  CRA(e->g, Tm * (size_t)c.gdn_v_heads * 4, false, ws);
+  CRA(e->beta, Tm * (size_t)c.gdn_v_heads * 4, false, ws);
+  CRA(e->hid, (size_t)e->max_batch * H * 4, false, ws);
+  CRA(e->d_logits, (size_t)e->max_batch * c.readout_rows * 4, false, ws);
+  CRA(e->d_ids, Tm * 4, false, ws);
+  CRA(e->d_lens, (size_t)e->max_batch * 4, false, ws);
+  CRA(e->d_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
+  CRA(e->d_last, (size_t)e->max_batch * 4, false, ws);
+  CRA(e->d_tokq, Tm * 4, false, ws);
+  CRA(e->d_tokpos, Tm * 4, false, ws);
+  CRA(e->d_err, 256, true, ws);
+  CRE(cudaMallocHost(&e->h_ids, Tm * 4), "pinned ids");
+  CRE(cudaMallocHost(&e->h_lens, (size_t)e->max_batch * 4), "pinned lens");
+  CRE(cudaMallocHost(&e->h_logits, (size_t)e->max_batch * c.readout_rows * 4), "pinned logits");
+  CRE(cudaMallocHost(&e->h_err, 64), "pinned err");
+  *e->h_err = 0;
+  CRE(cudaStreamSynchronize(e->stream), "create sync");
+#undef CRE
+#undef CRA
+  *out = e;
+  return DCD_OK;
+}
+
+void dcd_engine_destroy(dcd_engine* e) {
+  if (!e) return;
+  cudaSetDevice(e->device);
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  for (void* p : e->allocs) cudaFree(p);
+  if (e->h_ids) cudaFreeHost(e->h_ids);
+  if (e->h_lens) cudaFreeHost(e->h_lens);
+  if (e->h_logits) cudaFreeHost(e->h_logits);
+  if (e->h_err) cudaFreeHost(e->h_err);
+  for (auto& pr : e->prof.pairs) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
+  for (auto ev : e->prof.pool) cudaEventDestroy(ev);
+  if (e->t0) cudaEventDestroy(e->t0);
+  if (e->t1) cudaEventDestroy(e->t1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  delete e;
+}
+
+int dcd_engine_info(const dcd_engine* e, dcd_info* out) {
+  if (!e || !out) return DCD_E_INVALID;
+  memset(out, 0, sizeof *out);
+  out->device = e->device;
+  out->sm_count = e->sm_count;
+  out->cc_major = e->cc_major;
+  out->cc_minor = e->cc_minor;
+  snprintf(out->device_name, sizeof out->device_name, "%s", e->device_name);
+  out->hidden = e->c.hidden;
+  out->num_layers = e->c.num_layers;
+  out->readout_rows = e->c.readout_rows;
+  out->supports_vision = 0;
+  out->weight_bytes = e->weight_bytes;
+  out->workspace_bytes = e->workspace_bytes;
+  return DCD_OK;
+}
+
+int dcd_rebind_blas(dcd_engine* e) { return e ? DCD_OK : DCD_E_INVALID; }
+
+static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind) {
+  Loc L;
+  if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  const GenSpec sp = spec_for(kind, e->bf);
+  const float cc = (float)((double)sp.p0 / IH8_STD);
+  const uint64_t key = gen_tensor_key(seed, layer, kind);
+  const uint64_t count = (uint64_t)L.rows * L.cols;
+  e->launches += 1;
+  if (L.f32) CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
+  else if (e->bf) CK(e, launch_gen_tensor<bf16>((bf16*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
+  else CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
+  return DCD_OK;
+}
+
+int dcd_engine_init_random(dcd_engine* e, uint64_t seed) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  static const int globals[] = {DCD_T_EMBED, DCD_T_FINAL_NORM, DCD_T_READOUT};
+  static const int common[] = {DCD_T_INPUT_NORM, DCD_T_POST_NORM, DCD_T_GATE, DCD_T_UP, DCD_T_DOWN};
+  static const int full[] = {DCD_T_Q, DCD_T_K, DCD_T_V, DCD_T_O, DCD_T_QNORM, DCD_T_KNORM};
+  static const int gdn[] = {DCD_T_IN_QKV, DCD_T_IN_Z, DCD_T_IN_B, DCD_T_IN_A, DCD_T_OUT, DCD_T_CONV, DCD_T_A_LOG, DCD_T_DT_BIAS, DCD_T_GNORM};
+  int rc;
+  for (int k : globals) if ((rc = gen_one(e, seed, -1, k))) return rc;
+  for (int i = 0; i < e->c.num_layers; ++i) {
+    for (int k : common) if ((rc = gen_one(e, seed, i, k))) return rc;
+    if (e->layers[i].full) { for (int k : full) if ((rc = gen_one(e, seed, i, k))) return rc; }
+    else { for (int k : gdn) if ((rc = gen_one(e, seed, i, k))) return rc; }
+  }
+  CK(e, cudaStreamSynchronize(e->stream), "init_random sync");
+  e->weights_ready = true;
+  return DCD_OK;
+}
+
+int dcd_engine_load_tensor(dcd_engine* e, int layer, int kind, const float* host, size_t count) {
+  if (!e || !host) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  Loc L;
+  if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  if (count != L.rows * L.cols) return fail(e, DCD_E_INVALID, "tensor kind %d expects %zu values, got %zu", kind, L.rows * L.cols, count);
+  float* tmp = nullptr;
+  void* tmpT = nullptr;
+  cudaError_t ce = cudaMalloc(&tmp, count * 4);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "load_tensor staging");
+  int rc = DCD_OK;
+  do {
+    if ((ce = cudaMemcpyAsync(tmp, host, count * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess) break;
+    e->launches += 2;
+    if (L.f32 || !e->bf) {
+      ce = launch_place_rows<float>(tmp, (float*)L.base, L.rows, (int)L.cols, L.mode, L.row_offset, L.dst_stride, false, e->stream);
+    } else {
+      if ((ce = cudaMalloc(&tmpT, count * 2)) != cudaSuccess) break;
+      if ((ce = launch_from_f32<bf16>(tmp, (bf16*)tmpT, count, e->stream)) != cudaSuccess) break;
+      ce = launch_place_rows<bf16>((const bf16*)tmpT, (bf16*)L.base, L.rows, (int)L.cols, L.mode, L.row_offset, L.dst_stride, false, e->stream);
+    }
+    if (ce != cudaSuccess) break;
+    ce = cudaStreamSynchronize(e->stream);
+  } while (0);
+  if (ce != cudaSuccess) rc = cuda_fail(e, ce, "load_tensor");
+  cudaFree(tmp);
+  if (tmpT) cudaFree(tmpT);
+  if (rc == DCD_OK) e->weights_ready = true;
+  return rc;
+}
+
+int dcd_engine_read_tensor(dcd_engine* e, int layer, int kind, float* host, size_t count) {
+  if (!e || !host) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  Loc L;
+  if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  if (count != L.rows * L.cols) return fail(e, DCD_E_INVALID, "tensor kind %d holds %zu values, asked for %zu", kind, L.rows * L.cols, count);
+  float* tmp = nullptr;
+  void* tmpT = nullptr;
+  cudaError_t ce = cudaMalloc(&tmp, count * 4);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "read_tensor staging");
+  do {
+    e->launches += 2;
+    if (L.f32 || !e->bf) {
+      ce = launch_place_rows<float>((const float*)L.base, tmp, L.rows, (int)L.cols, L.mode, L.row_offset, L.dst_stride, true, e->stream);
+    } else {
+      if ((ce = cudaMalloc(&tmpT, count * 2)) != cudaSuccess) break;
+      if ((ce = launch_place_rows<bf16>((const bf16*)L.base, (bf16*)tmpT, L.rows, (int)L.cols, L.mode, L.row_offset, L.dst_stride, true, e->stream)) != cudaSuccess) break;
+      ce = launch_to_f32<bf16>((const bf16*)tmpT, tmp, count, e->stream);
+    }
+    if (ce != cudaSuccess) break;
+    if ((ce = cudaMemcpyAsync(host, tmp, count * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess) break;
+    ce = cudaStreamSynchronize(e->stream);
+  } while (0);
+  cudaFree(tmp);
+  if (tmpT) cudaFree(tmpT);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "read_tensor");
+  return DCD_OK;
+}
+
+// ---- hot path ---------------------------------------------------------------------
+
+int dcd_capture_state_device(dcd_engine* e, const uint32_t* d_ids, size_t n, dcd_state** out) {
+  if (!e || !out) return DCD_E_INVALID;
+  *out = nullptr;
+  cudaSetDevice(e->device);
+  if (!e->weights_ready) return fail(e, DCD_E_INVALID, "weights are not loaded");
+  if (n < 2) return fail(e, DCD_E_INVALID, "a state block needs at least two tokens, got %zu", n);
+  if (n > (size_t)e->Tm) return fail(e, DCD_E_INVALID, "state of %zu tokens exceeds max_pass_tokens %d", n, e->Tm);
+  if (n > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "state of %zu tokens exceeds the RoPE table", n);
+  dcd_state* st = nullptr;
+  int rc = new_state(e, n, &st);
+  if (rc) return rc;
+  const int32_t len = (int32_t)n;
+  cudaError_t ce = cudaMemcpyAsync(e->d_lens, &len, 4, cudaMemcpyHostToDevice, e->stream);  // 4-byte pageable copy: staged by the driver
+  if (ce != cudaSuccess) { dcd_state_free(e, st); return cuda_fail(e, ce, "lens upload"); }
+  Pass p{0, (int)n, 1, (int)n};
+  p.cap = st;
+  rc = run_pass_any(e, p, d_ids, e->d_lens, 0, nullptr);
+  if (rc) { dcd_state_free(e, st); return rc; }
+  *out = st;
+  return DCD_OK;
+}
+
+int dcd_capture_state(dcd_engine* e, const uint32_t* ids, size_t n, const uint32_t (*pos)[3], dcd_state** out) {
+  if (!e || !out) return DCD_E_INVALID;
+  *out = nullptr;
+  if (!ids) return fail(e, DCD_E_INVALID, "null ids");
+  cudaSetDevice(e->device);
+  if (n < 2) return fail(e, DCD_E_INVALID, "a state block needs at least two tokens, got %zu", n);
+  if (n > (size_t)e->Tm) return fail(e, DCD_E_INVALID, "state of %zu tokens exceeds max_pass_tokens %d", n, e->Tm);
+  if (pos) {
+    // text-only: every triple must be (t,t,t); anything else belongs to the image path
+    for (size_t t = 0; t < n; ++t)
+      if (pos[t][0] != t || pos[t][1] != t || pos[t][2] != t)
+        return fail(e, DCD_E_UNSUPPORTED, "mRoPE positions other than (t,t,t) need the vision path, which is not built");
+  }
+  memcpy(e->h_ids, ids, n * 4);
+  CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, n * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
+  dcd_state* st = nullptr;
+  int rc = dcd_capture_state_device(e, e->d_ids, n, &st);
+  if (rc) return rc;
+  rc = sync_and_check(e);
+  if (rc) { dcd_state_free(e, st); return rc; }
+  *out = st;
+  return DCD_OK;
+}
+
+int dcd_readout_state_once_device(dcd_engine* e, const dcd_state* st, const uint32_t* d_ids, const int32_t* d_lens, size_t B,
+                                  size_t total, size_t max_len, float* d_out) {
+  if (!e || !st || !d_ids || !d_lens || !d_out) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  if (!e->weights_ready) return fail(e, DCD_E_INVALID, "weights are not loaded");
+  if (B == 0) return fail(e, DCD_E_INVALID, "empty state-once question batch");
+  if (total > (size_t)e->Tm || B > (size_t)e->max_batch) return fail(e, DCD_E_INVALID, "pass of %zu tokens exceeds max_pass_tokens %d", total, e->Tm);
+  if (st->pos_end + max_len > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "positions exceed the RoPE table");
+  Pass p{1, (int)total, (int)B, (int)max_len};
+  p.cache = st;
+  return run_pass_any(e, p, d_ids, d_lens, (int)st->pos_end, d_out);
+}
+
+// One chunk through the host-buffer path: ids/lens already in pinned staging.
+static int run_chunk_host(dcd_engine* e, const dcd_state* st, size_t B, size_t total, size_t max_len) {
+  CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, total * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
+  CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, B * 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
+  int rc = dcd_readout_state_once_device(e, st, e->d_ids, e->d_lens, B, total, max_len, e->d_logits);
+  if (rc) return rc;
+  CK(e, cudaMemcpyAsync(e->h_logits, e->d_logits, B * e->c.readout_rows * 4, cudaMemcpyDeviceToHost, e->stream), "logits download");
+  return sync_and_check(e);
+}
+
+int dcd_readout_state_once_batch(dcd_engine* e, const dcd_state* st, const uint32_t* const* questions, const size_t* lens, size_t B,
+                                 float* out) {
+  if (!e) return DCD_E_INVALID;
+  if (!st || !out) return fail(e, DCD_E_INVALID, "null argument");
+  if (B == 0 || !questions || !lens) return fail(e, DCD_E_INVALID, "empty state-once question batch");
+  for (size_t i = 0; i < B; ++i)
+    if (lens[i] == 0 || !questions[i]) return fail(e, DCD_E_INVALID, "batch item %zu has no tokens", i);
+  cudaSetDevice(e->device);
+  std::vector<int32_t> order(B), chunk_of(B);
+  int32_t n_chunks = 0;
+  int rc = plan_chunks_host(lens, B, st->state_len, (size_t)e->o.max_rows, (size_t)e->o.max_keys, (size_t)e->o.max_scores,
+                            (size_t)e->Tm, order.data(), chunk_of.data(), &n_chunks);
+  if (rc == -5) return fail(e, DCD_E_INVALID, "one question exceeds the key/score/token caps of a pass");
+  if (rc) return fail(e, DCD_E_INVALID, "empty state-once question batch");
+  const int R = e->c.readout_rows;
+  if (n_chunks <= 1) {
+    size_t total = 0, mx = 0;
+    for (size_t i = 0; i < B; ++i) {
+      memcpy(e->h_ids + total, questions[i], lens[i] * 4);
+      e->h_lens[i] = (int32_t)lens[i];
+      total += lens[i];
+      if (lens[i] > mx) mx = lens[i];
+    }
+    rc = run_chunk_host(e, st, B, total, mx);
+    if (rc) return rc;
+    memcpy(out, e->h_logits, B * R * sizeof(float));
+    return DCD_OK;
+  }
+  // several chunks: questions of a chunk run in sorted order; rows go back to input order
+  size_t n = 0;
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    size_t first = n, total = 0, mx = 0, nb = 0;
+    while (n < B && chunk_of[order[n]] == ch) {
+      const size_t i = order[n];
+      memcpy(e->h_ids + total, questions[i], lens[i] * 4);
+      e->h_lens[nb++] = (int32_t)lens[i];
+      total += lens[i];
+      if (lens[i] > mx) mx = lens[i];
+      ++n;
+    }
+    rc = run_chunk_host(e, st, nb, total, mx);
+    if (rc) return rc;
+    for (size_t j = 0; j < nb; ++j) memcpy(out + (size_t)order[first + j] * R, e->h_logits + j * R, R * sizeof(float));
+  }
+  return DCD_OK;
+}
+
+int dcd_readout_state_once_flat(dcd_engine* e, const dcd_state* st, const uint32_t* flat_ids, const uint32_t* lens, size_t B, float* out) {
+  if (!e) return DCD_E_INVALID;
+  if (B == 0 || !flat_ids || !lens) return fail(e, DCD_E_INVALID, "empty state-once question batch");
+  std::vector<const uint32_t*> ptrs(B);
+  std::vector<size_t> ls(B);
+  size_t off = 0;
+  for (size_t i = 0; i < B; ++i) {
+    ptrs[i] = flat_ids + off;
+    ls[i] = lens[i];
+    off += lens[i];
+  }
+  return dcd_readout_state_once_batch(e, st, ptrs.data(), ls.data(), B, out);
+}
+
+int dcd_decision_logits_split(dcd_engine* e, const uint32_t* ids, size_t seq, size_t split, float* out) {
+  if (!e) return DCD_E_INVALID;
+  if (!ids || !out) return fail(e, DCD_E_INVALID, "null argument");
+  cudaSetDevice(e->device);
+  if (!e->weights_ready) return fail(e, DCD_E_INVALID, "weights are not loaded");
+  if (split == 0 || split >= seq) return fail(e, DCD_E_INVALID, "block split %zu out of range for %zu tokens", split, seq);
+  if (seq > (size_t)e->Tm || seq > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "sequence of %zu tokens exceeds max_pass_tokens %d", seq, e->Tm);
+  memcpy(e->h_ids, ids, seq * 4);
+  e->h_lens[0] = (int32_t)seq;
+  CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, seq * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
+  CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
+  Pass p{2, (int)seq, 1, (int)seq};
+  p.split = (int)split;
+  int rc = run_pass_any(e, p, e->d_ids, e->d_lens, 0, e->d_logits);
+  if (rc) return rc;
+  CK(e, cudaMemcpyAsync(e->h_logits, e->d_logits, (size_t)e->c.readout_rows * 4, cudaMemcpyDeviceToHost, e->stream), "logits download");
+  rc = sync_and_check(e);
+  if (rc) return rc;
+  memcpy(out, e->h_logits, (size_t)e->c.readout_rows * 4);
+  return DCD_OK;
+}
+
+// ---- StateCache ---------------------------------------------------------------------
+void dcd_state_free(dcd_engine* e, dcd_state* st) {
+  if (!st) return;
+  if (st->block && e) {
+    cudaSetDevice(e->device);
+    cudaFreeAsync(st->block, e->stream);
+  }
+  delete st;
+}
+size_t dcd_state_tokens(const dcd_state* st) { return st ? st->state_len : 0; }
+size_t dcd_state_pos_end(const dcd_state* st) { return st ? st->pos_end : 0; }
+size_t dcd_state_bytes(const dcd_state* st) { return st ? st->bytes : 0; }
+
+int dcd_state_offload(dcd_engine* e, const dcd_state* st, dcd_host_state** out) {
+  if (!e || !st || !out) return DCD_E_INVALID;
+  *out = nullptr;
+  cudaSetDevice(e->device);
+  dcd_host_state* hs = new dcd_host_state();
+  hs->state_len = st->state_len;
+  hs->pos_end = st->pos_end;
+  hs->bytes = st->bytes;
+  cudaError_t ce = cudaMallocHost(&hs->block, st->bytes);
+  if (ce != cudaSuccess) {
+    delete hs;
+    cudaGetLastError();
+    return fail(e, DCD_E_OOM, "host state cache: out of memory (%zu bytes pinned)", st->bytes);
+  }
+  ce = cudaMemcpyAsync(hs->block, st->block, st->bytes, cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) { dcd_host_state_free(hs); return cuda_fail(e, ce, "state offload"); }
+  *out = hs;
+  return DCD_OK;
+}
+
+int dcd_state_restore(dcd_engine* e, const dcd_host_state* hs, dcd_state** out) {
+  if (!e || !hs || !out) return DCD_E_INVALID;
+  *out = nullptr;
+  cudaSetDevice(e->device);
+  if (hs->bytes != state_bytes_for(e, hs->state_len)) return fail(e, DCD_E_INVALID, "host state does not match this engine's model");
+  dcd_state* st = nullptr;
+  int rc = new_state(e, hs->state_len, &st);
+  if (rc) return rc;
+  st->pos_end = hs->pos_end;
+  cudaError_t ce = cudaMemcpyAsync(st->block, hs->block, hs->bytes, cudaMemcpyHostToDevice, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) { dcd_state_free(e, st); return cuda_fail(e, ce, "state restore"); }
+  *out = st;
+  return DCD_OK;
+}
+
+void dcd_host_state_free(dcd_host_state* hs) {
+  if (!hs) return;
+  if (hs->block) cudaFreeHost(hs->block);
+  delete hs;
+}
+
+int dcd_state_zero_gdn_state(dcd_engine* e, dcd_state* st, int layer) {
+  if (!e || !st || layer < 0 || layer >= e->c.num_layers || !st->gstate[layer]) return fail(e, DCD_E_INVALID, "layer %d has no GDN state", layer);
+  cudaSetDevice(e->device);
+  CK(e, cudaMemsetAsync(st->gstate[layer], 0, (size_t)e->c.gdn_v_heads * e->c.gdn_dk * e->c.gdn_dv * 4, e->stream), "zero state");
+  CK(e, cudaStreamSynchronize(e->stream), "sync");
+  return DCD_OK;
+}
+int dcd_state_zero_gdn_hist(dcd_engine* e, dcd_state* st, int layer) {
+  if (!e || !st || layer < 0 || layer >= e->c.num_layers || !st->hist[layer]) return fail(e, DCD_E_INVALID, "layer %d has no conv tail", layer);
+  cudaSetDevice(e->device);
+  CK(e, cudaMemsetAsync(st->hist[layer], 0, (size_t)3 * e->conv_dim * e->esz, e->stream), "zero hist");
+  CK(e, cudaStreamSynchronize(e->stream), "sync");
+  return DCD_OK;
+}
+
+int dcd_state_read_tensor(dcd_engine* e, const dcd_state* st, int layer, int what, float* host, size_t* count) {
+  if (!e || !st || !count || layer < 0 || layer >= e->c.num_layers) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  const dcd_model_config& c = e->c;
+  const void* src = nullptr;
+  size_t n = 0;
+  bool f32 = false;
+  if (what == 0 || what == 1) { src = what == 0 ? st->k[layer] : st->v[layer]; n = st->state_len * c.kv_heads * c.head_dim; }
+  else if (what == 2) { src = st->gstate[layer]; n = (size_t)c.gdn_v_heads * c.gdn_dk * c.gdn_dv; f32 = true; }
+  else if (what == 3) { src = st->hist[layer]; n = (size_t)3 * e->conv_dim; }
+  if (!src) return fail(e, DCD_E_INVALID, "layer %d has no cached tensor %d", layer, what);
+  *count = n;
+  if (!host) return DCD_OK;
+  float* tmp = nullptr;
+  cudaError_t ce = cudaMalloc(&tmp, n * 4);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "state read staging");
+  e->launches += 1;
+  if (f32 || !e->bf) ce = cudaMemcpyAsync(tmp, src, n * 4, cudaMemcpyDeviceToDevice, e->stream);
+  else ce = launch_to_f32<bf16>((const bf16*)src, tmp, n, e->stream);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(host, tmp, n * 4, cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  cudaFree(tmp);
+  if (ce != cudaSuccess) return cuda_fail(e, ce, "state read");
+  return DCD_OK;
+}
+
+// ---- pools, memory, timers ----------------------------------------------------------
+int dcd_trim_pools(dcd_engine* e) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  cudaMemPool_t pool;
+  CK(e, cudaStreamSynchronize(e->stream), "sync");
+  CK(e, cudaDeviceGetDefaultMemPool(&pool, e->device), "mem pool");
+  CK(e, cudaMemPoolTrimTo(pool, 0), "pool trim");
+  return DCD_OK;
+}
+int dcd_mem_info(dcd_engine* e, size_t* free_bytes, size_t* total_bytes) {
+  if (!e || !free_bytes || !total_bytes) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  CK(e, cudaMemGetInfo(free_bytes, total_bytes), "mem info");
+  return DCD_OK;
+}
+int dcd_timer_begin(dcd_engine* e) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  CK(e, cudaEventRecord(e->t0, e->stream), "timer begin");
+  return DCD_OK;
+}
+int dcd_timer_end(dcd_engine* e) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  CK(e, cudaEventRecord(e->t1, e->stream), "timer end");
+  return DCD_OK;
+}
+double dcd_timer_seconds(dcd_engine* e) {
+  if (!e) return -1.0;
+  cudaSetDevice(e->device);
+  float ms = 0.f;
+  if (cudaEventSynchronize(e->t1) != cudaSuccess || cudaEventElapsedTime(&ms, e->t0, e->t1) != cudaSuccess) return -1.0;
+  return (double)ms * 1e-3;
+}
+int dcd_vision_encode(dcd_engine* e, const void*, size_t) { return fail(e, DCD_E_UNSUPPORTED, "the vision tower is not part of this library"); }
+int dcd_engine_sync(dcd_engine* e) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  return sync_and_check(e);
+}
+
+int dcd_profile_enable(dcd_engine* e, int on) {
+  if (!e) return DCD_E_INVALID;
+  e->prof.on = on != 0;
+  return DCD_OK;
+}
+int dcd_profile_read(dcd_engine* e, dcd_prof_entry out[DCD_PROF_COUNT]) {
+  if (!e || !out) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  CK(e, cudaStreamSynchronize(e->stream), "sync");
+  for (auto& pr : e->prof.pairs) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pr.a, pr.b) == cudaSuccess) {
+      e->prof.acc[pr.kind].ms += ms;
+      e->prof.acc[pr.kind].work += pr.work;
+      e->prof.acc[pr.kind].launches += 1;
+    }
+    e->prof.pool.push_back(pr.a);
+    e->prof.pool.push_back(pr.b);
+  }
+  e->prof.pairs.clear();
+  for (int i = 0; i < DCD_PROF_COUNT; ++i) { out[i] = e->prof.acc[i]; e->prof.acc[i] = dcd_prof_entry{}; }
+  return DCD_OK;
+}
+int64_t dcd_launch_count(const dcd_engine* e) { return e ? e->launches : 0; }
+
+int dcd_debug_layer_outputs(dcd_engine* e, float* host_sink, size_t capacity) {
+  if (!e) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  if (host_sink && !e->tap_dev) {
+    cudaError_t ce = cudaMalloc(&e->tap_dev, (size_t)e->Tm * e->H * 4);
+    if (ce != cudaSuccess) return cuda_fail(e, ce, "tap buffer");
+    e->allocs.push_back(e->tap_dev);
+  }
+  e->tap_sink = host_sink;
+  e->tap_cap = host_sink ? capacity : 0;
+  return DCD_OK;
+}
+
+int dcd_pack(dcd_engine* e, const int32_t* lens, size_t B, int32_t pos_start, int32_t* cu_seqlens, int32_t* positions, int32_t* tok_q,
+             int32_t* last_row) {
+  if (!e) return DCD_E_INVALID;
+  if (B == 0 || !lens) return fail(e, DCD_E_INVALID, "empty batch");
+  cudaSetDevice(e->device);
+  size_t total = 0;
+  for (size_t i = 0; i < B; ++i) total += lens[i] > 0 ? (size_t)lens[i] : 0;
+  if (B > (size_t)e->max_batch || total > (size_t)e->Tm) return fail(e, DCD_E_INVALID, "batch exceeds max_pass_tokens %d", e->Tm);
+  memcpy(e->h_lens, lens, B * 4);
+  CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, B * 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
+  e->launches += 2;
+  CK(e, launch_pack(e->d_lens, (int)B, (int)total, pos_start, e->d_cu, e->d_last, e->d_tokq, e->d_tokpos, e->d_err, e->stream), "pack");
+  CK(e, cudaMemcpyAsync(cu_seqlens, e->d_cu, (B + 1) * 4, cudaMemcpyDeviceToHost, e->stream), "download");
+  CK(e, cudaMemcpyAsync(last_row, e->d_last, B * 4, cudaMemcpyDeviceToHost, e->stream), "download");
+  if (total) {
+    CK(e, cudaMemcpyAsync(positions, e->d_tokpos, total * 4, cudaMemcpyDeviceToHost, e->stream), "download");
+    CK(e, cudaMemcpyAsync(tok_q, e->d_tokq, total * 4, cudaMemcpyDeviceToHost, e->stream), "download");
+  }
+  return sync_and_check(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,379 @@
+// C[M,N] = X[M,K] . W[N,K]^T for bf16 operands on the sm_100a tensor cores.
+//
+// Replaces the cuBLAS BF16 GEMM of Engine::gemm_core (native/src/engine.rs:4321-4350 in
+// juanqui/decidra): same contraction, f32 accumulation, bf16 output.
+//
+// Design (one CTA per SM, persistent over output tiles, no clusters):
+//   * tile 128 (M) x 256 (N), K sliced in 64-element (128-byte) blocks;
+//   * warp 0   : TMA producer. cp.async.bulk.tensor.2d loads of the X tile (128x64) and the
+//                W tile (256x64) into a 4-stage shared-memory ring, 128-byte swizzle;
+//   * warp 1   : MMA issuer. One elected thread issues tcgen05.mma (M128 N256 K16,
+//                kind::f16, bf16 in / f32 out) reading both operands from shared memory
+//                through UMMA descriptors; accumulators live in TMEM (2 x 256 columns so
+//                the epilogue of tile i overlaps the main loop of tile i+1);
+//   * warps 2-5: epilogue. tcgen05.ld 32 lanes x 32 columns at a time, convert to bf16
+//                (optionally SwiGLU-combine the two column halves), 16-byte global stores.
+// Every mbarrier wait is bounded: when a wait gives up the kernel raises an error word,
+// lets in-flight copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+
+namespace tcg {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16, ACC_STAGES = 2;
+constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t BAR_BYTES = 256;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int GROUP_M = 16;  // rasterisation: 16 M-tiles share each W tile while it is hot in L2
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait. Returns false if it gave up or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart. Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused
+// for swizzled K-major, set to 1), [32,46) stride offset>>4 = 64, [46,48) version 1,
+// [61,64) layout 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor, kind::f16: D f32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both
+// K-major, N>>3 at [17,23), M>>4 at [24,29).
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
+  const int per_group = GROUP_M * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(GROUP_M, num_m - first_m);
+  const int r = tile - g * per_group;
+  m_idx = first_m + r % gsize;
+  n_idx = r / gsize;
+}
+
+// EPI 0: C[M,N] bf16. EPI 1: SwiGLU — W rows are interleaved per 256-row tile as
+// [128 gate rows | 128 up rows]; the kernel writes act[M, N/2] = bf16(bf16(silu(bf16(gate))) * bf16(up))
+// (silu_mul_bf16, native/kernels/kernels.cu:492-501, applied to the bf16-rounded GEMM outputs).
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
+                    int M, int N, int K, int ldc, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t tiles_base = raw + pad;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bars_base = tiles_base + STAGES * STAGE_BYTES;
+  // barrier layout: full[STAGES], empty[STAGES], tfull[ACC], tempty[ACC]
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + ACC_STAGES + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < ACC_STAGES; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_idx, n_idx;
+        tile_coords(tile, num_m, num_n, m_idx, n_idx);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
+          tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK, m_idx * BM);
+          tma_load_2d(a_dst + A_BYTES, &tmB, full_bar(stage), kb * BK, n_idx * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
+          const uint64_t da = make_desc(a_src), db = make_desc(a_src + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance 32 bytes (16 bf16) along K inside the swizzled 128-byte row
+            umma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // Epilogue warps 2..5; a warp may only touch TMEM lanes 32*(warp%4) .. +31.
+    const int lane_base = 32 * (warp & 3);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m_idx, n_idx;
+      tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_idx * BM + lane_base + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(acc * BN);
+      if (EPI == 0) {
+        bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = n_idx * BN + c * 32 + v * 8;
+              if (col + 8 <= N) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
+        // gate = columns [0,128), up = columns [128,256) of this tile → 128 output columns
+        bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c * 32, g);
+          tmem_ld32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = n_idx * (BN / 2) + c * 32 + v * 8;
+              if (col + 8 <= ldc) {  // ldc = true output width I (the interleaved N/2 may be padded)
+                float a[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float gg = Ty<bf16>::rnd(__uint_as_float(g[v * 8 + j]));
+                  const float uu = Ty<bf16>::rnd(__uint_as_float(u[v * 8 + j]));
+                  a[j] = Ty<bf16>::rnd(silu_f(gg)) * uu;
+                }
+                uint4 o;
+                o.x = pack_bf16(a[0], a[1]);
+                o.y = pack_bf16(a[2], a[3]);
+                o.z = pack_bf16(a[4], a[5]);
+                o.w = pack_bf16(a[6], a[7]);
+                *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up: report, then give copies and MMAs already in flight time to land
+    // before shared memory and TMEM are released.
+    if (threadIdx.x == 0) set_err(err, DERR_GEMM_TIMEOUT);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace tcg
+
+// Row-major [rows, cols] bf16 matrix, box = box_rows x 64 columns, 128-byte swizzle, zero fill
+// outside the matrix.
+int tc_make_tmap(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  static_assert(sizeof(TcTensorMap) == sizeof(CUtensorMap), "tensor map size");
+  auto fn = tcg::encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)tcg::BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+int tc_make_tmap_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K) { return tc_make_tmap(out, X, M, K, tcg::BM); }
+int tc_make_tmap_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K) { return tc_make_tmap(out, W, N, K, tcg::BN); }
+
+bool tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 8) == 0 && (N % 8) == 0; }
+
+cudaError_t tc_gemm_prepare_device() {
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  return cudaSuccess;
+}
+
+cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
+                           int sm_count, int* err, cudaStream_t stream) {
+  const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
+  const int grid = num_tiles < sm_count ? num_tiles : sm_count;
+  if (epi == 0) {
+    tcg::gemm_bf16_tc_kernel<0><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(
+        *reinterpret_cast<const CUtensorMap*>(tmA), *reinterpret_cast<const CUtensorMap*>(tmB), (bf16*)C, M, N, K, ldc, err);
+  } else {
+    tcg::gemm_bf16_tc_kernel<1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(
+        *reinterpret_cast<const CUtensorMap*>(tmA), *reinterpret_cast<const CUtensorMap*>(tmB), (bf16*)C, M, N, K, ldc, err);
+  }
+  return cudaGetLastError();
+}

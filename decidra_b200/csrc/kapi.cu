@@ -1,0 +1,99 @@
+// Kernel-level C entry points: raw device pointers in, one launch out. They exist so that every
+// kernel can be checked against the CPU oracle and timed on its own through the C ABI.
+#include "../../include/decidra_b200.h"
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+#include "kernels.h"
+
+namespace {
+inline int rc_of(cudaError_t e) { return e == cudaSuccess ? DCD_OK : (e == cudaErrorInvalidValue ? DCD_E_INVALID : DCD_E_CUDA); }
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+}  // namespace
+
+#define DISPATCH(dtype, call_f32, call_bf16) ((dtype) == 0 ? rc_of(call_f32) : (dtype) == 1 ? rc_of(call_bf16) : DCD_E_INVALID)
+
+extern "C" {
+
+int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int epi, int sm_count, int* err, void* stream) {
+  if (!tc_shape_ok(M, N, K) || sm_count <= 0 || (epi != 0 && epi != 1)) return DCD_E_INVALID;
+  TcTensorMap ta, tb;
+  if (tc_make_tmap_a(&ta, X, M, K) || tc_make_tmap_b(&tb, W, N, K)) return DCD_E_CUDA;
+  if (tc_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  return rc_of(tc_gemm_launch(&ta, &tb, C, M, N, K, ldc, epi, sm_count, err, S(stream)));
+}
+
+int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
+  return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
+                  launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));
+}
+
+int dcd_k_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, float eps, int zero_centered, int dtype, void* stream) {
+  return DISPATCH(dtype, launch_rmsnorm<float>((const float*)x, (const float*)w, (float*)out, rows, cols, eps, zero_centered != 0, S(stream)),
+                  launch_rmsnorm<bf16>((const bf16*)x, (const bf16*)w, (bf16*)out, rows, cols, eps, zero_centered != 0, S(stream)));
+}
+
+int dcd_k_add_rmsnorm(const void* x, const void* mix, const void* w, void* residual, void* out, int rows, int cols, float eps, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_add_rmsnorm<float>((const float*)x, (const float*)mix, (const float*)w, (float*)residual, (float*)out, rows, cols, eps, S(stream)),
+                  launch_add_rmsnorm<bf16>((const bf16*)x, (const bf16*)mix, (const bf16*)w, (bf16*)residual, (bf16*)out, rows, cols, eps, S(stream)));
+}
+
+int dcd_k_rmsnorm_gated(const void* x, const void* z, int z_stride, const void* w, void* out, int tokens, int heads, int cols, float eps, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_rmsnorm_gated<float>((const float*)x, (const float*)z, z_stride, (const float*)w, (float*)out, tokens, heads, cols, eps, S(stream)),
+                  launch_rmsnorm_gated<bf16>((const bf16*)x, (const bf16*)z, z_stride, (const bf16*)w, (bf16*)out, tokens, heads, cols, eps, S(stream)));
+}
+
+int dcd_k_silu_mul(const void* gate, const void* up, void* out, size_t n, int dtype, void* stream) {
+  return DISPATCH(dtype, launch_silu_mul<float>((const float*)gate, (const float*)up, (float*)out, n, S(stream)),
+                  launch_silu_mul<bf16>((const bf16*)gate, (const bf16*)up, (bf16*)out, n, S(stream)));
+}
+
+int dcd_k_add(const void* a, const void* b, void* out, size_t n, int dtype, void* stream) {
+  return DISPATCH(dtype, launch_add<float>((const float*)a, (const float*)b, (float*)out, n, S(stream)),
+                  launch_add<bf16>((const bf16*)a, (const bf16*)b, (bf16*)out, n, S(stream)));
+}
+
+int dcd_k_conv1d_silu(const void* x, int x_stride, const void* hist, const void* w, void* out, const int32_t* cu_seqlens,
+                      const int32_t* tok_q, int total, int ch, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_conv1d_silu<float>((const float*)x, x_stride, (const float*)hist, (const float*)w, (float*)out, cu_seqlens, tok_q, total, ch, S(stream)),
+                  launch_conv1d_silu<bf16>((const bf16*)x, x_stride, (const bf16*)hist, (const bf16*)w, (bf16*)out, cu_seqlens, tok_q, total, ch, S(stream)));
+}
+
+int dcd_k_gdn_prepare(const void* conv, int conv_stride, const void* b, const void* a, int ba_stride, const float* A_log, const float* dt_bias,
+                      float* qf, float* kf, float* g, float* beta, int T, int nk, int nv, int dk, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_gdn_prepare<float>((const float*)conv, conv_stride, (const float*)b, (const float*)a, ba_stride, A_log, dt_bias, qf, kf, g, beta, T, nk, nv, dk, S(stream)),
+                  launch_gdn_prepare<bf16>((const bf16*)conv, conv_stride, (const bf16*)b, (const bf16*)a, ba_stride, A_log, dt_bias, qf, kf, g, beta, T, nk, nv, dk, S(stream)));
+}
+
+int dcd_k_gdn_recurrent(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                        const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv, int dk,
+                        int dv, int narrow, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_gdn_recurrent<float>(qf, kf, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)),
+                  launch_gdn_recurrent<bf16>(qf, kf, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)));
+}
+
+int dcd_k_qk_norm_rope(const void* qg, int qg_stride, const void* kraw, int k_stride, const void* qw, const void* kw, const void* cos_t,
+                       const void* sin_t, const int32_t* positions, int max_pos, void* q, void* k, int T, int heads, int kv, int hd,
+                       int rotary_dim, float eps, int* err, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_qk_norm_rope<float>((const float*)qg, qg_stride, (const float*)kraw, k_stride, (const float*)qw, (const float*)kw, (const float*)cos_t, (const float*)sin_t, positions, 0, max_pos, (float*)q, (float*)k, kv * hd, T, heads, kv, hd, rotary_dim, eps, err, S(stream)),
+                  launch_qk_norm_rope<bf16>((const bf16*)qg, qg_stride, (const bf16*)kraw, k_stride, (const bf16*)qw, (const bf16*)kw, (const bf16*)cos_t, (const bf16*)sin_t, positions, 0, max_pos, (bf16*)q, (bf16*)k, kv * hd, T, heads, kv, hd, rotary_dim, eps, err, S(stream)));
+}
+
+int dcd_k_attention(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                    const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out, const int32_t* cu_seqlens,
+                    const int32_t* tok_q, int T, int heads, int kv, int hd, int split, int dtype, void* stream) {
+  return DISPATCH(dtype,
+                  launch_attn_fma<float>((const float*)q, (const float*)k_own, k_stride, (const float*)v_own, v_stride, (const float*)k_state, (const float*)v_state, n_state, (const float*)gate_qg, qg_stride, (float*)out, cu_seqlens, tok_q, T, heads, kv, hd, split, S(stream)),
+                  launch_attn_fma<bf16>((const bf16*)q, (const bf16*)k_own, k_stride, (const bf16*)v_own, v_stride, (const bf16*)k_state, (const bf16*)v_state, n_state, (const bf16*)gate_qg, qg_stride, (bf16*)out, cu_seqlens, tok_q, T, heads, kv, hd, split, S(stream)));
+}
+
+int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream) {
+  return rc_of(launch_readout(x, W, out, B, H, R, S(stream)));
+}
+
+}  // extern "C"

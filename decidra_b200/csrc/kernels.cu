@@ -1,0 +1,872 @@
+// Bandwidth / latency kernels of the state-once question path (everything except the
+// tensor-core GEMM): packing, embedding gather, norms, RoPE, varlen prefix-bidirectional
+// attention (plain-FMA form), causal conv, gated-delta-net prepare + recurrence, gated norm,
+// residuals, last-row gather + readout, and the seeded weight generator.
+//
+// Each kernel names the reference code (paths inside juanqui/decidra) whose arithmetic it
+// reproduces. All are templated on the storage type T (float for the f32 engine, bf16 for
+// the bf16 engine); Ty<T>::rnd() rounds at the points where the reference rounds through bf16.
+#include "common.cuh"
+#include "kernels.h"
+
+// ---------------------------------------------------------------------------
+// Packing: lens[B] -> cu_seqlens[B+1], last_row[B]; then per token (question, position).
+// Replaces the host loops of BatchInfo::new / positions / last_row_indices
+// (native/src/engine.rs:693-735, 1669-1674) and their H2D copies.
+// ---------------------------------------------------------------------------
+__global__ void pack_scan_kernel(const int32_t* __restrict__ lens, int B, int32_t* __restrict__ cu,
+                                 int32_t* __restrict__ last_row, int* __restrict__ err) {
+  __shared__ int part[1024];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int per = (B + nt - 1) / nt;
+  const int lo = min(tid * per, B), hi = min(lo + per, B);
+  int s = 0;
+  bool bad = false;
+  for (int i = lo; i < hi; ++i) {
+    const int l = lens[i];
+    bad |= (l <= 0);
+    s += l;
+  }
+  if (bad) set_err(err, DERR_EMPTY_ITEM);
+  part[tid] = s;
+  __syncthreads();
+  for (int off = 1; off < nt; off <<= 1) {
+    int v = tid >= off ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  int run = part[tid] - s;  // exclusive prefix
+  for (int i = lo; i < hi; ++i) {
+    cu[i] = run;
+    run += lens[i];
+    last_row[i] = run - 1;
+  }
+  if (tid == nt - 1) cu[B] = part[tid];
+}
+
+__global__ void pack_fill_kernel(const int32_t* __restrict__ cu, int B, int total, int pos_start,
+                                 int32_t* __restrict__ tok_q, int32_t* __restrict__ tok_pos) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  int lo = 0, hi = B;  // largest b with cu[b] <= t
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cu[mid] <= t) lo = mid; else hi = mid;
+  }
+  tok_q[t] = lo;
+  tok_pos[t] = pos_start + (t - cu[lo]);
+}
+
+cudaError_t launch_pack(const int32_t* lens, int B, int total, int pos_start, int32_t* cu, int32_t* last_row,
+                        int32_t* tok_q, int32_t* tok_pos, int* err, cudaStream_t s) {
+  pack_scan_kernel<<<1, 1024, 0, s>>>(lens, B, cu, last_row, err);
+  if (total > 0) pack_fill_kernel<<<(total + 255) / 256, 256, 0, s>>>(cu, B, total, pos_start, tok_q, tok_pos);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Embedding gather with vocabulary bound check (error word, rows zeroed; never clamps):
+// Engine::embed (native/src/engine.rs:1364-1439), embed_gather_bf16 (native/kernels/kernels.cu:84-94).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const uint32_t* __restrict__ ids, T* __restrict__ out, int H,
+                             uint32_t vocab, int* __restrict__ err) {
+  const int row = blockIdx.x;
+  const uint32_t id = ids[row];
+  const int n16 = (int)((size_t)H * sizeof(T) / 16);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * H);
+  if (id >= vocab) {
+    if (threadIdx.x == 0) set_err(err, DERR_TOKEN_RANGE);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * H);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+}
+
+template <typename T>
+cudaError_t launch_embed(const T* table, const uint32_t* ids, T* out, int T_rows, int H, int vocab, int* err, cudaStream_t s) {
+  embed_kernel<T><<<T_rows, 128, 0, s>>>(table, ids, out, H, (uint32_t)vocab, err);
+  return cudaGetLastError();
+}
+template cudaError_t launch_embed<float>(const float*, const uint32_t*, float*, int, int, int, int*, cudaStream_t);
+template cudaError_t launch_embed<bf16>(const bf16*, const uint32_t*, bf16*, int, int, int, int*, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// RMSNorm family. One CTA per row; f32 sum of squares; scale = 1/sqrt(mean+eps);
+// out = T(x * scale * (w + zero_centered)).  rmsnorm_bf16 / add_rmsnorm_bf16,
+// native/kernels/kernels.cu:378-426. `rows_idx` (optional) gathers input rows
+// (gather_rows_bf16, native/kernels/kernels.cu:2351-2361 — the last-row gather is applied
+// before the final norm here, which is the same function row by row).
+// ---------------------------------------------------------------------------
+template <typename T, typename TO>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __restrict__ out, int cols, float eps,
+                               float wofs, const int32_t* __restrict__ rows_idx) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const T* xr = x + (size_t)(rows_idx ? rows_idx[row] : row) * cols;
+  TO* orow = out + (size_t)row * cols;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float v = Ty<T>::ld(xr + j);
+    ss += v * v;
+  }
+  const float mean = block_sum(ss, red) / (float)cols;
+  const float scale = 1.0f / sqrtf(mean + eps);
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float wv = Ty<T>::ld(w + j) + wofs;
+    const float y = Ty<T>::rnd(Ty<T>::ld(xr + j) * scale * wv);
+    orow[j] = (TO)y;
+  }
+}
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ mix, const T* __restrict__ w,
+                                   T* __restrict__ residual, T* __restrict__ out, int cols, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const T* xr = x + (size_t)row * cols;
+  const T* mr = mix + (size_t)row * cols;
+  T* rr = residual + (size_t)row * cols;
+  T* orow = out + (size_t)row * cols;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float r = Ty<T>::rnd(Ty<T>::ld(xr + j) + Ty<T>::ld(mr + j));
+    Ty<T>::st(rr + j, r);
+    ss += r * r;
+  }
+  const float mean = block_sum(ss, red) / (float)cols;
+  const float scale = 1.0f / sqrtf(mean + eps);
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    const float wv = Ty<T>::ld(w + j) + 1.0f;
+    Ty<T>::st(orow + j, Ty<T>::ld(rr + j) * scale * wv);
+  }
+}
+
+template <typename T>
+cudaError_t launch_rmsnorm(const T* x, const T* w, T* out, int rows, int cols, float eps, bool zero_centered, cudaStream_t s) {
+  rmsnorm_kernel<T, T><<<rows, 256, 0, s>>>(x, w, out, cols, eps, zero_centered ? 1.0f : 0.0f, nullptr);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_add_rmsnorm(const T* x, const T* mix, const T* w, T* residual, T* out, int rows, int cols, float eps, cudaStream_t s) {
+  add_rmsnorm_kernel<T><<<rows, 256, 0, s>>>(x, mix, w, residual, out, cols, eps);
+  return cudaGetLastError();
+}
+// Final norm of the gathered last rows, widened to f32 for the readout
+// (native/src/engine.rs:4968-4975).
+template <typename T>
+cudaError_t launch_final_norm_rows(const T* x, const T* w, float* out, const int32_t* rows_idx, int B, int cols, float eps, cudaStream_t s) {
+  rmsnorm_kernel<T, float><<<B, 256, 0, s>>>(x, w, out, cols, eps, 1.0f, rows_idx);
+  return cudaGetLastError();
+}
+#define INST_NORM(T)                                                                                                   \
+  template cudaError_t launch_rmsnorm<T>(const T*, const T*, T*, int, int, float, bool, cudaStream_t);                  \
+  template cudaError_t launch_add_rmsnorm<T>(const T*, const T*, const T*, T*, T*, int, int, float, cudaStream_t);      \
+  template cudaError_t launch_final_norm_rows<T>(const T*, const T*, float*, const int32_t*, int, int, float, cudaStream_t);
+INST_NORM(float)
+INST_NORM(bf16)
+
+// Gated RMSNorm, one warp per (token, value head) row of `cols` = dv:
+// n = T(x*scale); y = T(n*w) (weight not zero-centred); out = T(y * T(silu(z))).
+// rmsnorm_gated_bf16, native/kernels/kernels.cu:430-455. z is read with a row stride
+// because it lives inside the fused input-projection output.
+template <typename T>
+__global__ void rmsnorm_gated_kernel(const T* __restrict__ x, const T* __restrict__ z, int z_stride, const T* __restrict__ w,
+                                     T* __restrict__ out, int rows, int heads, int cols, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int t = row / heads, h = row - t * heads;
+  const T* xr = x + (size_t)row * cols;
+  const T* zr = z + (size_t)t * z_stride + (size_t)h * cols;
+  T* orow = out + (size_t)row * cols;
+  float ss = 0.f;
+  for (int j = lane; j < cols; j += 32) {
+    const float v = Ty<T>::ld(xr + j);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)cols + eps);
+  for (int j = lane; j < cols; j += 32) {
+    const float normed = Ty<T>::rnd(Ty<T>::ld(xr + j) * scale);
+    const float scaled = Ty<T>::rnd(normed * Ty<T>::ld(w + j));
+    const float g = Ty<T>::ld(zr + j);
+    Ty<T>::st(orow + j, scaled * Ty<T>::rnd(silu_f(g)));
+  }
+}
+template <typename T>
+cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* w, T* out, int tokens, int heads, int cols, float eps, cudaStream_t s) {
+  const int rows = tokens * heads;
+  rmsnorm_gated_kernel<T><<<(rows + 7) / 8, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, cols, eps);
+  return cudaGetLastError();
+}
+template cudaError_t launch_rmsnorm_gated<float>(const float*, const float*, int, const float*, float*, int, int, int, float, cudaStream_t);
+template cudaError_t launch_rmsnorm_gated<bf16>(const bf16*, const bf16*, int, const bf16*, bf16*, int, int, int, float, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Elementwise: residual add (add_bf16, kernels.cu:485-490) and SwiGLU over the
+// tile-interleaved gate/up GEMM output (silu_mul_bf16, kernels.cu:492-501).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) Ty<T>::st(out + i, Ty<T>::ld(a + i) + Ty<T>::ld(b + i));
+}
+template <typename T>
+cudaError_t launch_add(const T* a, const T* b, T* out, size_t n, cudaStream_t s) {
+  add_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, out, n);
+  return cudaGetLastError();
+}
+template cudaError_t launch_add<float>(const float*, const float*, float*, size_t, cudaStream_t);
+template cudaError_t launch_add<bf16>(const bf16*, const bf16*, bf16*, size_t, cudaStream_t);
+
+// gu: [T, gu_stride] where each 256-column tile holds 128 gate then 128 up columns.
+template <typename T>
+__global__ void silu_mul_interleaved_kernel(const T* __restrict__ gu, int gu_stride, T* __restrict__ out, int I, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / I;
+  const int c = (int)(i - t * I);
+  const T* row = gu + t * gu_stride + (size_t)(c >> 7) * 256 + (c & 127);
+  const float g = Ty<T>::ld(row), u = Ty<T>::ld(row + 128);
+  Ty<T>::st(out + i, Ty<T>::rnd(silu_f(g)) * u);
+}
+template <typename T>
+cudaError_t launch_silu_mul_interleaved(const T* gu, int gu_stride, T* out, int tokens, int I, cudaStream_t s) {
+  const size_t n = (size_t)tokens * I;
+  silu_mul_interleaved_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gu, gu_stride, out, I, n);
+  return cudaGetLastError();
+}
+template cudaError_t launch_silu_mul_interleaved<float>(const float*, int, float*, int, int, cudaStream_t);
+template cudaError_t launch_silu_mul_interleaved<bf16>(const bf16*, int, bf16*, int, int, cudaStream_t);
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ out, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) Ty<T>::st(out + i, Ty<T>::rnd(silu_f(Ty<T>::ld(g + i))) * Ty<T>::ld(u + i));
+}
+template <typename T>
+cudaError_t launch_silu_mul(const T* g, const T* u, T* out, size_t n, cudaStream_t s) {
+  silu_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(g, u, out, n);
+  return cudaGetLastError();
+}
+template cudaError_t launch_silu_mul<float>(const float*, const float*, float*, size_t, cudaStream_t);
+template cudaError_t launch_silu_mul<bf16>(const bf16*, const bf16*, bf16*, size_t, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// split_q_gate + head RMSNorm(1+w) + partial NeoX RoPE, one warp per (token, head).
+// split_q_gate_bf16 / rmsnorm_bf16 / rope_bf16: native/kernels/kernels.cu:516-557, 406-426.
+// q heads are read from the fused projection [T, *, 2*hd] (first hd of each head), k heads
+// from [T, kv, hd]; both with a row stride. cos/sin are tables [max_pos, rhalf] in T
+// (host-built exactly like Engine::rope_tables_positions, native/src/engine.rs:1619-1643).
+// ---------------------------------------------------------------------------
+template <typename T, int HD>
+__global__ void qk_norm_rope_kernel(const T* __restrict__ qg, int qg_stride, const T* __restrict__ kraw, int k_stride,
+                                    const T* __restrict__ qw, const T* __restrict__ kw, const T* __restrict__ cos_t,
+                                    const T* __restrict__ sin_t, const int32_t* __restrict__ positions, int pos_base,
+                                    int max_pos, T* __restrict__ q, T* __restrict__ k, int k_out_stride, int tokens,
+                                    int heads, int kv, int rhalf, float eps, int* __restrict__ err) {
+  constexpr int V = HD / 32;
+  __shared__ float sh[8][HD];
+  const int wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * 8 + wi;
+  const int slots = heads + kv;
+  if (idx >= tokens * slots) return;
+  const int t = idx / slots, hs = idx - t * slots;
+  const T* src;
+  const T* w;
+  T* dst;
+  if (hs < heads) {
+    src = qg + (size_t)t * qg_stride + (size_t)hs * 2 * HD;
+    w = qw;
+    dst = q + ((size_t)t * heads + hs) * HD;
+  } else {
+    src = kraw + (size_t)t * k_stride + (size_t)(hs - heads) * HD;
+    w = kw;
+    dst = k + (size_t)t * k_out_stride + (size_t)(hs - heads) * HD;
+  }
+  float v[V];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    v[i] = Ty<T>::ld(src + lane * V + i);
+    ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    v[i] = Ty<T>::rnd(v[i] * scale * (Ty<T>::ld(w + lane * V + i) + 1.0f));
+    sh[wi][lane * V + i] = v[i];
+  }
+  __syncwarp();
+  int pos = positions ? positions[t] : pos_base + t;
+  if (pos < 0 || pos >= max_pos) {
+    if (lane == 0) set_err(err, DERR_POSITION_RANGE);
+    pos = 0;
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int d = lane * V + i;
+    float y = v[i];
+    if (d < 2 * rhalf) {
+      const int f = d < rhalf ? d : d - rhalf;
+      const float c = Ty<T>::ld(cos_t + (size_t)pos * rhalf + f);
+      const float s = Ty<T>::ld(sin_t + (size_t)pos * rhalf + f);
+      const float a = sh[wi][f], b = sh[wi][f + rhalf];
+      if (d < rhalf)
+        y = Ty<T>::rnd(__fsub_rn(Ty<T>::rnd(__fmul_rn(a, c)), Ty<T>::rnd(__fmul_rn(b, s))));
+      else
+        y = Ty<T>::rnd(__fadd_rn(Ty<T>::rnd(__fmul_rn(b, c)), Ty<T>::rnd(__fmul_rn(a, s))));
+    }
+    Ty<T>::st(dst + d, y);
+  }
+}
+
+template <typename T>
+cudaError_t launch_qk_norm_rope(const T* qg, int qg_stride, const T* kraw, int k_stride, const T* qw, const T* kw, const T* cos_t,
+                                const T* sin_t, const int32_t* positions, int pos_base, int max_pos, T* q, T* k, int k_out_stride,
+                                int tokens, int heads, int kv, int hd, int rotary_dim, float eps, int* err, cudaStream_t s) {
+  const int n = tokens * (heads + kv);
+  const int grid = (n + 7) / 8;
+#define QK_CASE(HD_)                                                                                                     \
+  case HD_:                                                                                                              \
+    qk_norm_rope_kernel<T, HD_><<<grid, 256, 0, s>>>(qg, qg_stride, kraw, k_stride, qw, kw, cos_t, sin_t, positions,     \
+                                                     pos_base, max_pos, q, k, k_out_stride, tokens, heads, kv,           \
+                                                     rotary_dim / 2, eps, err);                                         \
+    break;
+  switch (hd) {
+    QK_CASE(64)
+    QK_CASE(128)
+    QK_CASE(256)
+    default: return cudaErrorInvalidValue;
+  }
+#undef QK_CASE
+  return cudaGetLastError();
+}
+template cudaError_t launch_qk_norm_rope<float>(const float*, int, const float*, int, const float*, const float*, const float*, const float*, const int32_t*, int, int, float*, float*, int, int, int, int, int, int, float, int*, cudaStream_t);
+template cudaError_t launch_qk_norm_rope<bf16>(const bf16*, int, const bf16*, int, const bf16*, const bf16*, const bf16*, const bf16*, const int32_t*, int, int, bf16*, bf16*, int, int, int, int, int, int, float, int*, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Varlen prefix-bidirectional attention, plain-FMA form: one warp per (token, head), keys
+// streamed four at a time with an online softmax. Each packed question attends to
+// [state K/V (n_state rows) || its own K/V rows]; no causal mask. Output is multiplied by
+// the sigmoid output gate when gate_qg is given.
+//   Engine::full_attention_batch cascade branch (native/src/engine.rs:1985-2042),
+//   fi_prefill_bf16_ext (native/third_party/flashinfer/fi_prefill.cu:161-173; scale 1/sqrt(hd),
+//   GQA group heads/kv, probabilities rounded to the storage type before P.V),
+//   sigmoid_gate_bf16 (native/kernels/kernels.cu:504-512).
+// split > 0: single sequence [state || question] with the block-cascade mask of
+//   block_cascade_mask (native/src/engine.rs:490-504): rows < split see keys < split.
+// ---------------------------------------------------------------------------
+template <typename T, int HD>
+__global__ void attn_fma_kernel(const T* __restrict__ q, const T* __restrict__ k_own, int k_stride, const T* __restrict__ v_own,
+                                int v_stride, const T* __restrict__ k_state, const T* __restrict__ v_state, int n_state,
+                                const T* __restrict__ gate_qg, int qg_stride, T* __restrict__ out,
+                                const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int tokens, int heads, int kv,
+                                int split) {
+  constexpr int V = HD / 32;
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = idx / heads, h = idx - t * heads;
+  const int kh = h / (heads / kv);
+  const int qi = tok_q ? tok_q[t] : 0;
+  const int off = cu ? cu[qi] : 0;
+  int len = cu ? cu[qi + 1] - off : tokens;
+  if (split > 0 && t < split) len = split;
+  const float scale = 1.0f / sqrtf((float)HD);
+  float qv[V], acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    qv[i] = Ty<T>::ld(q + ((size_t)t * heads + h) * HD + lane * V + i);
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  const int nk = n_state + len;
+  for (int j0 = 0; j0 < nk; j0 += 4) {
+    float sc[4];
+    const T* vp[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      float d = 0.f;
+      vp[u] = nullptr;
+      if (j < nk) {
+        const T* kp;
+        if (j < n_state) {
+          kp = k_state + ((size_t)j * kv + kh) * HD;
+          vp[u] = v_state + ((size_t)j * kv + kh) * HD;
+        } else {
+          kp = k_own + (size_t)(off + j - n_state) * k_stride + (size_t)kh * HD;
+          vp[u] = v_own + (size_t)(off + j - n_state) * v_stride + (size_t)kh * HD;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) d += qv[i] * Ty<T>::ld(kp + lane * V + i);
+      }
+      sc[u] = d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+    }
+    float mx = m;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      sc[u] = (j0 + u < nk) ? sc[u] * scale : -INFINITY;
+      mx = fmaxf(mx, sc[u]);
+    }
+    const float corr = expf(m - mx);
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (j0 + u < nk) {
+        const float p = Ty<T>::rnd(expf(sc[u] - mx));
+        l += p;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] += p * Ty<T>::ld(vp[u] + lane * V + i);
+      }
+    }
+    m = mx;
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    float o = Ty<T>::rnd(acc[i] * inv);
+    if (gate_qg) {
+      const float g = Ty<T>::ld(gate_qg + (size_t)t * qg_stride + (size_t)h * 2 * HD + HD + lane * V + i);
+      o = o * Ty<T>::rnd(sigmoid_f(g));
+    }
+    Ty<T>::st(out + ((size_t)t * heads + h) * HD + lane * V + i, o);
+  }
+}
+
+template <typename T>
+cudaError_t launch_attn_fma(const T* q, const T* k_own, int k_stride, const T* v_own, int v_stride, const T* k_state,
+                            const T* v_state, int n_state, const T* gate_qg, int qg_stride, T* out, const int32_t* cu,
+                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s) {
+  const int n = tokens * heads;
+  const int grid = (n + 3) / 4;
+#define AT_CASE(HD_)                                                                                                      \
+  case HD_:                                                                                                               \
+    attn_fma_kernel<T, HD_><<<grid, 128, 0, s>>>(q, k_own, k_stride, v_own, v_stride, k_state, v_state, n_state, gate_qg, \
+                                                 qg_stride, out, cu, tok_q, tokens, heads, kv, split);                   \
+    break;
+  switch (hd) {
+    AT_CASE(64)
+    AT_CASE(128)
+    AT_CASE(256)
+    default: return cudaErrorInvalidValue;
+  }
+#undef AT_CASE
+  return cudaGetLastError();
+}
+template cudaError_t launch_attn_fma<float>(const float*, const float*, int, const float*, int, const float*, const float*, int, const float*, int, float*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t);
+template cudaError_t launch_attn_fma<bf16>(const bf16*, const bf16*, int, const bf16*, int, const bf16*, const bf16*, int, const bf16*, int, bf16*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Depthwise causal conv (4 taps) + SiLU over a packed batch; taps before a sequence start
+// come from the cached 3-row tail `hist` (or zero). fmaf chain in tap order, round, SiLU:
+// conv1d_silu_seeded_tiled_bf16, native/kernels/kernels.cu:2085-2122.
+// x is read with a row stride (it is the first conv_dim columns of the fused projection).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void conv1d_silu_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ hist, const T* __restrict__ w,
+                                   T* __restrict__ out, const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q,
+                                   int ch) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  const int t = blockIdx.y;
+  const int off = cu ? cu[tok_q[t]] : 0;
+  const int lt = t - off;
+  float xs[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int src = lt - 3 + j;
+    if (src < 0)
+      xs[j] = hist ? Ty<T>::ld(hist + (size_t)(src + 3) * ch + c) : 0.f;
+    else
+      xs[j] = Ty<T>::ld(x + (size_t)(off + src) * x_stride + c);
+  }
+  float acc = fmaf(xs[0], Ty<T>::ld(w + c * 4 + 0), 0.f);
+  acc = fmaf(xs[1], Ty<T>::ld(w + c * 4 + 1), acc);
+  acc = fmaf(xs[2], Ty<T>::ld(w + c * 4 + 2), acc);
+  acc = fmaf(xs[3], Ty<T>::ld(w + c * 4 + 3), acc);
+  const float v = Ty<T>::rnd(acc);
+  Ty<T>::st(out + (size_t)t * ch + c, silu_f(v));
+}
+template <typename T>
+cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T* w, T* out, const int32_t* cu,
+                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s) {
+  dim3 grid((ch + 255) / 256, tokens);
+  conv1d_silu_kernel<T><<<grid, 256, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch);
+  return cudaGetLastError();
+}
+template cudaError_t launch_conv1d_silu<float>(const float*, int, const float*, const float*, float*, const int32_t*, const int32_t*, int, int, cudaStream_t);
+template cudaError_t launch_conv1d_silu<bf16>(const bf16*, int, const bf16*, const bf16*, bf16*, const int32_t*, const int32_t*, int, int, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// GDN prepare (compact form): per (token, key head) L2-normalised q (also scaled by
+// dk^-1/2) and k in f32; per (token, value head) g = -exp(A_log)*softplus(a+dt_bias) and
+// beta = T(sigmoid(b)). gdn_prepare_compact_bf16, native/kernels/kernels.cu:765-815.
+// b and a are read from the fused projection output with a row stride.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gdn_prepare_kernel(const T* __restrict__ conv, int conv_stride, const T* __restrict__ b, const T* __restrict__ a,
+                                   int ba_stride, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                   float* __restrict__ qf, float* __restrict__ kf, float* __restrict__ g, float* __restrict__ beta,
+                                   int nk, int nv, int dk) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, kh = blockIdx.y;
+  const int key_dim = nk * dk;
+  const T* row = conv + (size_t)t * conv_stride;
+  const int j = threadIdx.x;  // blockDim.x == dk
+  const float qv = Ty<T>::ld(row + kh * dk + j);
+  const float kvv = Ty<T>::ld(row + key_dim + kh * dk + j);
+  const float qn = block_sum(qv * qv, red);
+  const float kn = block_sum(kvv * kvv, red);
+  const float qscale = (1.0f / sqrtf(qn + 1e-6f)) * (1.0f / sqrtf((float)dk));
+  const float kscale = 1.0f / sqrtf(kn + 1e-6f);
+  qf[((size_t)t * nk + kh) * dk + j] = qv * qscale;
+  kf[((size_t)t * nk + kh) * dk + j] = kvv * kscale;
+  const int rep = nv / nk;
+  if (j < rep) {
+    const int vh = kh * rep + j;
+    const float av = Ty<T>::ld(a + (size_t)t * ba_stride + vh) + dt_bias[vh];
+    const float sp = av > 20.f ? av : log1pf(expf(av));
+    g[(size_t)t * nv + vh] = -expf(A_log[vh]) * sp;
+    beta[(size_t)t * nv + vh] = Ty<T>::rnd(sigmoid_f(Ty<T>::ld(b + (size_t)t * ba_stride + vh)));
+  }
+}
+template <typename T>
+cudaError_t launch_gdn_prepare(const T* conv, int conv_stride, const T* b, const T* a, int ba_stride, const float* A_log,
+                               const float* dt_bias, float* qf, float* kf, float* g, float* beta, int tokens, int nk, int nv,
+                               int dk, cudaStream_t s) {
+  if (dk % 32 != 0 || dk > 1024 || nv / nk > dk) return cudaErrorInvalidValue;
+  dim3 grid(tokens, nk);
+  gdn_prepare_kernel<T><<<grid, dk, 0, s>>>(conv, conv_stride, b, a, ba_stride, A_log, dt_bias, qf, kf, g, beta, nk, nv, dk);
+  return cudaGetLastError();
+}
+template cudaError_t launch_gdn_prepare<float>(const float*, int, const float*, const float*, int, const float*, const float*, float*, float*, float*, float*, int, int, int, int, cudaStream_t);
+template cudaError_t launch_gdn_prepare<bf16>(const bf16*, int, const bf16*, const bf16*, int, const float*, const float*, float*, float*, float*, float*, int, int, int, int, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Gated delta rule, sequential in time, f32 state in registers. One CTA per
+// (value head, slice of VC value columns, packed sequence); 4 lanes share a column and
+// each holds DK/4 state rows. Starts from the immutable cached state `seed` (or zero) and
+// optionally stores the final state (capture). Per step:
+//   S *= exp(g); kv = S^T k; delta = (v - kv) * beta; S += k delta^T; o = S^T q.
+// gdn_recurrent (scalar statement, native/kernels/kernels.cu:834-865) and
+// gdn_recurrent_reg_split_seeded_bf16 (production form, :2245-2300).
+// v is read straight from the conv output (value columns start at 2*nk*dk).
+// ---------------------------------------------------------------------------
+template <typename T, int DK, int VC>
+__global__ void __launch_bounds__(VC * 4)
+gdn_recurrent_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const T* __restrict__ conv, int conv_stride,
+                     const float* __restrict__ g, const float* __restrict__ beta, const float* __restrict__ seed,
+                     float* __restrict__ final_state, T* __restrict__ out, const int32_t* __restrict__ cu, int nk, int nv, int dv) {
+  constexpr int R = DK / 4;     // state rows per lane
+  constexpr int TS = 8;         // time steps staged per shared-memory tile
+  constexpr int KP = R + 4;     // padded chunk stride (avoids 4-way bank conflicts)
+  __shared__ __align__(16) float sk[TS][4 * KP];
+  __shared__ __align__(16) float sq[TS][4 * KP];
+  __shared__ float sv[TS][VC];
+  __shared__ float sg[TS], sb[TS];
+  const int slices = dv / VC;
+  const int head = blockIdx.x / slices, cbase = (blockIdx.x - head * slices) * VC;
+  const int b = blockIdx.y;
+  const int off = cu ? cu[b] : 0;
+  const int len = cu ? cu[b + 1] - off : 0;
+  const int kh = head / (nv / nk);
+  const int tid = threadIdx.x, col = tid >> 2, sub = tid & 3;
+  const int vcol0 = 2 * nk * DK + head * dv + cbase;
+
+  float S[R];
+  if (seed) {
+#pragma unroll
+    for (int m = 0; m < R; ++m) S[m] = seed[((size_t)head * DK + sub * R + m) * dv + cbase + col];
+  } else {
+#pragma unroll
+    for (int m = 0; m < R; ++m) S[m] = 0.f;
+  }
+
+  for (int t0 = 0; t0 < len; t0 += TS) {
+    const int nt = min(TS, len - t0);
+    __syncthreads();
+    for (int i = tid; i < nt * DK; i += VC * 4) {
+      const int tt = i / DK, d = i - tt * DK;
+      const size_t src = ((size_t)(off + t0 + tt) * nk + kh) * DK + d;
+      const int dst = (d / R) * KP + (d % R);
+      sk[tt][dst] = kf[src];
+      sq[tt][dst] = qf[src];
+    }
+    for (int i = tid; i < nt * VC; i += VC * 4) {
+      const int tt = i / VC, c = i - tt * VC;
+      sv[tt][c] = Ty<T>::ld(conv + (size_t)(off + t0 + tt) * conv_stride + vcol0 + c);
+    }
+    if (tid < nt) {
+      sg[tid] = expf(g[(size_t)(off + t0 + tid) * nv + head]);
+      sb[tid] = beta[(size_t)(off + t0 + tid) * nv + head];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dec = sg[tt], bt = sb[tt];
+      const float* kp = &sk[tt][sub * KP];
+      const float* qp = &sq[tt][sub * KP];
+      float kvp = 0.f;
+#pragma unroll
+      for (int m = 0; m < R; m += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + m);
+        S[m] *= dec; S[m + 1] *= dec; S[m + 2] *= dec; S[m + 3] *= dec;
+        kvp += S[m] * k4.x; kvp += S[m + 1] * k4.y; kvp += S[m + 2] * k4.z; kvp += S[m + 3] * k4.w;
+      }
+      kvp += __shfl_xor_sync(0xffffffffu, kvp, 1);
+      kvp += __shfl_xor_sync(0xffffffffu, kvp, 2);
+      const float del = (sv[tt][col] - kvp) * bt;
+      float op = 0.f;
+#pragma unroll
+      for (int m = 0; m < R; m += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + m);
+        const float4 q4 = *reinterpret_cast<const float4*>(qp + m);
+        S[m] += k4.x * del; S[m + 1] += k4.y * del; S[m + 2] += k4.z * del; S[m + 3] += k4.w * del;
+        op += S[m] * q4.x; op += S[m + 1] * q4.y; op += S[m + 2] * q4.z; op += S[m + 3] * q4.w;
+      }
+      op += __shfl_xor_sync(0xffffffffu, op, 1);
+      op += __shfl_xor_sync(0xffffffffu, op, 2);
+      if (sub == 0) Ty<T>::st(out + (size_t)(off + t0 + tt) * (nv * dv) + head * dv + cbase + col, op);
+    }
+  }
+  if (final_state) {
+#pragma unroll
+    for (int m = 0; m < R; ++m)
+      final_state[(((size_t)b * nv + head) * DK + sub * R + m) * dv + cbase + col] = S[m];
+  }
+}
+
+template <typename T>
+cudaError_t launch_gdn_recurrent(const float* qf, const float* kf, const T* conv, int conv_stride, const float* g, const float* beta,
+                                 const float* seed, float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int dk,
+                                 int dv, bool few_sequences, cudaStream_t s) {
+  // Many sequences (question pass): 64 columns per CTA. One long sequence (capture): 16
+  // columns per CTA so that the grid still covers the GPU.
+  const int vc = (few_sequences && dv % 16 == 0) ? 16 : 64;
+  if (dv % vc != 0) return cudaErrorInvalidValue;
+  dim3 grid(nv * (dv / vc), B);
+#define GDN_CASE(DK_, VC_)                                                                                              \
+  gdn_recurrent_kernel<T, DK_, VC_><<<grid, VC_ * 4, 0, s>>>(qf, kf, conv, conv_stride, g, beta, seed, final_state, out, \
+                                                             cu, nk, nv, dv)
+  if (dk == 128 && vc == 64) GDN_CASE(128, 64);
+  else if (dk == 128 && vc == 16) GDN_CASE(128, 16);
+  else if (dk == 64 && vc == 64) GDN_CASE(64, 64);
+  else if (dk == 64 && vc == 16) GDN_CASE(64, 16);
+  else return cudaErrorInvalidValue;
+#undef GDN_CASE
+  return cudaGetLastError();
+}
+template cudaError_t launch_gdn_recurrent<float>(const float*, const float*, const float*, int, const float*, const float*, const float*, float*, float*, const int32_t*, int, int, int, int, int, bool, cudaStream_t);
+template cudaError_t launch_gdn_recurrent<bf16>(const float*, const float*, const bf16*, int, const float*, const float*, const float*, float*, bf16*, const int32_t*, int, int, int, int, int, bool, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// F32 readout: logits[B, R] = x[B, H] . W[R, H]^T, all f32
+// (blas_gemm_f32 call at native/src/engine.rs:4977-4984; HeadMatrix kept in F32, :737-783).
+// One CTA per readout row; the row of W is staged in shared memory once and each warp
+// produces logits for a strided subset of the B hidden rows.
+// ---------------------------------------------------------------------------
+__global__ void readout_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int B, int H, int R) {
+  extern __shared__ float wrow[];
+  const int n = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) wrow[i] = W[(size_t)n * H + i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int b = warp; b < B; b += nw) {
+    const float* xr = x + (size_t)b * H;
+    float acc = 0.f;
+    for (int i = lane; i < H; i += 32) acc += xr[i] * wrow[i];
+    acc = warp_sum(acc);
+    if (lane == 0) out[(size_t)b * R + n] = acc;
+  }
+}
+cudaError_t launch_readout(const float* x, const float* W, float* out, int B, int H, int R, cudaStream_t s) {
+  readout_kernel<<<R, 256, (size_t)H * sizeof(float), s>>>(x, W, out, B, H, R);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Plain-FMA GEMM C[M,N] = X[M,K] . W[N,K]^T with f32 accumulation (f32 engine; diagnostic
+// path of the bf16 engine). 64x64 tile, 16-wide K slices, 256 threads, 4x4 per thread.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_fma_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict__ C, int M,
+                                                        int N, int K, int ldc) {
+  __shared__ float xs[16][64 + 4];
+  __shared__ float ws[16][64 + 4];
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tid = threadIdx.x;
+  const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = tid; i < 64 * 16; i += 256) {
+      const int r = i / 16, kk = i % 16;
+      const int gm = m0 + r, gn = n0 + r, gk = k0 + kk;
+      xs[kk][r] = (gm < M && gk < K) ? Ty<T>::ld(X + (size_t)gm * K + gk) : 0.f;
+      ws[kk][r] = (gn < N && gk < K) ? Ty<T>::ld(W + (size_t)gn * K + gk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = xs[kk][tm + i]; b[i] = ws[kk][tn + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gm = m0 + tm + i, gn = n0 + tn + j;
+      if (gm < M && gn < N) Ty<T>::st(C + (size_t)gm * ldc + gn, acc[i][j]);
+    }
+}
+template <typename T>
+cudaError_t launch_gemm_fma(const T* X, const T* W, T* C, int M, int N, int K, int ldc, cudaStream_t s) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  gemm_fma_kernel<T><<<grid, 256, 0, s>>>(X, W, C, M, N, K, ldc);
+  return cudaGetLastError();
+}
+template cudaError_t launch_gemm_fma<float>(const float*, const float*, float*, int, int, int, int, cudaStream_t);
+template cudaError_t launch_gemm_fma<bf16>(const bf16*, const bf16*, bf16*, int, int, int, int, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Strided row copy (V rows of the fused projection into the contiguous StateCache,
+// last three pre-conv rows into the conv tail; native/src/engine.rs:3014-3025, 3348-3361).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void copy_rows_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int rows, int cols) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * cols) return;
+  const size_t r = i / cols, c = i - r * cols;
+  dst[r * dst_stride + c] = src[r * src_stride + c];
+}
+template <typename T>
+cudaError_t launch_copy_rows(const T* src, int src_stride, T* dst, int dst_stride, int rows, int cols, cudaStream_t s) {
+  const size_t n = (size_t)rows * cols;
+  if (n == 0) return cudaSuccess;
+  copy_rows_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, src_stride, dst, dst_stride, rows, cols);
+  return cudaGetLastError();
+}
+template cudaError_t launch_copy_rows<float>(const float*, int, float*, int, int, int, cudaStream_t);
+template cudaError_t launch_copy_rows<bf16>(const bf16*, int, bf16*, int, int, int, cudaStream_t);
+
+// T -> f32 widening copy (debug taps, state reads) and f32 -> T narrowing (tensor upload).
+template <typename T>
+__global__ void to_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = Ty<T>::ld(src + i);
+}
+template <typename T>
+__global__ void from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) Ty<T>::st(dst + i, src[i]);
+}
+template <typename T>
+cudaError_t launch_to_f32(const T* src, float* dst, size_t n, cudaStream_t s) {
+  if (n) to_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+template <typename T>
+cudaError_t launch_from_f32(const float* src, T* dst, size_t n, cudaStream_t s) {
+  if (n) from_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n);
+  return cudaGetLastError();
+}
+template cudaError_t launch_to_f32<float>(const float*, float*, size_t, cudaStream_t);
+template cudaError_t launch_to_f32<bf16>(const bf16*, float*, size_t, cudaStream_t);
+template cudaError_t launch_from_f32<float>(const float*, float*, size_t, cudaStream_t);
+template cudaError_t launch_from_f32<bf16>(const float*, bf16*, size_t, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Seeded weight generator (device twin; integer hashing plus one float multiply, so the
+// values are bit-identical to a host evaluation of the same rule):
+//   key = mix64(mix64(seed) ^ tensor_id); a = mix64(key+2i); b = mix64(key+2i+1)
+//   normal : (sum of the eight 16-bit lanes of a,b - 262140) * c + shift   (Irwin-Hall 8)
+//   uniform: fmaf(hi-lo, (a>>40) * 2^-24, lo)
+// Rows are scattered through `row_map`: mode 0 dst_row = row_offset + r; mode 1/2 place
+// gate/up rows in 256-row tiles (128 gate rows then 128 up rows) for the SwiGLU epilogue.
+// ---------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+uint64_t gen_tensor_key(uint64_t seed, int layer, int kind) {
+  return mix64(mix64(seed) ^ ((uint64_t)(layer + 1) * 64 + (uint64_t)kind));
+}
+__device__ __forceinline__ size_t map_row(size_t r, int mode, int row_offset) {
+  if (mode == 0) return (size_t)row_offset + r;
+  return (r >> 7) * 256 + (r & 127) + (mode == 2 ? 128 : 0);
+}
+template <typename T>
+__global__ void gen_tensor_kernel(T* __restrict__ dst, uint64_t key, uint64_t first, uint64_t count, int cols, int dist, float p0,
+                                  float p1, float c, int round_bf, int mode, int row_offset, int dst_stride) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const uint64_t e = first + i;
+  const uint64_t a = mix64(key + 2 * e);
+  float v;
+  if (dist == 0) {
+    const uint64_t b = mix64(key + 2 * e + 1);
+    int s = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      s += (int)((a >> (16 * q)) & 0xffff);
+      s += (int)((b >> (16 * q)) & 0xffff);
+    }
+    v = __fadd_rn(__fmul_rn((float)(s - 262140), c), p1);
+  } else {
+    const float u = __fmul_rn((float)(a >> 40), 1.0f / 16777216.0f);
+    v = __fmaf_rn(__fsub_rn(p1, p0), u, p0);
+  }
+  if (round_bf) v = __bfloat162float(__float2bfloat16_rn(v));
+  const size_t r = (size_t)(i / cols), cc = (size_t)(i % cols);
+  Ty<T>::st(dst + map_row(r, mode, row_offset) * dst_stride + cc, v);
+}
+template <typename T>
+cudaError_t launch_gen_tensor(T* dst, uint64_t key, uint64_t first, uint64_t count, int cols, int dist, float p0, float p1, float c,
+                              bool round_bf, int mode, int row_offset, int dst_stride, cudaStream_t s) {
+  if (count == 0) return cudaSuccess;
+  gen_tensor_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, s>>>(dst, key, first, count, cols, dist, p0, p1, c, round_bf ? 1 : 0,
+                                                                      mode, row_offset, dst_stride);
+  return cudaGetLastError();
+}
+template cudaError_t launch_gen_tensor<float>(float*, uint64_t, uint64_t, uint64_t, int, int, float, float, float, bool, int, int, int, cudaStream_t);
+template cudaError_t launch_gen_tensor<bf16>(bf16*, uint64_t, uint64_t, uint64_t, int, int, float, float, float, bool, int, int, int, cudaStream_t);
+
+// Scatter / gather rows between the standard [rows, cols] layout and a placed layout.
+template <typename T>
+__global__ void place_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, size_t n, int cols, int mode, int row_offset,
+                                  int dst_stride, int inverse) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t r = i / cols, c = i - r * cols;
+  const size_t p = map_row(r, mode, row_offset) * dst_stride + c;
+  if (inverse) dst[i] = src[p]; else dst[p] = src[i];
+}
+template <typename T>
+cudaError_t launch_place_rows(const T* src, T* dst, size_t rows, int cols, int mode, int row_offset, int dst_stride, bool inverse,
+                              cudaStream_t s) {
+  const size_t n = rows * cols;
+  if (n == 0) return cudaSuccess;
+  place_rows_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n, cols, mode, row_offset, dst_stride, inverse ? 1 : 0);
+  return cudaGetLastError();
+}
+template cudaError_t launch_place_rows<float>(const float*, float*, size_t, int, int, int, int, bool, cudaStream_t);
+template cudaError_t launch_place_rows<bf16>(const bf16*, bf16*, size_t, int, int, int, int, bool, cudaStream_t);

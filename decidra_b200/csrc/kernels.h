@@ -1,0 +1,61 @@
+// Launch wrappers of kernels.cu (all enqueue on the given stream and return the launch status).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+cudaError_t launch_pack(const int32_t* lens, int B, int total, int pos_start, int32_t* cu, int32_t* last_row, int32_t* tok_q,
+                        int32_t* tok_pos, int* err, cudaStream_t s);
+template <typename T>
+cudaError_t launch_embed(const T* table, const uint32_t* ids, T* out, int rows, int H, int vocab, int* err, cudaStream_t s);
+template <typename T>
+cudaError_t launch_rmsnorm(const T* x, const T* w, T* out, int rows, int cols, float eps, bool zero_centered, cudaStream_t s);
+template <typename T>
+cudaError_t launch_add_rmsnorm(const T* x, const T* mix, const T* w, T* residual, T* out, int rows, int cols, float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_final_norm_rows(const T* x, const T* w, float* out, const int32_t* rows_idx, int B, int cols, float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* w, T* out, int tokens, int heads, int cols, float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_add(const T* a, const T* b, T* out, size_t n, cudaStream_t s);
+template <typename T>
+cudaError_t launch_silu_mul(const T* g, const T* u, T* out, size_t n, cudaStream_t s);
+template <typename T>
+cudaError_t launch_silu_mul_interleaved(const T* gu, int gu_stride, T* out, int tokens, int I, cudaStream_t s);
+template <typename T>
+cudaError_t launch_qk_norm_rope(const T* qg, int qg_stride, const T* kraw, int k_stride, const T* qw, const T* kw, const T* cos_t,
+                                const T* sin_t, const int32_t* positions, int pos_base, int max_pos, T* q, T* k, int k_out_stride,
+                                int tokens, int heads, int kv, int hd, int rotary_dim, float eps, int* err, cudaStream_t s);
+template <typename T>
+cudaError_t launch_attn_fma(const T* q, const T* k_own, int k_stride, const T* v_own, int v_stride, const T* k_state,
+                            const T* v_state, int n_state, const T* gate_qg, int qg_stride, T* out, const int32_t* cu,
+                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s);
+template <typename T>
+cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T* w, T* out, const int32_t* cu,
+                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s);
+template <typename T>
+cudaError_t launch_gdn_prepare(const T* conv, int conv_stride, const T* b, const T* a, int ba_stride, const float* A_log,
+                               const float* dt_bias, float* qf, float* kf, float* g, float* beta, int tokens, int nk, int nv,
+                               int dk, cudaStream_t s);
+template <typename T>
+cudaError_t launch_gdn_recurrent(const float* qf, const float* kf, const T* conv, int conv_stride, const float* g, const float* beta,
+                                 const float* seed, float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int dk,
+                                 int dv, bool few_sequences, cudaStream_t s);
+cudaError_t launch_readout(const float* x, const float* W, float* out, int B, int H, int R, cudaStream_t s);
+template <typename T>
+cudaError_t launch_gemm_fma(const T* X, const T* W, T* C, int M, int N, int K, int ldc, cudaStream_t s);
+template <typename T>
+cudaError_t launch_copy_rows(const T* src, int src_stride, T* dst, int dst_stride, int rows, int cols, cudaStream_t s);
+template <typename T>
+cudaError_t launch_to_f32(const T* src, float* dst, size_t n, cudaStream_t s);
+template <typename T>
+cudaError_t launch_from_f32(const float* src, T* dst, size_t n, cudaStream_t s);
+
+uint64_t gen_tensor_key(uint64_t seed, int layer, int kind);
+template <typename T>
+cudaError_t launch_gen_tensor(T* dst, uint64_t key, uint64_t first, uint64_t count, int cols, int dist, float p0, float p1, float c,
+                              bool round_bf, int mode, int row_offset, int dst_stride, cudaStream_t s);
+template <typename T>
+cudaError_t launch_place_rows(const T* src, T* dst, size_t rows, int cols, int mode, int row_offset, int dst_stride, bool inverse,
+                              cudaStream_t s);

@@ -1,0 +1,289 @@
+/*
+ * decidra_b200 — C ABI of the B200-native (sm_100a) state-once question path.
+ *
+ * This header is the drop-in boundary: it exports, as plain C, the surface that
+ * juanqui/decidra's Rust host (src/batch.rs, src/native_backend.rs) calls on its
+ * `decidra_native` crate. Every entry point cites the reference interface it
+ * replaces (paths inside juanqui/decidra). No C++ types, exceptions or torch
+ * objects cross this boundary: plain pointers, sizes and int status codes.
+ *
+ * Threading model (same as the reference, native/src/engine.rs:374-377, 483-486):
+ * one engine is used by one thread at a time and owns one device and one stream.
+ * Eight data-parallel replicas are eight engines on eight devices.
+ *
+ * All "host" entry points are synchronous: they return after the engine stream
+ * is synchronised and results are in the caller's host buffer. The "*_device"
+ * forms enqueue on the engine stream and return without synchronising.
+ */
+#ifndef DECIDRA_B200_H
+#define DECIDRA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DCD_API __attribute__((visibility("default")))
+
+/* Status codes. The message behind DCD_E_OOM always contains "out of memory",
+ * because the reference scheduler retries on that substring (src/batch.rs:767,863). */
+enum {
+  DCD_OK = 0,
+  DCD_E_INVALID = 1,     /* bad argument: empty batch, empty question, token >= vocab, split out of range, caps */
+  DCD_E_OOM = 2,         /* device or host allocation failed */
+  DCD_E_UNSUPPORTED = 3, /* vision, unsupported precision or shape */
+  DCD_E_CUDA = 4,        /* a CUDA call failed */
+  DCD_E_TIMEOUT = 5      /* a bounded device-side wait gave up (kernel reported it, context stays usable) */
+};
+
+/* Model description. Replaces Config::from_dir (native/src/config.rs:49-158) as a plain
+ * struct; only attention_mode = prefix_bidir exists here (the reference fails closed on
+ * anything else, native/src/config.rs:111-133). */
+typedef struct dcd_model_config {
+  int32_t num_layers;
+  int32_t hidden;
+  int32_t heads, kv_heads, head_dim, rotary_dim; /* rotary_dim = (head_dim*partial_rotary_factor)&~1 */
+  float rope_theta;
+  int32_t gdn_k_heads, gdn_v_heads, gdn_dk, gdn_dv, conv_kernel; /* conv_kernel must be 4 */
+  int32_t intermediate;
+  int32_t vocab;
+  int32_t readout_rows; /* 255 for d3 */
+  float rms_eps;
+  int32_t dtype;        /* 0 = f32 weights and activations, 1 = bf16 */
+  uint8_t layer_is_full[256]; /* layer_types: 1 = full_attention, 0 = linear_attention (GDN) */
+} dcd_model_config;
+
+/* Engine options. Replaces the Engine setters called before preload_all
+ * (src/native_backend.rs:81-95) and the env caps read in
+ * Engine::state_once_batch_rows (native/src/engine.rs:4870-4881). Zero = default. */
+typedef struct dcd_options {
+  int32_t precision;        /* 0 = the config dtype; 1 = w4a16_g128; 2 = fp8; 3 = nvfp4 (1..3 not built yet: DCD_E_UNSUPPORTED) */
+  int32_t max_pass_tokens;  /* workspace rows; also the longest state that can be captured. default 16384 */
+  int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
+  int64_t max_keys;
+  int64_t max_scores;
+  int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMM (bf16 only); 1 = plain FMA GEMM (diagnostic) */
+  int32_t attn_path;        /* 0 = default; 1 = plain FMA attention (diagnostic) */
+  int32_t max_positions;    /* RoPE table length; default 65536 */
+  int32_t reserved[8];
+} dcd_options;
+
+typedef struct dcd_info {
+  int32_t device;
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  char device_name[128];
+  int32_t hidden, num_layers, readout_rows;
+  int32_t supports_vision; /* always 0 */
+  uint64_t weight_bytes, workspace_bytes;
+} dcd_info;
+
+typedef struct dcd_engine dcd_engine;
+typedef struct dcd_state dcd_state;           /* device StateCache (native/src/engine.rs:533-543) */
+typedef struct dcd_host_state dcd_host_state; /* HostStateCache (native/src/engine.rs:545-551) */
+
+/* ---- engine lifecycle ------------------------------------------------------ */
+
+/* Engine::new (native/src/engine.rs:785-870) + Gpu::new (native/src/cuda.rs:30-70):
+ * binds `device`, allocates weights and workspace. On failure *out is NULL and
+ * dcd_last_error(NULL) describes it. */
+DCD_API int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int device, dcd_engine** out);
+DCD_API void dcd_engine_destroy(dcd_engine* e);
+/* Message of the last failed call on this engine (NULL: last failed create on this thread). */
+DCD_API const char* dcd_last_error(const dcd_engine* e);
+/* engine.cfg.*, engine.gpu.{sms,device_name,compute_capability}, supports_vision
+ * (src/native_backend.rs:70-156). */
+DCD_API int dcd_engine_info(const dcd_engine* e, dcd_info* out);
+
+/* Fill every weight tensor from the seeded generator (random-init N(0,0.02); there is no
+ * checkpoint). Stands where Engine::preload_all loads the checkpoint
+ * (src/native_backend.rs:97). Generator (integer hashing plus one float multiply, so a host
+ * evaluation of the same rule gives bit-identical tensors):
+ *   key = mix64(mix64(seed) ^ ((layer+1)*64 + kind)), mix64 = the splitmix64 step;
+ *   a = mix64(key+2i), b = mix64(key+2i+1) for element i (row-major);
+ *   normal : (sum of the eight 16-bit lanes of a,b - 262140) * (std/53509.919921) [+ shift]
+ *   uniform: fmaf(hi-lo, (a>>40)*2^-24, lo)
+ * Matrices, embedding, readout (f32) and zero-centred norm weights: normal std 0.02; GDN gated-norm
+ * weight 1 + normal 0.02; conv taps uniform(-0.5,0.5); A_log uniform(0, ln 16); dt_bias
+ * uniform(-6.9,-2.3). bf16 engines round to bf16 (A_log, dt_bias, readout stay f32). */
+DCD_API int dcd_engine_init_random(dcd_engine* e, uint64_t seed);
+/* Upload one tensor from host memory (row-major, f32 values converted to the engine dtype).
+ * Replaces weights.rs tensor loads (native/src/weights.rs:232-330). layer = -1 for global
+ * tensors; kind = DCD_T_*. */
+DCD_API int dcd_engine_load_tensor(dcd_engine* e, int layer, int kind, const float* host, size_t count);
+/* Read a weight tensor back as f32 (tests: generator parity). */
+DCD_API int dcd_engine_read_tensor(dcd_engine* e, int layer, int kind, float* host, size_t count);
+
+enum {
+  DCD_T_EMBED = 0, DCD_T_FINAL_NORM = 1, DCD_T_READOUT = 2,
+  DCD_T_INPUT_NORM = 10, DCD_T_POST_NORM = 11, DCD_T_GATE = 12, DCD_T_UP = 13, DCD_T_DOWN = 14,
+  DCD_T_Q = 20, DCD_T_K = 21, DCD_T_V = 22, DCD_T_O = 23, DCD_T_QNORM = 24, DCD_T_KNORM = 25,
+  DCD_T_IN_QKV = 30, DCD_T_IN_Z = 31, DCD_T_IN_B = 32, DCD_T_IN_A = 33, DCD_T_OUT = 34, DCD_T_CONV = 35,
+  DCD_T_A_LOG = 36, DCD_T_DT_BIAS = 37, DCD_T_GNORM = 38
+};
+
+/* engine.rebind_blas() (src/batch.rs:294): no vendor BLAS on this path; kept so the
+ * scheduler's call compiles. Always DCD_OK. */
+DCD_API int dcd_rebind_blas(dcd_engine* e);
+
+/* ---- the hot path ---------------------------------------------------------- */
+
+/* Engine::capture_state / capture_state_mm (native/src/engine.rs:4607-4763; called at
+ * src/batch.rs:763). ids: n state tokens (n >= 2). pos: optional n mRoPE triples; text
+ * states pass NULL (t,t,t). Image features are not supported (DCD_E_UNSUPPORTED path is
+ * dcd_vision_encode). */
+DCD_API int dcd_capture_state(dcd_engine* e, const uint32_t* ids, size_t n, const uint32_t (*pos)[3], dcd_state** out);
+
+/* Engine::readout_state_once_batch(&StateCache, &[&[u32]]) (native/src/engine.rs:4847-4987;
+ * called at src/batch.rs:860,879). questions[i] points at lens[i] token ids. Writes
+ * B x readout_rows f32 logits, row i = question i (input order). Splits into chunks under
+ * the caps like the reference and scatters back. */
+DCD_API int dcd_readout_state_once_batch(dcd_engine* e, const dcd_state* st, const uint32_t* const* questions,
+                                         const size_t* lens, size_t B, float* out);
+/* Same, with the questions already flattened (what src/batch.rs:835-841 builds). */
+DCD_API int dcd_readout_state_once_flat(dcd_engine* e, const dcd_state* st, const uint32_t* flat_ids,
+                                        const uint32_t* lens, size_t B, float* out);
+/* Device-resident form of one chunk: d_ids[total] and d_lens[B] already in HBM, logits
+ * written to d_out[B*readout_rows] (device). Enqueues on the engine stream; no sync, no
+ * host copies. max_len = longest question. */
+DCD_API int dcd_readout_state_once_device(dcd_engine* e, const dcd_state* st, const uint32_t* d_ids,
+                                          const int32_t* d_lens, size_t B, size_t total, size_t max_len, float* d_out);
+/* Device-resident capture: d_ids[n] in HBM; no host copies; the state is valid after the
+ * engine stream reaches this point. */
+DCD_API int dcd_capture_state_device(dcd_engine* e, const uint32_t* d_ids, size_t n, dcd_state** out);
+
+/* Engine::decision_logits_split (native/src/engine.rs:4585-4601; self-test use at
+ * src/native_backend.rs:251-253): per-row reference formulation over [state || question]
+ * with the block-cascade mask. Writes readout_rows logits. */
+DCD_API int dcd_decision_logits_split(dcd_engine* e, const uint32_t* ids, size_t seq, size_t split, float* out);
+
+/* ---- StateCache ------------------------------------------------------------- */
+DCD_API void dcd_state_free(dcd_engine* e, dcd_state* st);
+DCD_API size_t dcd_state_tokens(const dcd_state* st);   /* StateCache::state_tokens */
+DCD_API size_t dcd_state_pos_end(const dcd_state* st);
+DCD_API size_t dcd_state_bytes(const dcd_state* st);    /* state_cache_bytes_for, src/batch.rs:212-214 */
+/* StateCache::offload / restore (native/src/engine.rs:559-648; src/batch.rs:683,1034). */
+DCD_API int dcd_state_offload(dcd_engine* e, const dcd_state* st, dcd_host_state** out);
+DCD_API int dcd_state_restore(dcd_engine* e, const dcd_host_state* hs, dcd_state** out);
+DCD_API void dcd_host_state_free(dcd_host_state* hs);
+/* StateCache::zero_gdn_state / zero_gdn_hist (native/src/engine.rs:652-669): negative controls. */
+DCD_API int dcd_state_zero_gdn_state(dcd_engine* e, dcd_state* st, int layer);
+DCD_API int dcd_state_zero_gdn_hist(dcd_engine* e, dcd_state* st, int layer);
+/* Read one cached tensor as f32. what: 0 K [S,kv,hd], 1 V, 2 gdn_state [nv,dk,dv], 3 gdn_hist [3,conv_dim].
+ * host == NULL returns the element count through *count. */
+DCD_API int dcd_state_read_tensor(dcd_engine* e, const dcd_state* st, int layer, int what, float* host, size_t* count);
+
+/* ---- pools, memory, timers -------------------------------------------------- */
+DCD_API int dcd_trim_pools(dcd_engine* e);                                   /* Engine::trim_pools, src/batch.rs:773 */
+DCD_API int dcd_mem_info(dcd_engine* e, size_t* free_bytes, size_t* total_bytes); /* gpu.mem_info, src/batch.rs:556 */
+/* PhaseTimer (native/src/cuda.rs:173-189): CUDA-event pair on the engine stream. */
+DCD_API int dcd_timer_begin(dcd_engine* e);
+DCD_API int dcd_timer_end(dcd_engine* e);      /* records the stop event */
+DCD_API double dcd_timer_seconds(dcd_engine* e); /* synchronises on the stop event */
+/* Engine::vision_encode (src/batch.rs:727): not part of this path. Always DCD_E_UNSUPPORTED. */
+DCD_API int dcd_vision_encode(dcd_engine* e, const void* pixels, size_t bytes);
+DCD_API int dcd_engine_sync(dcd_engine* e);
+
+/* Per-kernel-family device timing (DECIDRA_PROFILE's timed! regions,
+ * native/src/engine.rs:135-153, 1133-1201): when enabled, a CUDA-event pair brackets each
+ * launch family; read returns accumulated milliseconds, launches and algorithmic work. */
+enum { DCD_PROF_GEMM = 0, DCD_PROF_ATTN = 1, DCD_PROF_GDN = 2, DCD_PROF_ELEMENTWISE = 3, DCD_PROF_READOUT = 4, DCD_PROF_COUNT = 5 };
+typedef struct dcd_prof_entry {
+  double ms;       /* summed device time */
+  double work;     /* algorithmic FLOPs (GEMM, ATTN, GDN, READOUT) or bytes (ELEMENTWISE) */
+  int64_t launches;
+} dcd_prof_entry;
+DCD_API int dcd_profile_enable(dcd_engine* e, int on);
+DCD_API int dcd_profile_read(dcd_engine* e, dcd_prof_entry out[DCD_PROF_COUNT]); /* synchronises; resets counters */
+/* Kernels launched by this library on this engine since creation. */
+DCD_API int64_t dcd_launch_count(const dcd_engine* e);
+
+/* Named intermediate taps (Engine::set_dump, native/src/engine.rs:1230-1263): when a tap
+ * sink is set, every layer output [T,hidden] is copied there as f32 (debug/tests). */
+DCD_API int dcd_debug_layer_outputs(dcd_engine* e, float* host_sink /* [layers*T*hidden] or NULL to disable */, size_t capacity);
+
+/* ---- host-side integer logic (bit-exact parts) ------------------------------ */
+
+/* block_cascade_mask (native/src/engine.rs:490-504): bit q*seq+k set iff k < (q<split ? split : seq),
+ * LSB-first. mask must hold ceil(seq*seq/8) zeroed bytes. DCD_E_INVALID if split==0 or split>=seq. */
+DCD_API int dcd_block_cascade_mask(size_t seq, size_t split, uint8_t* mask);
+/* Chunk planner of Engine::state_once_batch_rows (native/src/engine.rs:4893-4918): stable sort by
+ * length, greedy chunks under the caps. order[B] = sorted indices, chunk_of[B] = chunk per
+ * question. *n_chunks out. DCD_E_INVALID if empty or one question alone exceeds the caps. */
+DCD_API int dcd_plan_chunks(const size_t* lens, size_t B, size_t state_len, size_t max_rows, size_t max_keys,
+                            size_t max_scores, int32_t* order, int32_t* chunk_of, int32_t* n_chunks);
+/* Answer decoding: NativeBackend::answers (src/native_backend.rs:611-619) + d3::to_answer,
+ * choice_confidence, score_confidence (src/d3.rs:373-478). kind: 0 choice, 1 noul, 2 score.
+ * shares[count] = renormalised probabilities; out2[0] = choice index | noul p[1] | score,
+ * out2[1] = confidence. */
+DCD_API int dcd_decode_answer(const float* logits, int count, float temperature, int kind, float* shares, float* out2);
+/* GPU packing kernel run on its own (BatchInfo::new/positions/last_row_indices,
+ * native/src/engine.rs:693-735, 1669-1674): lens[B] (host) -> cu_seqlens[B+1], positions[total],
+ * tok_q[total], last_row[B] (host copies of what the kernel built on the device). */
+DCD_API int dcd_pack(dcd_engine* e, const int32_t* lens, size_t B, int32_t pos_start, int32_t* cu_seqlens,
+                     int32_t* positions, int32_t* tok_q, int32_t* last_row);
+
+/* ---- kernel-level entry points (device pointers; per-kernel parity tests and benchmarks) ----
+ * All take raw device pointers and enqueue one launch on `stream` (a cudaStream_t passed as
+ * void*; NULL = the default stream). dtype: 0 = f32 arrays, 1 = bf16 arrays for everything marked
+ * "T". Row strides are in elements. */
+
+/* C[M,N] = X[M,K] . W[N,K]^T on the tcgen05 tensor cores: bf16 in, f32 accumulate in TMEM, bf16
+ * out (row stride ldc). Replaces the cuBLAS call of Engine::gemm_core
+ * (native/src/engine.rs:4321-4350). Needs K % 8 == 0 and N % 8 == 0.
+ * epi 0: plain store. epi 1: SwiGLU — W holds, per 256-row tile, 128 gate rows then 128 up rows;
+ * C[M, ldc] = bf16(bf16(silu(bf16(gate))) * bf16(up)) (silu_mul_bf16, native/kernels/kernels.cu:492-501).
+ * `err` is a device int the kernel sets non-zero when a bounded barrier wait gives up. */
+DCD_API int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int epi, int sm_count,
+                               int* err, void* stream);
+/* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
+DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
+/* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */
+DCD_API int dcd_k_rmsnorm(const void* x, const void* w, void* out, int rows, int cols, float eps, int zero_centered, int dtype, void* stream);
+DCD_API int dcd_k_add_rmsnorm(const void* x, const void* mix, const void* w, void* residual, void* out, int rows, int cols, float eps, int dtype, void* stream);
+/* rmsnorm_gated_bf16 (native/kernels/kernels.cu:430-455): x [tokens*heads, cols], gate z read at
+ * z + t*z_stride + head*cols. */
+DCD_API int dcd_k_rmsnorm_gated(const void* x, const void* z, int z_stride, const void* w, void* out, int tokens, int heads, int cols, float eps, int dtype, void* stream);
+/* silu_mul_bf16 / add_bf16 (native/kernels/kernels.cu:485-501). */
+DCD_API int dcd_k_silu_mul(const void* gate, const void* up, void* out, size_t n, int dtype, void* stream);
+DCD_API int dcd_k_add(const void* a, const void* b, void* out, size_t n, int dtype, void* stream);
+/* conv1d_silu_seeded_tiled_bf16 (native/kernels/kernels.cu:2085-2122) over a packed batch; hist may
+ * be NULL (zero tail). x rows have stride x_stride; out is [total, ch]. */
+DCD_API int dcd_k_conv1d_silu(const void* x, int x_stride, const void* hist, const void* w, void* out, const int32_t* cu_seqlens,
+                              const int32_t* tok_q, int total, int ch, int dtype, void* stream);
+/* gdn_prepare_compact_bf16 (native/kernels/kernels.cu:765-815): qf,kf [T,nk,dk] f32; g,beta [T,nv] f32. */
+DCD_API int dcd_k_gdn_prepare(const void* conv, int conv_stride, const void* b, const void* a, int ba_stride, const float* A_log,
+                              const float* dt_bias, float* qf, float* kf, float* g, float* beta, int T, int nk, int nv, int dk,
+                              int dtype, void* stream);
+/* gdn_recurrent_reg_split_seeded_bf16 (native/kernels/kernels.cu:2245-2300): sequential gated delta
+ * rule per packed sequence from `seed` [nv,dk,dv] f32 (NULL = zeros); v is read from the conv output;
+ * final_state (NULL or [B,nv,dk,dv]) receives the end state; out: T [total, nv*dv]. narrow != 0
+ * uses 16 value columns per CTA (few long sequences) instead of 64. */
+DCD_API int dcd_k_gdn_recurrent(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                                const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv,
+                                int dk, int dv, int narrow, int dtype, void* stream);
+/* split_q_gate + q/k RMSNorm(1+w) + partial NeoX RoPE in one kernel
+ * (native/kernels/kernels.cu:516-557, 406-426; tables as native/src/engine.rs:1619-1643).
+ * qg [T,heads,2*hd] (row stride qg_stride), kraw [T,kv,hd] (row stride k_stride) -> q [T,heads,hd],
+ * k [T,kv,hd]. cos/sin [max_pos, rotary_dim/2] in T. */
+DCD_API int dcd_k_qk_norm_rope(const void* qg, int qg_stride, const void* kraw, int k_stride, const void* qw, const void* kw,
+                               const void* cos_t, const void* sin_t, const int32_t* positions, int max_pos, void* q, void* k, int T,
+                               int heads, int kv, int hd, int rotary_dim, float eps, int* err, int dtype, void* stream);
+/* Varlen prefix-bidirectional attention over [state K/V (n_state rows) || own K/V] for every packed
+ * question, fused with the sigmoid output gate (native/src/engine.rs:1985-2042,
+ * native/third_party/flashinfer/fi_prefill.cu:161-173, native/kernels/kernels.cu:504-512).
+ * gate_qg points at the [T,heads,2*hd] q projection (gate = second half of each head) or NULL.
+ * split > 0 selects the per-row reference mask for one sequence (rows < split see keys < split). */
+DCD_API int dcd_k_attention(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                            const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
+                            const int32_t* cu_seqlens, const int32_t* tok_q, int T, int heads, int kv, int hd, int split, int dtype,
+                            void* stream);
+/* logits[B,R] = x[B,H] . W[R,H]^T in f32 (blas_gemm_f32, native/src/engine.rs:3873-3901, 4977-4984). */
+DCD_API int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECIDRA_B200_H */
