@@ -37,9 +37,10 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "questions/sec (whole box) at 64 q/state, 2048-tok state"
 UNIT = "questions/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant GEMM shape, from the ncu
-# capture summarised under profiles/ (None until a capture exists).
-GEMM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up (SwiGLU epilogue) launch at M = 2048, the
+# largest GEMM of the step, from the ncu capture summarised in profiles/gemm_bf16_tc_d3_4layer.md
+# (algorithmic bytes of that launch: 448.8 MB).
+GEMM_TRAFFIC_BYTES = 443.2e6
 
 
 def parse():
