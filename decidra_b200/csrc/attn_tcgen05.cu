@@ -1,0 +1,374 @@
+// Varlen prefix-bidirectional attention on the sm_100a tensor cores (bf16, head_dim 256).
+//
+// Replaces, for the whole packed batch in ONE launch per layer, what juanqui/decidra does with
+// (2+2B) device copies and B FlashInfer launches per layer (Engine::full_attention_batch cascade
+// branch, native/src/engine.rs:1985-2042; fi_prefill_bf16_ext,
+// native/third_party/flashinfer/fi_prefill.cu:161-173), plus the sigmoid output gate
+// (sigmoid_gate_bf16, native/kernels/kernels.cu:504-512). Each question attends, without a causal
+// mask, to [cached state K/V || its own K/V]; the two segments are read in place through two pairs
+// of TMA descriptors — nothing is concatenated.
+//
+// One CTA = (question, KV head, tile of 128/G tokens), G = query heads per KV head. The G heads of
+// a token share K/V, so the M=128 MMA tile is packed with (token, head) rows by a 3-D TMA box
+// {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 64 through a 2-stage ring:
+//   S[128,64]  = Q[128,256] . K^T        tcgen05.mma, operands in shared memory, S in TMEM
+//   softmax    : thread r owns row r: tcgen05.ld S, base-2 online softmax with a lazy rescale
+//                (O is only rescaled when the running max grows by more than 2^8), P -> bf16 into
+//                shared memory in the 128-byte-swizzled K-major operand layout
+//   O[128,256] += P[128,64] . V[64,256]  tcgen05.mma, V read as an MN-major operand, O in TMEM
+// Warps 0-3 are the softmax/epilogue warps (TMEM lanes 32w..32w+31); warp 4 issues TMA and MMA.
+// All waits are bounded; a wait that gives up raises the error word and the CTA drains and exits.
+#include <cuda.h>
+
+#include "attn_tcgen05.h"
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace atc {
+using namespace tcc;
+
+constexpr int HD = 256, KT = 64, NKB = HD / 64;
+constexpr uint32_t Q_KB_BYTES = 128 * 128, Q_BYTES = NKB * Q_KB_BYTES;          // 64 KB
+constexpr uint32_t KV_CHUNK = KT * 128, K_BYTES = NKB * KV_CHUNK, V_BYTES = K_BYTES;  // 32 KB each
+constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;                              // 64 KB
+constexpr uint32_t P_BYTES = 128 * 128;                                          // 16 KB
+constexpr uint32_t SMEM_BYTES = Q_BYTES + 2 * STAGE_BYTES + P_BYTES + 256 + 1024;
+constexpr int NUM_THREADS = 160;
+constexpr uint32_t O_COL = 0, S_COL = 256;
+constexpr uint32_t IDESC_QK = umma_idesc(128, KT, 0);
+constexpr uint32_t IDESC_PV = umma_idesc(128, HD, 1);
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct Params {
+  const int32_t* cu;       // [B+1] packed sequence offsets
+  const int32_t* tile_cu;  // [B+1] prefix sum of token tiles per sequence
+  int B, n_state, heads, kv, total_tokens;
+  const bf16* gate_qg;     // fused q projection [T, qg_stride]; gate = dims [hd, 2hd) of each head; may be null
+  int qg_stride;
+  bf16* out;               // [T, heads, hd]
+  float scale_log2e;
+  int* err;
+};
+
+template <int G>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKs,
+               const __grid_constant__ CUtensorMap tmVs, const __grid_constant__ CUtensorMap tmKo,
+               const __grid_constant__ CUtensorMap tmVo, const Params p) {
+  constexpr int TT = 128 / G;  // tokens per tile
+  // ---- which (sequence, token tile) is this CTA? ------------------------------------------------
+  const int ti = blockIdx.x, kh = blockIdx.y;
+  if (ti >= p.tile_cu[p.B]) return;
+  int b = 0;
+  {
+    int lo = 0, hi = p.B;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.tile_cu[mid] <= ti) lo = mid; else hi = mid;
+    }
+    b = lo;
+  }
+  const int off = p.cu[b], L = p.cu[b + 1] - off;
+  const int t0 = (ti - p.tile_cu[b]) * TT;
+  const int ntok = min(TT, L - t0);
+  const int n_st = (p.n_state + KT - 1) / KT, n_own = (L + KT - 1) / KT, n_tiles = n_st + n_own;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t q_base = raw + pad;
+  const uint32_t st_base = q_base + Q_BYTES;
+  const uint32_t p_base = st_base + 2 * STAGE_BYTES;
+  const uint32_t bars = p_base + P_BYTES;
+  uint8_t* p_ptr = smem + Q_BYTES + 2 * STAGE_BYTES;
+  uint8_t* bars_ptr = p_ptr + P_BYTES;
+  const uint32_t bar_q = bars, bar_kv0 = bars + 8, bar_s = bars + 24, bar_p = bars + 32, bar_o = bars + 40;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 48);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 52);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_kv0, 1);
+    mbar_init(bar_kv0 + 8, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // rows TT*G .. 127 of the Q tile are never written by TMA: zero them so that they stay finite
+  if (threadIdx.x < 128) {
+    constexpr int ROW0 = TT * G;
+    constexpr int NZ = (128 - ROW0) * 8;  // 16-byte chunks per k-block
+    for (int i = threadIdx.x; i < NKB * NZ; i += 128) {
+      const int kb = i / NZ, c = i - kb * NZ;
+      *reinterpret_cast<uint4*>(smem + kb * Q_KB_BYTES + ROW0 * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- TMA + MMA issuer -------------------------------------------------------------------
+      auto load_kv = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kdst = st_base + s * STAGE_BYTES, vdst = kdst + K_BYTES, bar = bar_kv0 + 8 * s;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const bool st = j < n_st;
+        const CUtensorMap* mk = st ? &tmKs : &tmKo;
+        const CUtensorMap* mv = st ? &tmVs : &tmVo;
+        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+#pragma unroll
+        for (int c = 0; c < NKB; ++c) {
+          tma_load_2d(kdst + c * KV_CHUNK, mk, bar, kh * HD + c * 64, row0);
+          tma_load_2d(vdst + c * KV_CHUNK, mv, bar, kh * HD + c * 64, row0);
+        }
+      };
+      mbar_expect_tx(bar_q, (uint32_t)(NKB * TT * G * 128));
+#pragma unroll
+      for (int c = 0; c < NKB; ++c) tma_load_3d(q_base + c * Q_KB_BYTES, &tmQ, bar_q, c * 64, kh * G, off + t0);
+      load_kv(0);
+      if (n_tiles > 1) load_kv(1);
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        if (!(ok = mbar_wait(bar_kv0 + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
+        tc_fence_after();
+        const uint32_t kb_base = st_base + s * STAGE_BYTES;
+#pragma unroll
+        for (int c = 0; c < NKB; ++c) {
+          const uint64_t dq = umma_desc(q_base + c * Q_KB_BYTES, 16, 1024);
+          const uint64_t dk = umma_desc(kb_base + c * KV_CHUNK, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(tmem_base + S_COL, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+        }
+        umma_commit_to(bar_s);
+        if (j >= 1) {
+          if (!(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
+          if (j + 1 < n_tiles) load_kv(j + 1);  // the stage of tile j-1 is free again
+        }
+        if (!(ok = mbar_wait(bar_p, (uint32_t)(j & 1), abort_flag))) break;
+        tc_fence_after();
+        const uint64_t dp = umma_desc(p_base, 16, 1024);
+        const uint64_t dv = umma_desc(kb_base + K_BYTES, KV_CHUNK, 1024);
+#pragma unroll
+        for (int k = 0; k < KT / 16; ++k)
+          umma_f16(tmem_base + O_COL, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
+        umma_commit_to(bar_o);
+      }
+    }
+  } else {
+    // ---- softmax + epilogue: thread r owns row r of the tile --------------------------------------
+    const int r = threadIdx.x;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int valid = j < n_st ? min(KT, p.n_state - j * KT) : min(KT, L - (j - n_st) * KT);
+      ok = mbar_wait(bar_s, (uint32_t)(j & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float x[KT];
+      {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + S_COL, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
+        tmem_ld32(tmem_base + lane_addr + S_COL + 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[32 + i] = __uint_as_float(v[i]);
+      }
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < KT; ++i) {
+        x[i] = i < valid ? x[i] * p.scale_log2e : -INFINITY;
+        tmax = fmaxf(tmax, x[i]);
+      }
+      const bool need = tmax > m_used + RESCALE_THRESHOLD;  // also true on the first tile (m_used = -inf)
+      if (j >= 1) {
+        ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag);  // PV of tile j-1 done: P buffer free, O stable
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (__any_sync(0xffffffffu, need)) {
+          tc_fence_after();
+          const float f = need ? exp2f(m_used - tmax) : 1.0f;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st32(tmem_base + lane_addr + O_COL + c * 32, v);
+          }
+          tmem_st_wait();
+          l *= f;
+        }
+      }
+      if (need) m_used = tmax;
+      // P = exp2(x - m_used) rounded to bf16; the denominator sums the rounded values
+      uint8_t* prow = p_ptr + r * 128;
+#pragma unroll
+      for (int c = 0; c < KT / 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h2 = 0; h2 < 4; ++h2) {
+          const __nv_bfloat162 pr = __floats2bfloat162_rn(exp2f(x[c * 8 + 2 * h2] - m_used), exp2f(x[c * 8 + 2 * h2 + 1] - m_used));
+          l += __low2float(pr) + __high2float(pr);
+          w[h2] = *reinterpret_cast<const uint32_t*>(&pr);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(bar_p);
+    }
+    // ---- epilogue: O / l, output gate, store --------------------------------------------------------
+    if (ok) {
+      ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1), abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int tt = r / G, g = r - tt * G;
+      const bool live = tt < ntok;
+      const int t = off + t0 + tt, head = kh * G + g;
+      const float inv = 1.0f / l;
+      bf16* orow = p.out + ((size_t)t * p.heads + head) * HD;
+      const bf16* grow = p.gate_qg ? p.gate_qg + (size_t)t * p.qg_stride + (size_t)head * 2 * HD + HD : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = Ty<bf16>::rnd(__uint_as_float(v[q4 * 8 + i]) * inv);
+            if (grow) {
+              const uint4 gv = *reinterpret_cast<const uint4*>(grow + c * 32 + q4 * 8);
+              const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                o[2 * i] *= Ty<bf16>::rnd(sigmoid_f(__low2float(g2[i])));
+                o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_f(__high2float(g2[i])));
+              }
+            }
+            uint4 ov;
+            ov.x = pack_bf16(o[0], o[1]);
+            ov.y = pack_bf16(o[2], o[3]);
+            ov.z = pack_bf16(o[4], o[5]);
+            ov.w = pack_bf16(o[6], o[7]);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = ov;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) set_err(p.err, DERR_ATTN_TIMEOUT);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// tile_cu[b] = number of token tiles of the sequences before b (single CTA scan).
+__global__ void attn_tiles_kernel(const int32_t* __restrict__ cu, int B, int tokens_per_tile, int32_t* __restrict__ tile_cu) {
+  __shared__ int part[1024];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int per = (B + nt - 1) / nt;
+  const int lo = min(tid * per, B), hi = min(lo + per, B);
+  int s = 0;
+  for (int i = lo; i < hi; ++i) s += (cu[i + 1] - cu[i] + tokens_per_tile - 1) / tokens_per_tile;
+  part[tid] = s;
+  __syncthreads();
+  for (int o = 1; o < nt; o <<= 1) {
+    const int v = tid >= o ? part[tid - o] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  int run = part[tid] - s;
+  for (int i = lo; i < hi; ++i) {
+    tile_cu[i] = run;
+    run += (cu[i + 1] - cu[i] + tokens_per_tile - 1) / tokens_per_tile;
+  }
+  if (tid == nt - 1) tile_cu[B] = part[tid];
+}
+
+}  // namespace atc
+
+bool attn_tc_supported(int heads, int kv, int hd) { return hd == 256 && kv > 0 && heads % kv == 0 && heads / kv == 6; }
+int attn_tc_tokens_per_tile(int heads, int kv) { return 128 / (heads / kv); }
+
+cudaError_t attn_tc_prepare_device() {
+  return cudaFuncSetAttribute(atc::attn_tc_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES);
+}
+
+cudaError_t attn_tc_build_tiles(const int32_t* cu, int B, int tokens_per_tile, int32_t* tile_cu, cudaStream_t s) {
+  atc::attn_tiles_kernel<<<1, 1024, 0, s>>>(cu, B, tokens_per_tile, tile_cu);
+  return cudaGetLastError();
+}
+
+int attn_tc_make_maps(AttnTcMaps* m, const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                      const void* v_state, int n_state, int T, int heads, int kv, int hd) {
+  const int G = heads / kv, TT = 128 / G;
+  int bad = tc_make_tmap_3d(&m->q, q, hd, heads, T, hd, (uint64_t)heads * hd, G, TT);
+  bad |= tc_make_tmap_strided(&m->k_own, k_own, T, (uint64_t)kv * hd, k_stride, atc::KT);
+  bad |= tc_make_tmap_strided(&m->v_own, v_own, T, (uint64_t)kv * hd, v_stride, atc::KT);
+  if (n_state > 0) {
+    bad |= tc_make_tmap_strided(&m->k_state, k_state, n_state, (uint64_t)kv * hd, (uint64_t)kv * hd, atc::KT);
+    bad |= tc_make_tmap_strided(&m->v_state, v_state, n_state, (uint64_t)kv * hd, (uint64_t)kv * hd, atc::KT);
+  } else {
+    m->k_state = m->k_own;
+    m->v_state = m->v_own;
+  }
+  return bad;
+}
+
+cudaError_t attn_tc_launch(const AttnTcMaps* m, const int32_t* cu, const int32_t* tile_cu, int B, int n_state, int T, int max_tiles,
+                           int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s) {
+  if (!attn_tc_supported(heads, kv, hd)) return cudaErrorInvalidValue;
+  atc::Params p;
+  p.cu = cu;
+  p.tile_cu = tile_cu;
+  p.B = B;
+  p.n_state = n_state;
+  p.heads = heads;
+  p.kv = kv;
+  p.total_tokens = T;
+  p.gate_qg = (const bf16*)gate_qg;
+  p.qg_stride = qg_stride;
+  p.out = (bf16*)out;
+  p.scale_log2e = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
+  p.err = err;
+  dim3 grid(max_tiles, kv);
+  atc::attn_tc_kernel<6><<<grid, atc::NUM_THREADS, atc::SMEM_BYTES, s>>>(
+      *reinterpret_cast<const CUtensorMap*>(&m->q), *reinterpret_cast<const CUtensorMap*>(&m->k_state),
+      *reinterpret_cast<const CUtensorMap*>(&m->v_state), *reinterpret_cast<const CUtensorMap*>(&m->k_own),
+      *reinterpret_cast<const CUtensorMap*>(&m->v_own), p);
+  return cudaGetLastError();
+}

@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "../../include/decidra_b200.h"
+#include "attn_tcgen05.h"
 #include "common.cuh"
 #include "gemm_tcgen05.h"
 #include "host_logic.h"
@@ -86,7 +87,8 @@ struct dcd_engine {
   void *bufA = nullptr, *bufB = nullptr, *conv = nullptr, *act = nullptr;
   float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
   uint32_t* d_ids = nullptr;
-  int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr;
+  int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
+  bool attn_tc = false;
   int* d_err = nullptr;
   int max_batch = 0;
 
@@ -299,9 +301,19 @@ int run_layers(dcd_engine* e, const Pass& p) {
         else if (p.mode == 0) keys = (double)T_ * T_;
         else keys = (double)p.split * p.split + (double)(T_ - p.split) * T_;
         Scope sc(e, DCD_PROF_ATTN, 4.0 * heads * hd * keys, 1);
-        CK(e, launch_attn_fma<T>((const T*)e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? (const T*)p.cache->k[li] : nullptr,
-                                 p.mode == 1 ? (const T*)p.cache->v[li] : nullptr, n_state, big, e->qkv_n, (T*)e->bufA, e->d_cu,
-                                 e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
+        if (e->attn_tc && p.mode != 2) {
+          AttnTcMaps maps;
+          if (attn_tc_make_maps(&maps, e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? p.cache->k[li] : nullptr,
+                                p.mode == 1 ? p.cache->v[li] : nullptr, n_state, T_, heads, kv, hd))
+            return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an attention operand");
+          const int tt = attn_tc_tokens_per_tile(heads, kv);
+          CK(e, attn_tc_launch(&maps, e->d_cu, e->d_tile_cu, p.B, n_state, T_, (T_ + tt - 1) / tt + p.B, heads, kv, hd, big, e->qkv_n,
+                               e->bufA, e->d_err, s), "tcgen05 attention");
+        } else {
+          CK(e, launch_attn_fma<T>((const T*)e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? (const T*)p.cache->k[li] : nullptr,
+                                   p.mode == 1 ? (const T*)p.cache->v[li] : nullptr, n_state, big, e->qkv_n, (T*)e->bufA, e->d_cu,
+                                   e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
+        }
       }
       rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, e->mix, T_, H, heads * hd, H, 0);
       if (rc) return rc;
@@ -382,6 +394,10 @@ int run_pass(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t*
   {
     Scope sc(e, DCD_PROF_ELEMENTWISE, 12.0 * p.T, 2);
     CK(e, launch_pack(d_lens, p.B, p.T, pos_start, e->d_cu, e->d_last, e->d_tokq, e->d_tokpos, e->d_err, s), "pack");
+    if (e->attn_tc && p.mode != 2) {
+      e->launches += 1;
+      CK(e, attn_tc_build_tiles(e->d_cu, p.B, attn_tc_tokens_per_tile(e->c.heads, e->c.kv_heads), e->d_tile_cu, s), "attention tiles");
+    }
   }
   {
     Scope sc(e, DCD_PROF_ELEMENTWISE, 2.0 * p.T * e->H * e->esz, 1);
@@ -415,6 +431,7 @@ int check_device_error(dcd_engine* e) {
     case DERR_EMPTY_ITEM: return fail(e, DCD_E_INVALID, "batch item has no tokens");
     case DERR_POSITION_RANGE: return fail(e, DCD_E_INVALID, "position beyond the RoPE table (%d)", e->o.max_positions);
     case DERR_GEMM_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 GEMM: a bounded barrier wait gave up");
+    case DERR_ATTN_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 attention: a bounded barrier wait gave up");
     default: return fail(e, DCD_E_CUDA, "device error word %d", code);
   }
 }
@@ -561,6 +578,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRE(cudaEventCreate(&e->t0), "event");
   CRE(cudaEventCreate(&e->t1), "event");
   if (e->bf) CRE(tc_gemm_prepare_device(), "tcgen05 GEMM shared-memory attribute");
+  e->attn_tc = e->bf && o.attn_path == 0 && attn_tc_supported(c.heads, c.kv_heads, c.head_dim);
+  if (e->attn_tc) CRE(attn_tc_prepare_device(), "tcgen05 attention shared-memory attribute");
 
   const size_t es = e->esz, H = e->H;
   // ---- weights
@@ -649,6 +668,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRA(e->d_lens, (size_t)e->max_batch * 4, false, ws);
   CRA(e->d_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
   CRA(e->d_last, (size_t)e->max_batch * 4, false, ws);
+  CRA(e->d_tile_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
   CRA(e->d_tokq, Tm * 4, false, ws);
   CRA(e->d_tokpos, Tm * 4, false, ws);
   CRA(e->d_err, 256, true, ws);

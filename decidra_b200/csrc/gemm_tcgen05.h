@@ -10,6 +10,11 @@ struct alignas(64) TcTensorMap { uint64_t opaque[16]; };
 // W[N,K] (box 256 rows); both row-major bf16 with K contiguous. 0 on success.
 int tc_make_tmap_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K);
 int tc_make_tmap_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K);
+// Strided 2-D view (row stride in elements) with a box of box_rows x 64 columns, and a 3-D view
+// [d2, d1, d0] (d0 contiguous) with a box of box2 x box1 x 64; both bf16, 128-byte swizzle.
+int tc_make_tmap_strided(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows);
+int tc_make_tmap_3d(TcTensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1, uint64_t stride2,
+                    uint32_t box1, uint32_t box2);
 bool tc_shape_ok(int M, int N, int K);
 // Raises the kernel's dynamic shared-memory limit on the current device (call once per device).
 cudaError_t tc_gemm_prepare_device();

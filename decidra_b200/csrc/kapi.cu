@@ -1,6 +1,7 @@
 // Kernel-level C entry points: raw device pointers in, one launch out. They exist so that every
 // kernel can be checked against the CPU oracle and timed on its own through the C ABI.
 #include "../../include/decidra_b200.h"
+#include "attn_tcgen05.h"
 #include "common.cuh"
 #include "gemm_tcgen05.h"
 #include "kernels.h"
@@ -90,6 +91,19 @@ int dcd_k_attention(const void* q, const void* k_own, int k_stride, const void* 
   return DISPATCH(dtype,
                   launch_attn_fma<float>((const float*)q, (const float*)k_own, k_stride, (const float*)v_own, v_stride, (const float*)k_state, (const float*)v_state, n_state, (const float*)gate_qg, qg_stride, (float*)out, cu_seqlens, tok_q, T, heads, kv, hd, split, S(stream)),
                   launch_attn_fma<bf16>((const bf16*)q, (const bf16*)k_own, k_stride, (const bf16*)v_own, v_stride, (const bf16*)k_state, (const bf16*)v_state, n_state, (const bf16*)gate_qg, qg_stride, (bf16*)out, cu_seqlens, tok_q, T, heads, kv, hd, split, S(stream)));
+}
+
+int dcd_k_attention_tc(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                       const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out, const int32_t* cu_seqlens,
+                       int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err, void* stream) {
+  if (!attn_tc_supported(heads, kv, hd) || B <= 0 || T <= 0) return DCD_E_INVALID;
+  if (attn_tc_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  const int tt = attn_tc_tokens_per_tile(heads, kv);
+  AttnTcMaps maps;
+  if (attn_tc_make_maps(&maps, q, k_own, k_stride, v_own, v_stride, k_state, v_state, n_state, T, heads, kv, hd)) return DCD_E_CUDA;
+  cudaError_t ce = attn_tc_build_tiles(cu_seqlens, B, tt, tile_cu, S(stream));
+  if (ce != cudaSuccess) return rc_of(ce);
+  return rc_of(attn_tc_launch(&maps, cu_seqlens, tile_cu, B, n_state, T, (T + tt - 1) / tt + B, heads, kv, hd, gate_qg, qg_stride, out, err, S(stream)));
 }
 
 int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream) {

@@ -65,7 +65,7 @@ typedef struct dcd_options {
   int64_t max_keys;
   int64_t max_scores;
   int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMM (bf16 only); 1 = plain FMA GEMM (diagnostic) */
-  int32_t attn_path;        /* 0 = default; 1 = plain FMA attention (diagnostic) */
+  int32_t attn_path;        /* 0 = tcgen05 attention where the shape allows (bf16, head_dim 256, 6:1 GQA); 1 = plain FMA attention */
   int32_t max_positions;    /* RoPE table length; default 65536 */
   int32_t reserved[8];
 } dcd_options;
@@ -280,6 +280,13 @@ DCD_API int dcd_k_attention(const void* q, const void* k_own, int k_stride, cons
                             const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
                             const int32_t* cu_seqlens, const int32_t* tok_q, int T, int heads, int kv, int hd, int split, int dtype,
                             void* stream);
+/* The same attention on the tcgen05 tensor cores (bf16, head_dim 256, 6 query heads per KV head):
+ * one launch for the whole packed batch, K/V of both segments read in place through TMA, S and O
+ * accumulators in TMEM. tile_cu is device scratch of B+1 ints. `err` as in dcd_k_gemm_bf16_tc. */
+DCD_API int dcd_k_attention_tc(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                               const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
+                               const int32_t* cu_seqlens, int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err,
+                               void* stream);
 /* logits[B,R] = x[B,H] . W[R,H]^T in f32 (blas_gemm_f32, native/src/engine.rs:3873-3901, 4977-4984). */
 DCD_API int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream);
 
