@@ -287,6 +287,26 @@ DCD_API int dcd_k_attention_tc(const void* q, const void* k_own, int k_stride, c
                                const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
                                const int32_t* cu_seqlens, int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err,
                                void* stream);
+/* dcd_k_attention_tc for callers that cannot allocate device memory. It has no counterpart in the
+ * reference; it exists for hosts that drive these kernels from a request thread where
+ * cudaMalloc/cudaFree are off limits (both synchronise the whole device and would stall every other
+ * stream, other replicas included) or that have already handed all of the GPU's memory to weights
+ * and state caches, so that an allocation could fail mid-request. Same operands and result as
+ * dcd_k_attention_tc, but the tile-prefix scratch is a fixed array inside the library (16 KB held
+ * on every GPU that loads the library, until the process exits) instead of a caller buffer.
+ *  - At most DCD_NOALLOC_MAX_SEQUENCES packed sequences per call; more is refused with
+ *    DCD_E_INVALID and a message in msg (msg may be NULL).
+ *  - The first call on each device looks up the array's device address and raises the kernel's
+ *    shared-memory limit; make that first call before starting any stream capture.
+ *  - Every call on a device shares the one array. Its contents are rewritten in full by each call,
+ *    so nothing needs clearing, but two calls that overlap on the GPU (different streams, or
+ *    different threads on one device) race on it: serialise them.
+ *  - Calls no cudaMalloc, cudaFree or other allocating routine. */
+#define DCD_NOALLOC_MAX_SEQUENCES 4096
+DCD_API int dcd_k_attention_tc_noalloc(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride,
+                                       const void* k_state, const void* v_state, int n_state, const void* gate_qg, int qg_stride,
+                                       void* out, const int32_t* cu_seqlens, int B, int T, int heads, int kv, int hd, int* err,
+                                       void* stream, char* msg, size_t msg_len);
 /* logits[B,R] = x[B,H] . W[R,H]^T in f32 (blas_gemm_f32, native/src/engine.rs:3873-3901, 4977-4984). */
 DCD_API int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream);
 
