@@ -70,7 +70,8 @@ class Options(C.Structure):
         ("gemm_path", C.c_int32),
         ("attn_path", C.c_int32),
         ("max_positions", C.c_int32),
-        ("reserved", C.c_int32 * 8),
+        ("gdn_path", C.c_int32),
+        ("reserved", C.c_int32 * 7),
     ]
 
 

@@ -88,7 +88,7 @@ struct dcd_engine {
   float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
-  bool attn_tc = false;
+  bool attn_tc = false, gdn_chunked = false;
   int* d_err = nullptr;
   int max_batch = 0;
 
@@ -342,9 +342,14 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       {
         Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
-        CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta,
-                                      p.mode == 1 ? p.cache->gstate[li] : nullptr, p.mode == 0 ? p.cap->gstate[li] : nullptr, (T*)e->bufA,
-                                      e->d_cu, p.B, nk, nv, dk, dv, p.B < 8, s), "gdn_recurrent");
+        const float* seed = p.mode == 1 ? p.cache->gstate[li] : nullptr;
+        float* fin = p.mode == 0 ? p.cap->gstate[li] : nullptr;
+        if (e->gdn_chunked)
+          CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, dk,
+                                      dv, p.B < 2, s), "gdn_chunked");
+        else
+          CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv,
+                                        dk, dv, p.B < 8, s), "gdn_recurrent");
       }
       {
         Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->vd * e->esz * 3.0, 1);
@@ -580,6 +585,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (e->bf) CRE(tc_gemm_prepare_device(), "tcgen05 GEMM shared-memory attribute");
   e->attn_tc = e->bf && o.attn_path == 0 && attn_tc_supported(c.heads, c.kv_heads, c.head_dim);
   if (e->attn_tc) CRE(attn_tc_prepare_device(), "tcgen05 attention shared-memory attribute");
+  e->gdn_chunked = e->bf && o.gdn_path == 0 && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
+  if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
   const size_t es = e->esz, H = e->H;
   // ---- weights

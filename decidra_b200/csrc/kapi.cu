@@ -77,6 +77,16 @@ int dcd_k_gdn_recurrent(const float* qf, const float* kf, const void* conv, int 
                   launch_gdn_recurrent<bf16>(qf, kf, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)));
 }
 
+int dcd_k_gdn_chunked(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                      const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv, int dk, int dv,
+                      int narrow, int dtype, void* stream) {
+  if (!gdn_chunked_supported(dk, dv)) return DCD_E_INVALID;
+  if ((dtype == 0 ? gdn_chunked_prepare_device<float>() : gdn_chunked_prepare_device<bf16>()) != cudaSuccess) return DCD_E_CUDA;
+  return DISPATCH(dtype,
+                  launch_gdn_chunked<float>(qf, kf, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)),
+                  launch_gdn_chunked<bf16>(qf, kf, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)));
+}
+
 int dcd_k_qk_norm_rope(const void* qg, int qg_stride, const void* kraw, int k_stride, const void* qw, const void* kw, const void* cos_t,
                        const void* sin_t, const int32_t* positions, int max_pos, void* q, void* k, int T, int heads, int kv, int hd,
                        int rotary_dim, float eps, int* err, int dtype, void* stream) {

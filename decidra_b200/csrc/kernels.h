@@ -59,3 +59,12 @@ cudaError_t launch_gen_tensor(T* dst, uint64_t key, uint64_t first, uint64_t cou
 template <typename T>
 cudaError_t launch_place_rows(const T* src, T* dst, size_t rows, int cols, int mode, int row_offset, int dst_stride, bool inverse,
                               cudaStream_t s);
+
+// Chunked tensor-core form of the gated delta rule (gdn_chunked.cu); dk must be 128 and dv a multiple of 64.
+bool gdn_chunked_supported(int dk, int dv);
+template <typename T>
+cudaError_t gdn_chunked_prepare_device();
+template <typename T>
+cudaError_t launch_gdn_chunked(const float* qf, const float* kf, const T* conv, int conv_stride, const float* g, const float* beta,
+                               const float* seed, float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int dk, int dv,
+                               bool few_sequences, cudaStream_t s);

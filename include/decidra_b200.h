@@ -67,7 +67,8 @@ typedef struct dcd_options {
   int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMM (bf16 only); 1 = plain FMA GEMM (diagnostic) */
   int32_t attn_path;        /* 0 = tcgen05 attention where the shape allows (bf16, head_dim 256, 6:1 GQA); 1 = plain FMA attention */
   int32_t max_positions;    /* RoPE table length; default 65536 */
-  int32_t reserved[8];
+  int32_t gdn_path;         /* 0 = chunked tensor-core gated delta rule where the shape allows (bf16, dk 128); 1 = sequential f32 */
+  int32_t reserved[7];
 } dcd_options;
 
 typedef struct dcd_info {
@@ -264,6 +265,13 @@ DCD_API int dcd_k_gdn_prepare(const void* conv, int conv_stride, const void* b, 
 DCD_API int dcd_k_gdn_recurrent(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
                                 const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv,
                                 int dk, int dv, int narrow, int dtype, void* stream);
+/* The same recurrence in chunked form (chunk 32) with TF32 tensor-core contractions and the f32 state
+ * slice resident in shared memory (gdn_chunked_tc_body, native/kernels/kernels.cu:1671-1933). Same
+ * operands as dcd_k_gdn_recurrent; dk must be 128 and dv a multiple of 64. narrow != 0 uses 32 value
+ * columns per CTA (one long sequence) instead of 64. */
+DCD_API int dcd_k_gdn_chunked(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                              const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv,
+                              int dk, int dv, int narrow, int dtype, void* stream);
 /* split_q_gate + q/k RMSNorm(1+w) + partial NeoX RoPE in one kernel
  * (native/kernels/kernels.cu:516-557, 406-426; tables as native/src/engine.rs:1619-1643).
  * qg [T,heads,2*hd] (row stride qg_stride), kraw [T,kv,hd] (row stride k_stride) -> q [T,heads,hd],

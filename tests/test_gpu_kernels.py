@@ -358,3 +358,41 @@ def test_attention_tcgen05_vs_oracle(G, oracle, lens, S):
         t_, h_, d_ = np.nonzero(bad)
         pytest.fail(f"{bad.mean():.4%} mismatched, nan {np.isnan(got).mean():.4%}; tokens {np.unique(t_)[:20]} heads {np.unique(h_)[:24]} dims {d_.min()}..{d_.max()}; "
                     f"first got {got[t_[0], h_[0], d_[0]]} want {want[t_[0], h_[0], d_[0]]}; max abs {np.nanmax(np.abs(got - want))}")
+
+
+@pytest.mark.parametrize("dtype,nk,nv,dv,narrow", [(1, 16, 48, 128, 0), (1, 16, 48, 128, 1), (0, 2, 6, 64, 0), (0, 2, 6, 64, 1)])
+def test_gdn_chunked_vs_oracle(G, oracle, dtype, nk, nv, dv, narrow):
+    """Chunked tensor-core gated delta rule against the sequential oracle, with the tolerances of the
+    reference's own chunked-vs-sequential test (native/tests/gdn_chunked.rs:109-111): out max < 2e-2,
+    mean < 2e-4, state max < 2e-3; lengths straddle the 32-token chunk (1, 31, 33, 64, 73, 89)."""
+    dk = 128
+    lens = [73, 64, 89, 1, 31, 33]
+    T = sum(lens)
+    conv, q, k, g, beta = _gdn_inputs(oracle, T, nk, nv, dk, dv, dtype)
+    cd = conv.shape[1]
+    seed = (0.05 * _host_data(nv * dk * dv, 1.0, 1.0)).reshape(nv, dk, dv).astype(np.float32)
+    cu, _ = _pack(oracle, lens)
+    out = G.empty((T, nv * dv), dtype)
+    fin = G.devf(np.zeros((len(lens), nv, dk, dv)))
+    G.call("dcd_k_gdn_chunked", G.devf(q), G.devf(k), G.dev(conv, dtype), cd, G.devf(g), G.devf(beta), G.devf(seed), fin, out, G.devi(cu), len(lens),
+           nk, nv, dk, dv, narrow, dtype, None)
+    rep = nv // nk
+    got, gfin = G.host(out), G.host(fin)
+    worst = (0.0, 0.0, 0.0)
+    for i, L in enumerate(lens):
+        sl = slice(cu[i], cu[i + 1])
+        v = conv[sl, 2 * nk * dk:].reshape(L, nv, dv)
+        want, wstate = oracle.k_gdn_recurrent(np.repeat(q[sl], rep, 1), np.repeat(k[sl], rep, 1), v, g[sl], beta[sl], seed, bool(dtype))
+        d = np.abs(got[sl].reshape(L, nv, dv) - want)
+        ds = np.abs(gfin[i] - wstate).max()
+        worst = (max(worst[0], d.max()), max(worst[1], d.mean()), max(worst[2], ds))
+    print("gdn chunked vs sequential oracle: out max %.3g mean %.3g state max %.3g" % worst)
+    assert worst[0] < 2e-2 and worst[1] < 2e-4 and worst[2] < 2e-3, worst
+    # zero seed (capture) and no final-state store
+    out2 = G.empty((T, nv * dv), dtype)
+    G.call("dcd_k_gdn_chunked", G.devf(q), G.devf(k), G.dev(conv, dtype), cd, G.devf(g), G.devf(beta), None, None, out2, G.devi(cu), len(lens),
+           nk, nv, dk, dv, narrow, dtype, None)
+    sl = slice(cu[2], cu[3])
+    v = conv[sl, 2 * nk * dk:].reshape(lens[2], nv, dv)
+    want, _ = oracle.k_gdn_recurrent(np.repeat(q[sl], rep, 1), np.repeat(k[sl], rep, 1), v, g[sl], beta[sl], np.zeros_like(seed), bool(dtype))
+    assert np.abs(G.host(out2)[sl].reshape(lens[2], nv, dv) - want).max() < 2e-2
