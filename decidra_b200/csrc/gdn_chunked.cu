@@ -14,7 +14,8 @@
 // One CTA = (packed sequence, value head, slice of VC value columns); the state slice
 // S[dk=128, VC] stays in shared memory in f32 across chunks. K S, Q S, K K^T, Q K^T, P D and the
 // state update run on mma.sync.m16n8k8 TF32; the triangular solve is a right-looking
-// substitution with one thread per value column.
+// substitution with one thread per value column, overlapped with the Q-side products, and the
+// next chunk's rows are prefetched into registers while the current chunk is computed.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -66,30 +67,55 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
     sS[r * LDS + c] = seed ? seed[((size_t)head * DK + r) * dv + cbase + c] : 0.f;
   }
 
+  // register prefetch of one chunk's K/Q rows (4 float4 each per thread) and V values
+  constexpr int VPT = C * VC / 256;  // V elements per thread
+  float4 pk[4], pq[4];
+  float pv[VPT];
+  float pg = 0.f, pb = 0.f;
+  auto fetch = [&](int t0) {
+    const int nt = min(C, len - t0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = tid + j * 256;
+      const int r = i / (DK / 4), c4 = (i - r * (DK / 4)) * 4;
+      pk[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      pq[j] = pk[j];
+      if (r < nt) {
+        const size_t src = ((size_t)(off + t0 + r) * nk + kh) * DK + c4;
+        pk[j] = *reinterpret_cast<const float4*>(kf + src);
+        pq[j] = *reinterpret_cast<const float4*>(qf + src);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = tid + j * 256;
+      const int r = i / VC, c = i - r * VC;
+      pv[j] = r < nt ? Ty<T>::ld(conv + (size_t)(off + t0 + r) * conv_stride + vcol0 + c) : 0.f;
+    }
+    if (warp == 0) {
+      pg = lane < nt ? gl[(size_t)(off + t0 + lane) * nv + head] : 0.f;
+      pb = lane < nt ? beta[(size_t)(off + t0 + lane) * nv + head] : 0.f;
+    }
+  };
+  if (len > 0) fetch(0);
+
   for (int t0 = 0; t0 < len; t0 += C) {
     const int nt = min(C, len - t0);
     __syncthreads();  // previous chunk done with every buffer; S updated
-    // ---- load the chunk (rows beyond the sequence are zero: no decay, no update) ----------------
-    for (int i = tid; i < C * (DK / 4); i += 256) {
+    // ---- stage the prefetched chunk (rows beyond the sequence are zero: no decay, no update) ------
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = tid + j * 256;
       const int r = i / (DK / 4), c4 = (i - r * (DK / 4)) * 4;
-      float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f), qv4 = kv4;
-      if (r < nt) {
-        const size_t src = ((size_t)(off + t0 + r) * nk + kh) * DK + c4;
-        kv4 = *reinterpret_cast<const float4*>(kf + src);
-        qv4 = *reinterpret_cast<const float4*>(qf + src);
-      }
-      float* kd = sK + r * LDK + c4;
-      float* qd = sQ + r * LDK + c4;
-      kd[0] = __uint_as_float(tf32(kv4.x)); kd[1] = __uint_as_float(tf32(kv4.y)); kd[2] = __uint_as_float(tf32(kv4.z)); kd[3] = __uint_as_float(tf32(kv4.w));
-      qd[0] = __uint_as_float(tf32(qv4.x)); qd[1] = __uint_as_float(tf32(qv4.y)); qd[2] = __uint_as_float(tf32(qv4.z)); qd[3] = __uint_as_float(tf32(qv4.w));
+      *reinterpret_cast<float4*>(sK + r * LDK + c4) = make_float4(__uint_as_float(tf32(pk[j].x)), __uint_as_float(tf32(pk[j].y)),
+                                                                  __uint_as_float(tf32(pk[j].z)), __uint_as_float(tf32(pk[j].w)));
+      *reinterpret_cast<float4*>(sQ + r * LDK + c4) = make_float4(__uint_as_float(tf32(pq[j].x)), __uint_as_float(tf32(pq[j].y)),
+                                                                  __uint_as_float(tf32(pq[j].z)), __uint_as_float(tf32(pq[j].w)));
     }
-    for (int i = tid; i < C * VC; i += 256) {
-      const int r = i / VC, c = i - r * VC;
-      sV[i] = r < nt ? Ty<T>::ld(conv + (size_t)(off + t0 + r) * conv_stride + vcol0 + c) : 0.f;
-    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) sV[tid + j * 256] = pv[j];
     if (warp == 0) {
-      float gv = lane < nt ? gl[(size_t)(off + t0 + lane) * nv + head] : 0.f;
-      const float bv = lane < nt ? beta[(size_t)(off + t0 + lane) * nv + head] : 0.f;
+      float gv = pg;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, gv, o);
@@ -97,15 +123,15 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
       }
       const float glast = __shfl_sync(0xffffffffu, gv, 31);
       sG[lane] = gv;
-      sB[lane] = bv;
+      sB[lane] = pb;
       sE[lane] = expf(glast - gv);
     }
     __syncthreads();
+    if (t0 + C < len) fetch(t0 + C);  // loads for the next chunk stay in flight during this chunk's math
 
-    // ---- phase 1: K S and Q S  ([32 x VC], k = 128). warp -> (matrix, m-tile, half of the n-tiles)
-    {
-      const int mat = warp >> 2, mt = (warp >> 1) & 1, nh = warp & 1;
-      const float* X = mat ? sQ : sK;
+    // ---- phase 1: warps 0-3: K S -> rhs;  warps 4-7: K K^T -> A^T -------------------------------------
+    if (warp < 4) {
+      const int mt = warp >> 1, nh = warp & 1;
       float acc[NT / 2][4];
 #pragma unroll
       for (int n = 0; n < NT / 2; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
@@ -113,43 +139,29 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
 #pragma unroll 4
       for (int k0 = 0; k0 < DK; k0 += 8) {
         uint32_t a[4];
-        a[0] = __float_as_uint(X[r0 * LDK + k0 + tig]);
-        a[1] = __float_as_uint(X[(r0 + 8) * LDK + k0 + tig]);
-        a[2] = __float_as_uint(X[r0 * LDK + k0 + tig + 4]);
-        a[3] = __float_as_uint(X[(r0 + 8) * LDK + k0 + tig + 4]);
+        a[0] = __float_as_uint(sK[r0 * LDK + k0 + tig]);
+        a[1] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig]);
+        a[2] = __float_as_uint(sK[r0 * LDK + k0 + tig + 4]);
+        a[3] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig + 4]);
 #pragma unroll
         for (int n = 0; n < NT / 2; ++n) {
           const int n0 = (nh * (NT / 2) + n) * 8 + g;
           mma_tf32(acc[n], a, tf32(sS[(k0 + tig) * LDS + n0]), tf32(sS[(k0 + tig + 4) * LDS + n0]));
         }
       }
-      const float g0 = sG[r0], g1 = sG[r0 + 8];
-      const float gam0 = expf(g0), gam1 = expf(g1);
-      if (mat == 0) {
-        const float b0 = sB[r0], b1 = sB[r0 + 8];
+      const float gam0 = expf(sG[r0]), gam1 = expf(sG[r0 + 8]);
+      const float b0 = sB[r0], b1 = sB[r0 + 8];
 #pragma unroll
-        for (int n = 0; n < NT / 2; ++n) {
-          const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
-          sD[r0 * LDS + c] = b0 * (sV[r0 * VC + c] - gam0 * acc[n][0]);
-          sD[r0 * LDS + c + 1] = b0 * (sV[r0 * VC + c + 1] - gam0 * acc[n][1]);
-          sD[(r0 + 8) * LDS + c] = b1 * (sV[(r0 + 8) * VC + c] - gam1 * acc[n][2]);
-          sD[(r0 + 8) * LDS + c + 1] = b1 * (sV[(r0 + 8) * VC + c + 1] - gam1 * acc[n][3]);
-        }
-      } else {
-#pragma unroll
-        for (int n = 0; n < NT / 2; ++n) {
-          const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
-          sO[r0 * LDS + c] = gam0 * acc[n][0];
-          sO[r0 * LDS + c + 1] = gam0 * acc[n][1];
-          sO[(r0 + 8) * LDS + c] = gam1 * acc[n][2];
-          sO[(r0 + 8) * LDS + c + 1] = gam1 * acc[n][3];
-        }
+      for (int n = 0; n < NT / 2; ++n) {
+        const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
+        sD[r0 * LDS + c] = b0 * (sV[r0 * VC + c] - gam0 * acc[n][0]);
+        sD[r0 * LDS + c + 1] = b0 * (sV[r0 * VC + c + 1] - gam0 * acc[n][1]);
+        sD[(r0 + 8) * LDS + c] = b1 * (sV[(r0 + 8) * VC + c] - gam1 * acc[n][2]);
+        sD[(r0 + 8) * LDS + c + 1] = b1 * (sV[(r0 + 8) * VC + c + 1] - gam1 * acc[n][3]);
       }
-    }
-    // ---- phase 2: K K^T -> A^T and Q K^T -> P  ([32 x 32], k = 128). warp -> (matrix, m-tile, 2 n-tiles)
-    {
-      const int mat = warp >> 2, mt = (warp >> 1) & 1, nh = warp & 1;
-      const float* X = mat ? sQ : sK;
+    } else {
+      // K K^T: 2 m-tiles x 4 n-tiles; warp (4+i): m-tile = i>>1, n-tiles (i&1)*2 .. +1
+      const int mt = (warp - 4) >> 1, nh = (warp - 4) & 1;
       float acc[2][4];
 #pragma unroll
       for (int n = 0; n < 2; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
@@ -158,10 +170,10 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
 #pragma unroll 4
         for (int k0 = 0; k0 < DK; k0 += 8) {
           uint32_t a[4];
-          a[0] = __float_as_uint(X[r0 * LDK + k0 + tig]);
-          a[1] = __float_as_uint(X[(r0 + 8) * LDK + k0 + tig]);
-          a[2] = __float_as_uint(X[r0 * LDK + k0 + tig + 4]);
-          a[3] = __float_as_uint(X[(r0 + 8) * LDK + k0 + tig + 4]);
+          a[0] = __float_as_uint(sK[r0 * LDK + k0 + tig]);
+          a[1] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig]);
+          a[2] = __float_as_uint(sK[r0 * LDK + k0 + tig + 4]);
+          a[3] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig + 4]);
 #pragma unroll
           for (int n = 0; n < 2; ++n) {
             const int n0 = (nh * 2 + n) * 8 + g;
@@ -170,33 +182,94 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         }
       }
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int t = r0 + (e >> 1) * 8, s = (nh * 2 + n) * 8 + 2 * tig + (e & 1);
-          const float decay = s <= t ? expf(sG[t] - sG[s]) : 0.f;
-          if (mat == 0) sAT[s * LDA + t] = s < t ? sB[t] * decay * acc[n][e] : 0.f;
-          else sP[t * LDA + s] = __uint_as_float(tf32(decay * acc[n][e]));
+          const int t = r0 + (e >> 1) * 8, sidx = (nh * 2 + n) * 8 + 2 * tig + (e & 1);
+          sAT[sidx * LDA + t] = sidx < t ? sB[t] * expf(sG[t] - sG[sidx]) * acc[n][e] : 0.f;
         }
-      }
     }
     __syncthreads();
-    // ---- phase 3: solve (I + A) D = rhs, one thread per value column, right-looking ---------------
+    // ---- phase 2: warps 0-1 solve (I + A) D = rhs (one thread per value column, right-looking);
+    //      meanwhile warps 2-5: Gam (Q S) -> sO, warps 6-7: Q K^T -> P -------------------------------------
     if (tid < VC) {
       float r[C];
 #pragma unroll
       for (int t = 0; t < C; ++t) r[t] = sD[t * LDS + tid];
 #pragma unroll
-      for (int s = 0; s < C; ++s) {
-        const float x = r[s];
+      for (int sidx = 0; sidx < C - 1; ++sidx) {
+        const float x = r[sidx];
 #pragma unroll
-        for (int t = s + 1; t < C; ++t) r[t] = fmaf(-sAT[s * LDA + t], x, r[t]);
+        for (int t4 = ((sidx + 1) / 4) * 4; t4 < C; t4 += 4) {
+          const float4 av = *reinterpret_cast<const float4*>(sAT + sidx * LDA + t4);
+          if (t4 + 0 > sidx) r[t4 + 0] = fmaf(-av.x, x, r[t4 + 0]);
+          if (t4 + 1 > sidx) r[t4 + 1] = fmaf(-av.y, x, r[t4 + 1]);
+          if (t4 + 2 > sidx) r[t4 + 2] = fmaf(-av.z, x, r[t4 + 2]);
+          if (t4 + 3 > sidx) r[t4 + 3] = fmaf(-av.w, x, r[t4 + 3]);
+        }
       }
 #pragma unroll
       for (int t = 0; t < C; ++t) sD[t * LDS + tid] = __uint_as_float(tf32(r[t]));
+    } else if (warp >= 2 && warp < 6) {
+      const int mt = (warp - 2) >> 1, nh = (warp - 2) & 1;
+      float acc[NT / 2][4];
+#pragma unroll
+      for (int n = 0; n < NT / 2; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      const int r0 = mt * 16 + g;
+#pragma unroll 4
+      for (int k0 = 0; k0 < DK; k0 += 8) {
+        uint32_t a[4];
+        a[0] = __float_as_uint(sQ[r0 * LDK + k0 + tig]);
+        a[1] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig]);
+        a[2] = __float_as_uint(sQ[r0 * LDK + k0 + tig + 4]);
+        a[3] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig + 4]);
+#pragma unroll
+        for (int n = 0; n < NT / 2; ++n) {
+          const int n0 = (nh * (NT / 2) + n) * 8 + g;
+          mma_tf32(acc[n], a, tf32(sS[(k0 + tig) * LDS + n0]), tf32(sS[(k0 + tig + 4) * LDS + n0]));
+        }
+      }
+      const float gam0 = expf(sG[r0]), gam1 = expf(sG[r0 + 8]);
+#pragma unroll
+      for (int n = 0; n < NT / 2; ++n) {
+        const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
+        sO[r0 * LDS + c] = gam0 * acc[n][0];
+        sO[r0 * LDS + c + 1] = gam0 * acc[n][1];
+        sO[(r0 + 8) * LDS + c] = gam1 * acc[n][2];
+        sO[(r0 + 8) * LDS + c + 1] = gam1 * acc[n][3];
+      }
+    } else if (warp >= 6) {
+      // Q K^T: warp 6 -> m-tile 0 (n-tiles 0,1), warp 7 -> m-tile 1 (n-tiles 0..3)
+      const int mt = warp - 6;
+      float acc[4][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      const int r0 = mt * 16 + g;
+#pragma unroll 4
+      for (int k0 = 0; k0 < DK; k0 += 8) {
+        uint32_t a[4];
+        a[0] = __float_as_uint(sQ[r0 * LDK + k0 + tig]);
+        a[1] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig]);
+        a[2] = __float_as_uint(sQ[r0 * LDK + k0 + tig + 4]);
+        a[3] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig + 4]);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          if (n < 2 * (mt + 1)) {
+            const int n0 = n * 8 + g;
+            mma_tf32(acc[n], a, __float_as_uint(sK[n0 * LDK + k0 + tig]), __float_as_uint(sK[n0 * LDK + k0 + tig + 4]));
+          }
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int t = r0 + (e >> 1) * 8, sidx = n * 8 + 2 * tig + (e & 1);
+          sP[t * LDA + sidx] = sidx <= t ? __uint_as_float(tf32(expf(sG[t] - sG[sidx]) * acc[n][e])) : 0.f;
+        }
     }
     __syncthreads();
-    // ---- phase 4a: O = Gam (Q S) + P D  ([32 x VC], k = 32). warp -> (m-tile, quarter of the n-tiles)
+    // ---- phase 3a: O = Gam (Q S) + P D  ([32 x VC], k = 32). warp -> (m-tile, quarter of the n-tiles)
     {
       const int mt = warp & 1, nq = warp >> 1;  // NT/4 n-tiles per warp
       const int r0 = mt * 16 + g;
@@ -231,7 +304,7 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         if (r0 + 8 < nt) { Ty<T>::st(o1, acc[n][2]); Ty<T>::st(o1 + 1, acc[n][3]); }
       }
     }
-    // ---- phase 4b: S' = exp(G_C) S + (exp(G_C - G) K)^T D  ([128 x VC], k = 32). warp -> m-tile
+    // ---- phase 3b: S' = exp(G_C) S + (exp(G_C - G) K)^T D  ([128 x VC], k = 32). warp -> m-tile
     {
       const int m0 = warp * 16 + g;
       const float gamC = expf(sG[C - 1]);
@@ -252,7 +325,7 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
           mma_tf32(acc[n], a, __float_as_uint(sD[(k0 + tig) * LDS + n0]), __float_as_uint(sD[(k0 + tig + 4) * LDS + n0]));
         }
       }
-      // every warp passed the barrier after phase 2, so nobody still reads S from phase 1
+      // every warp passed the barrier after phase 2, so nobody still reads S
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         const int c = n * 8 + 2 * tig;

@@ -143,13 +143,95 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+
+// ---- 16-byte vectorised bf16 forms (cols % 8 == 0, cols <= 8 * 4 * blockDim): one pass, the row is
+// held in registers between the sum of squares and the scaling. Same arithmetic as the kernels above.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(h[i]);
+    f[2 * i + 1] = __high2float(h[i]);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+template <int NV, bool ADD, typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ mix, const bf16* __restrict__ w,
+                                                          bf16* __restrict__ residual, TO* __restrict__ out, int cols, float eps, float wofs,
+                                                          const int32_t* __restrict__ rows_idx) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const size_t in_row = rows_idx ? (size_t)rows_idx[row] : (size_t)row;
+  const int n8 = cols >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + in_row * cols);
+  const uint4* mr = ADD ? reinterpret_cast<const uint4*>(mix + in_row * cols) : nullptr;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NV; ++c) {
+    const int i = threadIdx.x + c * 256;
+    if (i < n8) {
+      unpack8(xr[i], v[c]);
+      if (ADD) {
+        float m[8];
+        unpack8(mr[i], m);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[c][j] = Ty<bf16>::rnd(v[c][j] + m[j]);
+        reinterpret_cast<uint4*>(residual + (size_t)row * cols)[i] = pack8(v[c]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
+    }
+  }
+  const float mean = block_sum(ss, red) / (float)cols;
+  const float scale = 1.0f / sqrtf(mean + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int c = 0; c < NV; ++c) {
+    const int i = threadIdx.x + c * 256;
+    if (i < n8) {
+      float wv[8], y[8];
+      unpack8(wr[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = Ty<bf16>::rnd(v[c][j] * scale * (wv[j] + wofs));
+      if constexpr (sizeof(TO) == 2) {
+        reinterpret_cast<uint4*>(out + (size_t)row * cols)[i] = pack8(y);
+      } else {
+        float4* o = reinterpret_cast<float4*>(out + (size_t)row * cols + (size_t)i * 8);
+        o[0] = make_float4(y[0], y[1], y[2], y[3]);
+        o[1] = make_float4(y[4], y[5], y[6], y[7]);
+      }
+    }
+  }
+}
+static inline bool vec_norm_ok(int cols) { return (cols % 8) == 0 && cols <= 8 * 4 * 256; }
+
 template <typename T>
 cudaError_t launch_rmsnorm(const T* x, const T* w, T* out, int rows, int cols, float eps, bool zero_centered, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if (vec_norm_ok(cols)) {
+      rmsnorm_vec_kernel<4, false, bf16><<<rows, 256, 0, s>>>(x, nullptr, w, nullptr, out, cols, eps, zero_centered ? 1.0f : 0.0f, nullptr);
+      return cudaGetLastError();
+    }
+  }
   rmsnorm_kernel<T, T><<<rows, 256, 0, s>>>(x, w, out, cols, eps, zero_centered ? 1.0f : 0.0f, nullptr);
   return cudaGetLastError();
 }
 template <typename T>
 cudaError_t launch_add_rmsnorm(const T* x, const T* mix, const T* w, T* residual, T* out, int rows, int cols, float eps, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if (vec_norm_ok(cols)) {
+      rmsnorm_vec_kernel<4, true, bf16><<<rows, 256, 0, s>>>(x, mix, w, residual, out, cols, eps, 1.0f, nullptr);
+      return cudaGetLastError();
+    }
+  }
   add_rmsnorm_kernel<T><<<rows, 256, 0, s>>>(x, mix, w, residual, out, cols, eps);
   return cudaGetLastError();
 }
@@ -157,6 +239,12 @@ cudaError_t launch_add_rmsnorm(const T* x, const T* mix, const T* w, T* residual
 // (native/src/engine.rs:4968-4975).
 template <typename T>
 cudaError_t launch_final_norm_rows(const T* x, const T* w, float* out, const int32_t* rows_idx, int B, int cols, float eps, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if (vec_norm_ok(cols)) {
+      rmsnorm_vec_kernel<4, false, float><<<B, 256, 0, s>>>(x, nullptr, w, nullptr, out, cols, eps, 1.0f, rows_idx);
+      return cudaGetLastError();
+    }
+  }
   rmsnorm_kernel<T, float><<<B, 256, 0, s>>>(x, w, out, cols, eps, 1.0f, rows_idx);
   return cudaGetLastError();
 }
@@ -195,9 +283,49 @@ __global__ void rmsnorm_gated_kernel(const T* __restrict__ x, const T* __restric
     Ty<T>::st(orow + j, scaled * Ty<T>::rnd(silu_f(g)));
   }
 }
+// bf16, cols == 128: each lane owns 4 consecutive elements (8-byte loads); same arithmetic.
+__global__ void __launch_bounds__(256) rmsnorm_gated_vec128_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int z_stride,
+                                                                    const bf16* __restrict__ w, bf16* __restrict__ out, int rows, int heads,
+                                                                    float eps) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int t = row / heads, h = row - t * heads;
+  const uint2 xv = reinterpret_cast<const uint2*>(x + (size_t)row * 128)[lane];
+  const uint2 zv = reinterpret_cast<const uint2*>(z + (size_t)t * z_stride + (size_t)h * 128)[lane];
+  const uint2 wv = reinterpret_cast<const uint2*>(w)[lane];
+  const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+  const __nv_bfloat162* zh = reinterpret_cast<const __nv_bfloat162*>(&zv);
+  const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+  float xf[4] = {__low2float(xh[0]), __high2float(xh[0]), __low2float(xh[1]), __high2float(xh[1])};
+  const float zf[4] = {__low2float(zh[0]), __high2float(zh[0]), __low2float(zh[1]), __high2float(zh[1])};
+  const float wf[4] = {__low2float(wh[0]), __high2float(wh[0]), __low2float(wh[1]), __high2float(wh[1])};
+  float ss = xf[0] * xf[0] + xf[1] * xf[1] + xf[2] * xf[2] + xf[3] * xf[3];
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+  float y[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float normed = Ty<bf16>::rnd(xf[j] * scale);
+    const float scaled = Ty<bf16>::rnd(normed * wf[j]);
+    y[j] = scaled * Ty<bf16>::rnd(silu_f(zf[j]));
+  }
+  uint2 ov;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+  oh[0] = __floats2bfloat162_rn(y[0], y[1]);
+  oh[1] = __floats2bfloat162_rn(y[2], y[3]);
+  reinterpret_cast<uint2*>(out + (size_t)row * 128)[lane] = ov;
+}
+
 template <typename T>
 cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* w, T* out, int tokens, int heads, int cols, float eps, cudaStream_t s) {
   const int rows = tokens * heads;
+  if constexpr (sizeof(T) == 2) {
+    if (cols == 128 && (z_stride % 4) == 0 && (reinterpret_cast<uintptr_t>(z) % 8) == 0) {
+      rmsnorm_gated_vec128_kernel<<<(rows + 7) / 8, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, eps);
+      return cudaGetLastError();
+    }
+  }
   rmsnorm_gated_kernel<T><<<(rows + 7) / 8, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, cols, eps);
   return cudaGetLastError();
 }
@@ -499,9 +627,61 @@ __global__ void conv1d_silu_kernel(const T* __restrict__ x, int x_stride, const 
   const float v = Ty<T>::rnd(acc);
   Ty<T>::st(out + (size_t)t * ch + c, silu_f(v));
 }
+// bf16, ch % 8 == 0: each thread owns 8 consecutive channels of one token (16-byte loads of the four
+// taps, the weights and the store). Same fmaf chain, rounding and SiLU per channel.
+__global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __restrict__ x, int x_stride, const bf16* __restrict__ hist,
+                                                               const bf16* __restrict__ w, bf16* __restrict__ out,
+                                                               const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int ch) {
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 * 8 >= ch) return;
+  const int c = c8 * 8;
+  const int t = blockIdx.y;
+  const int off = cu ? cu[tok_q[t]] : 0;
+  const int lt = t - off;
+  float xs[4][8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int src = lt - 3 + j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(off + src) * x_stride + c);
+    else if (hist) v = *reinterpret_cast<const uint4*>(hist + (size_t)(src + 3) * ch + c);
+    unpack8(v, xs[j]);
+  }
+  // weights [ch][4]: 8 channels x 4 taps = 32 bf16 = 4 x 16 bytes
+  float wt[8][4];
+  {
+    const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)c * 4);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float f[8];
+      unpack8(wp[q], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wt[q * 2 + (i >> 2)][i & 3] = f[i];
+    }
+  }
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float acc = fmaf(xs[0][i], wt[i][0], 0.f);
+    acc = fmaf(xs[1][i], wt[i][1], acc);
+    acc = fmaf(xs[2][i], wt[i][2], acc);
+    acc = fmaf(xs[3][i], wt[i][3], acc);
+    const float v = Ty<bf16>::rnd(acc);
+    y[i] = silu_f(v);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)t * ch + c) = pack8(y);
+}
+
 template <typename T>
 cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T* w, T* out, const int32_t* cu,
                                const int32_t* tok_q, int tokens, int ch, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if ((ch % 8) == 0 && (x_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
+      dim3 gridv((ch / 8 + 127) / 128, tokens);
+      conv1d_silu_vec8_kernel<<<gridv, 128, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch);
+      return cudaGetLastError();
+    }
+  }
   dim3 grid((ch + 255) / 256, tokens);
   conv1d_silu_kernel<T><<<grid, 256, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch);
   return cudaGetLastError();
@@ -542,11 +722,49 @@ __global__ void gdn_prepare_kernel(const T* __restrict__ conv, int conv_stride, 
     beta[(size_t)t * nv + vh] = Ty<T>::rnd(sigmoid_f(Ty<T>::ld(b + (size_t)t * ba_stride + vh)));
   }
 }
+// dk == 128: one warp per (token, key head), 4 elements per lane, shuffle reductions, float4 stores.
+template <typename T>
+__global__ void __launch_bounds__(256) gdn_prepare_warp128_kernel(const T* __restrict__ conv, int conv_stride, const T* __restrict__ b,
+                                                                  const T* __restrict__ a, int ba_stride, const float* __restrict__ A_log,
+                                                                  const float* __restrict__ dt_bias, float* __restrict__ qf,
+                                                                  float* __restrict__ kf, float* __restrict__ g, float* __restrict__ beta,
+                                                                  int tokens, int nk, int nv) {
+  const int idx = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (idx >= tokens * nk) return;
+  const int lane = threadIdx.x & 31;
+  const int t = idx / nk, kh = idx - t * nk;
+  const T* row = conv + (size_t)t * conv_stride;
+  float q[4], k[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    q[j] = Ty<T>::ld(row + kh * 128 + lane * 4 + j);
+    k[j] = Ty<T>::ld(row + nk * 128 + kh * 128 + lane * 4 + j);
+  }
+  const float qn = warp_sum(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+  const float kn = warp_sum(k[0] * k[0] + k[1] * k[1] + k[2] * k[2] + k[3] * k[3]);
+  const float qscale = (1.0f / sqrtf(qn + 1e-6f)) * (1.0f / sqrtf(128.0f));
+  const float kscale = 1.0f / sqrtf(kn + 1e-6f);
+  reinterpret_cast<float4*>(qf + ((size_t)t * nk + kh) * 128)[lane] = make_float4(q[0] * qscale, q[1] * qscale, q[2] * qscale, q[3] * qscale);
+  reinterpret_cast<float4*>(kf + ((size_t)t * nk + kh) * 128)[lane] = make_float4(k[0] * kscale, k[1] * kscale, k[2] * kscale, k[3] * kscale);
+  const int rep = nv / nk;
+  if (lane < rep) {
+    const int vh = kh * rep + lane;
+    const float av = Ty<T>::ld(a + (size_t)t * ba_stride + vh) + dt_bias[vh];
+    const float sp = av > 20.f ? av : log1pf(expf(av));
+    g[(size_t)t * nv + vh] = -expf(A_log[vh]) * sp;
+    beta[(size_t)t * nv + vh] = Ty<T>::rnd(sigmoid_f(Ty<T>::ld(b + (size_t)t * ba_stride + vh)));
+  }
+}
+
 template <typename T>
 cudaError_t launch_gdn_prepare(const T* conv, int conv_stride, const T* b, const T* a, int ba_stride, const float* A_log,
                                const float* dt_bias, float* qf, float* kf, float* g, float* beta, int tokens, int nk, int nv,
                                int dk, cudaStream_t s) {
   if (dk % 32 != 0 || dk > 1024 || nv / nk > dk) return cudaErrorInvalidValue;
+  if (dk == 128 && nv / nk <= 32) {
+    gdn_prepare_warp128_kernel<T><<<(tokens * nk + 7) / 8, 256, 0, s>>>(conv, conv_stride, b, a, ba_stride, A_log, dt_bias, qf, kf, g, beta, tokens, nk, nv);
+    return cudaGetLastError();
+  }
   dim3 grid(tokens, nk);
   gdn_prepare_kernel<T><<<grid, dk, 0, s>>>(conv, conv_stride, b, a, ba_stride, A_log, dt_bias, qf, kf, g, beta, nk, nv, dk);
   return cudaGetLastError();
