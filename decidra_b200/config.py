@@ -71,7 +71,8 @@ class Options(C.Structure):
         ("attn_path", C.c_int32),
         ("max_positions", C.c_int32),
         ("gdn_path", C.c_int32),
-        ("reserved", C.c_int32 * 7),
+        ("fp8_min_rows", C.c_int32),
+        ("reserved", C.c_int32 * 6),
     ]
 
 

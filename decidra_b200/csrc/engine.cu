@@ -42,6 +42,9 @@ struct LayerW {
   void *w_gin = nullptr, *w_out = nullptr, *conv = nullptr, *gnorm = nullptr;
   float *A_log = nullptr, *dt_bias = nullptr;
   TcTensorMap tm_gu, tm_down, tm_qkv, tm_o, tm_gin, tm_out;
+  // FP8 (e4m3) images of the six GEMM weights: values, per-output-row scales, TMA descriptors
+  struct Fp8W { uint8_t* q = nullptr; float* scale = nullptr; TcTensorMap tm; };
+  Fp8W f_gu, f_down, f_qkv, f_o, f_gin, f_out;
 };
 
 }  // namespace
@@ -89,6 +92,10 @@ struct dcd_engine {
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
   bool attn_tc = false, gdn_chunked = false;
+  bool fp8 = false, fp8_dirty = true;  // precision 2: e4m3 GEMMs in question passes of >= fp8_min_rows rows
+  uint8_t* aq = nullptr;               // [Tm, max K] quantised activations
+  float* a_scale = nullptr;            // [Tm] per-token scales
+  int max_k = 0;
   int* d_err = nullptr;
   int max_batch = 0;
 
@@ -236,10 +243,23 @@ struct Scope {
 };
 
 // ---- GEMM dispatch -------------------------------------------------------------
-// C[M,N] = X[M,K] . W[N,K]^T. tcgen05 path for the bf16 engine, plain FMA otherwise.
+// C[M,N] = X[M,K] . W[N,K]^T. bf16 engine: tcgen05 path (bf16 operands, or e4m3 operands when
+// `fw` is given: the activations are quantised per token first, Engine::fp8_gemm,
+// native/src/engine.rs:4144-4296); plain FMA otherwise.
 template <typename T>
-int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, void* C, int M, int N, int K,
-         int ldc, int epi) {
+int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw, void* C, int M,
+         int N, int K, int ldc, int epi) {
+  if (fw && e->bf && e->o.gemm_path == 0 && tc_fp8_shape_ok(M, N, K)) {
+    {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 3.0 * M * (double)K, 1);
+      CK(e, launch_quant_fp8_rows<bf16>((const bf16*)X, (size_t)K, e->aq, e->a_scale, M, K, 1.0f, e->stream), "fp8 activation quantisation");
+    }
+    TcTensorMap ta;
+    if (tc_make_tmap_fp8_a(&ta, e->aq, M, K)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an fp8 activation operand");
+    Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
+    CK(e, tc_gemm_fp8_launch(&ta, &fw->tm, C, M, N, K, ldc, epi, e->a_scale, fw->scale, e->sm_count, e->d_err, e->stream), "tcgen05 fp8 gemm");
+    return DCD_OK;
+  }
   Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
   if (e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K)) {
     CK(e, tc_gemm_launch(tmA, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream), "tcgen05 gemm");
@@ -265,6 +285,9 @@ int run_layers(dcd_engine* e, const Pass& p) {
   const int nk = c.gdn_k_heads, nv = c.gdn_v_heads, dk = c.gdn_dk, dv = c.gdn_dv;
   cudaStream_t s = e->stream;
   const bool tc = e->bf && e->o.gemm_path == 0;
+  // FP8 only in question passes with enough rows; capture and the per-row reference stay bf16
+  // (native/src/engine.rs:4321-4326, fp8_min_rows :246-257)
+  const bool q8 = e->fp8 && tc && p.mode == 1 && p.T >= e->o.fp8_min_rows;
   TcTensorMap tm_h, tm_A, tm_B, tm_act;
   if (tc) {
     if (tc_make_tmap_a(&tm_h, e->h, T_, H) || tc_make_tmap_a(&tm_A, e->bufA, T_, heads * hd) ||
@@ -279,7 +302,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
     }
     if (w.full) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
@@ -315,10 +338,10 @@ int run_layers(dcd_engine* e, const Pass& p) {
                                    e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
         }
       }
-      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, e->mix, T_, H, heads * hd, H, 0);
+      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, e->mix, T_, H, heads * hd, H, 0);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, e->big, T_, e->gin_n, H, e->gin_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       if (p.mode == 0) {
@@ -356,7 +379,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
         CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
                                       c.rms_eps, s), "rmsnorm_gated");
       }
-      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, e->mix, T_, H, e->vd, H, 0);
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, e->mix, T_, H, e->vd, H, 0);
       if (rc) return rc;
     }
     {
@@ -365,15 +388,15 @@ int run_layers(dcd_engine* e, const Pass& p) {
          "add_rmsnorm");
     }
     if (tc) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, e->act, T_, e->gu_rows, H, e->I, 1);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
       if (rc) return rc;
       Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->I * e->esz * 3.0, 1);
       CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
-    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, e->mix, T_, H, e->I, H, 0);
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, e->mix, T_, H, e->I, H, 0);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
@@ -421,7 +444,31 @@ int run_pass(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t*
   return DCD_OK;
 }
 
+// (Re)build the e4m3 weight images from the bf16 weights: per-output-row scale, as
+// weights.rs:472-492 does with quant_fp8_bf16 at load time.
+int ensure_fp8_weights(dcd_engine* e) {
+  if (!e->fp8 || !e->fp8_dirty) return DCD_OK;
+  auto q = [&](const void* w, LayerW::Fp8W& f, int n, int k) -> cudaError_t {
+    e->launches += 1;
+    return launch_quant_fp8_rows<bf16>((const bf16*)w, (size_t)k, f.q, f.scale, n, k, 1.0f, e->stream);
+  };
+  for (LayerW& w : e->layers) {
+    CK(e, q(w.w_gu, w.f_gu, e->gu_rows, e->H), "fp8 weight quantisation");
+    CK(e, q(w.w_down, w.f_down, e->H, e->I), "fp8 weight quantisation");
+    if (w.full) {
+      CK(e, q(w.w_qkv, w.f_qkv, e->qkv_n, e->H), "fp8 weight quantisation");
+      CK(e, q(w.w_o, w.f_o, e->H, e->c.heads * e->c.head_dim), "fp8 weight quantisation");
+    } else {
+      CK(e, q(w.w_gin, w.f_gin, e->gin_n, e->H), "fp8 weight quantisation");
+      CK(e, q(w.w_out, w.f_out, e->H, e->vd), "fp8 weight quantisation");
+    }
+  }
+  e->fp8_dirty = false;
+  return DCD_OK;
+}
+
 int run_pass_any(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t* d_lens, int pos_start, float* d_out) {
+  if (int rc = ensure_fp8_weights(e)) return rc;
   return e->bf ? run_pass<bf16>(e, p, d_ids, d_lens, pos_start, d_out) : run_pass<float>(e, p, d_ids, d_lens, pos_start, d_out);
 }
 
@@ -517,7 +564,9 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (c.dtype != 0 && c.dtype != 1) return fail(nullptr, DCD_E_INVALID, "dtype must be 0 (f32) or 1 (bf16)");
   dcd_options o = {};
   if (opt) o = *opt;
-  if (o.precision != 0) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (bf16/f32 only)", o.precision);
+  if (o.precision != 0 && o.precision != 2) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (0 = config dtype, 2 = fp8)", o.precision);
+  if (o.precision == 2 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "fp8 precision needs a bf16 engine (dtype 1)");
+  if (o.fp8_min_rows <= 0) o.fp8_min_rows = 512;
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -585,6 +634,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (e->bf) CRE(tc_gemm_prepare_device(), "tcgen05 GEMM shared-memory attribute");
   e->attn_tc = e->bf && o.attn_path == 0 && attn_tc_supported(c.heads, c.kv_heads, c.head_dim);
   if (e->attn_tc) CRE(attn_tc_prepare_device(), "tcgen05 attention shared-memory attribute");
+  e->fp8 = o.precision == 2 && o.gemm_path == 0;
   e->gdn_chunked = e->bf && o.gdn_path == 0 && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
@@ -613,6 +663,19 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
       CRA(w.gnorm, c.gdn_dv * es, true, &e->weight_bytes);
       CRA(w.A_log, c.gdn_v_heads * 4, true, &e->weight_bytes);
       CRA(w.dt_bias, c.gdn_v_heads * 4, true, &e->weight_bytes);
+    }
+    if (e->fp8) {
+      auto mk = [&](LayerW::Fp8W& f, size_t n, size_t k) -> int {
+        int rc = dev_alloc(e, reinterpret_cast<void**>(&f.q), n * k, false, &e->weight_bytes);
+        if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&f.scale), n * 4, false, &e->weight_bytes);
+        if (!rc && tc_make_tmap_fp8_b(&f.tm, f.q, n, k)) rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an fp8 weight operand");
+        return rc;
+      };
+      int rc = mk(w.f_gu, e->gu_rows, H);
+      if (!rc) rc = mk(w.f_down, H, e->I);
+      if (!rc && w.full) { rc = mk(w.f_qkv, e->qkv_n, H); if (!rc) rc = mk(w.f_o, H, (size_t)c.heads * c.head_dim); }
+      if (!rc && !w.full) { rc = mk(w.f_gin, e->gin_n, H); if (!rc) rc = mk(w.f_out, H, e->vd); }
+      if (rc) { g_create_error = e->err; dcd_engine_destroy(e); return rc; }
     }
     if (e->bf) {
       int bad = tc_make_tmap_b(&w.tm_gu, w.w_gu, e->gu_rows, H) | tc_make_tmap_b(&w.tm_down, w.w_down, H, e->I);
@@ -665,6 +728,13 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRA(e->bufB, Tm * aw * es, false, ws);
   CRA(e->conv, Tm * (size_t)e->conv_dim * es, false, ws);
   CRA(e->act, Tm * (size_t)e->I * es, false, ws);
+  e->max_k = e->I;
+  if (e->H > e->max_k) e->max_k = e->H;
+  if ((int)aw > e->max_k) e->max_k = (int)aw;
+  if (e->fp8) {
+    CRA(e->aq, Tm * (size_t)e->max_k, false, ws);
+    CRA(e->a_scale, Tm * 4, false, ws);
+  }
   CRA(e->qf, Tm * (size_t)c.gdn_k_heads * c.gdn_dk * 4, false, ws);
   CRA(e->kf, Tm * (size_t)c.gdn_k_heads * c.gdn_dk * 4, false, ws);
   CRA(e->g, Tm * (size_t)c.gdn_v_heads * 4, false, ws);
@@ -757,6 +827,7 @@ int dcd_engine_init_random(dcd_engine* e, uint64_t seed) {
   }
   CK(e, cudaStreamSynchronize(e->stream), "init_random sync");
   e->weights_ready = true;
+  e->fp8_dirty = true;
   return DCD_OK;
 }
 
@@ -787,7 +858,7 @@ int dcd_engine_load_tensor(dcd_engine* e, int layer, int kind, const float* host
   if (ce != cudaSuccess) rc = cuda_fail(e, ce, "load_tensor");
   cudaFree(tmp);
   if (tmpT) cudaFree(tmpT);
-  if (rc == DCD_OK) e->weights_ready = true;
+  if (rc == DCD_OK) { e->weights_ready = true; e->fp8_dirty = true; }
   return rc;
 }
 

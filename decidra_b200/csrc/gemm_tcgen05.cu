@@ -45,19 +45,33 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor, kind::f16: D f32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both
-// K-major, N>>3 at [17,23), M>>4 at [24,29).
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor: D f32 (bit 4); A/B format at bits 7 and 10 (kind::f16: 1 = bf16;
+// kind::f8f6f4: 0 = e4m3); both K-major; N>>3 at [17,23), M>>4 at [24,29).
+constexpr uint32_t IDESC_BF16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_E4M3 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
+// ESZ 2: bf16 operands (kind::f16, K = 16 per instruction); ESZ 1: e4m3 operands (kind::f8f6f4, K = 32).
+template <int ESZ>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d),
-      "l"(da), "l"(db), "r"(IDESC), "r"(accumulate)
-      : "memory");
+  if (ESZ == 2) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(IDESC_BF16), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(IDESC_E4M3), "r"(accumulate)
+        : "memory");
+  }
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -76,10 +90,14 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // EPI 0: C[M,N] bf16. EPI 1: SwiGLU — W rows are interleaved per 256-row tile as
 // [128 gate rows | 128 up rows]; the kernel writes act[M, N/2] = bf16(bf16(silu(bf16(gate))) * bf16(up))
 // (silu_mul_bf16, native/kernels/kernels.cu:492-501, applied to the bf16-rounded GEMM outputs).
-template <int EPI>
+// ESZ 1 (e4m3 operands): the accumulator is scaled by w_scale[column] * a_scale[row] before rounding
+// (scale_fp8_gemm_bf16, native/kernels/kernels.cu:208-220); ESZ 2 ignores the scale pointers.
+template <int EPI, int ESZ>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
-                    int M, int N, int K, int ldc, int* __restrict__ err) {
+                    int M, int N, int K, int ldc, const float* __restrict__ a_scale, const float* __restrict__ w_scale,
+                    int* __restrict__ err) {
+  constexpr int BKE = 128 / ESZ;  // K elements per 128-byte swizzled row
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
@@ -97,7 +115,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_tiles = num_m * num_n;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb = (K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -132,8 +150,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
-          tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BK, m_idx * BM);
-          tma_load_2d(a_dst + A_BYTES, &tmB, full_bar(stage), kb * BK, n_idx * BN);
+          tma_load_2d(a_dst, &tmA, full_bar(stage), kb * BKE, m_idx * BM);
+          tma_load_2d(a_dst + A_BYTES, &tmB, full_bar(stage), kb * BKE, n_idx * BN);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -153,9 +171,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
           const uint64_t da = make_desc(a_src), db = make_desc(a_src + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advance 32 bytes (16 bf16) along K inside the swizzled 128-byte row
-            umma(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            // advance 32 bytes (one instruction's K) inside the swizzled 128-byte row
+            umma<ESZ>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -180,6 +198,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m_idx * BM + lane_base + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(acc * BN);
+      const float rs = (ESZ == 1 && row < M) ? a_scale[row] : 1.0f;
       if (EPI == 0) {
         bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
 #pragma unroll 1
@@ -192,11 +211,20 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int v = 0; v < 4; ++v) {
               const int col = n_idx * BN + c * 32 + v * 8;
               if (col + 8 <= N) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                if (ESZ == 1) {
+                  const float4 w0 = __ldg(reinterpret_cast<const float4*>(w_scale + col));
+                  const float4 w1 = __ldg(reinterpret_cast<const float4*>(w_scale + col + 4));
+                  f[0] = f[0] * w0.x * rs; f[1] = f[1] * w0.y * rs; f[2] = f[2] * w0.z * rs; f[3] = f[3] * w0.w * rs;
+                  f[4] = f[4] * w1.x * rs; f[5] = f[5] * w1.y * rs; f[6] = f[6] * w1.z * rs; f[7] = f[7] * w1.w * rs;
+                }
                 uint4 o;
-                o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                o.x = pack_bf16(f[0], f[1]);
+                o.y = pack_bf16(f[2], f[3]);
+                o.z = pack_bf16(f[4], f[5]);
+                o.w = pack_bf16(f[6], f[7]);
                 *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
               }
             }
@@ -217,10 +245,20 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const int col = n_idx * (BN / 2) + c * 32 + v * 8;
               if (col + 8 <= ldc) {  // ldc = true output width I (the interleaved N/2 may be padded)
                 float a[8];
+                float wg[8], wu[8];
+                if (ESZ == 1) {
+                  const int gcol = n_idx * BN + c * 32 + v * 8;  // interleaved row index of the gate weights
+                  *reinterpret_cast<float4*>(&wg[0]) = __ldg(reinterpret_cast<const float4*>(w_scale + gcol));
+                  *reinterpret_cast<float4*>(&wg[4]) = __ldg(reinterpret_cast<const float4*>(w_scale + gcol + 4));
+                  *reinterpret_cast<float4*>(&wu[0]) = __ldg(reinterpret_cast<const float4*>(w_scale + gcol + BN / 2));
+                  *reinterpret_cast<float4*>(&wu[4]) = __ldg(reinterpret_cast<const float4*>(w_scale + gcol + BN / 2 + 4));
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  const float gg = Ty<bf16>::rnd(__uint_as_float(g[v * 8 + j]));
-                  const float uu = Ty<bf16>::rnd(__uint_as_float(u[v * 8 + j]));
+                  float ga = __uint_as_float(g[v * 8 + j]), ua = __uint_as_float(u[v * 8 + j]);
+                  if (ESZ == 1) { ga = ga * wg[j] * rs; ua = ua * wu[j] * rs; }
+                  const float gg = Ty<bf16>::rnd(ga);
+                  const float uu = Ty<bf16>::rnd(ua);
                   a[j] = Ty<bf16>::rnd(silu_f(gg)) * uu;
                 }
                 uint4 o;
@@ -324,8 +362,10 @@ int tc_make_tmap_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K) { re
 bool tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 8) == 0 && (N % 8) == 0; }
 
 cudaError_t tc_gemm_prepare_device() {
-  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
-  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(tcg::gemm_bf16_tc_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tcg::SMEM_BYTES));
   return cudaSuccess;
 }
 
@@ -333,12 +373,39 @@ cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void*
                            int sm_count, int* err, cudaStream_t stream) {
   const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
-  if (epi == 0) {
-    tcg::gemm_bf16_tc_kernel<0><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(
-        *reinterpret_cast<const CUtensorMap*>(tmA), *reinterpret_cast<const CUtensorMap*>(tmB), (bf16*)C, M, N, K, ldc, err);
-  } else {
-    tcg::gemm_bf16_tc_kernel<1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(
-        *reinterpret_cast<const CUtensorMap*>(tmA), *reinterpret_cast<const CUtensorMap*>(tmB), (bf16*)C, M, N, K, ldc, err);
-  }
+  const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
+  const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, err);
+  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, err);
   return cudaGetLastError();
 }
+
+// e4m3 operands (1 byte per element; maps made with tc_make_tmap_fp8_*), bf16 output scaled by
+// w_scale[n] * a_scale[m].
+cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
+                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream) {
+  const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
+  const int grid = num_tiles < sm_count ? num_tiles : sm_count;
+  const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
+  const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, err);
+  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, err);
+  return cudaGetLastError();
+}
+
+// Row-major [rows, cols] e4m3 (1 byte) matrix, box = box_rows x 128 columns, 128-byte swizzle.
+static int make_tmap_u8(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  auto fn = tcg::encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+int tc_make_tmap_fp8_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K) { return make_tmap_u8(out, X, M, K, tcg::BM); }
+int tc_make_tmap_fp8_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K) { return make_tmap_u8(out, W, N, K, tcg::BN); }
+bool tc_fp8_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 16) == 0 && (N % 8) == 0; }

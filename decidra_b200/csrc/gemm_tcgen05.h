@@ -21,3 +21,11 @@ cudaError_t tc_gemm_prepare_device();
 // epi 0: C[M,N] (row stride ldc). epi 1: SwiGLU over gate/up-interleaved weights, C[M,N/2].
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
                            int sm_count, int* err, cudaStream_t stream);
+
+// e4m3 (FP8) operand form: X[M,K] and W[N,K] hold one byte per element; the f32 accumulator is
+// scaled by w_scale[n] * a_scale[m] before rounding to bf16. Needs K % 16 == 0, N % 8 == 0.
+int tc_make_tmap_fp8_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K);
+int tc_make_tmap_fp8_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K);
+bool tc_fp8_shape_ok(int M, int N, int K);
+cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
+                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream);

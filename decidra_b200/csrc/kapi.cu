@@ -23,6 +23,20 @@ int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int 
   return rc_of(tc_gemm_launch(&ta, &tb, C, M, N, K, ldc, epi, sm_count, err, S(stream)));
 }
 
+int dcd_k_gemm_fp8_tc(const void* Xq, const void* Wq, void* C, int M, int N, int K, int ldc, int epi, const float* a_scale,
+                      const float* w_scale, int sm_count, int* err, void* stream) {
+  if (!tc_fp8_shape_ok(M, N, K) || sm_count <= 0 || (epi != 0 && epi != 1) || !a_scale || !w_scale) return DCD_E_INVALID;
+  TcTensorMap ta, tb;
+  if (tc_make_tmap_fp8_a(&ta, Xq, M, K) || tc_make_tmap_fp8_b(&tb, Wq, N, K)) return DCD_E_CUDA;
+  if (tc_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  return rc_of(tc_gemm_fp8_launch(&ta, &tb, C, M, N, K, ldc, epi, a_scale, w_scale, sm_count, err, S(stream)));
+}
+
+int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, float* scales, int rows, int cols, float clip, int dtype, void* stream) {
+  return DISPATCH(dtype, launch_quant_fp8_rows<float>((const float*)x, x_stride, (uint8_t*)out, scales, rows, cols, clip, S(stream)),
+                  launch_quant_fp8_rows<bf16>((const bf16*)x, x_stride, (uint8_t*)out, scales, rows, cols, clip, S(stream)));
+}
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

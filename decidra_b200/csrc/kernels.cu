@@ -6,6 +6,8 @@
 // Each kernel names the reference code (paths inside juanqui/decidra) whose arithmetic it
 // reproduces. All are templated on the storage type T (float for the f32 engine, bf16 for
 // the bf16 engine); Ty<T>::rnd() rounds at the points where the reference rounds through bf16.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -1088,3 +1090,74 @@ cudaError_t launch_place_rows(const T* src, T* dst, size_t rows, int cols, int m
 }
 template cudaError_t launch_place_rows<float>(const float*, float*, size_t, int, int, int, int, bool, cudaStream_t);
 template cudaError_t launch_place_rows<bf16>(const bf16*, bf16*, size_t, int, int, int, int, bool, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// Per-row symmetric FP8 E4M3 quantisation (activations per token, weights per output row):
+// scale = max(absmax * clip, 1e-10) / 448; q = e4m3_satfinite(x / scale).
+// quant_fp8_per_token_bf16, native/kernels/kernels.cu:182-205. x rows may be strided.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) quant_fp8_rows_kernel(const T* __restrict__ x, size_t x_stride, uint8_t* __restrict__ out,
+                                                             float* __restrict__ scales, int cols, float clip) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const T* xr = x + (size_t)row * x_stride;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, fabsf(Ty<T>::ld(xr + i)));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+  t = warp_max(t);
+  const float scale = fmaxf(t * clip, 1e-10f) / 448.f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  uint8_t* orow = out + (size_t)row * cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x)
+    orow[i] = (uint8_t)__nv_cvt_float_to_fp8(Ty<T>::ld(xr + i) / scale, __NV_SATFINITE, __NV_E4M3);
+}
+// bf16, cols % 8 == 0: 16-byte loads, 8-byte stores.
+__global__ void __launch_bounds__(256) quant_fp8_rows_vec_kernel(const bf16* __restrict__ x, size_t x_stride, uint8_t* __restrict__ out,
+                                                                 float* __restrict__ scales, int cols, float clip) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * x_stride);
+  const int n8 = cols >> 3;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < n8; i += 256) {
+    float f[8];
+    unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.f;
+  t = warp_max(t);
+  const float scale = fmaxf(t * clip, 1e-10f) / 448.f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  uint2* orow = reinterpret_cast<uint2*>(out + (size_t)row * cols);
+  for (int i = threadIdx.x; i < n8; i += 256) {
+    float f[8];
+    unpack8(xr[i], f);
+    uint32_t w[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(f[j] / scale, __NV_SATFINITE, __NV_E4M3) << (8 * (j & 3));
+    orow[i] = make_uint2(w[0], w[1]);
+  }
+}
+template <typename T>
+cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, float* scales, int rows, int cols, float clip, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if constexpr (sizeof(T) == 2) {
+    if ((cols % 8) == 0 && (x_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 8) == 0) {
+      quant_fp8_rows_vec_kernel<<<rows, 256, 0, s>>>(x, x_stride, out, scales, cols, clip);
+      return cudaGetLastError();
+    }
+  }
+  quant_fp8_rows_kernel<T><<<rows, 256, 0, s>>>(x, x_stride, out, scales, cols, clip);
+  return cudaGetLastError();
+}
+template cudaError_t launch_quant_fp8_rows<float>(const float*, size_t, uint8_t*, float*, int, int, float, cudaStream_t);
+template cudaError_t launch_quant_fp8_rows<bf16>(const bf16*, size_t, uint8_t*, float*, int, int, float, cudaStream_t);

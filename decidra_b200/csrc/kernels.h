@@ -68,3 +68,7 @@ template <typename T>
 cudaError_t launch_gdn_chunked(const float* qf, const float* kf, const T* conv, int conv_stride, const float* g, const float* beta,
                                const float* seed, float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int dk, int dv,
                                bool few_sequences, cudaStream_t s);
+
+// Per-row FP8 E4M3 quantisation: scale[row] = max(absmax*clip, 1e-10)/448, out = e4m3(x/scale).
+template <typename T>
+cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, float* scales, int rows, int cols, float clip, cudaStream_t s);

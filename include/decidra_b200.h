@@ -59,7 +59,9 @@ typedef struct dcd_model_config {
  * (src/native_backend.rs:81-95) and the env caps read in
  * Engine::state_once_batch_rows (native/src/engine.rs:4870-4881). Zero = default. */
 typedef struct dcd_options {
-  int32_t precision;        /* 0 = the config dtype; 1 = w4a16_g128; 2 = fp8; 3 = nvfp4 (1..3 not built yet: DCD_E_UNSUPPORTED) */
+  int32_t precision;        /* 0 = the config dtype; 2 = fp8 (e4m3 GEMMs, per-token x per-output-row scales, in question passes
+                               of >= fp8_min_rows rows; capture stays bf16 — Engine::fp8_gemm, native/src/engine.rs:4144-4296);
+                               1 = w4a16_g128 and 3 = nvfp4 are not built yet: DCD_E_UNSUPPORTED */
   int32_t max_pass_tokens;  /* workspace rows; also the longest state that can be captured. default 16384 */
   int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
   int64_t max_keys;
@@ -68,7 +70,8 @@ typedef struct dcd_options {
   int32_t attn_path;        /* 0 = tcgen05 attention where the shape allows (bf16, head_dim 256, 6:1 GQA); 1 = plain FMA attention */
   int32_t max_positions;    /* RoPE table length; default 65536 */
   int32_t gdn_path;         /* 0 = chunked tensor-core gated delta rule where the shape allows (bf16, dk 128); 1 = sequential f32 */
-  int32_t reserved[7];
+  int32_t fp8_min_rows;     /* fp8_min_rows() of native/src/engine.rs:246-257; default 512 */
+  int32_t reserved[6];
 } dcd_options;
 
 typedef struct dcd_info {
@@ -239,6 +242,15 @@ DCD_API int dcd_pack(dcd_engine* e, const int32_t* lens, size_t B, int32_t pos_s
  * `err` is a device int the kernel sets non-zero when a bounded barrier wait gives up. */
 DCD_API int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int epi, int sm_count,
                                int* err, void* stream);
+/* FP8 form: Xq[M,K] and Wq[N,K] are e4m3 bytes (dcd_k_quant_fp8_rows), C = bf16(acc * w_scale[n] * a_scale[m])
+ * (cuBLASLt E4M3 GEMM + scale_fp8_gemm_bf16, native/src/engine.rs:4179-4296, native/kernels/kernels.cu:208-220).
+ * Needs K % 16 == 0 and N % 8 == 0. epi as above (w_scale then indexes the interleaved rows). */
+DCD_API int dcd_k_gemm_fp8_tc(const void* Xq, const void* Wq, void* C, int M, int N, int K, int ldc, int epi, const float* a_scale,
+                              const float* w_scale, int sm_count, int* err, void* stream);
+/* quant_fp8_per_token_bf16 (native/kernels/kernels.cu:182-205): per row scale = max(absmax*clip,1e-10)/448,
+ * out = e4m3_satfinite(x/scale). x is T [rows, cols] with row stride x_stride (elements). */
+DCD_API int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, float* scales, int rows, int cols, float clip, int dtype,
+                                 void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

@@ -182,6 +182,10 @@ class Oracle:
             raise ValueError(f"oracle decision_logits_split failed rc={rc}")
         return out
 
+    def set_precision(self, precision: int, fp8_min_rows: int = 0) -> None:
+        """precision 2 = FP8 GEMMs in question passes of >= fp8_min_rows rows (default 512)."""
+        lib().orc_set_precision(self.h, precision, fp8_min_rows)
+
     def tap_enable(self, on: bool = True) -> None:
         lib().orc_tap_enable(self.h, int(on))
 
@@ -211,6 +215,31 @@ def k_gemm(X, W, bf16: bool) -> np.ndarray:
     N = W.shape[0]
     out = np.empty((T, N), dtype=np.float32)
     lib().orc_k_gemm(_fp(X), _fp(W), _fp(out), T, N, K, int(bf16))
+    return out
+
+
+def k_quant_fp8_rows(x, clip: float = 1.0):
+    """Returns (e4m3 codes uint8 [rows, cols], scales f32 [rows])."""
+    x = _f32(x)
+    codes = np.empty(x.shape, dtype=np.uint8)
+    scales = np.empty(x.shape[0], dtype=np.float32)
+    lib().orc_k_quant_fp8_rows(_fp(x), x.shape[0], x.shape[1], C.c_float(clip), codes.ctypes.data_as(C.POINTER(C.c_uint8)), _fp(scales))
+    return codes, scales
+
+
+def e4m3_to_f32(codes) -> np.ndarray:
+    lib().orc_k_e4m3_to_f32.restype = C.c_float
+    lib().orc_k_e4m3_to_f32.argtypes = [C.c_uint8]
+    table = np.array([lib().orc_k_e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+    return table[np.asarray(codes, dtype=np.uint8)]
+
+
+def k_gemm_fp8(X, W, bf16: bool = True) -> np.ndarray:
+    X, W = _f32(X), _f32(W)
+    T, K = X.shape
+    N = W.shape[0]
+    out = np.empty((T, N), dtype=np.float32)
+    lib().orc_k_gemm_fp8(_fp(X), _fp(W), _fp(out), T, N, K, int(bf16))
     return out
 
 

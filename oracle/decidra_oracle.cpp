@@ -205,6 +205,79 @@ static void gemm(const float* X, const float* W, float* C, int T, int N, int K, 
   }
 }
 
+// ---------------------------------------------------------------------------
+// FP8 E4M3 (satfinite, round-to-nearest-even): host twin of
+// __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3) as used by to_fp8_e4m3,
+// native/kernels/kernels.cu:174-179. Format: 1-4-3, bias 7, max 448, subnormal step 2^-9,
+// no infinities (0x7f/0xff are NaN).
+// ---------------------------------------------------------------------------
+static inline uint8_t f32_to_e4m3(float x) {
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  const uint8_t sign = (uint8_t)((u >> 24) & 0x80);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint8_t)(sign | 0x7f);  // NaN
+  float a = fabsf(x);
+  if (a >= 448.0f) return (uint8_t)(sign | 0x7e);                      // saturate (also +-inf)
+  if (a < 0.015625f) {                                                 // below the smallest normal 2^-6: step 2^-9
+    const float q = nearbyintf(a * 512.0f);                            // RNE in the default rounding mode
+    return (uint8_t)(sign | (uint8_t)q);                               // q == 8 encodes the smallest normal
+  }
+  int e;
+  const float m = frexpf(a, &e);        // a = m * 2^e, m in [0.5, 1)
+  const int E = e - 1;                  // a = (2m) * 2^E, 2m in [1, 2)
+  float q = nearbyintf((2.0f * m - 1.0f) * 8.0f);
+  int Eb = E + 7;
+  if (q == 8.0f) { q = 0.0f; Eb += 1; }
+  if (Eb > 15 || (Eb == 15 && q > 6.0f)) return (uint8_t)(sign | 0x7e);
+  return (uint8_t)(sign | (uint8_t)(Eb << 3) | (uint8_t)q);
+}
+static inline float e4m3_to_f32(uint8_t c) {
+  const int Eb = (c >> 3) & 0xf, mant = c & 7;
+  float v = Eb == 0 ? (float)mant * (1.0f / 512.0f) : ldexpf(1.0f + (float)mant / 8.0f, Eb - 7);
+  return (c & 0x80) ? -v : v;
+}
+// quant_fp8_per_token_bf16, native/kernels/kernels.cu:182-205: per-row scale and codes.
+static void quant_fp8_rows(const float* x, int rows, int cols, float clip, uint8_t* codes, float* scales) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const float* xr = x + (size_t)r * cols;
+    float m = 0.f;
+    for (int i = 0; i < cols; ++i) m = fmaxf(m, fabsf(xr[i]));
+    const float scale = fmaxf(m * clip, 1e-10f) / 448.f;
+    scales[r] = scale;
+    for (int i = 0; i < cols; ++i) codes[(size_t)r * cols + i] = f32_to_e4m3(xr[i] / scale);
+  }
+}
+// FP8 GEMM: Engine::fp8_gemm (native/src/engine.rs:4144-4296): activations quantised per token,
+// weights per output row (weights.rs:472-492), f32 accumulation of the e4m3 products,
+// out = R(acc * w_scale[n] * a_scale[m]) (scale_fp8_gemm_bf16, kernels.cu:208-220).
+struct Fp8Image { std::vector<float> vals, scale; };
+static void make_fp8_image(const float* W, int N, int K, Fp8Image& img) {
+  std::vector<uint8_t> codes((size_t)N * K);
+  img.scale.resize(N);
+  quant_fp8_rows(W, N, K, 1.0f, codes.data(), img.scale.data());
+  img.vals.resize(codes.size());
+  for (size_t i = 0; i < codes.size(); ++i) img.vals[i] = e4m3_to_f32(codes[i]);
+}
+static void gemm_fp8(const float* X, const Fp8Image& Wq, float* C, int T, int N, int K, Round R) {
+  std::vector<uint8_t> codes((size_t)T * K);
+  std::vector<float> xs(T), xv((size_t)T * K), acc((size_t)T * N);
+  quant_fp8_rows(X, T, K, 1.0f, codes.data(), xs.data());
+  for (size_t i = 0; i < codes.size(); ++i) xv[i] = e4m3_to_f32(codes[i]);
+  gemm(xv.data(), Wq.vals.data(), acc.data(), T, N, K, Round{false});
+  for (int t = 0; t < T; ++t)
+    for (int n = 0; n < N; ++n) C[(size_t)t * N + n] = R(acc[(size_t)t * N + n] * Wq.scale[n] * xs[t]);
+}
+ORC_API void orc_k_gemm_fp8(const float* X, const float* W, float* C, int T, int N, int K, int bf) {
+  Fp8Image img;
+  make_fp8_image(W, N, K, img);
+  gemm_fp8(X, img, C, T, N, K, Round{bf != 0});
+}
+ORC_API void orc_k_quant_fp8_rows(const float* x, int rows, int cols, float clip, uint8_t* codes, float* scales) {
+  quant_fp8_rows(x, rows, cols, clip, codes, scales);
+}
+ORC_API float orc_k_e4m3_to_f32(uint8_t c) { return e4m3_to_f32(c); }
+
 // RMSNorm: native/kernels/kernels.cu:406-426 (zero_centered → weight 1+w).
 static void rmsnorm(const float* x, const float* w, float* out, int rows, int cols, float eps, bool zero_centered, Round R) {
 #pragma omp parallel for schedule(static)
@@ -410,6 +483,10 @@ struct Oracle {
   std::vector<float> final_norm, readout;
   std::map<std::string, std::vector<float>> taps;
   bool tap_on = false;
+  // precision 2: FP8 GEMMs in question passes of >= fp8_min_rows rows (engine.rs:4321-4326, :246-257)
+  int precision = 0, fp8_min_rows = 512;
+  bool q8_now = false;
+  std::map<const float*, Fp8Image> fp8_cache;
   int conv_dim() const { return 2 * c.gdn_k_heads * c.gdn_dk + c.gdn_v_heads * c.gdn_dv; }
 };
 
@@ -486,6 +563,21 @@ static void tap(Oracle& o, const std::string& name, const std::vector<float>& v)
   if (o.tap_on) o.taps[name] = v;
 }
 
+// One linear layer of the model: bf16/f32 GEMM, or the FP8 path when it is active for this pass.
+static void lin(Oracle& o, const float* X, const std::vector<float>& W, float* C, int T, int N, int K) {
+  if (!o.q8_now) { gemm(X, W.data(), C, T, N, K, o.R); return; }
+  auto it = o.fp8_cache.find(W.data());
+  if (it == o.fp8_cache.end()) {
+    it = o.fp8_cache.emplace(W.data(), Fp8Image{}).first;
+    make_fp8_image(W.data(), N, K, it->second);
+  }
+  gemm_fp8(X, it->second, C, T, N, K, o.R);
+}
+ORC_API void orc_set_precision(Oracle* o, int precision, int fp8_min_rows) {
+  o->precision = precision;
+  if (fp8_min_rows > 0) o->fp8_min_rows = fp8_min_rows;
+}
+
 // Embedding gather with vocabulary bound check (error, not clamp):
 // native/src/engine.rs:1364-1439, native/kernels/kernels.cu:84-94.
 static int embed(const Oracle& o, const uint32_t* ids, int T, std::vector<float>& x) {
@@ -520,9 +612,9 @@ static void full_attention(Oracle& o, const LayerW& w, const std::vector<float>&
   const Round R = o.R;
   const int H = c.hidden, heads = c.heads, kv = c.kv_heads, hd = c.head_dim, rhalf = c.rotary_dim / 2;
   std::vector<float> qg((size_t)T * heads * 2 * hd), kk((size_t)T * kv * hd), vv((size_t)T * kv * hd);
-  gemm(h.data(), w.q.data(), qg.data(), T, heads * 2 * hd, H, R);
-  gemm(h.data(), w.k.data(), kk.data(), T, kv * hd, H, R);
-  gemm(h.data(), w.v.data(), vv.data(), T, kv * hd, H, R);
+  lin(o, h.data(), w.q, qg.data(), T, heads * 2 * hd, H);
+  lin(o, h.data(), w.k, kk.data(), T, kv * hd, H);
+  lin(o, h.data(), w.v, vv.data(), T, kv * hd, H);
   // split_q_gate: native/kernels/kernels.cu:516-529
   std::vector<float> q((size_t)T * heads * hd), gate((size_t)T * heads * hd);
   for (int t = 0; t < T; ++t)
@@ -569,7 +661,7 @@ static void full_attention(Oracle& o, const LayerW& w, const std::vector<float>&
   std::vector<float> gated(attn.size());
   for (size_t i = 0; i < attn.size(); ++i) gated[i] = R(attn[i] * R(1.0f / (1.0f + expf(-gate[i]))));
   mix.resize((size_t)T * H);
-  gemm(gated.data(), w.o.data(), mix.data(), T, H, heads * hd, R);
+  lin(o, gated.data(), w.o, mix.data(), T, H, heads * hd);
 }
 
 // The GDN mixer. seeds: per segment either (state, hist) from a cache (state-once),
@@ -585,10 +677,10 @@ static void gdn_mixer(Oracle& o, const LayerW& w, const std::vector<float>& h, i
   const int H = c.hidden, nk = c.gdn_k_heads, nv = c.gdn_v_heads, dk = c.gdn_dk, dv = c.gdn_dv;
   const int cd = o.conv_dim(), vd = nv * dv;
   std::vector<float> qkv((size_t)T * cd), z((size_t)T * vd), b((size_t)T * nv), a((size_t)T * nv);
-  gemm(h.data(), w.in_qkv.data(), qkv.data(), T, cd, H, R);
-  gemm(h.data(), w.in_z.data(), z.data(), T, vd, H, R);
-  gemm(h.data(), w.in_b.data(), b.data(), T, nv, H, R);
-  gemm(h.data(), w.in_a.data(), a.data(), T, nv, H, R);
+  lin(o, h.data(), w.in_qkv, qkv.data(), T, cd, H);
+  lin(o, h.data(), w.in_z, z.data(), T, vd, H);
+  lin(o, h.data(), w.in_b, b.data(), T, nv, H);
+  lin(o, h.data(), w.in_a, a.data(), T, nv, H);
   tap(o, "gdn_in_proj_qkv", qkv);
   if (hist_out) {
     hist_out->assign((size_t)3 * cd, 0.f);
@@ -615,7 +707,7 @@ static void gdn_mixer(Oracle& o, const LayerW& w, const std::vector<float>& h, i
   std::vector<float> normed((size_t)T * vd);
   rmsnorm_gated(core.data(), z.data(), w.gnorm.data(), normed.data(), T * nv, dv, c.rms_eps, R);
   mix.resize((size_t)T * H);
-  gemm(normed.data(), w.out.data(), mix.data(), T, H, vd, R);
+  lin(o, normed.data(), w.out, mix.data(), T, H, vd);
 }
 
 // MLP: native/src/engine.rs:2794-2885; SwiGLU elementwise native/kernels/kernels.cu:492-501.
@@ -623,15 +715,15 @@ static void mlp(Oracle& o, const LayerW& w, const std::vector<float>& h2, int T,
   const int H = o.c.hidden, I = o.c.intermediate;
   const Round R = o.R;
   std::vector<float> gt((size_t)T * I), up((size_t)T * I);
-  gemm(h2.data(), w.gate.data(), gt.data(), T, I, H, R);
-  gemm(h2.data(), w.up.data(), up.data(), T, I, H, R);
+  lin(o, h2.data(), w.gate, gt.data(), T, I, H);
+  lin(o, h2.data(), w.up, up.data(), T, I, H);
   for (size_t i = 0; i < gt.size(); ++i) {
     float gg = gt[i];
     float s = R(gg / (1.0f + expf(-gg)));
     gt[i] = R(s * up[i]);
   }
   out.resize((size_t)T * H);
-  gemm(gt.data(), w.down.data(), out.data(), T, H, I, R);
+  lin(o, gt.data(), w.down, out.data(), T, H, I);
 }
 
 struct LayerCtx {
@@ -646,6 +738,7 @@ static void run_layer(Oracle& o, int li, std::vector<float>& x, int T, const std
   const orc_config& c = o.c;
   const LayerW& w = o.layers[li];
   const int H = c.hidden;
+  o.q8_now = o.precision == 2 && ctx.mode == 1 && T >= o.fp8_min_rows;
   std::vector<float> h((size_t)T * H), mix;
   rmsnorm(x.data(), w.input_norm.data(), h.data(), T, H, c.rms_eps, true, o.R);
   if (w.full) {

@@ -250,3 +250,34 @@ def test_d3_shaped_slice_bf16_parity(dcd, oracle):
     prof = e.profile_read()
     assert prof["gemm"]["launches"] == 4 * 4 and prof["gemm"]["ms"] > 0
     e.close()
+
+
+def test_fp8_precision_tiny(dcd, oracle):
+    """precision = 2: e4m3 GEMMs (per-token x per-output-row scales) in the question pass once it has
+    fp8_min_rows rows; capture stays bf16. Checked against the oracle's FP8 mode on the same inputs; the
+    bar is the size of the quantisation effect itself (oracle FP8 vs oracle bf16)."""
+    cfg = dcd.tiny_config(1)
+    e8 = make_engine(dcd, cfg, max_pass_tokens=512, precision=2, fp8_min_rows=16)
+    e16 = make_engine(dcd, cfg, max_pass_tokens=512)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    state, questions = tiny_inputs()
+    ost = o.capture_state(state)
+    want16 = o.readout_state_once_batch(ost, questions)
+    o.set_precision(2, 16)
+    want8 = o.readout_state_once_batch(ost, questions)
+    effect = float(np.abs(want8 - want16).max())
+    st8, st16 = e8.capture_state(state), e16.capture_state(state)
+    for layer, what in [(0, 2), (0, 3), (3, 0), (3, 1)]:
+        assert st8.tensor(layer, what).tobytes() == st16.tensor(layer, what).tobytes()   # capture is bf16 in both
+    got8 = e8.readout_state_once_batch(st8, questions)
+    got16 = e16.readout_state_once_batch(st16, questions)
+    err = float(np.abs(got8 - want8).max())
+    print(f"fp8 tiny: GPU fp8 vs oracle fp8 {err:.4g}; fp8 effect (oracle fp8 vs bf16) {effect:.4g}; GPU fp8 vs GPU bf16 {np.abs(got8 - got16).max():.4g}")
+    assert effect > 1e-3                      # the FP8 path really changes the numbers
+    assert np.abs(got8 - got16).max() > 1e-3  # and it is active on the GPU
+    assert err < max(effect, BF16_ABS)
+    # below fp8_min_rows the pass stays bf16: one short question gives the bf16 engine's bits
+    a = e8.readout_state_once_batch(st8, [questions[0][:8]])
+    b = e16.readout_state_once_batch(st16, [questions[0][:8]])
+    assert a.tobytes() == b.tobytes()
+    e8.close(); e16.close()

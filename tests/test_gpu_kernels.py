@@ -396,3 +396,52 @@ def test_gdn_chunked_vs_oracle(G, oracle, dtype, nk, nv, dv, narrow):
     v = conv[sl, 2 * nk * dk:].reshape(lens[2], nv, dv)
     want, _ = oracle.k_gdn_recurrent(np.repeat(q[sl], rep, 1), np.repeat(k[sl], rep, 1), v, g[sl], beta[sl], np.zeros_like(seed), bool(dtype))
     assert np.abs(G.host(out2)[sl].reshape(lens[2], nv, dv) - want).max() < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# FP8 (E4M3) path
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_quant_fp8_rows_bit_exact(G, oracle, dtype):
+    import torch
+    rows, cols, stride = 9, 688, 720
+    r = rng(41)
+    xf = (r.standard_normal((rows, stride), dtype=np.float32) * np.exp(r.uniform(-6, 4, (rows, 1)))).astype(np.float32)
+    xf[3] = 0.0                      # an all-zero row: scale floor 1e-10/448
+    if dtype:
+        xf = oracle.rb(xf)
+    codes = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+    scales = G.devf(np.zeros(rows))
+    G.call("dcd_k_quant_fp8_rows", G.dev(xf, dtype), stride, codes, scales, rows, cols, C.c_float(1.0), dtype, None)
+    wc, ws = oracle.k_quant_fp8_rows(xf[:, :cols])
+    assert G.host(scales).tobytes() == ws.tobytes()
+    assert np.array_equal(codes.cpu().numpy(), wc)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 776, 256), (77, 48, 688), (1000, 640, 5120), (700, 5120, 17408)])
+def test_gemm_fp8_tc_vs_oracle(G, oracle, M, N, K):
+    import torch
+    r = rng(M + N + K)
+    X = oracle.rb(r.standard_normal((M, K), dtype=np.float32))
+    W = oracle.rb(r.standard_normal((N, K), dtype=np.float32) * 0.02)
+    xq = torch.zeros((M, K), dtype=torch.uint8, device="cuda")
+    wq = torch.zeros((N, K), dtype=torch.uint8, device="cuda")
+    xs, ws = G.devf(np.zeros(M)), G.devf(np.zeros(N))
+    G.call("dcd_k_quant_fp8_rows", G.dev(X, 1), K, xq, xs, M, K, C.c_float(1.0), 1, None)
+    G.call("dcd_k_quant_fp8_rows", G.dev(W, 1), K, wq, ws, N, K, C.c_float(1.0), 1, None)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = G.devi([0])
+    G.call("dcd_k_gemm_fp8_tc", xq, wq, out, M, N, K, N, 0, xs, ws, G.sm_count(), err, None)
+    assert int(err.item()) == 0
+    got = G.host(out)
+    if M * N * K <= 1000 * 640 * 5120:
+        want = oracle.k_gemm_fp8(X, W, True)
+    else:  # same arithmetic with torch: exact e4m3 products, f32 accumulation, the two scales, bf16 rounding
+        xv = torch.from_numpy(oracle.e4m3_to_f32(xq.cpu().numpy())).cuda()
+        wv = torch.from_numpy(oracle.e4m3_to_f32(wq.cpu().numpy())).cuda()
+        want = ((xv @ wv.T) * ws[None, :] * xs[:, None]).to(torch.bfloat16).float().cpu().numpy()
+    bad = ~(np.abs(got - want) <= 8e-3 * np.abs(want) + 2e-3 * np.abs(want).max())
+    assert not bad.any(), f"{bad.mean():.4%} mismatched, nan {np.isnan(got).mean():.4%}, max abs {np.nanmax(np.abs(got - want))}"
+    # and the quantisation error itself stays at the e4m3 level against the unquantised product
+    ref = X @ W.T
+    assert np.abs(got - ref).max() < 0.12 * np.abs(ref).max()
