@@ -55,7 +55,7 @@ def parse():
     ap.add_argument("--qmin", type=int, default=48)
     ap.add_argument("--qmax", type=int, default=160)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8"],
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8", "w4a16"],
                     help="bf16 = BASELINE configs[1] (the headline); fp8 = e4m3 GEMMs in the question pass (extra, not the headline)")
     return ap.parse_args()
 
@@ -71,7 +71,7 @@ def workload(args, rank):
 
 def config_dict(args, n_gpus):
     return {
-        "workload": ("d3-turbo-shaped BF16 random-init (BASELINE configs[1])" if args.precision == "bf16" else "d3-turbo-shaped, FP8 all-linear question pass (not the headline config)") + ": %d layers 3 GDN:1 full-attn, hidden 5120, "
+        "workload": ("d3-turbo-shaped BF16 random-init (BASELINE configs[1])" if args.precision == "bf16" else "d3-turbo-shaped, %s weights/GEMMs (not the headline config)" % args.precision) + ": %d layers 3 GDN:1 full-attn, hidden 5120, "
                     "1 state x %d tokens + %d questions len U[%d,%d] per step (cold: capture + question pass)"
                     % (args.layers, args.state_len, args.questions, args.qmin, args.qmax),
         "parallelism": "replicas sharded by state (dp%d), no collective on the data path" % n_gpus,
@@ -210,7 +210,7 @@ def run_ours(args):
     cfg = dcd.d3_config(num_layers=args.layers, dtype=1)
     opt = dcd.Options()
     opt.max_pass_tokens = max(args.state_len, args.questions * args.qmax)
-    opt.precision = 2 if args.precision == "fp8" else 0
+    opt.precision = {"bf16": 0, "w4a16": 1, "fp8": 2}[args.precision]
     eng = dcd.Engine(cfg, opt, device=local)
     eng.init_random(0)
 
@@ -286,7 +286,8 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": world * B * args.steps / t_dev, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16" if args.precision == "bf16" else "fp8 e4m3 GEMMs in the question pass (bf16 capture, bf16 activations elsewhere)",
+            "dtype": {"bf16": "bf16", "fp8": "fp8 e4m3 GEMMs in the question pass (bf16 capture, bf16 activations elsewhere)",
+                      "w4a16": "bf16 activations, int4 group-128 weights (BASELINE configs[2] format)"}[args.precision],
             "data": "synthetic", "config": config_dict(args, world),
             "states_per_s": world * args.steps / t_dev,
             "step_tflop": flops_step / 1e12, "model_tflops_per_gpu": flops_step * args.steps / t_dev / 1e12,

@@ -45,6 +45,9 @@ struct LayerW {
   // FP8 (e4m3) images of the six GEMM weights: values, per-output-row scales, TMA descriptors
   struct Fp8W { uint8_t* q = nullptr; float* scale = nullptr; TcTensorMap tm; };
   Fp8W f_gu, f_down, f_qkv, f_o, f_gin, f_out;
+  // W4A16 group-128 images (precision 1): the only resident copy of the six GEMM weights
+  struct W4 { uint32_t* q = nullptr; void* scale = nullptr; int N = 0, K = 0; };
+  W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
 };
 
 }  // namespace
@@ -92,6 +95,8 @@ struct dcd_engine {
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
   bool attn_tc = false, gdn_chunked = false;
+  bool w4 = false;                     // precision 1: int4 g128 weights, dequantised per GEMM into wstage
+  void* wstage = nullptr;              // bf16 [max N*K] stage shared by all W4 GEMMs
   bool fp8 = false, fp8_dirty = true;  // precision 2: e4m3 GEMMs in question passes of >= fp8_min_rows rows
   uint8_t* aq = nullptr;               // [Tm, max K] quantised activations
   float* a_scale = nullptr;            // [Tm] per-token scales
@@ -147,12 +152,18 @@ GenSpec spec_for(int kind, bool bf) {
 
 // Where a logical tensor lives: base pointer of the (possibly fused) destination, its logical
 // shape, the row mapping into the destination and whether it is stored as f32.
-struct Loc { void* base; size_t rows, cols; int mode, row_offset, dst_stride; bool f32; };
+struct Loc { void* base; size_t rows, cols; int mode, row_offset, dst_stride; bool f32; LayerW::W4* w4 = nullptr; };
 
 bool locate(dcd_engine* e, int layer, int kind, Loc* out) {
   const dcd_model_config& c = e->c;
   const size_t H = e->H;
-  auto L = [&](void* b, size_t r, size_t cc, int mode, int ro, int ds, bool f) { *out = Loc{b, r, cc, mode, ro, ds, f}; return b != nullptr; };
+  auto L = [&](void* b, size_t r, size_t cc, int mode, int ro, int ds, bool f) { *out = Loc{b, r, cc, mode, ro, ds, f, nullptr}; return b != nullptr; };
+  // GEMM weights of a W4 engine live as int4 images; the logical tensor is staged through wstage
+  auto G = [&](void* b, LayerW::W4& img, size_t r, size_t cc, int mode, int ro, int ds) {
+    if (!e->w4) return L(b, r, cc, mode, ro, ds, false);
+    *out = Loc{e->wstage, r, cc, mode, ro, ds, false, &img};
+    return true;
+  };
   if (layer < 0) {
     switch (kind) {
       case DCD_T_EMBED: return L(e->embed, c.vocab, H, 0, 0, (int)H, false);
@@ -167,27 +178,27 @@ bool locate(dcd_engine* e, int layer, int kind, Loc* out) {
   switch (kind) {
     case DCD_T_INPUT_NORM: return L(w.input_norm, 1, H, 0, 0, (int)H, false);
     case DCD_T_POST_NORM: return L(w.post_norm, 1, H, 0, 0, (int)H, false);
-    case DCD_T_GATE: return L(w.w_gu, e->I, H, 1, 0, (int)H, false);
-    case DCD_T_UP: return L(w.w_gu, e->I, H, 2, 0, (int)H, false);
-    case DCD_T_DOWN: return L(w.w_down, H, e->I, 0, 0, e->I, false);
+    case DCD_T_GATE: return G(w.w_gu, w.g_gu, e->I, H, 1, 0, (int)H);
+    case DCD_T_UP: return G(w.w_gu, w.g_gu, e->I, H, 2, 0, (int)H);
+    case DCD_T_DOWN: return G(w.w_down, w.g_down, H, e->I, 0, 0, e->I);
   }
   if (w.full) {
     switch (kind) {
-      case DCD_T_Q: return L(w.w_qkv, e->qcols, H, 0, 0, (int)H, false);
-      case DCD_T_K: return L(w.w_qkv, e->kvcols, H, 0, e->qcols, (int)H, false);
-      case DCD_T_V: return L(w.w_qkv, e->kvcols, H, 0, e->qcols + e->kvcols, (int)H, false);
-      case DCD_T_O: return L(w.w_o, H, (size_t)c.heads * hd, 0, 0, c.heads * hd, false);
+      case DCD_T_Q: return G(w.w_qkv, w.g_qkv, e->qcols, H, 0, 0, (int)H);
+      case DCD_T_K: return G(w.w_qkv, w.g_qkv, e->kvcols, H, 0, e->qcols, (int)H);
+      case DCD_T_V: return G(w.w_qkv, w.g_qkv, e->kvcols, H, 0, e->qcols + e->kvcols, (int)H);
+      case DCD_T_O: return G(w.w_o, w.g_o, H, (size_t)c.heads * hd, 0, 0, c.heads * hd);
       case DCD_T_QNORM: return L(w.qnorm, 1, hd, 0, 0, hd, false);
       case DCD_T_KNORM: return L(w.knorm, 1, hd, 0, 0, hd, false);
       default: return false;
     }
   }
   switch (kind) {
-    case DCD_T_IN_QKV: return L(w.w_gin, e->conv_dim, H, 0, 0, (int)H, false);
-    case DCD_T_IN_Z: return L(w.w_gin, e->vd, H, 0, e->conv_dim, (int)H, false);
-    case DCD_T_IN_B: return L(w.w_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd, (int)H, false);
-    case DCD_T_IN_A: return L(w.w_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd + c.gdn_v_heads, (int)H, false);
-    case DCD_T_OUT: return L(w.w_out, H, e->vd, 0, 0, e->vd, false);
+    case DCD_T_IN_QKV: return G(w.w_gin, w.g_gin, e->conv_dim, H, 0, 0, (int)H);
+    case DCD_T_IN_Z: return G(w.w_gin, w.g_gin, e->vd, H, 0, e->conv_dim, (int)H);
+    case DCD_T_IN_B: return G(w.w_gin, w.g_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd, (int)H);
+    case DCD_T_IN_A: return G(w.w_gin, w.g_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd + c.gdn_v_heads, (int)H);
+    case DCD_T_OUT: return G(w.w_out, w.g_out, H, e->vd, 0, 0, e->vd);
     case DCD_T_CONV: return L(w.conv, e->conv_dim, 4, 0, 0, 4, false);
     case DCD_T_A_LOG: return L(w.A_log, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
     case DCD_T_DT_BIAS: return L(w.dt_bias, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
@@ -247,8 +258,15 @@ struct Scope {
 // `fw` is given: the activations are quantised per token first, Engine::fp8_gemm,
 // native/src/engine.rs:4144-4296); plain FMA otherwise.
 template <typename T>
-int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw, void* C, int M,
-         int N, int K, int ldc, int epi) {
+int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
+         const LayerW::W4* g4, void* C, int M, int N, int K, int ldc, int epi) {
+  if (e->w4) {
+    // W4A16: int4 -> bf16 into the shared stage, then the bf16 tensor-core GEMM reads the stage
+    // (the reference's dequant_w4a16_bf16 + BF16 GEMM route, native/src/engine.rs:4516-4558)
+    Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5 * N * (double)K, 1);
+    CK(e, launch_dequant_w4_g128(g4->q, g4->scale, (bf16*)e->wstage, N, K, e->stream), "w4 dequantisation");
+    W = e->wstage;
+  }
   if (fw && e->bf && e->o.gemm_path == 0 && tc_fp8_shape_ok(M, N, K)) {
     {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 3.0 * M * (double)K, 1);
@@ -302,7 +320,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
     }
     if (w.full) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
@@ -338,10 +356,10 @@ int run_layers(dcd_engine* e, const Pass& p) {
                                    e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
         }
       }
-      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, e->mix, T_, H, heads * hd, H, 0);
+      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, e->mix, T_, H, heads * hd, H, 0);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, e->big, T_, e->gin_n, H, e->gin_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       if (p.mode == 0) {
@@ -379,7 +397,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
         CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
                                       c.rms_eps, s), "rmsnorm_gated");
       }
-      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, e->mix, T_, H, e->vd, H, 0);
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, e->mix, T_, H, e->vd, H, 0);
       if (rc) return rc;
     }
     {
@@ -388,15 +406,15 @@ int run_layers(dcd_engine* e, const Pass& p) {
          "add_rmsnorm");
     }
     if (tc) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, e->act, T_, e->gu_rows, H, e->I, 1);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
       if (rc) return rc;
       Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->I * e->esz * 3.0, 1);
       CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
-    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, e->mix, T_, H, e->I, H, 0);
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, e->mix, T_, H, e->I, H, 0);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
@@ -564,8 +582,9 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (c.dtype != 0 && c.dtype != 1) return fail(nullptr, DCD_E_INVALID, "dtype must be 0 (f32) or 1 (bf16)");
   dcd_options o = {};
   if (opt) o = *opt;
-  if (o.precision != 0 && o.precision != 2) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (0 = config dtype, 2 = fp8)", o.precision);
-  if (o.precision == 2 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "fp8 precision needs a bf16 engine (dtype 1)");
+  if (o.precision < 0 || o.precision > 2) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (0 = config dtype, 1 = w4a16 g128, 2 = fp8)", o.precision);
+  if (o.precision != 0 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 / fp8 precision needs a bf16 engine (dtype 1)");
+  if (o.precision == 1 && ((c.hidden % 8) || (c.intermediate % 8))) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 needs K multiples of 8");
   if (o.fp8_min_rows <= 0) o.fp8_min_rows = 512;
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
@@ -635,12 +654,19 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->attn_tc = e->bf && o.attn_path == 0 && attn_tc_supported(c.heads, c.kv_heads, c.head_dim);
   if (e->attn_tc) CRE(attn_tc_prepare_device(), "tcgen05 attention shared-memory attribute");
   e->fp8 = o.precision == 2 && o.gemm_path == 0;
+  e->w4 = o.precision == 1;
   e->gdn_chunked = e->bf && o.gdn_path == 0 && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
   const size_t es = e->esz, H = e->H;
   // ---- weights
   e->layers.resize(c.num_layers);
+  if (e->w4) {
+    size_t mx = (size_t)e->gu_rows * H;
+    auto up = [&](size_t n) { if (n > mx) mx = n; };
+    up(H * (size_t)e->I); up((size_t)e->qkv_n * H); up(H * (size_t)c.heads * c.head_dim); up((size_t)e->gin_n * H); up(H * (size_t)e->vd);
+    CRA(e->wstage, mx * 2, true, &e->weight_bytes);
+  }
   CRA(e->embed, (size_t)c.vocab * H * es, false, &e->weight_bytes);
   CRA(e->final_norm, H * es, true, &e->weight_bytes);
   CRA(e->readout, (size_t)c.readout_rows * H * 4, true, &e->weight_bytes);
@@ -649,6 +675,29 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
     w.full = c.layer_is_full[i] != 0;
     CRA(w.input_norm, H * es, true, &e->weight_bytes);
     CRA(w.post_norm, H * es, true, &e->weight_bytes);
+    if (e->w4) {
+      auto mk4 = [&](LayerW::W4& g, size_t n, size_t k) -> int {
+        g.N = (int)n; g.K = (int)k;
+        int rc = dev_alloc(e, reinterpret_cast<void**>(&g.q), n * ((k + 7) / 8) * 4, true, &e->weight_bytes);
+        if (!rc) rc = dev_alloc(e, &g.scale, n * ((k + 127) / 128) * 2, true, &e->weight_bytes);
+        return rc;
+      };
+      int rc = mk4(w.g_gu, e->gu_rows, H);
+      if (!rc) rc = mk4(w.g_down, H, e->I);
+      if (!rc && w.full) { rc = mk4(w.g_qkv, e->qkv_n, H); if (!rc) rc = mk4(w.g_o, H, (size_t)c.heads * c.head_dim); }
+      if (!rc && !w.full) { rc = mk4(w.g_gin, e->gin_n, H); if (!rc) rc = mk4(w.g_out, H, e->vd); }
+      if (rc) { g_create_error = e->err; dcd_engine_destroy(e); return rc; }
+      // every bf16 weight pointer aliases the shared stage (filled by the dequantiser before each GEMM)
+      w.w_gu = w.w_down = e->wstage;
+      if (w.full) { w.w_qkv = w.w_o = e->wstage; CRA(w.qnorm, c.head_dim * es, true, &e->weight_bytes); CRA(w.knorm, c.head_dim * es, true, &e->weight_bytes); }
+      else {
+        w.w_gin = w.w_out = e->wstage;
+        CRA(w.conv, (size_t)e->conv_dim * 4 * es, true, &e->weight_bytes);
+        CRA(w.gnorm, c.gdn_dv * es, true, &e->weight_bytes);
+        CRA(w.A_log, c.gdn_v_heads * 4, true, &e->weight_bytes);
+        CRA(w.dt_bias, c.gdn_v_heads * 4, true, &e->weight_bytes);
+      }
+    } else {
     CRA(w.w_gu, (size_t)e->gu_rows * H * es, true, &e->weight_bytes);
     CRA(w.w_down, H * (size_t)e->I * es, true, &e->weight_bytes);
     if (w.full) {
@@ -663,6 +712,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
       CRA(w.gnorm, c.gdn_dv * es, true, &e->weight_bytes);
       CRA(w.A_log, c.gdn_v_heads * 4, true, &e->weight_bytes);
       CRA(w.dt_bias, c.gdn_v_heads * 4, true, &e->weight_bytes);
+    }
     }
     if (e->fp8) {
       auto mk = [&](LayerW::Fp8W& f, size_t n, size_t k) -> int {
@@ -797,9 +847,25 @@ int dcd_engine_info(const dcd_engine* e, dcd_info* out) {
 
 int dcd_rebind_blas(dcd_engine* e) { return e ? DCD_OK : DCD_E_INVALID; }
 
+// W4 engines: a logical GEMM tensor is edited in the bf16 stage — bring the whole fused matrix in
+// (dequantise), let the caller write or read its rows, then quantise the matrix back.
+static int w4_stage_in(dcd_engine* e, const Loc& L) {
+  if (!L.w4) return DCD_OK;
+  e->launches += 1;
+  CK(e, launch_dequant_w4_g128(L.w4->q, L.w4->scale, (bf16*)e->wstage, L.w4->N, L.w4->K, e->stream), "w4 stage in");
+  return DCD_OK;
+}
+static int w4_stage_out(dcd_engine* e, const Loc& L) {
+  if (!L.w4) return DCD_OK;
+  e->launches += 1;
+  CK(e, launch_quant_w4_g128((const bf16*)e->wstage, L.w4->q, L.w4->scale, L.w4->N, L.w4->K, e->stream), "w4 stage out");
+  return DCD_OK;
+}
+
 static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind) {
   Loc L;
   if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  if (int rc = w4_stage_in(e, L)) return rc;
   const GenSpec sp = spec_for(kind, e->bf);
   const float cc = (float)((double)sp.p0 / IH8_STD);
   const uint64_t key = gen_tensor_key(seed, layer, kind);
@@ -808,7 +874,7 @@ static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind) {
   if (L.f32) CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
   else if (e->bf) CK(e, launch_gen_tensor<bf16>((bf16*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
   else CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
-  return DCD_OK;
+  return w4_stage_out(e, L);
 }
 
 int dcd_engine_init_random(dcd_engine* e, uint64_t seed) {
@@ -837,6 +903,7 @@ int dcd_engine_load_tensor(dcd_engine* e, int layer, int kind, const float* host
   Loc L;
   if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
   if (count != L.rows * L.cols) return fail(e, DCD_E_INVALID, "tensor kind %d expects %zu values, got %zu", kind, L.rows * L.cols, count);
+  if (int rc0 = w4_stage_in(e, L)) return rc0;
   float* tmp = nullptr;
   void* tmpT = nullptr;
   cudaError_t ce = cudaMalloc(&tmp, count * 4);
@@ -853,6 +920,7 @@ int dcd_engine_load_tensor(dcd_engine* e, int layer, int kind, const float* host
       ce = launch_place_rows<bf16>((const bf16*)tmpT, (bf16*)L.base, L.rows, (int)L.cols, L.mode, L.row_offset, L.dst_stride, false, e->stream);
     }
     if (ce != cudaSuccess) break;
+    if (w4_stage_out(e, L)) { rc = DCD_E_CUDA; break; }
     ce = cudaStreamSynchronize(e->stream);
   } while (0);
   if (ce != cudaSuccess) rc = cuda_fail(e, ce, "load_tensor");
@@ -868,6 +936,7 @@ int dcd_engine_read_tensor(dcd_engine* e, int layer, int kind, float* host, size
   Loc L;
   if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
   if (count != L.rows * L.cols) return fail(e, DCD_E_INVALID, "tensor kind %d holds %zu values, asked for %zu", kind, L.rows * L.cols, count);
+  if (int rc0 = w4_stage_in(e, L)) return rc0;
   float* tmp = nullptr;
   void* tmpT = nullptr;
   cudaError_t ce = cudaMalloc(&tmp, count * 4);

@@ -37,6 +37,13 @@ int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, float* scale
                   launch_quant_fp8_rows<bf16>((const bf16*)x, x_stride, (uint8_t*)out, scales, rows, cols, clip, S(stream)));
 }
 
+int dcd_k_quant_w4_g128(const void* W, void* packed, void* scales, int N, int K, void* stream) {
+  return rc_of(launch_quant_w4_g128((const bf16*)W, (uint32_t*)packed, scales, N, K, S(stream)));
+}
+int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N, int K, void* stream) {
+  return rc_of(launch_dequant_w4_g128((const uint32_t*)packed, scales, (bf16*)W, N, K, S(stream)));
+}
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

@@ -6,6 +6,7 @@
 // Each kernel names the reference code (paths inside juanqui/decidra) whose arithmetic it
 // reproduces. All are templated on the storage type T (float for the f32 engine, bf16 for
 // the bf16 engine); Ty<T>::rnd() rounds at the points where the reference rounds through bf16.
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -1161,3 +1162,76 @@ cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, flo
 }
 template cudaError_t launch_quant_fp8_rows<float>(const float*, size_t, uint8_t*, float*, int, int, float, cudaStream_t);
 template cudaError_t launch_quant_fp8_rows<bf16>(const bf16*, size_t, uint8_t*, float*, int, int, float, cudaStream_t);
+
+// ---------------------------------------------------------------------------
+// W4A16, group 128: compressed-tensors pack-quantized layout as the reference reads it
+// (native/src/weights.rs:292-330): packed [N, ceil(K/8)] words, nibble k of word j = input 8j+k,
+// symmetric zero-point 8, scales [N, ceil(K/128)] (fp16 here).
+//   dequant: w[o,i] = bf16(float(q - 8) * float(scale[o, i/128]))   dequant_w4a16_bf16, kernels.cu:867-892
+//   quant  : scale = fp16(absmax/7), q = clamp(rint(w/scale), -8, 7)  (round to nearest; one warp per group)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quant_w4_g128_kernel(const bf16* __restrict__ W, uint32_t* __restrict__ packed,
+                                                            __half* __restrict__ scales, int N, int K) {
+  const int groups = (K + 127) / 128, words = (K + 7) / 8;
+  const int gidx = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (gidx >= N * groups) return;
+  const int lane = threadIdx.x & 31;
+  const int o = gidx / groups, gi = gidx - o * groups;
+  const int k0 = gi * 128 + lane * 4;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[j] = (k0 + j) < K ? __bfloat162float(W[(size_t)o * K + k0 + j]) : 0.f;
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  amax = warp_max(amax);
+  const __half sh = __float2half_rn(amax / 7.0f);
+  const float sc = __half2float(sh);
+  if (lane == 0) scales[(size_t)o * groups + gi] = sh;
+  uint32_t nib = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int q = 0;
+    if (sc > 0.f) q = (int)fminf(fmaxf(rintf(v[j] / sc), -8.f), 7.f);
+    nib |= (uint32_t)((q + 8) & 0xf) << (4 * j);
+  }
+  // lanes 2m and 2m+1 hold the low and high halves of word m of the group
+  const uint32_t other = __shfl_xor_sync(0xffffffffu, nib, 1);
+  if ((lane & 1) == 0) {
+    const int w = (gi * 128 + lane * 4) >> 3;
+    if (w < words) packed[(size_t)o * words + w] = nib | (other << 16);
+  }
+}
+
+__global__ void __launch_bounds__(256) dequant_w4_g128_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales,
+                                                              bf16* __restrict__ W, int N, int K) {
+  const int words = (K + 7) / 8, groups = (K + 127) / 128;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)N * words) return;
+  const int o = (int)(idx / words), w = (int)(idx - (size_t)o * words);
+  const uint32_t word = packed[idx];
+  const float sc = __half2float(scales[(size_t)o * groups + (w * 8) / 128]);
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = (float)((int)((word >> (4 * j)) & 0xf) - 8) * sc;
+  bf16* dst = W + (size_t)o * K + (size_t)w * 8;
+  if (w * 8 + 8 <= K && (K % 8) == 0) {
+    *reinterpret_cast<uint4*>(dst) = pack8(f);
+  } else {
+    for (int j = 0; j < 8 && w * 8 + j < K; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+  }
+}
+
+cudaError_t launch_quant_w4_g128(const bf16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s) {
+  if (N <= 0 || (K % 8) != 0) return N <= 0 ? cudaSuccess : cudaErrorInvalidValue;
+  const int groups = (K + 127) / 128;
+  quant_w4_g128_kernel<<<(N * groups + 7) / 8, 256, 0, s>>>(W, packed, (__half*)scales, N, K);
+  return cudaGetLastError();
+}
+cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, bf16* W, int N, int K, cudaStream_t s) {
+  if (N <= 0) return cudaSuccess;
+  const size_t n = (size_t)N * ((K + 7) / 8);
+  dequant_w4_g128_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(packed, (const __half*)scales, W, N, K);
+  return cudaGetLastError();
+}

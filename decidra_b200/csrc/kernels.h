@@ -72,3 +72,8 @@ cudaError_t launch_gdn_chunked(const float* qf, const float* kf, const T* conv, 
 // Per-row FP8 E4M3 quantisation: scale[row] = max(absmax*clip, 1e-10)/448, out = e4m3(x/scale).
 template <typename T>
 cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, float* scales, int rows, int cols, float clip, cudaStream_t s);
+
+// W4A16 group-128 weights: packed [N, K/8] words (nibble k of word j = input 8j+k, zero-point 8) and
+// fp16 scales [N, ceil(K/128)]. K % 8 == 0.
+cudaError_t launch_quant_w4_g128(const __nv_bfloat16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s);
+cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, __nv_bfloat16* W, int N, int K, cudaStream_t s);

@@ -61,7 +61,9 @@ typedef struct dcd_model_config {
 typedef struct dcd_options {
   int32_t precision;        /* 0 = the config dtype; 2 = fp8 (e4m3 GEMMs, per-token x per-output-row scales, in question passes
                                of >= fp8_min_rows rows; capture stays bf16 — Engine::fp8_gemm, native/src/engine.rs:4144-4296);
-                               1 = w4a16_g128 and 3 = nvfp4 are not built yet: DCD_E_UNSUPPORTED */
+                               1 = w4a16 group 128: the GEMM weights are held only as int4 + fp16 group scales and
+                               dequantised per GEMM into a shared bf16 stage (dequant_w4a16_bf16 route,
+                               native/src/engine.rs:4516-4558), all passes; 3 = nvfp4 is not built yet: DCD_E_UNSUPPORTED */
   int32_t max_pass_tokens;  /* workspace rows; also the longest state that can be captured. default 16384 */
   int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
   int64_t max_keys;
@@ -251,6 +253,13 @@ DCD_API int dcd_k_gemm_fp8_tc(const void* Xq, const void* Wq, void* C, int M, in
  * out = e4m3_satfinite(x/scale). x is T [rows, cols] with row stride x_stride (elements). */
 DCD_API int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, float* scales, int rows, int cols, float clip, int dtype,
                                  void* stream);
+/* W4A16 group-128 weights in the compressed-tensors pack-quantized layout the reference reads
+ * (native/src/weights.rs:292-330): packed u32 [N, K/8], nibble k of word j = input 8j+k, symmetric
+ * zero-point 8; scales fp16 [N, ceil(K/128)]. dequant: w = bf16(float(q-8) * float(scale))
+ * (dequant_w4a16_bf16, native/kernels/kernels.cu:867-892); quant: round to nearest with
+ * scale = fp16(absmax/7). W is bf16 [N,K], K % 8 == 0. */
+DCD_API int dcd_k_quant_w4_g128(const void* W, void* packed, void* scales, int N, int K, void* stream);
+DCD_API int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N, int K, void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

@@ -243,6 +243,25 @@ def k_gemm_fp8(X, W, bf16: bool = True) -> np.ndarray:
     return out
 
 
+def k_quant_w4(W):
+    """int4 g128 round-to-nearest: (packed uint32 [N, ceil(K/8)], fp16 scales as uint16 [N, ceil(K/128)])."""
+    W = _f32(W)
+    N, K = W.shape
+    packed = np.zeros((N, (K + 7) // 8), dtype=np.uint32)
+    scales = np.zeros((N, (K + 127) // 128), dtype=np.uint16)
+    lib().orc_k_quant_w4(_fp(W), N, K, packed.ctypes.data_as(C.POINTER(C.c_uint32)), scales.ctypes.data_as(C.POINTER(C.c_uint16)))
+    return packed, scales
+
+
+def k_dequant_w4(packed, scales, K: int) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.uint16)
+    N = packed.shape[0]
+    W = np.empty((N, K), dtype=np.float32)
+    lib().orc_k_dequant_w4(packed.ctypes.data_as(C.POINTER(C.c_uint32)), scales.ctypes.data_as(C.POINTER(C.c_uint16)), N, K, _fp(W))
+    return W
+
+
 def k_rmsnorm(x, w, eps: float, zero_centered: bool, bf16: bool) -> np.ndarray:
     x, w = _f32(x), _f32(w)
     out = np.empty_like(x)

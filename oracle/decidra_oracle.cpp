@@ -278,6 +278,76 @@ ORC_API void orc_k_quant_fp8_rows(const float* x, int rows, int cols, float clip
 }
 ORC_API float orc_k_e4m3_to_f32(uint8_t c) { return e4m3_to_f32(c); }
 
+// ---------------------------------------------------------------------------
+// W4A16, group 128 (BASELINE config 3: "int4 symmetric, group 128, fp16 scales, quantised from seeded
+// random BF16"). Packing and dequantisation follow compressed-tensors pack-quantized as the reference
+// reads it (native/src/weights.rs:292-330; dequant_w4a16_bf16, native/kernels/kernels.cu:867-892):
+// nibble k of word packed[o, i>>3] holds input 8*(i>>3)+k, symmetric zero-point 8,
+// w[o,i] = bf16(float(q - 8) * float(scale[o, i/128])). The reference stores bf16 scales; BASELINE
+// asks for fp16. Round-to-nearest quantiser (the reference's checkpoints come from GPTQ, which is
+// offline tooling and out of scope): scale = fp16(absmax/7), q = clamp(rint(w/scale), -8, 7).
+// ---------------------------------------------------------------------------
+static inline uint16_t f32_to_f16(float x) {  // round-to-nearest-even, host twin of __float2half_rn
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  const uint16_t sign = (uint16_t)((u >> 16) & 0x8000);
+  const uint32_t a = u & 0x7fffffffu;
+  if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00);
+  if (a >= 0x477ff000u) return (uint16_t)(sign | 0x7c00);      // >= 65520 rounds to inf
+  if (a < 0x38800000u) {                                        // below 2^-14: subnormal half, step 2^-24
+    float f;
+    std::memcpy(&f, &a, 4);
+    return (uint16_t)(sign | (uint16_t)nearbyintf(f * 16777216.0f));
+  }
+  uint32_t m = a - 0x38000000u;                                 // rebias exponent 127 -> 15
+  const uint32_t lsb = (m >> 13) & 1u;
+  m += 0x0fffu + lsb;
+  return (uint16_t)(sign | (uint16_t)(m >> 13));
+}
+static inline float f16_to_f32(uint16_t h) {
+  const int e = (h >> 10) & 0x1f, m = h & 0x3ff;
+  float v = e == 0 ? ldexpf((float)m, -24) : e == 31 ? (m ? NAN : INFINITY) : ldexpf(1.0f + (float)m / 1024.0f, e - 15);
+  return (h & 0x8000) ? -v : v;
+}
+// Quantises W[N,K] (values representable in bf16): packed [N, ceil(K/8)] words, scales fp16 [N, ceil(K/128)].
+static void quant_w4_g128(const float* W, int N, int K, uint32_t* packed, uint16_t* scales) {
+  const int words = (K + 7) / 8, groups = (K + 127) / 128;
+#pragma omp parallel for schedule(static)
+  for (int o = 0; o < N; ++o) {
+    for (int w = 0; w < words; ++w) packed[(size_t)o * words + w] = 0;
+    for (int gi = 0; gi < groups; ++gi) {
+      const int k0 = gi * 128, k1 = std::min(K, k0 + 128);
+      float amax = 0.f;
+      for (int i = k0; i < k1; ++i) amax = fmaxf(amax, fabsf(W[(size_t)o * K + i]));
+      const uint16_t sh = f32_to_f16(amax / 7.0f);
+      scales[(size_t)o * groups + gi] = sh;
+      const float sc = f16_to_f32(sh);
+      for (int i = k0; i < k1; ++i) {
+        int q = 0;
+        if (sc > 0.f) q = (int)fminf(fmaxf(nearbyintf(W[(size_t)o * K + i] / sc), -8.f), 7.f);
+        packed[(size_t)o * words + (i >> 3)] |= (uint32_t)((q + 8) & 0xf) << (4 * (i & 7));
+      }
+    }
+  }
+}
+static void dequant_w4_g128(const uint32_t* packed, const uint16_t* scales, int N, int K, float* W) {
+  const int words = (K + 7) / 8, groups = (K + 127) / 128;
+#pragma omp parallel for schedule(static)
+  for (int o = 0; o < N; ++o)
+    for (int i = 0; i < K; ++i) {
+      const int q = (int)((packed[(size_t)o * words + (i >> 3)] >> (4 * (i & 7))) & 0xf);
+      W[(size_t)o * K + i] = rb((float)(q - 8) * f16_to_f32(scales[(size_t)o * groups + i / 128]));
+    }
+}
+static void fake_quant_w4(std::vector<float>& W, int N, int K) {
+  std::vector<uint32_t> packed((size_t)N * ((K + 7) / 8));
+  std::vector<uint16_t> sc((size_t)N * ((K + 127) / 128));
+  quant_w4_g128(W.data(), N, K, packed.data(), sc.data());
+  dequant_w4_g128(packed.data(), sc.data(), N, K, W.data());
+}
+ORC_API void orc_k_quant_w4(const float* W, int N, int K, uint32_t* packed, uint16_t* scales) { quant_w4_g128(W, N, K, packed, scales); }
+ORC_API void orc_k_dequant_w4(const uint32_t* packed, const uint16_t* scales, int N, int K, float* W) { dequant_w4_g128(packed, scales, N, K, W); }
+
 // RMSNorm: native/kernels/kernels.cu:406-426 (zero_centered → weight 1+w).
 static void rmsnorm(const float* x, const float* w, float* out, int rows, int cols, float eps, bool zero_centered, Round R) {
 #pragma omp parallel for schedule(static)
@@ -485,7 +555,7 @@ struct Oracle {
   bool tap_on = false;
   // precision 2: FP8 GEMMs in question passes of >= fp8_min_rows rows (engine.rs:4321-4326, :246-257)
   int precision = 0, fp8_min_rows = 512;
-  bool q8_now = false;
+  bool q8_now = false, w4_done = false;
   std::map<const float*, Fp8Image> fp8_cache;
   int conv_dim() const { return 2 * c.gdn_k_heads * c.gdn_dk + c.gdn_v_heads * c.gdn_dv; }
 };
@@ -573,7 +643,24 @@ static void lin(Oracle& o, const float* X, const std::vector<float>& W, float* C
   }
   gemm_fp8(X, it->second, C, T, N, K, o.R);
 }
+// precision 1 (W4A16 g128): every GEMM weight is replaced once by its int4 round trip; all passes
+// (capture included) then run on the dequantised bf16 values, as the reference's W4 paths do.
 ORC_API void orc_set_precision(Oracle* o, int precision, int fp8_min_rows) {
+  if (precision == 1 && !o->w4_done) {
+    const orc_config& c = o->c;
+    const int H = c.hidden, I = c.intermediate, hd = c.head_dim, vd = c.gdn_v_heads * c.gdn_dv;
+    for (LayerW& w : o->layers) {
+      fake_quant_w4(w.gate, I, H); fake_quant_w4(w.up, I, H); fake_quant_w4(w.down, H, I);
+      if (w.full) {
+        fake_quant_w4(w.q, c.heads * 2 * hd, H); fake_quant_w4(w.k, c.kv_heads * hd, H); fake_quant_w4(w.v, c.kv_heads * hd, H);
+        fake_quant_w4(w.o, H, c.heads * hd);
+      } else {
+        fake_quant_w4(w.in_qkv, o->conv_dim(), H); fake_quant_w4(w.in_z, vd, H); fake_quant_w4(w.in_b, c.gdn_v_heads, H);
+        fake_quant_w4(w.in_a, c.gdn_v_heads, H); fake_quant_w4(w.out, H, vd);
+      }
+    }
+    o->w4_done = true;
+  }
   o->precision = precision;
   if (fp8_min_rows > 0) o->fp8_min_rows = fp8_min_rows;
 }

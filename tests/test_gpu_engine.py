@@ -281,3 +281,41 @@ def test_fp8_precision_tiny(dcd, oracle):
     b = e16.readout_state_once_batch(st16, [questions[0][:8]])
     assert a.tobytes() == b.tobytes()
     e8.close(); e16.close()
+
+
+def test_w4a16_precision(dcd, oracle):
+    """precision = 1 (BASELINE config 3): GEMM weights held as int4 group-128 + fp16 scales, dequantised per
+    GEMM; all passes. Against the oracle with the same round-to-nearest quantiser: the dequantised weights
+    are bit-identical, so the bars are those of the bf16 engine."""
+    cfg = dcd.tiny_config(1)
+    e = make_engine(dcd, cfg, max_pass_tokens=512, precision=1)
+    e16 = make_engine(dcd, cfg, max_pass_tokens=512)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    H, I = cfg.hidden, cfg.intermediate
+    plain = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    o.set_precision(1)
+    # weights read back = int4 round trip of the generator's values, bit-exact vs the oracle's quantiser
+    for layer, kind, n, k in [(0, 12, I, H), (0, 13, I, H), (0, 14, H, I), (0, 30, cfg.conv_dim(), H), (0, 33, 4, H), (3, 20, 512, H), (3, 22, 64, H), (3, 23, H, 256)]:
+        want = oracle.gen_tensor(0, layer, kind, n * k, bf16=True).reshape(n, k)
+        p, s = oracle.k_quant_w4(want)
+        assert e.read_tensor(layer, kind, n * k).tobytes() == oracle.k_dequant_w4(p, s, k).tobytes(), (layer, kind)
+    state, questions = tiny_inputs()
+    st, ost = e.capture_state(state), o.capture_state(state)
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    base = plain.readout_state_once_batch(plain.capture_state(state), questions)
+    err, effect = float(np.abs(got - want).max()), float(np.abs(want - base).max())
+    print(f"w4a16 tiny: GPU vs oracle {err:.4g}; quantisation effect (oracle w4 vs bf16) {effect:.4g}")
+    assert err < BF16_ABS and effect > 1e-3
+    agree, near = argmax_report(got, want)
+    assert (agree | near).all()
+    info, info16 = e.info(), e16.info()
+    assert info.weight_bytes < 0.7 * info16.weight_bytes   # embedding, RoPE tables and the bf16 stage stay; the GEMM weights shrink ~3.5x
+    # a logical tensor can be uploaded into a fused int4 matrix without disturbing its neighbours
+    up_before = e.read_tensor(1, 13, I * H)
+    vals = oracle.rb(np.random.default_rng(2).standard_normal(I * H).astype(np.float32) * 0.02)
+    e.load_tensor(1, 12, vals)
+    p, s = oracle.k_quant_w4(vals.reshape(I, H))
+    assert e.read_tensor(1, 12, I * H).tobytes() == oracle.k_dequant_w4(p, s, H).tobytes()
+    assert e.read_tensor(1, 13, I * H).tobytes() == up_before.tobytes()
+    e.close(); e16.close()

@@ -445,3 +445,24 @@ def test_gemm_fp8_tc_vs_oracle(G, oracle, M, N, K):
     # and the quantisation error itself stays at the e4m3 level against the unquantised product
     ref = X @ W.T
     assert np.abs(got - ref).max() < 0.12 * np.abs(ref).max()
+
+
+# ---------------------------------------------------------------------------------------------
+# W4A16 group 128
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(7, 688), (300, 5120), (64, 17408)])
+def test_w4_quant_dequant_bit_exact(G, oracle, N, K):
+    import torch
+    r = rng(N + K)
+    W = oracle.rb((r.standard_normal((N, K)) * 0.02).astype(np.float32))
+    W[1] = 0.0
+    W[2, :128] *= 1e-4
+    packed = torch.zeros((N, K // 8), dtype=torch.int32, device="cuda")
+    scales = torch.zeros((N, (K + 127) // 128), dtype=torch.float16, device="cuda")
+    G.call("dcd_k_quant_w4_g128", G.dev(W, 1), packed, scales, N, K, None)
+    wp, ws = oracle.k_quant_w4(W)
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32), wp)
+    assert np.array_equal(scales.cpu().numpy().view(np.uint16), ws)
+    out = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_dequant_w4_g128", packed, scales, out, N, K, None)
+    assert G.host(out).tobytes() == oracle.k_dequant_w4(wp, ws, K).tobytes()
