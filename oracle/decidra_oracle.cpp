@@ -12,11 +12,17 @@
 //   dtype 1 (bf16) : every point where the reference's kernels round through
 //                    bf16 (rb()/f2bf in native/kernels/kernels.cu) rounds here.
 //
-// Pinning: the integer/layout parts (mask, chunk planner, NVFP4 scale tiling,
-// answer decoding) are checked against the reference's own unit-test vectors in
-// tests/test_oracle_golden.py. The floating-point model path has no golden
-// vectors in the reference that work without its checkpoint, so model-level
-// parity is "unpinned": it rests on this restatement's citations.
+// Pinning:
+//  * integer/layout parts (mask, chunk planner, NVFP4 scale tiling, answer decoding): the
+//    reference's own unit-test vectors, tests/test_oracle_golden.py;
+//  * per-kernel floating-point arithmetic (norms, RoPE, conv, GDN prepare and recurrences, gated
+//    norm, SwiGLU, sigmoid gate, FP8 quantiser, W4 dequantiser): the reference's own kernels.cu
+//    compiled for sm_100a (oracle/Makefile `ref`) and run on the GPU next to this restatement,
+//    tests/test_gpu_reference_kernels.py;
+//  * GEMM and attention arithmetic lives in third-party code of the reference (cuBLAS via
+//    cudarc 0.19.10; FlashInfer 0.7.0.post1 templates) and the model-level goldens need its
+//    checkpoint: there parity is unpinned and rests on the published algorithms
+//    (f32-accumulated GEMM; softmax(QK^T/sqrt(d))V with bf16 probabilities).
 //
 // Build: see oracle/Makefile (g++ -O3 -mavx2 -ffp-contract=off -fopenmp).
 
