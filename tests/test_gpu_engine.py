@@ -319,3 +319,53 @@ def test_w4a16_precision(dcd, oracle):
     assert e.read_tensor(1, 12, I * H).tobytes() == oracle.k_dequant_w4(p, s, H).tobytes()
     assert e.read_tensor(1, 13, I * H).tobytes() == up_before.tobytes()
     e.close(); e16.close()
+
+
+def test_ragged_stress_shapes_tiny(dcd, oracle):
+    """BASELINE config 5 in miniature (seed 7): a long state, many questions with lengths uniform in
+    [16,512], more tokens than one pass holds, so the planner splits by tokens and rows come back in
+    input order. Checked against the oracle question by question."""
+    cfg = dcd.tiny_config(1)
+    rng_ = np.random.Generator(np.random.PCG64(7))
+    S = 3000
+    lens = rng_.integers(16, 513, 23).tolist() + [16, 512, 1]
+    state = rng_.integers(0, cfg.vocab, S, dtype=np.uint32)
+    questions = [rng_.integers(0, cfg.vocab, n, dtype=np.uint32) for n in lens]
+    e = make_engine(dcd, cfg, max_pass_tokens=4096)          # sum(lens) ~ 6.9k tokens -> at least two passes
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    st, ost = e.capture_state(state), o.capture_state(state)
+    assert st.state_len == S
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    err = float(np.abs(got - want).max())
+    agree, near = argmax_report(got, want)
+    print(f"ragged tiny: S={S}, B={len(lens)}, tokens={sum(lens)}: max-abs {err:.4g}, argmax agree {agree.mean():.3f}, near-ties {int(near.sum())}")
+    assert err < BF16_ABS
+    assert (agree | near).all()
+    # one question alone larger than the workspace is refused, like a question over the reference's caps
+    with pytest.raises(dcd.EngineError, match="exceeds"):
+        e.readout_state_once_batch(st, [rng_.integers(0, cfg.vocab, 5000, dtype=np.uint32)])
+    with pytest.raises(dcd.EngineError, match="exceeds"):
+        e.capture_state(rng_.integers(0, cfg.vocab, 5000, dtype=np.uint32))
+    e.close()
+
+
+def test_long_state_d3_attention_path(dcd, oracle):
+    """A 2-layer [GDN, full] d3-shaped engine over a 1100-token state: many key tiles in the tcgen05
+    attention kernel and 35 chunks in the chunked GDN kernel, against the oracle."""
+    cfg = dcd.d3_config(num_layers=2, dtype=1, vocab=4096)
+    cfg.layer_is_full[0], cfg.layer_is_full[1] = 0, 1
+    e = make_engine(dcd, cfg, max_pass_tokens=2048)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    state, questions = tiny_inputs(seed=21, vocab=4096, state_len=1100, qlens=(70, 21, 129, 5))
+    st, ost = e.capture_state(state), o.capture_state(state)
+    for layer, what, tol in [(0, 2, 2e-2), (0, 3, 5e-2), (1, 0, 0.12), (1, 1, 0.12)]:
+        d = float(np.abs(st.tensor(layer, what) - ost.tensor(layer, what)).max())
+        assert d < tol, (layer, what, d)
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    err = float(np.abs(got - want).max())
+    agree, near = argmax_report(got, want, gap=0.06)
+    print(f"long-state d3 2-layer: max-abs {err:.4g}, argmax agree {agree.mean():.3f}, near-ties {int(near.sum())}")
+    assert err < 0.12 and (agree | near).all()
+    e.close()
