@@ -55,7 +55,7 @@ def parse():
     ap.add_argument("--qmin", type=int, default=48)
     ap.add_argument("--qmax", type=int, default=160)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8", "w4a16"],
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8", "w4a16", "nvfp4"],
                     help="bf16 = BASELINE configs[1] (the headline); fp8 = e4m3 GEMMs in the question pass (extra, not the headline)")
     return ap.parse_args()
 
@@ -210,7 +210,7 @@ def run_ours(args):
     cfg = dcd.d3_config(num_layers=args.layers, dtype=1)
     opt = dcd.Options()
     opt.max_pass_tokens = max(args.state_len, args.questions * args.qmax)
-    opt.precision = {"bf16": 0, "w4a16": 1, "fp8": 2}[args.precision]
+    opt.precision = {"bf16": 0, "w4a16": 1, "fp8": 2, "nvfp4": 3}[args.precision]
     eng = dcd.Engine(cfg, opt, device=local)
     eng.init_random(0)
 
@@ -287,7 +287,8 @@ def run_ours(args):
             "metric": METRIC, "value": world * B * args.steps / t_dev, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"bf16": "bf16", "fp8": "fp8 e4m3 GEMMs in the question pass (bf16 capture, bf16 activations elsewhere)",
-                      "w4a16": "bf16 activations, int4 group-128 weights (BASELINE configs[2] format)"}[args.precision],
+                      "w4a16": "bf16 activations, int4 group-128 weights (BASELINE configs[2] format)",
+                      "nvfp4": "NVFP4 weights and activations (W4A4 semantics) computed on the bf16 tensor-core GEMM"}[args.precision],
             "data": "synthetic", "config": config_dict(args, world),
             "states_per_s": world * args.steps / t_dev,
             "step_tflop": flops_step / 1e12, "model_tflops_per_gpu": flops_step * args.steps / t_dev / 1e12,

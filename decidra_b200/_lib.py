@@ -73,6 +73,9 @@ SIGNATURES = {
     "dcd_k_quant_fp8_rows": (I, [P, SZ, P, P, I, I, F, I, P]),
     "dcd_k_quant_w4_g128": (I, [P, P, P, I, I, P]),
     "dcd_k_dequant_w4_g128": (I, [P, P, P, I, I, P]),
+    "dcd_k_nvfp4_quant_rows": (I, [P, SZ, F, P, P, I, I, P]),
+    "dcd_k_nvfp4_dequant_rows": (I, [P, P, P, I, I, P]),
+    "dcd_k_nvfp4_fakequant_rows": (I, [P, SZ, F, P, I, I, P]),
     "dcd_k_gemm_fma": (I, [P, P, P, I, I, I, I, P]),
     "dcd_k_rmsnorm": (I, [P, P, P, I, I, F, I, I, P]),
     "dcd_k_add_rmsnorm": (I, [P, P, P, P, P, I, I, F, I, P]),

@@ -48,6 +48,9 @@ struct LayerW {
   // W4A16 group-128 images (precision 1): the only resident copy of the six GEMM weights
   struct W4 { uint32_t* q = nullptr; void* scale = nullptr; int N = 0, K = 0; };
   W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
+  // NVFP4 images (precision 3): e2m1 codes, e4m3 scale per 16, f32 tensor scale and GEMM alpha on the device
+  struct NV4 { uint8_t* q = nullptr; uint8_t* sf = nullptr; float* wg = nullptr; float* alpha = nullptr; int N = 0, K = 0; };
+  NV4 n_gu, n_down, n_qkv, n_o, n_gin, n_out;
 };
 
 }  // namespace
@@ -95,6 +98,9 @@ struct dcd_engine {
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
   bool attn_tc = false, gdn_chunked = false;
+  bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
+  void* xstage = nullptr;              // bf16 [Tm, max K]: activations after the NVFP4 round trip
+  unsigned int* amax_tmp = nullptr;
   bool w4 = false;                     // precision 1: int4 g128 weights, dequantised per GEMM into wstage
   void* wstage = nullptr;              // bf16 [max N*K] stage shared by all W4 GEMMs
   bool fp8 = false, fp8_dirty = true;  // precision 2: e4m3 GEMMs in question passes of >= fp8_min_rows rows
@@ -152,17 +158,17 @@ GenSpec spec_for(int kind, bool bf) {
 
 // Where a logical tensor lives: base pointer of the (possibly fused) destination, its logical
 // shape, the row mapping into the destination and whether it is stored as f32.
-struct Loc { void* base; size_t rows, cols; int mode, row_offset, dst_stride; bool f32; LayerW::W4* w4 = nullptr; };
+struct Loc { void* base; size_t rows, cols; int mode, row_offset, dst_stride; bool f32; LayerW::W4* w4 = nullptr; LayerW::NV4* nv = nullptr; };
 
 bool locate(dcd_engine* e, int layer, int kind, Loc* out) {
   const dcd_model_config& c = e->c;
   const size_t H = e->H;
   auto L = [&](void* b, size_t r, size_t cc, int mode, int ro, int ds, bool f) { *out = Loc{b, r, cc, mode, ro, ds, f, nullptr}; return b != nullptr; };
   // GEMM weights of a W4 engine live as int4 images; the logical tensor is staged through wstage
-  auto G = [&](void* b, LayerW::W4& img, size_t r, size_t cc, int mode, int ro, int ds) {
-    if (!e->w4) return L(b, r, cc, mode, ro, ds, false);
-    *out = Loc{e->wstage, r, cc, mode, ro, ds, false, &img};
-    return true;
+  auto G = [&](void* b, LayerW::W4& img, LayerW::NV4& nimg, size_t r, size_t cc, int mode, int ro, int ds) {
+    if (e->w4) { *out = Loc{e->wstage, r, cc, mode, ro, ds, false, &img, nullptr}; return true; }
+    if (e->nv4) { *out = Loc{e->wstage, r, cc, mode, ro, ds, false, nullptr, &nimg}; return true; }
+    return L(b, r, cc, mode, ro, ds, false);
   };
   if (layer < 0) {
     switch (kind) {
@@ -178,27 +184,27 @@ bool locate(dcd_engine* e, int layer, int kind, Loc* out) {
   switch (kind) {
     case DCD_T_INPUT_NORM: return L(w.input_norm, 1, H, 0, 0, (int)H, false);
     case DCD_T_POST_NORM: return L(w.post_norm, 1, H, 0, 0, (int)H, false);
-    case DCD_T_GATE: return G(w.w_gu, w.g_gu, e->I, H, 1, 0, (int)H);
-    case DCD_T_UP: return G(w.w_gu, w.g_gu, e->I, H, 2, 0, (int)H);
-    case DCD_T_DOWN: return G(w.w_down, w.g_down, H, e->I, 0, 0, e->I);
+    case DCD_T_GATE: return G(w.w_gu, w.g_gu, w.n_gu, e->I, H, 1, 0, (int)H);
+    case DCD_T_UP: return G(w.w_gu, w.g_gu, w.n_gu, e->I, H, 2, 0, (int)H);
+    case DCD_T_DOWN: return G(w.w_down, w.g_down, w.n_down, H, e->I, 0, 0, e->I);
   }
   if (w.full) {
     switch (kind) {
-      case DCD_T_Q: return G(w.w_qkv, w.g_qkv, e->qcols, H, 0, 0, (int)H);
-      case DCD_T_K: return G(w.w_qkv, w.g_qkv, e->kvcols, H, 0, e->qcols, (int)H);
-      case DCD_T_V: return G(w.w_qkv, w.g_qkv, e->kvcols, H, 0, e->qcols + e->kvcols, (int)H);
-      case DCD_T_O: return G(w.w_o, w.g_o, H, (size_t)c.heads * hd, 0, 0, c.heads * hd);
+      case DCD_T_Q: return G(w.w_qkv, w.g_qkv, w.n_qkv, e->qcols, H, 0, 0, (int)H);
+      case DCD_T_K: return G(w.w_qkv, w.g_qkv, w.n_qkv, e->kvcols, H, 0, e->qcols, (int)H);
+      case DCD_T_V: return G(w.w_qkv, w.g_qkv, w.n_qkv, e->kvcols, H, 0, e->qcols + e->kvcols, (int)H);
+      case DCD_T_O: return G(w.w_o, w.g_o, w.n_o, H, (size_t)c.heads * hd, 0, 0, c.heads * hd);
       case DCD_T_QNORM: return L(w.qnorm, 1, hd, 0, 0, hd, false);
       case DCD_T_KNORM: return L(w.knorm, 1, hd, 0, 0, hd, false);
       default: return false;
     }
   }
   switch (kind) {
-    case DCD_T_IN_QKV: return G(w.w_gin, w.g_gin, e->conv_dim, H, 0, 0, (int)H);
-    case DCD_T_IN_Z: return G(w.w_gin, w.g_gin, e->vd, H, 0, e->conv_dim, (int)H);
-    case DCD_T_IN_B: return G(w.w_gin, w.g_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd, (int)H);
-    case DCD_T_IN_A: return G(w.w_gin, w.g_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd + c.gdn_v_heads, (int)H);
-    case DCD_T_OUT: return G(w.w_out, w.g_out, H, e->vd, 0, 0, e->vd);
+    case DCD_T_IN_QKV: return G(w.w_gin, w.g_gin, w.n_gin, e->conv_dim, H, 0, 0, (int)H);
+    case DCD_T_IN_Z: return G(w.w_gin, w.g_gin, w.n_gin, e->vd, H, 0, e->conv_dim, (int)H);
+    case DCD_T_IN_B: return G(w.w_gin, w.g_gin, w.n_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd, (int)H);
+    case DCD_T_IN_A: return G(w.w_gin, w.g_gin, w.n_gin, c.gdn_v_heads, H, 0, e->conv_dim + e->vd + c.gdn_v_heads, (int)H);
+    case DCD_T_OUT: return G(w.w_out, w.g_out, w.n_out, H, e->vd, 0, 0, e->vd);
     case DCD_T_CONV: return L(w.conv, e->conv_dim, 4, 0, 0, 4, false);
     case DCD_T_A_LOG: return L(w.A_log, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
     case DCD_T_DT_BIAS: return L(w.dt_bias, 1, c.gdn_v_heads, 0, 0, c.gdn_v_heads, true);
@@ -259,7 +265,22 @@ struct Scope {
 // native/src/engine.rs:4144-4296); plain FMA otherwise.
 template <typename T>
 int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
-         const LayerW::W4* g4, void* C, int M, int N, int K, int ldc, int epi) {
+         const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi) {
+  if (e->nv4) {
+    // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131): both operands go through the
+    // e2m1/e4m3 round trip; their dequantised values are exact in bf16, so the bf16 tensor-core GEMM
+    // gives the block-scaled product; alpha = 1/(weight_global*input_global) in the epilogue.
+    {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 0.5625 * N * (double)K + 2.0 * N * (double)K + 4.0 * M * (double)K, 2);
+      CK(e, launch_nvfp4_dequant_rows(n4->q, n4->sf, nullptr, (bf16*)e->wstage, N, K, e->stream), "nvfp4 weight dequantisation");
+      CK(e, launch_nvfp4_fakequant_rows((const bf16*)X, (size_t)K, 1.0f, (bf16*)e->xstage, M, K, e->stream), "nvfp4 activation quantisation");
+    }
+    TcTensorMap ta;
+    if (tc_make_tmap_a(&ta, e->xstage, M, K)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
+    Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
+    CK(e, tc_gemm_launch(&ta, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream, n4->alpha), "tcgen05 gemm (nvfp4 operands)");
+    return DCD_OK;
+  }
   if (e->w4) {
     // W4A16: int4 -> bf16 into the shared stage, then the bf16 tensor-core GEMM reads the stage
     // (the reference's dequant_w4a16_bf16 + BF16 GEMM route, native/src/engine.rs:4516-4558)
@@ -320,7 +341,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
     }
     if (w.full) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, &w.n_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
@@ -356,10 +377,10 @@ int run_layers(dcd_engine* e, const Pass& p) {
                                    e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
         }
       }
-      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, e->mix, T_, H, heads * hd, H, 0);
+      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, e->mix, T_, H, heads * hd, H, 0);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, &w.n_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
       if (rc) return rc;
       T* big = (T*)e->big;
       if (p.mode == 0) {
@@ -397,7 +418,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
         CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
                                       c.rms_eps, s), "rmsnorm_gated");
       }
-      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, e->mix, T_, H, e->vd, H, 0);
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, e->mix, T_, H, e->vd, H, 0);
       if (rc) return rc;
     }
     {
@@ -406,15 +427,15 @@ int run_layers(dcd_engine* e, const Pass& p) {
          "add_rmsnorm");
     }
     if (tc) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, e->act, T_, e->gu_rows, H, e->I, 1);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, &w.n_gu, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, &w.n_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
       if (rc) return rc;
       Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->I * e->esz * 3.0, 1);
       CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
-    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, e->mix, T_, H, e->I, H, 0);
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, e->mix, T_, H, e->I, H, 0);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
@@ -582,7 +603,9 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (c.dtype != 0 && c.dtype != 1) return fail(nullptr, DCD_E_INVALID, "dtype must be 0 (f32) or 1 (bf16)");
   dcd_options o = {};
   if (opt) o = *opt;
-  if (o.precision < 0 || o.precision > 2) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d is not built yet (0 = config dtype, 1 = w4a16 g128, 2 = fp8)", o.precision);
+  if (o.precision < 0 || o.precision > 3) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d unknown (0 = config dtype, 1 = w4a16 g128, 2 = fp8, 3 = nvfp4)", o.precision);
+  if (o.precision == 3 && ((c.hidden % 16) || (c.intermediate % 16) || ((c.heads * c.head_dim) % 16) || ((c.gdn_v_heads * c.gdn_dv) % 16) || o.gemm_path != 0))
+    return fail(nullptr, DCD_E_UNSUPPORTED, "nvfp4 needs every GEMM K to be a multiple of 16 and the tensor-core GEMM path");
   if (o.precision != 0 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 / fp8 precision needs a bf16 engine (dtype 1)");
   if (o.precision == 1 && ((c.hidden % 8) || (c.intermediate % 8))) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 needs K multiples of 8");
   if (o.fp8_min_rows <= 0) o.fp8_min_rows = 512;
@@ -655,17 +678,19 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (e->attn_tc) CRE(attn_tc_prepare_device(), "tcgen05 attention shared-memory attribute");
   e->fp8 = o.precision == 2 && o.gemm_path == 0;
   e->w4 = o.precision == 1;
+  e->nv4 = o.precision == 3;
   e->gdn_chunked = e->bf && o.gdn_path == 0 && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
   const size_t es = e->esz, H = e->H;
   // ---- weights
   e->layers.resize(c.num_layers);
-  if (e->w4) {
+  if (e->w4 || e->nv4) {
     size_t mx = (size_t)e->gu_rows * H;
     auto up = [&](size_t n) { if (n > mx) mx = n; };
     up(H * (size_t)e->I); up((size_t)e->qkv_n * H); up(H * (size_t)c.heads * c.head_dim); up((size_t)e->gin_n * H); up(H * (size_t)e->vd);
     CRA(e->wstage, mx * 2, true, &e->weight_bytes);
+    if (e->nv4) CRA(e->amax_tmp, 256, true, &e->weight_bytes);
   }
   CRA(e->embed, (size_t)c.vocab * H * es, false, &e->weight_bytes);
   CRA(e->final_norm, H * es, true, &e->weight_bytes);
@@ -675,8 +700,24 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
     w.full = c.layer_is_full[i] != 0;
     CRA(w.input_norm, H * es, true, &e->weight_bytes);
     CRA(w.post_norm, H * es, true, &e->weight_bytes);
-    if (e->w4) {
+    if (e->nv4) {
+      auto mkn = [&](LayerW::NV4& g, size_t n, size_t k) -> int {
+        g.N = (int)n; g.K = (int)k;
+        int rc = dev_alloc(e, reinterpret_cast<void**>(&g.q), n * k / 2, true, &e->weight_bytes);
+        if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&g.sf), n * k / 16, true, &e->weight_bytes);
+        if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&g.wg), 256, true, &e->weight_bytes);
+        g.alpha = g.wg + 1;
+        return rc;
+      };
+      int rc = mkn(w.n_gu, e->gu_rows, H);
+      if (!rc) rc = mkn(w.n_down, H, e->I);
+      if (!rc && w.full) { rc = mkn(w.n_qkv, e->qkv_n, H); if (!rc) rc = mkn(w.n_o, H, (size_t)c.heads * c.head_dim); }
+      if (!rc && !w.full) { rc = mkn(w.n_gin, e->gin_n, H); if (!rc) rc = mkn(w.n_out, H, e->vd); }
+      if (rc) { g_create_error = e->err; dcd_engine_destroy(e); return rc; }
+    }
+    if (e->w4 || e->nv4) {
       auto mk4 = [&](LayerW::W4& g, size_t n, size_t k) -> int {
+        if (!e->w4) return DCD_OK;
         g.N = (int)n; g.K = (int)k;
         int rc = dev_alloc(e, reinterpret_cast<void**>(&g.q), n * ((k + 7) / 8) * 4, true, &e->weight_bytes);
         if (!rc) rc = dev_alloc(e, &g.scale, n * ((k + 127) / 128) * 2, true, &e->weight_bytes);
@@ -781,6 +822,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->max_k = e->I;
   if (e->H > e->max_k) e->max_k = e->H;
   if ((int)aw > e->max_k) e->max_k = (int)aw;
+  if (e->nv4) CRA(e->xstage, Tm * (size_t)e->max_k * 2, false, ws);
   if (e->fp8) {
     CRA(e->aq, Tm * (size_t)e->max_k, false, ws);
     CRA(e->a_scale, Tm * 4, false, ws);
@@ -850,22 +892,41 @@ int dcd_rebind_blas(dcd_engine* e) { return e ? DCD_OK : DCD_E_INVALID; }
 // W4 engines: a logical GEMM tensor is edited in the bf16 stage — bring the whole fused matrix in
 // (dequantise), let the caller write or read its rows, then quantise the matrix back.
 static int w4_stage_in(dcd_engine* e, const Loc& L) {
+  if (L.nv) {
+    e->launches += 1;
+    CK(e, launch_nvfp4_dequant_rows(L.nv->q, L.nv->sf, L.nv->wg, (bf16*)e->wstage, L.nv->N, L.nv->K, e->stream), "nvfp4 stage in");
+    return DCD_OK;
+  }
   if (!L.w4) return DCD_OK;
   e->launches += 1;
   CK(e, launch_dequant_w4_g128(L.w4->q, L.w4->scale, (bf16*)e->wstage, L.w4->N, L.w4->K, e->stream), "w4 stage in");
   return DCD_OK;
 }
 static int w4_stage_out(dcd_engine* e, const Loc& L) {
+  if (L.nv) {
+    // tensor scale 2688/absmax of the whole fused matrix, then per-16 e4m3 scales and e2m1 codes
+    e->launches += 3;
+    CK(e, launch_absmax_bf16((const bf16*)e->wstage, (size_t)L.nv->N * L.nv->K, e->amax_tmp, e->stream), "nvfp4 absmax");
+    CK(e, launch_nvfp4_global(e->amax_tmp, L.nv->wg, L.nv->alpha, 1.0f, e->stream), "nvfp4 tensor scale");
+    CK(e, launch_nvfp4_quant_rows((const bf16*)e->wstage, (size_t)L.nv->K, L.nv->wg, 0.f, L.nv->q, L.nv->sf, L.nv->N, L.nv->K, e->stream), "nvfp4 stage out");
+    return DCD_OK;
+  }
   if (!L.w4) return DCD_OK;
   e->launches += 1;
   CK(e, launch_quant_w4_g128((const bf16*)e->wstage, L.w4->q, L.w4->scale, L.w4->N, L.w4->K, e->stream), "w4 stage out");
   return DCD_OK;
 }
 
-static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind) {
+// first/last: position of this logical tensor inside its fused matrix. Quantised engines zero the
+// stage before the first tensor and quantise the whole fused matrix once after the last one (the
+// NVFP4 tensor scale is taken over the complete matrix).
+static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind, bool first = true, bool last = true) {
   Loc L;
   if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
-  if (int rc = w4_stage_in(e, L)) return rc;
+  if ((L.w4 || L.nv) && first) {
+    const size_t n = L.w4 ? (size_t)L.w4->N * L.w4->K : (size_t)L.nv->N * L.nv->K;
+    CK(e, cudaMemsetAsync(e->wstage, 0, n * 2, e->stream), "stage clear");
+  }
   const GenSpec sp = spec_for(kind, e->bf);
   const float cc = (float)((double)sp.p0 / IH8_STD);
   const uint64_t key = gen_tensor_key(seed, layer, kind);
@@ -874,22 +935,27 @@ static int gen_one(dcd_engine* e, uint64_t seed, int layer, int kind) {
   if (L.f32) CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
   else if (e->bf) CK(e, launch_gen_tensor<bf16>((bf16*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
   else CK(e, launch_gen_tensor<float>((float*)L.base, key, 0, count, (int)L.cols, sp.dist, sp.p0, sp.p1, cc, sp.round_bf, L.mode, L.row_offset, L.dst_stride, e->stream), "gen");
-  return w4_stage_out(e, L);
+  return last ? w4_stage_out(e, L) : DCD_OK;
 }
 
 int dcd_engine_init_random(dcd_engine* e, uint64_t seed) {
   if (!e) return DCD_E_INVALID;
   cudaSetDevice(e->device);
-  static const int globals[] = {DCD_T_EMBED, DCD_T_FINAL_NORM, DCD_T_READOUT};
-  static const int common[] = {DCD_T_INPUT_NORM, DCD_T_POST_NORM, DCD_T_GATE, DCD_T_UP, DCD_T_DOWN};
-  static const int full[] = {DCD_T_Q, DCD_T_K, DCD_T_V, DCD_T_O, DCD_T_QNORM, DCD_T_KNORM};
-  static const int gdn[] = {DCD_T_IN_QKV, DCD_T_IN_Z, DCD_T_IN_B, DCD_T_IN_A, DCD_T_OUT, DCD_T_CONV, DCD_T_A_LOG, DCD_T_DT_BIAS, DCD_T_GNORM};
+  struct K { int kind; bool first, last; };
+  static const K globals[] = {{DCD_T_EMBED, true, true}, {DCD_T_FINAL_NORM, true, true}, {DCD_T_READOUT, true, true}};
+  static const K common[] = {{DCD_T_INPUT_NORM, true, true}, {DCD_T_POST_NORM, true, true}, {DCD_T_GATE, true, false}, {DCD_T_UP, false, true},
+                             {DCD_T_DOWN, true, true}};
+  static const K full[] = {{DCD_T_Q, true, false}, {DCD_T_K, false, false}, {DCD_T_V, false, true}, {DCD_T_O, true, true},
+                           {DCD_T_QNORM, true, true}, {DCD_T_KNORM, true, true}};
+  static const K gdn[] = {{DCD_T_IN_QKV, true, false}, {DCD_T_IN_Z, false, false}, {DCD_T_IN_B, false, false}, {DCD_T_IN_A, false, true},
+                          {DCD_T_OUT, true, true}, {DCD_T_CONV, true, true}, {DCD_T_A_LOG, true, true}, {DCD_T_DT_BIAS, true, true},
+                          {DCD_T_GNORM, true, true}};
   int rc;
-  for (int k : globals) if ((rc = gen_one(e, seed, -1, k))) return rc;
+  for (const K& k : globals) if ((rc = gen_one(e, seed, -1, k.kind, k.first, k.last))) return rc;
   for (int i = 0; i < e->c.num_layers; ++i) {
-    for (int k : common) if ((rc = gen_one(e, seed, i, k))) return rc;
-    if (e->layers[i].full) { for (int k : full) if ((rc = gen_one(e, seed, i, k))) return rc; }
-    else { for (int k : gdn) if ((rc = gen_one(e, seed, i, k))) return rc; }
+    for (const K& k : common) if ((rc = gen_one(e, seed, i, k.kind, k.first, k.last))) return rc;
+    if (e->layers[i].full) { for (const K& k : full) if ((rc = gen_one(e, seed, i, k.kind, k.first, k.last))) return rc; }
+    else { for (const K& k : gdn) if ((rc = gen_one(e, seed, i, k.kind, k.first, k.last))) return rc; }
   }
   CK(e, cudaStreamSynchronize(e->stream), "init_random sync");
   e->weights_ready = true;

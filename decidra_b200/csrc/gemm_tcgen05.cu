@@ -92,11 +92,13 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // (silu_mul_bf16, native/kernels/kernels.cu:492-501, applied to the bf16-rounded GEMM outputs).
 // ESZ 1 (e4m3 operands): the accumulator is scaled by w_scale[column] * a_scale[row] before rounding
 // (scale_fp8_gemm_bf16, native/kernels/kernels.cu:208-220); ESZ 2 ignores the scale pointers.
+// alpha (device scalar, may be null): the accumulator is multiplied by *alpha before rounding
+// (cuBLASLt alpha = 1/(weight_global*input_global) of the NVFP4 path, native/src/engine.rs:4108).
 template <int EPI, int ESZ>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
                     int M, int N, int K, int ldc, const float* __restrict__ a_scale, const float* __restrict__ w_scale,
-                    int* __restrict__ err) {
+                    const float* __restrict__ alpha, int* __restrict__ err) {
   constexpr int BKE = 128 / ESZ;  // K elements per 128-byte swizzled row
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -199,6 +201,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row = m_idx * BM + lane_base + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(acc * BN);
       const float rs = (ESZ == 1 && row < M) ? a_scale[row] : 1.0f;
+      const float al = alpha ? __ldg(alpha) : 1.0f;
       if (EPI == 0) {
         bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
 #pragma unroll 1
@@ -213,7 +216,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (col + 8 <= N) {
                 float f[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * al;
                 if (ESZ == 1) {
                   const float4 w0 = __ldg(reinterpret_cast<const float4*>(w_scale + col));
                   const float4 w1 = __ldg(reinterpret_cast<const float4*>(w_scale + col + 4));
@@ -255,7 +258,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  float ga = __uint_as_float(g[v * 8 + j]), ua = __uint_as_float(u[v * 8 + j]);
+                  float ga = __uint_as_float(g[v * 8 + j]) * al, ua = __uint_as_float(u[v * 8 + j]) * al;
                   if (ESZ == 1) { ga = ga * wg[j] * rs; ua = ua * wu[j] * rs; }
                   const float gg = Ty<bf16>::rnd(ga);
                   const float uu = Ty<bf16>::rnd(ua);
@@ -370,13 +373,13 @@ cudaError_t tc_gemm_prepare_device() {
 }
 
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                           int sm_count, int* err, cudaStream_t stream) {
+                           int sm_count, int* err, cudaStream_t stream, const float* alpha) {
   const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, err);
-  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, err);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err);
+  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err);
   return cudaGetLastError();
 }
 
@@ -388,8 +391,8 @@ cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, v
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, err);
-  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, err);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err);
+  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err);
   return cudaGetLastError();
 }
 

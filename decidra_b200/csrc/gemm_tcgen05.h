@@ -19,8 +19,9 @@ bool tc_shape_ok(int M, int N, int K);
 // Raises the kernel's dynamic shared-memory limit on the current device (call once per device).
 cudaError_t tc_gemm_prepare_device();
 // epi 0: C[M,N] (row stride ldc). epi 1: SwiGLU over gate/up-interleaved weights, C[M,N/2].
+// alpha: optional device scalar multiplied into the accumulator before rounding.
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                           int sm_count, int* err, cudaStream_t stream);
+                           int sm_count, int* err, cudaStream_t stream, const float* alpha = nullptr);
 
 // e4m3 (FP8) operand form: X[M,K] and W[N,K] hold one byte per element; the f32 accumulator is
 // scaled by w_scale[n] * a_scale[m] before rounding to bf16. Needs K % 16 == 0, N % 8 == 0.

@@ -44,6 +44,16 @@ int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N
   return rc_of(launch_dequant_w4_g128((const uint32_t*)packed, scales, (bf16*)W, N, K, S(stream)));
 }
 
+int dcd_k_nvfp4_quant_rows(const void* x, size_t x_stride, float global, void* packed, void* scales, int rows, int K, void* stream) {
+  return rc_of(launch_nvfp4_quant_rows((const bf16*)x, x_stride, nullptr, global, (uint8_t*)packed, (uint8_t*)scales, rows, K, S(stream)));
+}
+int dcd_k_nvfp4_dequant_rows(const void* packed, const void* scales, void* out, int rows, int K, void* stream) {
+  return rc_of(launch_nvfp4_dequant_rows((const uint8_t*)packed, (const uint8_t*)scales, nullptr, (bf16*)out, rows, K, S(stream)));
+}
+int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, void* out, int rows, int K, void* stream) {
+  return rc_of(launch_nvfp4_fakequant_rows((const bf16*)x, x_stride, global, (bf16*)out, rows, K, S(stream)));
+}
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

@@ -1235,3 +1235,160 @@ cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, b
   dequant_w4_g128_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(packed, (const __half*)scales, W, N, K);
   return cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// NVFP4: e2m1 values, one e4m3 scale per 16 elements along K, one f32 scale per tensor.
+// Quantisation rule of quant_nvfp4_act_bf16 / fp4_encode (native/kernels/kernels.cu:222-277):
+//   v = x * global; sf = e4m3_satfinite(max(absmax16(v)/6, 1e-10)); code = fp4_encode(v / decode(sf));
+//   packed byte = low nibble even k, high nibble odd k. (Scales are kept row-major [rows, K/16] here.)
+// e2m1 * e4m3 has at most five significant bits, so the dequantised element decode(code)*decode(sf)
+// is exact in bf16: the bf16 tensor-core GEMM on dequantised operands reproduces the block-scaled
+// FP4 product exactly up to the f32 summation order; alpha = 1/(weight_global*input_global) is
+// applied in the GEMM epilogue (native/src/engine.rs:4108).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t fp4_encode(float x) {
+  const float a = fabsf(x);
+  uint8_t e;
+  if (a < 0.25f) e = 0;
+  else if (a < 0.75f) e = 1;
+  else if (a < 1.25f) e = 2;
+  else if (a < 1.75f) e = 3;
+  else if (a < 2.5f) e = 4;
+  else if (a < 3.5f) e = 5;
+  else if (a < 5.0f) e = 6;
+  else e = 7;
+  return (x < 0.f) ? (uint8_t)(e | 8) : e;
+}
+__device__ __forceinline__ float fp4_decode(uint8_t c) {
+  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float v = mag[c & 7];
+  return (c & 8) ? -v : v;
+}
+__device__ __forceinline__ float e4m3_decode(uint8_t c) {
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(c, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&hr));
+}
+
+// |x| maximum of a bf16 matrix into *out (float bits; non-negative floats order like unsigned ints).
+__global__ void absmax_bf16_kernel(const bf16* __restrict__ x, size_t n, unsigned int* __restrict__ out) {
+  float m = 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(__bfloat162float(x[i])));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));
+}
+// *global = 2688 / absmax (448 * 6: the largest group scale lands on the top of the e4m3 range)
+__global__ void nvfp4_global_from_absmax_kernel(const unsigned int* __restrict__ amax, float* __restrict__ global, float* __restrict__ alpha,
+                                                float input_global) {
+  const float a = __uint_as_float(*amax);
+  const float g = a > 0.f ? 2688.0f / a : 1.0f;
+  *global = g;
+  *alpha = 1.0f / (g * input_global);
+}
+
+// mode 0: store codes + scales. mode 1: store the dequantised value decode(code)*decode(sf) (no global) as bf16.
+template <int MODE>
+__global__ void __launch_bounds__(256) nvfp4_rows_kernel(const bf16* __restrict__ x, size_t x_stride, const float* __restrict__ global_ptr,
+                                                         float global_imm, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                                                         bf16* __restrict__ deq, int K) {
+  const int row = blockIdx.x;
+  const float gl = global_ptr ? __ldg(global_ptr) : global_imm;
+  const bf16* src = x + (size_t)row * x_stride;
+  const int groups = K / 16;
+  for (int j = threadIdx.x; j < groups; j += blockDim.x) {
+    float v[16];
+    float m = 0.f;
+    const uint4 lo = *reinterpret_cast<const uint4*>(src + j * 16);
+    const uint4 hi = *reinterpret_cast<const uint4*>(src + j * 16 + 8);
+    float f[8];
+    unpack8(lo, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = f[i] * gl;
+    unpack8(hi, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[8 + i] = f[i] * gl;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    const float sf = fmaxf(m / 6.0f, 1e-10f);
+    const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+    const float sd = e4m3_decode(sb);
+    if (MODE == 0) {
+      uint32_t w[2] = {0, 0};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t byte = (uint32_t)fp4_encode(v[2 * i] / sd) | ((uint32_t)fp4_encode(v[2 * i + 1] / sd) << 4);
+        w[i >> 2] |= byte << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(packed + (size_t)row * (K / 2) + j * 8) = make_uint2(w[0], w[1]);
+      scales[(size_t)row * groups + j] = sb;
+    } else {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = fp4_decode(fp4_encode(v[i] / sd)) * sd;
+      *reinterpret_cast<uint4*>(deq + (size_t)row * K + j * 16) = pack8(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = fp4_decode(fp4_encode(v[8 + i] / sd)) * sd;
+      *reinterpret_cast<uint4*>(deq + (size_t)row * K + j * 16 + 8) = pack8(o);
+    }
+  }
+}
+// codes + scales -> bf16 decode(code)*decode(sf) [* inv_global when given]
+__global__ void __launch_bounds__(256) nvfp4_dequant_rows_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                                                 const float* __restrict__ global_ptr, bf16* __restrict__ out, size_t total_groups,
+                                                                 int K) {
+  const size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gi >= total_groups) return;
+  const int groups = K / 16;
+  const size_t row = gi / groups;
+  const int j = (int)(gi - row * groups);
+  float sd = e4m3_decode(scales[gi]);
+  if (global_ptr) {
+    const float gsc = __ldg(global_ptr);
+    if (gsc > 0.f) sd = sd / gsc;
+  }
+  const uint2 w = *reinterpret_cast<const uint2*>(packed + row * (K / 2) + j * 8);
+  const uint32_t ww[2] = {w.x, w.y};
+  float o[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t byte = (ww[i >> 2] >> (8 * (i & 3))) & 0xff;
+    o[2 * i] = fp4_decode((uint8_t)(byte & 0xf)) * sd;
+    o[2 * i + 1] = fp4_decode((uint8_t)(byte >> 4)) * sd;
+  }
+  float a[8], b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { a[i] = o[i]; b[i] = o[8 + i]; }
+  *reinterpret_cast<uint4*>(out + row * K + j * 16) = pack8(a);
+  *reinterpret_cast<uint4*>(out + row * K + j * 16 + 8) = pack8(b);
+}
+
+cudaError_t launch_absmax_bf16(const bf16* x, size_t n, unsigned int* out, cudaStream_t s) {
+  cudaError_t e = cudaMemsetAsync(out, 0, 4, s);
+  if (e != cudaSuccess) return e;
+  absmax_bf16_kernel<<<1024, 256, 0, s>>>(x, n, out);
+  return cudaGetLastError();
+}
+cudaError_t launch_nvfp4_global(const unsigned int* amax, float* global, float* alpha, float input_global, cudaStream_t s) {
+  nvfp4_global_from_absmax_kernel<<<1, 1, 0, s>>>(amax, global, alpha, input_global);
+  return cudaGetLastError();
+}
+cudaError_t launch_nvfp4_quant_rows(const bf16* x, size_t x_stride, const float* global_ptr, float global_imm, uint8_t* packed, uint8_t* scales,
+                                    int rows, int K, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if ((K % 16) || (x_stride % 8)) return cudaErrorInvalidValue;
+  nvfp4_rows_kernel<0><<<rows, 256, 0, s>>>(x, x_stride, global_ptr, global_imm, packed, scales, nullptr, K);
+  return cudaGetLastError();
+}
+cudaError_t launch_nvfp4_fakequant_rows(const bf16* x, size_t x_stride, float global_imm, bf16* out, int rows, int K, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if ((K % 16) || (x_stride % 8)) return cudaErrorInvalidValue;
+  nvfp4_rows_kernel<1><<<rows, 256, 0, s>>>(x, x_stride, nullptr, global_imm, nullptr, nullptr, out, K);
+  return cudaGetLastError();
+}
+cudaError_t launch_nvfp4_dequant_rows(const uint8_t* packed, const uint8_t* scales, const float* global_ptr, bf16* out, int rows, int K,
+                                      cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  const size_t groups = (size_t)rows * (K / 16);
+  nvfp4_dequant_rows_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, s>>>(packed, scales, global_ptr, out, groups, K);
+  return cudaGetLastError();
+}

@@ -77,3 +77,13 @@ cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, flo
 // fp16 scales [N, ceil(K/128)]. K % 8 == 0.
 cudaError_t launch_quant_w4_g128(const __nv_bfloat16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s);
 cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, __nv_bfloat16* W, int N, int K, cudaStream_t s);
+
+// NVFP4 (e2m1 + e4m3 per 16 + f32 per tensor). K % 16 == 0. Scales row-major [rows, K/16].
+cudaError_t launch_absmax_bf16(const __nv_bfloat16* x, size_t n, unsigned int* out, cudaStream_t s);
+cudaError_t launch_nvfp4_global(const unsigned int* amax, float* global, float* alpha, float input_global, cudaStream_t s);
+cudaError_t launch_nvfp4_quant_rows(const __nv_bfloat16* x, size_t x_stride, const float* global_ptr, float global_imm, uint8_t* packed,
+                                    uint8_t* scales, int rows, int K, cudaStream_t s);
+cudaError_t launch_nvfp4_fakequant_rows(const __nv_bfloat16* x, size_t x_stride, float global_imm, __nv_bfloat16* out, int rows, int K,
+                                        cudaStream_t s);
+cudaError_t launch_nvfp4_dequant_rows(const uint8_t* packed, const uint8_t* scales, const float* global_ptr, __nv_bfloat16* out, int rows,
+                                      int K, cudaStream_t s);

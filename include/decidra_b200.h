@@ -63,7 +63,11 @@ typedef struct dcd_options {
                                of >= fp8_min_rows rows; capture stays bf16 — Engine::fp8_gemm, native/src/engine.rs:4144-4296);
                                1 = w4a16 group 128: the GEMM weights are held only as int4 + fp16 group scales and
                                dequantised per GEMM into a shared bf16 stage (dequant_w4a16_bf16 route,
-                               native/src/engine.rs:4516-4558), all passes; 3 = nvfp4 is not built yet: DCD_E_UNSUPPORTED */
+                               native/src/engine.rs:4516-4558), all passes; 3 = nvfp4 with the reference's W4A4 semantics
+                               (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131): weights held as e2m1 + e4m3 scale per 16 +
+                               f32 tensor scale, activations through the same round trip per GEMM, all passes; the operands'
+                               dequantised values are exact in bf16 and feed the bf16 tensor-core GEMM (a native block-scaled
+                               FP4 MMA kernel is not built yet) */
   int32_t max_pass_tokens;  /* workspace rows; also the longest state that can be captured. default 16384 */
   int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
   int64_t max_keys;
@@ -260,6 +264,13 @@ DCD_API int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, floa
  * scale = fp16(absmax/7). W is bf16 [N,K], K % 8 == 0. */
 DCD_API int dcd_k_quant_w4_g128(const void* W, void* packed, void* scales, int N, int K, void* stream);
 DCD_API int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N, int K, void* stream);
+/* NVFP4 rows (quant_nvfp4_act_bf16 / fp4_encode, native/kernels/kernels.cu:222-277): v = x*global,
+ * sf = e4m3(max(absmax16(v)/6, 1e-10)), code = fp4_encode(v/decode(sf)); packed [rows, K/2] (low nibble =
+ * even k), scales row-major [rows, K/16]. dequant writes decode(code)*decode(sf) as bf16 (exact);
+ * fakequant is quant followed by dequant without storing the codes. x is bf16, K % 16 == 0. */
+DCD_API int dcd_k_nvfp4_quant_rows(const void* x, size_t x_stride, float global, void* packed, void* scales, int rows, int K, void* stream);
+DCD_API int dcd_k_nvfp4_dequant_rows(const void* packed, const void* scales, void* out, int rows, int K, void* stream);
+DCD_API int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, void* out, int rows, int K, void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

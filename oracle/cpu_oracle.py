@@ -262,6 +262,18 @@ def k_dequant_w4(packed, scales, K: int) -> np.ndarray:
     return W
 
 
+def k_nvfp4_rows(x, global_scale: float = 1.0):
+    """NVFP4 round trip of each row: (packed uint8 [rows, K/2], e4m3 scales uint8 [rows, K/16], dequantised f32)."""
+    x = _f32(x)
+    rows, K = x.shape
+    packed = np.zeros((rows, K // 2), dtype=np.uint8)
+    scales = np.zeros((rows, K // 16), dtype=np.uint8)
+    deq = np.empty((rows, K), dtype=np.float32)
+    u8 = C.POINTER(C.c_uint8)
+    lib().orc_k_nvfp4_rows(_fp(x), rows, K, C.c_float(global_scale), packed.ctypes.data_as(u8), scales.ctypes.data_as(u8), _fp(deq))
+    return packed, scales, deq
+
+
 def k_rmsnorm(x, w, eps: float, zero_centered: bool, bf16: bool) -> np.ndarray:
     x, w = _f32(x), _f32(w)
     out = np.empty_like(x)

@@ -354,6 +354,54 @@ static void fake_quant_w4(std::vector<float>& W, int N, int K) {
 ORC_API void orc_k_quant_w4(const float* W, int N, int K, uint32_t* packed, uint16_t* scales) { quant_w4_g128(W, N, K, packed, scales); }
 ORC_API void orc_k_dequant_w4(const uint32_t* packed, const uint16_t* scales, int N, int K, float* W) { dequant_w4_g128(packed, scales, N, K, W); }
 
+// ---------------------------------------------------------------------------
+// NVFP4 (reference W4A4 path: quant_nvfp4_act_bf16 + fp4_encode, native/kernels/kernels.cu:222-277;
+// Engine::nvfp4_gemm, native/src/engine.rs:3962-4131, alpha = 1/(weight_global*input_global) :4108).
+// v = x*global; sf = e4m3(max(absmax16(v)/6, 1e-10)); code = fp4_encode(v/decode(sf)).
+// ---------------------------------------------------------------------------
+static inline uint8_t fp4_encode(float x) {
+  const float a = fabsf(x);
+  uint8_t e;
+  if (a < 0.25f) e = 0;
+  else if (a < 0.75f) e = 1;
+  else if (a < 1.25f) e = 2;
+  else if (a < 1.75f) e = 3;
+  else if (a < 2.5f) e = 4;
+  else if (a < 3.5f) e = 5;
+  else if (a < 5.0f) e = 6;
+  else e = 7;
+  return (x < 0.f) ? (uint8_t)(e | 8) : e;
+}
+static inline float fp4_decode(uint8_t c) {
+  static const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  return (c & 8) ? -mag[c & 7] : mag[c & 7];
+}
+// codes/scales may be null; deq (may be null) receives decode(code)*decode(sf) (no global).
+static void nvfp4_rows(const float* x, int rows, int K, float global, uint8_t* packed, uint8_t* scales, float* deq) {
+  const int groups = K / 16;
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r)
+    for (int j = 0; j < groups; ++j) {
+      float v[16], m = 0.f;
+      for (int i = 0; i < 16; ++i) { v[i] = x[(size_t)r * K + j * 16 + i] * global; m = fmaxf(m, fabsf(v[i])); }
+      const uint8_t sb = f32_to_e4m3(fmaxf(m / 6.0f, 1e-10f));
+      const float sd = e4m3_to_f32(sb);
+      if (scales) scales[(size_t)r * groups + j] = sb;
+      for (int i = 0; i < 16; ++i) {
+        const uint8_t c = fp4_encode(v[i] / sd);
+        if (packed) {
+          uint8_t& b = packed[(size_t)r * (K / 2) + j * 8 + i / 2];
+          b = (i & 1) ? (uint8_t)((b & 0x0f) | (c << 4)) : (uint8_t)((b & 0xf0) | c);
+        }
+        if (deq) deq[(size_t)r * K + j * 16 + i] = fp4_decode(c) * sd;
+      }
+    }
+}
+ORC_API void orc_k_nvfp4_rows(const float* x, int rows, int K, float global, uint8_t* packed, uint8_t* scales, float* deq) {
+  nvfp4_rows(x, rows, K, global, packed, scales, deq);
+}
+struct Nv4Image { std::vector<float> vals; float alpha; };
+
 // RMSNorm: native/kernels/kernels.cu:406-426 (zero_centered → weight 1+w).
 static void rmsnorm(const float* x, const float* w, float* out, int rows, int cols, float eps, bool zero_centered, Round R) {
 #pragma omp parallel for schedule(static)
@@ -563,6 +611,8 @@ struct Oracle {
   int precision = 0, fp8_min_rows = 512;
   bool q8_now = false, w4_done = false;
   std::map<const float*, Fp8Image> fp8_cache;
+  // precision 3: per GEMM weight, the NVFP4 round trip (without the tensor scale) and alpha = 1/(wg*ig)
+  std::map<const float*, Nv4Image> nv4_cache;
   int conv_dim() const { return 2 * c.gdn_k_heads * c.gdn_dk + c.gdn_v_heads * c.gdn_dv; }
 };
 
@@ -641,6 +691,14 @@ static void tap(Oracle& o, const std::string& name, const std::vector<float>& v)
 
 // One linear layer of the model: bf16/f32 GEMM, or the FP8 path when it is active for this pass.
 static void lin(Oracle& o, const float* X, const std::vector<float>& W, float* C, int T, int N, int K) {
+  if (o.precision == 3) {
+    const Nv4Image& img = o.nv4_cache.at(W.data());
+    std::vector<float> xq((size_t)T * K), acc((size_t)T * N);
+    nvfp4_rows(X, T, K, 1.0f, nullptr, nullptr, xq.data());
+    gemm(xq.data(), img.vals.data(), acc.data(), T, N, K, Round{false});
+    for (size_t i = 0; i < acc.size(); ++i) C[i] = o.R(acc[i] * img.alpha);
+    return;
+  }
   if (!o.q8_now) { gemm(X, W.data(), C, T, N, K, o.R); return; }
   auto it = o.fp8_cache.find(W.data());
   if (it == o.fp8_cache.end()) {
@@ -666,6 +724,34 @@ ORC_API void orc_set_precision(Oracle* o, int precision, int fp8_min_rows) {
       }
     }
     o->w4_done = true;
+  }
+  if (precision == 3 && o->nv4_cache.empty()) {
+    // one tensor scale per fused matrix of the engine: {gate,up}, {down}, {q,k,v}, {o}, {in_qkv,in_z,in_b,in_a}, {out}
+    const orc_config& c = o->c;
+    const int H = c.hidden, I = c.intermediate, hd = c.head_dim, vd = c.gdn_v_heads * c.gdn_dv;
+    auto group = [&](std::vector<std::pair<std::vector<float>*, int>> ts, int K) {
+      float amax = 0.f;
+      for (auto& t : ts) for (float v : *t.first) amax = fmaxf(amax, fabsf(v));
+      const float wg = amax > 0.f ? 2688.0f / amax : 1.0f;
+      for (auto& t : ts) {
+        Nv4Image img;
+        img.vals.resize(t.first->size());
+        nvfp4_rows(t.first->data(), t.second, K, wg, nullptr, nullptr, img.vals.data());
+        img.alpha = 1.0f / (wg * 1.0f);
+        o->nv4_cache.emplace(t.first->data(), std::move(img));
+      }
+    };
+    for (LayerW& w : o->layers) {
+      group({{&w.gate, I}, {&w.up, I}}, H);
+      group({{&w.down, H}}, I);
+      if (w.full) {
+        group({{&w.q, c.heads * 2 * hd}, {&w.k, c.kv_heads * hd}, {&w.v, c.kv_heads * hd}}, H);
+        group({{&w.o, H}}, c.heads * hd);
+      } else {
+        group({{&w.in_qkv, o->conv_dim()}, {&w.in_z, vd}, {&w.in_b, c.gdn_v_heads}, {&w.in_a, c.gdn_v_heads}}, H);
+        group({{&w.out, H}}, vd);
+      }
+    }
   }
   o->precision = precision;
   if (fp8_min_rows > 0) o->fp8_min_rows = fp8_min_rows;

@@ -369,3 +369,26 @@ def test_long_state_d3_attention_path(dcd, oracle):
     print(f"long-state d3 2-layer: max-abs {err:.4g}, argmax agree {agree.mean():.3f}, near-ties {int(near.sum())}")
     assert err < 0.12 and (agree | near).all()
     e.close()
+
+
+def test_nvfp4_precision(dcd, oracle):
+    """precision = 3: NVFP4 weights (e2m1 + e4m3 per 16 + f32 tensor scale) and NVFP4-quantised activations
+    per GEMM, the reference's W4A4 semantics, in every pass. Against the oracle's NVFP4 mode; the bar is the
+    size of the quantisation effect (W4A4 is coarse: the reference reports it failing its own accuracy gate)."""
+    cfg = dcd.tiny_config(1)
+    e = make_engine(dcd, cfg, max_pass_tokens=512, precision=3)
+    o = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    plain = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    o.set_precision(3)
+    state, questions = tiny_inputs()
+    st, ost = e.capture_state(state), o.capture_state(state)
+    got = e.readout_state_once_batch(st, questions)
+    want = o.readout_state_once_batch(ost, questions)
+    base = plain.readout_state_once_batch(plain.capture_state(state), questions)
+    err, effect = float(np.abs(got - want).max()), float(np.abs(want - base).max())
+    print(f"nvfp4 tiny: GPU vs oracle {err:.4g}; quantisation effect (oracle nvfp4 vs bf16) {effect:.4g}")
+    assert np.isfinite(got).all() and effect > 1e-2
+    assert err < max(0.5 * effect, BF16_ABS)
+    info16 = make_engine(dcd, cfg, max_pass_tokens=512)
+    assert e.info().weight_bytes < 0.7 * info16.info().weight_bytes
+    info16.close(); e.close()

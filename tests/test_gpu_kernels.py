@@ -466,3 +466,30 @@ def test_w4_quant_dequant_bit_exact(G, oracle, N, K):
     out = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
     G.call("dcd_k_dequant_w4_g128", packed, scales, out, N, K, None)
     assert G.host(out).tobytes() == oracle.k_dequant_w4(wp, ws, K).tobytes()
+
+
+# ---------------------------------------------------------------------------------------------
+# NVFP4
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("glob", [1.0, 26880.0])
+def test_nvfp4_rows_bit_exact(G, oracle, glob):
+    import torch
+    rows, K, stride = 7, 688, 704
+    r = rng(51)
+    scale = 1.0 if glob == 1.0 else 0.02
+    xf = oracle.rb((r.standard_normal((rows, stride)) * scale * np.exp(r.uniform(-2, 2, (rows, 1)))).astype(np.float32))
+    xf[2] = 0.0
+    packed = torch.zeros((rows, K // 2), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros((rows, K // 16), dtype=torch.uint8, device="cuda")
+    dx = G.dev(xf, 1)
+    G.call("dcd_k_nvfp4_quant_rows", dx, stride, C.c_float(glob), packed, scales, rows, K, None)
+    wp, ws, wd = oracle.k_nvfp4_rows(xf[:, :K], glob)
+    assert np.array_equal(scales.cpu().numpy(), ws)
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    out = torch.zeros((rows, K), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_nvfp4_dequant_rows", packed, scales, out, rows, K, None)
+    assert G.host(out).tobytes() == wd.tobytes()          # e2m1 x e4m3 is exact in bf16
+    assert oracle.rb(wd).tobytes() == wd.tobytes()
+    out2 = torch.zeros((rows, K), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_nvfp4_fakequant_rows", dx, stride, C.c_float(glob), out2, rows, K, None)
+    assert G.host(out2).tobytes() == wd.tobytes()

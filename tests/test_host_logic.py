@@ -39,9 +39,12 @@ def test_create_rejects_bad_config(dcd):
     rc = _lib.load().dcd_engine_create(C.byref(cfg), None, 0, C.byref(out))
     assert rc == 3 and not out.value and b"conv" in _lib.load().dcd_last_error(None)
     opt = dcd.Options()
-    opt.precision = 3
+    opt.precision = 7
     rc = _lib.load().dcd_engine_create(C.byref(dcd.tiny_config()), C.byref(opt), 0, C.byref(out))
-    assert rc == 3 and b"not built" in _lib.load().dcd_last_error(None)
+    assert rc == 3 and b"unknown" in _lib.load().dcd_last_error(None)
+    opt.precision = 2   # quantised precisions need a bf16 engine; tiny_config() is f32
+    rc = _lib.load().dcd_engine_create(C.byref(dcd.tiny_config()), C.byref(opt), 0, C.byref(out))
+    assert rc == 3 and b"bf16 engine" in _lib.load().dcd_last_error(None)
 
 
 @settings(max_examples=200, deadline=None)
