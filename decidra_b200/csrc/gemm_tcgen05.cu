@@ -262,7 +262,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   if (ESZ == 1) { ga = ga * wg[j] * rs; ua = ua * wu[j] * rs; }
                   const float gg = Ty<bf16>::rnd(ga);
                   const float uu = Ty<bf16>::rnd(ua);
-                  a[j] = Ty<bf16>::rnd(silu_f(gg)) * uu;
+                  a[j] = Ty<bf16>::rnd(__fdividef(gg, 1.0f + __expf(-gg))) * uu;
                 }
                 uint4 o;
                 o.x = pack_bf16(a[0], a[1]);

@@ -149,6 +149,10 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict_
 
 // ---- 16-byte vectorised bf16 forms (cols % 8 == 0, cols <= 8 * 4 * blockDim): one pass, the row is
 // held in registers between the sum of squares and the scaling. Same arithmetic as the kernels above.
+// SiLU with the hardware exp2/reciprocal approximations (about 2 ulp in f32): used only where the
+// result is rounded to bf16 straight away, which hides the difference except on rare rounding ties.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -311,7 +315,7 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_vec128_kernel(const bf16* _
   for (int j = 0; j < 4; ++j) {
     const float normed = Ty<bf16>::rnd(xf[j] * scale);
     const float scaled = Ty<bf16>::rnd(normed * wf[j]);
-    y[j] = scaled * Ty<bf16>::rnd(silu_f(zf[j]));
+    y[j] = scaled * Ty<bf16>::rnd(silu_fast(zf[j]));
   }
   uint2 ov;
   __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
@@ -630,27 +634,18 @@ __global__ void conv1d_silu_kernel(const T* __restrict__ x, int x_stride, const 
   const float v = Ty<T>::rnd(acc);
   Ty<T>::st(out + (size_t)t * ch + c, silu_f(v));
 }
-// bf16, ch % 8 == 0: each thread owns 8 consecutive channels of one token (16-byte loads of the four
-// taps, the weights and the store). Same fmaf chain, rounding and SiLU per channel.
+// bf16, ch % 8 == 0: each thread owns 8 consecutive channels and CONV_TT consecutive packed tokens,
+// sliding the three previous rows through registers (16-byte loads and stores). Same fmaf chain,
+// rounding and SiLU per channel; the window restarts from the cached tail at every sequence start.
+constexpr int CONV_TT = 8;
 __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __restrict__ x, int x_stride, const bf16* __restrict__ hist,
                                                                const bf16* __restrict__ w, bf16* __restrict__ out,
-                                                               const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int ch) {
+                                                               const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int ch,
+                                                               int tokens) {
   const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
   if (c8 * 8 >= ch) return;
   const int c = c8 * 8;
-  const int t = blockIdx.y;
-  const int off = cu ? cu[tok_q[t]] : 0;
-  const int lt = t - off;
-  float xs[4][8];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int src = lt - 3 + j;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(off + src) * x_stride + c);
-    else if (hist) v = *reinterpret_cast<const uint4*>(hist + (size_t)(src + 3) * ch + c);
-    unpack8(v, xs[j]);
-  }
-  // weights [ch][4]: 8 channels x 4 taps = 32 bf16 = 4 x 16 bytes
+  const int t_begin = blockIdx.y * CONV_TT, t_end = min(t_begin + CONV_TT, tokens);
   float wt[8][4];
   {
     const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)c * 4);
@@ -662,17 +657,38 @@ __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __res
       for (int i = 0; i < 8; ++i) wt[q * 2 + (i >> 2)][i & 3] = f[i];
     }
   }
-  float y[8];
+  auto row_at = [&](int off, int src, float (&f)[8]) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(off + src) * x_stride + c);
+    else if (hist) v = *reinterpret_cast<const uint4*>(hist + (size_t)(src + 3) * ch + c);
+    unpack8(v, f);
+  };
+  float x3[8], x2[8], x1[8], x0[8];
+  int cur_off = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int off = cu ? cu[tok_q[t]] : 0;
+    const int lt = t - off;
+    if (off != cur_off || t == t_begin) {  // (re)start the window: new tile or new sequence
+      row_at(off, lt - 3, x3);
+      row_at(off, lt - 2, x2);
+      row_at(off, lt - 1, x1);
+      cur_off = off;
+    }
+    row_at(off, lt, x0);
+    float y[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float acc = fmaf(xs[0][i], wt[i][0], 0.f);
-    acc = fmaf(xs[1][i], wt[i][1], acc);
-    acc = fmaf(xs[2][i], wt[i][2], acc);
-    acc = fmaf(xs[3][i], wt[i][3], acc);
-    const float v = Ty<bf16>::rnd(acc);
-    y[i] = silu_f(v);
+    for (int i = 0; i < 8; ++i) {
+      float acc = fmaf(x3[i], wt[i][0], 0.f);
+      acc = fmaf(x2[i], wt[i][1], acc);
+      acc = fmaf(x1[i], wt[i][2], acc);
+      acc = fmaf(x0[i], wt[i][3], acc);
+      y[i] = silu_fast(Ty<bf16>::rnd(acc));
+      x3[i] = x2[i];
+      x2[i] = x1[i];
+      x1[i] = x0[i];
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * ch + c) = pack8(y);
   }
-  *reinterpret_cast<uint4*>(out + (size_t)t * ch + c) = pack8(y);
 }
 
 template <typename T>
@@ -680,8 +696,8 @@ cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T*
                                const int32_t* tok_q, int tokens, int ch, cudaStream_t s) {
   if constexpr (sizeof(T) == 2) {
     if ((ch % 8) == 0 && (x_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
-      dim3 gridv((ch / 8 + 127) / 128, tokens);
-      conv1d_silu_vec8_kernel<<<gridv, 128, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch);
+      dim3 gridv((ch / 8 + 127) / 128, (tokens + CONV_TT - 1) / CONV_TT);
+      conv1d_silu_vec8_kernel<<<gridv, 128, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch, tokens);
       return cudaGetLastError();
     }
   }
