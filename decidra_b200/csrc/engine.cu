@@ -356,6 +356,9 @@ int run_layers(dcd_engine* e, const Pass& p) {
         Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * kv * hd * e->esz * 2.0, 1);
         CK(e, launch_copy_rows<T>(vsrc, e->qkv_n, (T*)p.cap->v[li], kv * hd, T_, kv * hd, s), "copy V");
       }
+      // Capture keeps nothing of the last layer beyond its cache entries: the reference computes the
+      // rest of that layer and discards it (native/src/engine.rs:4616-4763 builds no final norm or readout).
+      if (p.mode == 0 && li + 1 == c.num_layers) break;
       {
         const int n_state = p.mode == 1 ? (int)p.cache->state_len : 0;
         double keys = 0;  // sum over rows of visible keys
@@ -413,6 +416,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
           CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv,
                                         dk, dv, p.B < 8, s), "gdn_recurrent");
       }
+      if (p.mode == 0 && li + 1 == c.num_layers) break;  // last capture layer: the state and conv tail are stored
       {
         Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->vd * e->esz * 3.0, 1);
         CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
