@@ -10,14 +10,15 @@
 //   P_ts  = exp(G_t-G_s) (q_t.k_s)                   s <= t
 //   O     = Gam (Q S) + P D
 //   S'    = exp(G_C) S + (exp(G_C-G) K)^T D
-// Only differences of cumulative log decays are exponentiated (never ratios of products). The
-// state slice feeds the tensor cores as raw f32 bits (the hardware drops the low 13 mantissa bits);
-// K, Q, P and the deltas are rounded to TF32 (cvt.rna) when they are written to shared memory.
+// Only differences of cumulative log decays are exponentiated (never ratios of products).
 // One CTA = (packed sequence, value head, slice of VC value columns); the state slice
 // S[dk=128, VC] stays in shared memory in f32 across chunks. K S, Q S, K K^T, Q K^T, P D and the
 // state update run on mma.sync.m16n8k8 TF32; the triangular solve is a right-looking
 // substitution with one thread per value column, overlapped with the Q-side products, and the
 // next chunk's rows are prefetched into registers while the current chunk is computed.
+// K, Q, P and the deltas are rounded to TF32 (cvt.rna) when they are written to shared memory; the
+// f32 state is fed to the tensor core as stored (the unit ignores the low mantissa bits), which
+// saves one conversion per B fragment in the two state products.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -36,34 +37,6 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// B-fragment vectors: the value columns of S, D and O are stored permuted inside groups of
-// GW = 8*NPW logical columns (NPW = n-tiles owned by one warp): logical column grp*GW + tile*8 + g
-// lives at grp*GW + g*NPW + tile, so that the NPW fragments a lane needs for one k index are one
-// 8- or 16-byte shared-memory load (bank-conflict-free with the row stride VC+8).
-template <int NPW> struct BVec;
-template <> struct BVec<4> { float4 v; __device__ __forceinline__ uint32_t operator[](int i) const { return __float_as_uint(i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w); } };
-template <> struct BVec<2> { float2 v; __device__ __forceinline__ uint32_t operator[](int i) const { return __float_as_uint(i == 0 ? v.x : v.y); } };
-template <int NPW> __device__ __forceinline__ BVec<NPW> load_bvec(const float* p) {
-  BVec<NPW> r;
-  r.v = *reinterpret_cast<const decltype(r.v)*>(p);
-  return r;
-}
-
-// With that permutation the accumulator fragments a lane owns for its NPW tiles (columns 2tig and
-// 2tig+1 of each) are 2*NPW consecutive floats starting at group_base + 2*tig*NPW: element
-// h*NPW + n is (tile n, column 2tig+h). They move as 16-byte vectors.
-template <int NPW> __device__ __forceinline__ void ld_frag(const float* p, float (&f)[2 * NPW]) {
-#pragma unroll
-  for (int i = 0; i < 2 * NPW; i += 4) {
-    const float4 v = *reinterpret_cast<const float4*>(p + i);
-    f[i] = v.x; f[i + 1] = v.y; f[i + 2] = v.z; f[i + 3] = v.w;
-  }
-}
-template <int NPW> __device__ __forceinline__ void st_frag(float* p, const float (&f)[2 * NPW]) {
-#pragma unroll
-  for (int i = 0; i < 2 * NPW; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-}
-
 template <typename T, int VC>
 __global__ void __launch_bounds__(256)
 gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const T* __restrict__ conv, int conv_stride,
@@ -71,9 +44,6 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
                    float* __restrict__ final_state, T* __restrict__ out, const int32_t* __restrict__ cu, int nk, int nv, int dv) {
   constexpr int LDS = VC + 8;   // row stride of S, D, O tiles
   constexpr int NT = VC / 8;    // n-tiles across the value slice
-  constexpr int NPW = NT / 2;   // n-tiles per warp in the state products = width of a B-fragment vector
-  constexpr int GW = 8 * NPW;   // logical columns per permutation group (two groups)
-  auto phys = [](int c) { return (c / GW) * GW + (c % 8) * NPW + (c % GW) / 8; };
   extern __shared__ __align__(16) float sm[];
   float* sK = sm;                    // [C][LDK]   tf32-rounded keys
   float* sQ = sK + C * LDK;          // [C][LDK]   tf32-rounded queries
@@ -97,7 +67,7 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
 
   for (int i = tid; i < DK * VC; i += 256) {
     const int r = i / VC, c = i - r * VC;
-    sS[r * LDS + phys(c)] = seed ? seed[((size_t)head * DK + r) * dv + cbase + c] : 0.f;
+    sS[r * LDS + c] = seed ? seed[((size_t)head * DK + r) * dv + cbase + c] : 0.f;
   }
 
   // register prefetch of one chunk's K/Q rows (4 float4 each per thread) and V values
@@ -146,10 +116,7 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
                                                                   __uint_as_float(tf32(pq[j].z)), __uint_as_float(tf32(pq[j].w)));
     }
 #pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int i = tid + j * 256;
-      sV[(i / VC) * VC + phys(i % VC)] = pv[j];
-    }
+    for (int j = 0; j < VPT; ++j) sV[tid + j * 256] = pv[j];
     if (warp == 0) {
       float gv = pg;
 #pragma unroll
@@ -179,24 +146,21 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         a[1] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig]);
         a[2] = __float_as_uint(sK[r0 * LDK + k0 + tig + 4]);
         a[3] = __float_as_uint(sK[(r0 + 8) * LDK + k0 + tig + 4]);
-        const BVec<NPW> b0v = load_bvec<NPW>(sS + (k0 + tig) * LDS + nh * GW + g * NPW);
-        const BVec<NPW> b1v = load_bvec<NPW>(sS + (k0 + tig + 4) * LDS + nh * GW + g * NPW);
 #pragma unroll
-        for (int n = 0; n < NPW; ++n) mma_tf32(acc[n], a, b0v[n], b1v[n]);
+        for (int n = 0; n < NT / 2; ++n) {
+          const int n0 = (nh * (NT / 2) + n) * 8 + g;
+          mma_tf32(acc[n], a, __float_as_uint(sS[(k0 + tig) * LDS + n0]), __float_as_uint(sS[(k0 + tig + 4) * LDS + n0]));
+        }
       }
       const float gam0 = expf(sG[r0]), gam1 = expf(sG[r0 + 8]);
       const float b0 = sB[r0], b1 = sB[r0 + 8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {  // rows r0 and r0 + 8
-        const int r = r0 + 8 * half;
-        const float bb = half ? b1 : b0, gm = half ? gam1 : gam0;
-        float f[2 * NPW];
-        ld_frag<NPW>(sV + r * VC + nh * GW + 2 * tig * NPW, f);
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int n = 0; n < NPW; ++n) f[h * NPW + n] = bb * (f[h * NPW + n] - gm * acc[n][2 * half + h]);
-        st_frag<NPW>(sD + r * LDS + nh * GW + 2 * tig * NPW, f);
+      for (int n = 0; n < NT / 2; ++n) {
+        const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
+        sD[r0 * LDS + c] = b0 * (sV[r0 * VC + c] - gam0 * acc[n][0]);
+        sD[r0 * LDS + c + 1] = b0 * (sV[r0 * VC + c + 1] - gam0 * acc[n][1]);
+        sD[(r0 + 8) * LDS + c] = b1 * (sV[(r0 + 8) * VC + c] - gam1 * acc[n][2]);
+        sD[(r0 + 8) * LDS + c + 1] = b1 * (sV[(r0 + 8) * VC + c + 1] - gam1 * acc[n][3]);
       }
     } else {
       // K K^T: 2 m-tiles x 4 n-tiles; warp (4+i): m-tile = i>>1, n-tiles (i&1)*2 .. +1
@@ -262,21 +226,20 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         a[1] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig]);
         a[2] = __float_as_uint(sQ[r0 * LDK + k0 + tig + 4]);
         a[3] = __float_as_uint(sQ[(r0 + 8) * LDK + k0 + tig + 4]);
-        const BVec<NPW> b0v = load_bvec<NPW>(sS + (k0 + tig) * LDS + nh * GW + g * NPW);
-        const BVec<NPW> b1v = load_bvec<NPW>(sS + (k0 + tig + 4) * LDS + nh * GW + g * NPW);
 #pragma unroll
-        for (int n = 0; n < NPW; ++n) mma_tf32(acc[n], a, b0v[n], b1v[n]);
+        for (int n = 0; n < NT / 2; ++n) {
+          const int n0 = (nh * (NT / 2) + n) * 8 + g;
+          mma_tf32(acc[n], a, __float_as_uint(sS[(k0 + tig) * LDS + n0]), __float_as_uint(sS[(k0 + tig + 4) * LDS + n0]));
+        }
       }
       const float gam0 = expf(sG[r0]), gam1 = expf(sG[r0 + 8]);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const float gm = half ? gam1 : gam0;
-        float f[2 * NPW];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int n = 0; n < NPW; ++n) f[h * NPW + n] = gm * acc[n][2 * half + h];
-        st_frag<NPW>(sO + (r0 + 8 * half) * LDS + nh * GW + 2 * tig * NPW, f);
+      for (int n = 0; n < NT / 2; ++n) {
+        const int c = (nh * (NT / 2) + n) * 8 + 2 * tig;
+        sO[r0 * LDS + c] = gam0 * acc[n][0];
+        sO[r0 * LDS + c + 1] = gam0 * acc[n][1];
+        sO[(r0 + 8) * LDS + c] = gam1 * acc[n][2];
+        sO[(r0 + 8) * LDS + c + 1] = gam1 * acc[n][3];
       }
     } else if (warp >= 6) {
       // Q K^T: warp 6 -> m-tile 0 (n-tiles 0,1), warp 7 -> m-tile 1 (n-tiles 0..3)
@@ -316,12 +279,11 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
       float acc[NT / 4][4];
 #pragma unroll
       for (int n = 0; n < NT / 4; ++n) {
-        const int tile = nq * (NT / 4) + n;
-        const int c = (tile / NPW) * GW + 2 * tig * NPW + tile % NPW, c1 = c + NPW;
+        const int c = (nq * (NT / 4) + n) * 8 + 2 * tig;
         acc[n][0] = sO[r0 * LDS + c];
-        acc[n][1] = sO[r0 * LDS + c1];
+        acc[n][1] = sO[r0 * LDS + c + 1];
         acc[n][2] = sO[(r0 + 8) * LDS + c];
-        acc[n][3] = sO[(r0 + 8) * LDS + c1];
+        acc[n][3] = sO[(r0 + 8) * LDS + c + 1];
       }
 #pragma unroll
       for (int k0 = 0; k0 < C; k0 += 8) {
@@ -332,8 +294,7 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         a[3] = __float_as_uint(sP[(r0 + 8) * LDA + k0 + tig + 4]);
 #pragma unroll
         for (int n = 0; n < NT / 4; ++n) {
-          const int tile = nq * (NT / 4) + n;
-          const int n0 = (tile / NPW) * GW + g * NPW + tile % NPW;
+          const int n0 = (nq * (NT / 4) + n) * 8 + g;
           mma_tf32(acc[n], a, __float_as_uint(sD[(k0 + tig) * LDS + n0]), __float_as_uint(sD[(k0 + tig + 4) * LDS + n0]));
         }
       }
@@ -362,34 +323,29 @@ gdn_chunked_kernel(const float* __restrict__ qf, const float* __restrict__ kf, c
         a[2] = tf32(sK[(k0 + tig + 4) * LDK + m0] * e1);
         a[3] = tf32(sK[(k0 + tig + 4) * LDK + m0 + 8] * e1);
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-          const BVec<NPW> b0v = load_bvec<NPW>(sD + (k0 + tig) * LDS + grp * GW + g * NPW);
-          const BVec<NPW> b1v = load_bvec<NPW>(sD + (k0 + tig + 4) * LDS + grp * GW + g * NPW);
-#pragma unroll
-          for (int n = 0; n < NPW; ++n) mma_tf32(acc[grp * NPW + n], a, b0v[n], b1v[n]);
+        for (int n = 0; n < NT; ++n) {
+          const int n0 = n * 8 + g;
+          mma_tf32(acc[n], a, __float_as_uint(sD[(k0 + tig) * LDS + n0]), __float_as_uint(sD[(k0 + tig + 4) * LDS + n0]));
         }
       }
       // every warp passed the barrier after phase 2, so nobody still reads S
 #pragma unroll
-      for (int grp = 0; grp < 2; ++grp)
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float* p = sS + (m0 + 8 * half) * LDS + grp * GW + 2 * tig * NPW;
-          float f[2 * NPW];
-          ld_frag<NPW>(p, f);
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int n = 0; n < NPW; ++n) f[h * NPW + n] = fmaf(gamC, f[h * NPW + n], acc[grp * NPW + n][2 * half + h]);
-          st_frag<NPW>(p, f);
-        }
+      for (int n = 0; n < NT; ++n) {
+        const int c = n * 8 + 2 * tig;
+        float* s0 = sS + m0 * LDS + c;
+        float* s1 = sS + (m0 + 8) * LDS + c;
+        s0[0] = fmaf(gamC, s0[0], acc[n][0]);
+        s0[1] = fmaf(gamC, s0[1], acc[n][1]);
+        s1[0] = fmaf(gamC, s1[0], acc[n][2]);
+        s1[1] = fmaf(gamC, s1[1], acc[n][3]);
+      }
     }
   }
   if (final_state) {
     __syncthreads();
     for (int i = tid; i < DK * VC; i += 256) {
       const int r = i / VC, c = i - r * VC;
-      final_state[(((size_t)b * nv + head) * DK + r) * dv + cbase + c] = sS[r * LDS + phys(c)];
+      final_state[(((size_t)b * nv + head) * DK + r) * dv + cbase + c] = sS[r * LDS + c];
     }
   }
 }
