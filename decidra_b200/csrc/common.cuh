@@ -13,7 +13,8 @@ enum : int {
   DERR_EMPTY_ITEM = 2,    // a packed sequence has length <= 0
   DERR_GEMM_TIMEOUT = 3,  // a bounded mbarrier wait gave up in the tcgen05 GEMM
   DERR_ATTN_TIMEOUT = 4,
-  DERR_POSITION_RANGE = 5 // RoPE position beyond the table
+  DERR_POSITION_RANGE = 5, // RoPE position beyond the table
+  DERR_GDN_TIMEOUT = 6
 };
 
 __device__ __forceinline__ void set_err(int* err, int code) {

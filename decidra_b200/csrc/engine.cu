@@ -97,7 +97,9 @@ struct dcd_engine {
   float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
-  bool attn_tc = false, gdn_chunked = false;
+  bool attn_tc = false, gdn_chunked = false, gdn_tc = false;
+  TcTensorMap tm_gdn[2];  // q/k views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
+  int tm_gdn_tokens = -1;
   bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
   void* xstage = nullptr;              // bf16 [Tm, max K]: activations after the NVFP4 round trip
   unsigned int* amax_tmp = nullptr;
@@ -409,7 +411,14 @@ int run_layers(dcd_engine* e, const Pass& p) {
         Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
         const float* seed = p.mode == 1 ? p.cache->gstate[li] : nullptr;
         float* fin = p.mode == 0 ? p.cap->gstate[li] : nullptr;
-        if (e->gdn_chunked)
+        if (e->gdn_tc) {
+          if (e->tm_gdn_tokens != T_) {
+            if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
+            e->tm_gdn_tokens = T_;
+          }
+          CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, e->d_err, s),
+             "gdn_tc");
+        } else if (e->gdn_chunked)
           CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, dk,
                                       dv, p.B < 2, s), "gdn_chunked");
         else
@@ -527,6 +536,7 @@ int check_device_error(dcd_engine* e) {
     case DERR_POSITION_RANGE: return fail(e, DCD_E_INVALID, "position beyond the RoPE table (%d)", e->o.max_positions);
     case DERR_GEMM_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 GEMM: a bounded barrier wait gave up");
     case DERR_ATTN_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 attention: a bounded barrier wait gave up");
+    case DERR_GDN_TIMEOUT: return fail(e, DCD_E_TIMEOUT, "tcgen05 gated delta rule: a bounded barrier wait gave up");
     default: return fail(e, DCD_E_CUDA, "device error word %d", code);
   }
 }
@@ -683,7 +693,9 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->fp8 = o.precision == 2 && o.gemm_path == 0;
   e->w4 = o.precision == 1;
   e->nv4 = o.precision == 3;
-  e->gdn_chunked = e->bf && o.gdn_path == 0 && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
+  e->gdn_tc = e->bf && o.gdn_path == 0 && gdn_tc_supported(c.gdn_dk, c.gdn_dv);
+  if (e->gdn_tc) CRE(gdn_tc_prepare_device<bf16>(), "tcgen05 GDN shared-memory attribute");
+  e->gdn_chunked = e->bf && !e->gdn_tc && (o.gdn_path == 0 || o.gdn_path == 2) && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
   const size_t es = e->esz, H = e->H;

@@ -359,6 +359,20 @@ int tc_make_tmap_3d(TcTensorMap* out, const void* ptr, uint64_t d0, uint64_t d1,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
+// Row-major [rows, cols] f32 view with an explicit row stride (elements); box = box_rows x 32 columns
+// (128 bytes), 128-byte swizzle, zero fill outside the matrix. Feeds kind::tf32 operands.
+int tc_make_tmap_f32(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows) {
+  auto fn = tcg::encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride * 4};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
 int tc_make_tmap_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K) { return tc_make_tmap(out, X, M, K, tcg::BM); }
 int tc_make_tmap_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K) { return tc_make_tmap(out, W, N, K, tcg::BN); }
 

@@ -15,6 +15,8 @@ int tc_make_tmap_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K);
 int tc_make_tmap_strided(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows);
 int tc_make_tmap_3d(TcTensorMap* out, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1, uint64_t stride2,
                     uint32_t box1, uint32_t box2);
+// Strided 2-D f32 view (row stride in elements), box of box_rows x 32 columns, 128-byte swizzle.
+int tc_make_tmap_f32(TcTensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows);
 bool tc_shape_ok(int M, int N, int K);
 // Raises the kernel's dynamic shared-memory limit on the current device (call once per device).
 cudaError_t tc_gemm_prepare_device();

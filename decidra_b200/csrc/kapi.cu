@@ -118,6 +118,18 @@ int dcd_k_gdn_chunked(const float* qf, const float* kf, const void* conv, int co
                   launch_gdn_chunked<bf16>(qf, kf, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, dk, dv, narrow != 0, S(stream)));
 }
 
+int dcd_k_gdn_chunked_tc(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                         const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens, int nk,
+                         int nv, int dk, int dv, int* err, int dtype, void* stream) {
+  if (!gdn_tc_supported(dk, dv) || total_tokens <= 0 || nk <= 0 || nv % nk != 0) return DCD_E_INVALID;
+  if ((dtype == 0 ? gdn_tc_prepare_device<float>() : gdn_tc_prepare_device<bf16>()) != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap maps[2];
+  if (gdn_tc_make_maps(maps, qf, kf, total_tokens, nk) != 0) return DCD_E_CUDA;
+  return DISPATCH(dtype,
+                  launch_gdn_tc<float>(maps, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, err, S(stream)),
+                  launch_gdn_tc<bf16>(maps, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, err, S(stream)));
+}
+
 int dcd_k_qk_norm_rope(const void* qg, int qg_stride, const void* kraw, int k_stride, const void* qw, const void* kw, const void* cos_t,
                        const void* sin_t, const int32_t* positions, int max_pos, void* q, void* k, int T, int heads, int kv, int hd,
                        int rotary_dim, float eps, int* err, int dtype, void* stream) {

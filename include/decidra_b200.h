@@ -75,7 +75,7 @@ typedef struct dcd_options {
   int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMM (bf16 only); 1 = plain FMA GEMM (diagnostic) */
   int32_t attn_path;        /* 0 = tcgen05 attention where the shape allows (bf16, head_dim 256, 6:1 GQA); 1 = plain FMA attention */
   int32_t max_positions;    /* RoPE table length; default 65536 */
-  int32_t gdn_path;         /* 0 = chunked tensor-core gated delta rule where the shape allows (bf16, dk 128); 1 = sequential f32 */
+  int32_t gdn_path;         /* 0 = chunked gated delta rule on tcgen05 (bf16, dk = dv = 128), else on mma.sync (dk 128); 1 = sequential f32; 2 = mma.sync chunked */
   int32_t fp8_min_rows;     /* fp8_min_rows() of native/src/engine.rs:246-257; default 512 */
   int32_t reserved[6];
 } dcd_options;
@@ -304,6 +304,14 @@ DCD_API int dcd_k_gdn_recurrent(const float* qf, const float* kf, const void* co
 DCD_API int dcd_k_gdn_chunked(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
                               const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int nk, int nv,
                               int dk, int dv, int narrow, int dtype, void* stream);
+/* The same recurrence in chunked form (chunk 64) on tcgen05.mma kind::tf32 with TMEM accumulators and
+ * TMA-fed q/k tiles; one CTA per (sequence, value head), the f32 state kept in TMEM across chunks
+ * (replaces gdn_chunked_tc_body, native/kernels/kernels.cu:1671-1933). Same operands as
+ * dcd_k_gdn_recurrent plus total_tokens (rows of qf/kf) and the device error word; dk and dv must both
+ * be 128. The tensor core drops the low 13 mantissa bits of qf/kf. */
+DCD_API int dcd_k_gdn_chunked_tc(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                                 const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens,
+                                 int nk, int nv, int dk, int dv, int* err, int dtype, void* stream);
 /* split_q_gate + q/k RMSNorm(1+w) + partial NeoX RoPE in one kernel
  * (native/kernels/kernels.cu:516-557, 406-426; tables as native/src/engine.rs:1619-1643).
  * qg [T,heads,2*hd] (row stride qg_stride), kraw [T,kv,hd] (row stride k_stride) -> q [T,heads,hd],
