@@ -286,6 +286,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 0) set_err(p.err, DERR_ATTN_TIMEOUT);
+#pragma unroll 1
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }

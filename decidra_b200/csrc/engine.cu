@@ -98,7 +98,7 @@ struct dcd_engine {
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
   bool attn_tc = false, gdn_chunked = false, gdn_tc = false;
-  TcTensorMap tm_gdn[2];  // q/k views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
+  TcTensorMap tm_gdn[3];  // q/k/conv views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
   int tm_gdn_tokens = -1;
   bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
   void* xstage = nullptr;              // bf16 [Tm, max K]: activations after the NVFP4 round trip
@@ -413,7 +413,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
         float* fin = p.mode == 0 ? p.cap->gstate[li] : nullptr;
         if (e->gdn_tc) {
           if (e->tm_gdn_tokens != T_) {
-            if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
+            if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, e->conv, e->conv_dim, e->conv_dim, (int)e->esz, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
             e->tm_gdn_tokens = T_;
           }
           CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, e->d_err, s),

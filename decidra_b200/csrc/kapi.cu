@@ -123,8 +123,8 @@ int dcd_k_gdn_chunked_tc(const float* qf, const float* kf, const void* conv, int
                          int nv, int dk, int dv, int* err, int dtype, void* stream) {
   if (!gdn_tc_supported(dk, dv) || total_tokens <= 0 || nk <= 0 || nv % nk != 0) return DCD_E_INVALID;
   if ((dtype == 0 ? gdn_tc_prepare_device<float>() : gdn_tc_prepare_device<bf16>()) != cudaSuccess) return DCD_E_CUDA;
-  TcTensorMap maps[2];
-  if (gdn_tc_make_maps(maps, qf, kf, total_tokens, nk) != 0) return DCD_E_CUDA;
+  TcTensorMap maps[3];
+  if (gdn_tc_make_maps(maps, qf, kf, conv, conv_stride, 2 * nk * dk + nv * dv, dtype == 0 ? 4 : 2, total_tokens, nk) != 0) return DCD_E_CUDA;
   return DISPATCH(dtype,
                   launch_gdn_tc<float>(maps, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, err, S(stream)),
                   launch_gdn_tc<bf16>(maps, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, err, S(stream)));

@@ -70,15 +70,17 @@ cudaError_t launch_gdn_chunked(const float* qf, const float* kf, const T* conv, 
                                bool few_sequences, cudaStream_t s);
 
 // tcgen05 (kind::tf32) form of the chunked gated delta rule (gdn_tcgen05.cu); dk and dv must both be 128.
-// maps[0]/maps[1] are TMA descriptors of the f32 q/k buffers [tokens, nk*128] made by gdn_tc_make_maps
-// (rows = the token count of this launch, so that a partial last chunk reads the zero fill).
+// maps[0..2] are TMA descriptors of the f32 q/k buffers [tokens, nk*128] and (16-bit storage) of the conv
+// output [tokens, conv_cols], made by gdn_tc_make_maps with rows = the token count of this launch, so that
+// a partial last chunk reads the zero fill.
 struct TcTensorMap;
 bool gdn_tc_supported(int dk, int dv);
 template <typename T>
 cudaError_t gdn_tc_prepare_device();
-int gdn_tc_make_maps(TcTensorMap maps[2], const float* qf, const float* kf, int tokens, int nk);
+int gdn_tc_make_maps(TcTensorMap maps[3], const float* qf, const float* kf, const void* conv, int conv_stride, int conv_cols, int elem_size,
+                     int tokens, int nk);
 template <typename T>
-cudaError_t launch_gdn_tc(const TcTensorMap maps[2], const T* conv, int conv_stride, const float* g, const float* beta, const float* seed,
+cudaError_t launch_gdn_tc(const TcTensorMap maps[3], const T* conv, int conv_stride, const float* g, const float* beta, const float* seed,
                           float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int* err, cudaStream_t s);
 
 // Per-row FP8 E4M3 quantisation: scale[row] = max(absmax*clip, 1e-10)/448, out = e4m3(x/scale).
