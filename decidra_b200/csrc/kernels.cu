@@ -637,6 +637,9 @@ __global__ void conv1d_silu_kernel(const T* __restrict__ x, int x_stride, const 
 // bf16, ch % 8 == 0: each thread owns 8 consecutive channels and CONV_TT consecutive packed tokens,
 // sliding the three previous rows through registers (16-byte loads and stores). Same fmaf chain,
 // rounding and SiLU per channel; the window restarts from the cached tail at every sequence start.
+// Packed row t of x is token t whatever its sequence, so the CONV_TT + 3 rows of a tile, the cached
+// tail and the per-token sequence offsets are all fetched up front (independent loads in flight
+// together); only the choice between an x row and a tail row depends on the offsets.
 constexpr int CONV_TT = 8;
 __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __restrict__ x, int x_stride, const bf16* __restrict__ hist,
                                                                const bf16* __restrict__ w, bf16* __restrict__ out,
@@ -646,6 +649,18 @@ __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __res
   if (c8 * 8 >= ch) return;
   const int c = c8 * 8;
   const int t_begin = blockIdx.y * CONV_TT, t_end = min(t_begin + CONV_TT, tokens);
+  int offs[CONV_TT];
+#pragma unroll
+  for (int i = 0; i < CONV_TT; ++i) offs[i] = cu ? cu[tok_q[min(t_begin + i, tokens - 1)]] : 0;
+  uint4 xr[CONV_TT + 3];
+#pragma unroll
+  for (int k = 0; k < CONV_TT + 3; ++k) {
+    const int r = min(max(t_begin - 3 + k, 0), tokens - 1);
+    xr[k] = *reinterpret_cast<const uint4*>(x + (size_t)r * x_stride + c);
+  }
+  uint4 hr[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) hr[k] = hist ? *reinterpret_cast<const uint4*>(hist + (size_t)k * ch + c) : make_uint4(0, 0, 0, 0);
   float wt[8][4];
   {
     const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)c * 4);
@@ -657,37 +672,43 @@ __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __res
       for (int i = 0; i < 8; ++i) wt[q * 2 + (i >> 2)][i & 3] = f[i];
     }
   }
-  auto row_at = [&](int off, int src, float (&f)[8]) {
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(off + src) * x_stride + c);
-    else if (hist) v = *reinterpret_cast<const uint4*>(hist + (size_t)(src + 3) * ch + c);
-    unpack8(v, f);
-  };
   float x3[8], x2[8], x1[8], x0[8];
-  int cur_off = -1;
-  for (int t = t_begin; t < t_end; ++t) {
-    const int off = cu ? cu[tok_q[t]] : 0;
-    const int lt = t - off;
-    if (off != cur_off || t == t_begin) {  // (re)start the window: new tile or new sequence
-      row_at(off, lt - 3, x3);
-      row_at(off, lt - 2, x2);
-      row_at(off, lt - 1, x1);
-      cur_off = off;
-    }
-    row_at(off, lt, x0);
-    float y[8];
+  {  // window of the tile's first token: rows lt-3..lt-1, from x while they are inside the sequence, else from the tail
+    const int lt = t_begin - offs[0];
+    auto pick = [&](int j, const uint4& xrow, float (&f)[8]) {  // j = 3, 2, 1: row lt - j
+      const int src = lt - j;
+      uint4 v = xrow;
+      if (src < 0) v = src == -3 ? hr[0] : (src == -2 ? hr[1] : hr[2]);
+      unpack8(v, f);
+    };
+    pick(3, xr[0], x3);
+    pick(2, xr[1], x2);
+    pick(1, xr[2], x1);
+  }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float acc = fmaf(x3[i], wt[i][0], 0.f);
-      acc = fmaf(x2[i], wt[i][1], acc);
-      acc = fmaf(x1[i], wt[i][2], acc);
-      acc = fmaf(x0[i], wt[i][3], acc);
-      y[i] = silu_fast(Ty<bf16>::rnd(acc));
-      x3[i] = x2[i];
-      x2[i] = x1[i];
-      x1[i] = x0[i];
+  for (int i = 0; i < CONV_TT; ++i) {
+    const int t = t_begin + i;
+    if (t < t_end) {
+      if (i > 0 && t == offs[i]) {  // a new sequence starts here: restart from the tail
+        unpack8(hr[0], x3);
+        unpack8(hr[1], x2);
+        unpack8(hr[2], x1);
+      }
+      unpack8(xr[i + 3], x0);
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float acc = fmaf(x3[e], wt[e][0], 0.f);
+        acc = fmaf(x2[e], wt[e][1], acc);
+        acc = fmaf(x1[e], wt[e][2], acc);
+        acc = fmaf(x0[e], wt[e][3], acc);
+        y[e] = silu_fast(Ty<bf16>::rnd(acc));
+        x3[e] = x2[e];
+        x2[e] = x1[e];
+        x1[e] = x0[e];
+      }
+      *reinterpret_cast<uint4*>(out + (size_t)t * ch + c) = pack8(y);
     }
-    *reinterpret_cast<uint4*>(out + (size_t)t * ch + c) = pack8(y);
   }
 }
 
