@@ -12,8 +12,11 @@
 //   S'    = exp(G_C) S + (exp(G_C-G) K)^T D
 // Only differences of cumulative log decays are exponentiated (never ratios of products).
 //
-// One CTA = (packed sequence, value head) with all 128 value columns; 128 threads. Everything
-// that depends on the state is kept transposed so that TMEM lane = value column = thread:
+// One CTA = (packed sequence, value head) with all 128 value columns; 256 threads = two warpgroups.
+// Everything that depends on the state is kept transposed so that TMEM lane = value column; thread
+// `ln` of each warpgroup owns lane ln, and the two warpgroups split every per-lane loop in halves
+// (with one warp per scheduler the chunk body ran at a third of an instruction per cycle, all of it
+// exposed latency). The forward substitution is sequential per column and runs on warpgroup 0.
 //   D1 [row, s]   = [K;Q] K^T            (rows 0-63 key tokens, 64-127 query tokens)
 //   D2 [vc, t]    = S^T [K;Q]^T          (columns 0-63 (K S)^T, 64-127 (Q S)^T)
 //   O2 [vc, t]    = D^T P^T
@@ -78,7 +81,7 @@ template <> __device__ __forceinline__ void st_if<bf16>(bf16* p, float v, bool p
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(256, 1)
 gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
               const T* __restrict__ conv, int conv_stride,
               const float* __restrict__ gl, const float* __restrict__ beta, const float* __restrict__ seed, float* __restrict__ final_state,
@@ -87,11 +90,12 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int off = cu[b], len = cu[b + 1] - off;
   const int kh = head / (nv / nk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2, ln = tid & 127;  // warpgroup; TMEM lane / operand row owned by this thread
   const int vcol0 = 2 * nk * DK + head * DV;
 
   if (len <= 0) {  // nothing to run: the final state is the seed
-    if (final_state)
-      for (int r = 0; r < DK; ++r) final_state[(((size_t)b * nv + head) * DK + r) * DV + tid] = seed ? seed[((size_t)head * DK + r) * DV + tid] : 0.f;
+    if (final_state && wg == 0)
+      for (int r = 0; r < DK; ++r) final_state[(((size_t)b * nv + head) * DK + r) * DV + ln] = seed ? seed[((size_t)head * DK + r) * DV + ln] : 0.f;
     return;
   }
 
@@ -120,7 +124,7 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tlane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
   constexpr bool V_TMA = sizeof(T) == 2;  // the V tile of a 16-bit conv output fits the P space
   auto load_kq = [&](int t0) {  // one elected thread; K/Q tiles and (16-bit storage) the V tile of the chunk at t0
@@ -135,12 +139,12 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tma_load_2d(sbase + P_OFF + 8192, &tmV, bar_kq, vcol0 + 64, off + t0);
     }
   };
-  // Scalars of the chunk at t0 into set `set` (warp 2: decays, warp 3: beta; warp 0 issues the MMAs meanwhile). A set is rewritten two
+  // Scalars of the chunk at t0 into set `set` (warp 6: decays, warp 7: beta; warp 0 issues the MMAs meanwhile). A set is rewritten two
   // chunks later, after every thread has passed a barrier that follows its last read.
   auto scalars = [&](int t0, int set) {
     const int nt = min(C, len - t0);
     float* sG = sc + set * 256;
-    if (warp == 2) {
+    if (warp == 6) {
       float g0 = lane < nt ? gl[(size_t)(off + t0 + lane) * nv + head] : 0.f;
       float g1 = lane + 32 < nt ? gl[(size_t)(off + t0 + lane + 32) * nv + head] : 0.f;
 #pragma unroll
@@ -156,24 +160,24 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       sG[192 + lane + 32] = expf(g1);
       sG[128 + lane] = expf(gend - g0);
       sG[128 + lane + 32] = expf(gend - g1);
-    } else if (warp == 3) {
+    } else if (warp == 7) {
       sG[64 + lane] = lane < nt ? beta[(size_t)(off + t0 + lane) * nv + head] : 0.f;
       sG[64 + lane + 32] = lane + 32 < nt ? beta[(size_t)(off + t0 + lane + 32) * nv + head] : 0.f;
     }
   };
   // 32-bit storage: this thread's V column of the chunk at t0 into its TMEM scratch (all loads in flight together).
-  auto park_v = [&](int t0) {
+  auto park_v = [&](int t0) {  // each warpgroup parks its half of the chunk's rows
     const int nt = min(C, len - t0);
-    const T* vp = conv + (size_t)(off + t0) * conv_stride + vcol0 + tid;
-    uint32_t v[C];
+    const T* vp = conv + (size_t)(off + t0) * conv_stride + vcol0 + ln;
+    uint32_t v[C / 2];
 #pragma unroll
-    for (int t = 0; t < C; ++t) {
-      const float x = Ty<T>::ld(vp);
-      v[t] = f2u(t < nt ? x : 0.f);
-      if (t + 1 < nt) vp += conv_stride;
+    for (int i = 0; i < C / 2; ++i) {
+      const int t = wg * (C / 2) + i;
+      const float x = Ty<T>::ld(vp + (size_t)min(t, nt - 1) * conv_stride);
+      v[i] = f2u(t < nt ? x : 0.f);
     }
 #pragma unroll
-    for (int j = 0; j < C / BLK; ++j) tmem_st16(tlane + VR_COL + j * BLK, v + j * BLK);
+    for (int j = 0; j < C / BLK / 2; ++j) tmem_st16(tlane + VR_COL + (wg * 2 + j) * BLK, v + j * BLK);
     tmem_st_wait();
   };
 
@@ -182,13 +186,13 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (!V_TMA) park_v(0);
   // ---- seed: S^T row of this thread's value column into shared memory ------------------------------------
 #pragma unroll 1
-  for (int j = 0; j < DK / BLK; ++j) {
+  for (int j = wg * 4; j < wg * 4 + 4; ++j) {
     float v[BLK];
 #pragma unroll
-    for (int i = 0; i < BLK; ++i) v[i] = seed ? seed[((size_t)head * DK + j * BLK + i) * DV + tid] : 0.f;
+    for (int i = 0; i < BLK; ++i) v[i] = seed ? seed[((size_t)head * DK + j * BLK + i) * DV + ln] : 0.f;
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      *reinterpret_cast<float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(tid, (j & 1) * 4 + q)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      *reinterpret_cast<float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(ln, (j & 1) * 4 + q)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before();
@@ -226,18 +230,20 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       umma_commit_to(bar_mma);
     }
-    // ---- meanwhile: row dk = tid of (exp(G_C-G) K)^T, the K-major B operand of the state update ---------------
+    // ---- meanwhile: row dk = ln of (exp(G_C-G) K)^T, the K-major B operand of the state update (32 tokens per
+    // warpgroup) ------------------------------------------------------------------------------------------------
     if (ok) {
-      const uint8_t* kcol = smem + KQ_OFF + (tid >> 5) * REG + (tid & 3) * 4;
-      const int c16 = (tid & 31) >> 2;
+      const uint8_t* kcol = smem + KQ_OFF + (ln >> 5) * REG + (ln & 3) * 4;
+      const int c16 = (ln & 31) >> 2;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int cc = 0; cc < 8; ++cc) {
+        const int c = wg * 8 + cc;
         const float4 e4 = *reinterpret_cast<const float4*>(sE + 4 * c);
         const float k0 = e4.x * *reinterpret_cast<const float*>(kcol + (4 * c + 0) * 128 + ((c16 ^ ((4 * c + 0) & 7)) << 4));
         const float k1 = e4.y * *reinterpret_cast<const float*>(kcol + (4 * c + 1) * 128 + ((c16 ^ ((4 * c + 1) & 7)) << 4));
         const float k2 = e4.z * *reinterpret_cast<const float*>(kcol + (4 * c + 2) * 128 + ((c16 ^ ((4 * c + 2) & 7)) << 4));
         const float k3 = e4.w * *reinterpret_cast<const float*>(kcol + (4 * c + 3) * 128 + ((c16 ^ ((4 * c + 3) & 7)) << 4));
-        *reinterpret_cast<float4*>(smem + KT_OFF + (uint32_t)(c >> 3) * REG + sw_off(tid, c & 7)) = tf32x4(k0, k1, k2, k3);
+        *reinterpret_cast<float4*>(smem + KT_OFF + (uint32_t)(c >> 3) * REG + sw_off(ln, c & 7)) = tf32x4(k0, k1, k2, k3);
       }
     }
     ok = ok && mbar_wait(bar_mma, mma_phase, abort_flag);
@@ -247,12 +253,12 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     // ---- right-hand side beta (V - Gam (K S)) for this value column into the scratch ------------------------------
 #pragma unroll 1
-    for (int j = 0; j < C / BLK; ++j) {
+    for (int j = wg * 2; j < wg * 2 + 2; ++j) {
       uint32_t x[BLK], v[BLK];
       tmem_ld16(tlane + D2_COL + j * BLK, x);
       if (V_TMA) {
-        const uint8_t* vcol = smem + P_OFF + (tid >> 6) * 8192 + (tid & 7) * 2;
-        const int c16 = (tid & 63) >> 3;
+        const uint8_t* vcol = smem + P_OFF + (ln >> 6) * 8192 + (ln & 7) * 2;
+        const int c16 = (ln & 63) >> 3;
 #pragma unroll
         for (int i = 0; i < BLK; ++i) {
           const int t = j * BLK + i;
@@ -273,15 +279,17 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       tmem_st16(tlane + VR_COL + j * BLK, v);
     }
+    tmem_st_wait();
+    tc_fence_before();  // the other warpgroup's half of the right-hand side is read by the solve below
     if (V_TMA) __syncthreads();  // the V tile has been read by everyone: P may overwrite it
 
     // ---- D1 rows: key-token rows give A^T, query-token rows give P -------------------------------------
     // (exponents are clamped to <= 0 and the result selected, so the loops stay branch-free)
-    if (tid < 64) {
-      const int t = tid;
+    if (ln < 64) {
+      const int t = ln;
       const float Gt = sG[t], bt = sB[t];
 #pragma unroll 1
-      for (int j = 0; j < C / BLK; ++j) {
+      for (int j = wg * 2; j < wg * 2 + 2; ++j) {
         uint32_t v[BLK];
         tmem_ld16(tlane + D1_COL + j * BLK, v);
         tmem_ld_wait();
@@ -298,10 +306,10 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
     } else {
-      const int t = tid - 64;
+      const int t = ln - 64;
       const float Gt = sG[t];
 #pragma unroll 1
-      for (int j = 0; j < C / BLK; ++j) {
+      for (int j = wg * 2; j < wg * 2 + 2; ++j) {
         uint32_t v[BLK];
         tmem_ld16(tlane + D1_COL + j * BLK, v);
         tmem_ld_wait();
@@ -320,10 +328,11 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
     }
-    tmem_st_wait();
-    __syncthreads();  // A^T complete
+    __syncthreads();  // A^T complete; the right-hand sides of both warpgroups are in the scratch
 
     // ---- forward substitution, blocked 16x16, left-looking; block j ends up holding D[16j .. 16j+15] ----------
+    if (wg == 0) {
+    tc_fence_after();
 #pragma unroll 1
     for (int jb = 0; jb < C / BLK; ++jb) {
       float r[BLK];
@@ -374,17 +383,20 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tmem_st16(tlane + VR_COL + jb * BLK, rv);
       tmem_st_wait();
     }
+    }
+    tc_fence_before();
     __syncthreads();  // every thread is done with A^T (D^T below overwrites it)
 
     // ---- D^T row as a K-major tf32 operand ---------------------------------------------------------------------
+    tc_fence_after();
 #pragma unroll 1
-    for (int j = 0; j < C / BLK; ++j) {
+    for (int j = wg * 2; j < wg * 2 + 2; ++j) {
       uint32_t d[BLK];
       tmem_ld16(tlane + VR_COL + j * BLK, d);
       tmem_ld_wait();
 #pragma unroll
       for (int q = 0; q < 4; ++q)
-        *reinterpret_cast<float4*>(smem + DT_OFF + (uint32_t)(j >> 1) * REG + sw_off(tid, (j & 1) * 4 + q)) =
+        *reinterpret_cast<float4*>(smem + DT_OFF + (uint32_t)(j >> 1) * REG + sw_off(ln, (j & 1) * 4 + q)) =
             tf32x4(u2f(d[4 * q]), u2f(d[4 * q + 1]), u2f(d[4 * q + 2]), u2f(d[4 * q + 3]));
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -419,10 +431,10 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     // ---- outputs O[t, vc] = Gam_t (Q S)[t, vc] + (P D)[t, vc] ----------------------------------------------------
     {
-      T* op = out + (size_t)(off + t0) * nv * DV + (size_t)head * DV + tid;
+      T* op = out + (size_t)(off + t0) * nv * DV + (size_t)head * DV + ln;
       const size_t os = (size_t)nv * DV;
 #pragma unroll 1
-      for (int j = 0; j < C / BLK; ++j) {
+      for (int j = wg * 2; j < wg * 2 + 2; ++j) {
         uint32_t qs[BLK], pd[BLK];
         tmem_ld16(tlane + D2_COL + 64 + j * BLK, qs);
         tmem_ld16(tlane + O2_COL + j * BLK, pd);
@@ -443,12 +455,12 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     {
       const float gamC = sGam[C - 1];
 #pragma unroll 1
-      for (int j = 0; j < DK / BLK; ++j) {
+      for (int j = wg * 4; j < wg * 4 + 4; ++j) {
         uint32_t dl[BLK];
         tmem_ld16(tlane + RD_COL + j * BLK, dl);
         float4 o4[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) o4[q] = *reinterpret_cast<const float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(tid, (j & 1) * 4 + q));
+        for (int q = 0; q < 4; ++q) o4[q] = *reinterpret_cast<const float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(ln, (j & 1) * 4 + q));
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -459,9 +471,9 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         if (!last) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) *reinterpret_cast<float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(tid, (j & 1) * 4 + q)) = o4[q];
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<float4*>(smem + ST_OFF + (uint32_t)(j >> 1) * REG + sw_off(ln, (j & 1) * 4 + q)) = o4[q];
         } else if (final_state) {
-          float* fp = final_state + (((size_t)b * nv + head) * DK + j * BLK) * DV + tid;
+          float* fp = final_state + (((size_t)b * nv + head) * DK + j * BLK) * DV + ln;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             fp[(size_t)(4 * q + 0) * DV] = o4[q].x;
@@ -519,7 +531,7 @@ cudaError_t launch_gdn_tc(const TcTensorMap maps[3], const T* conv, int conv_str
   if (B <= 0) return cudaSuccess;
   if (B > 65535 || nk <= 0 || nv % nk != 0) return cudaErrorInvalidValue;
   dim3 grid(nv, B);
-  gtc::gdn_tc_kernel<T><<<grid, 128, gtc::SMEM_BYTES, s>>>(*reinterpret_cast<const CUtensorMap*>(&maps[0]), *reinterpret_cast<const CUtensorMap*>(&maps[1]),
+  gtc::gdn_tc_kernel<T><<<grid, 256, gtc::SMEM_BYTES, s>>>(*reinterpret_cast<const CUtensorMap*>(&maps[0]), *reinterpret_cast<const CUtensorMap*>(&maps[1]),
                                                             *reinterpret_cast<const CUtensorMap*>(&maps[2]), conv, conv_stride, g, beta, seed, final_state,
                                                             out, cu, nk, nv, err);
   return cudaGetLastError();
