@@ -10,13 +10,19 @@
 //
 // One CTA = (question, KV head, tile of 128/G tokens), G = query heads per KV head. The G heads of
 // a token share K/V, so the M=128 MMA tile is packed with (token, head) rows by a 3-D TMA box
-// {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 64 through a 2-stage ring:
+// {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 64 through 2-stage K and V rings:
 //   S[128,64]  = Q[128,256] . K^T        tcgen05.mma, operands in shared memory, S in TMEM
 //   softmax    : thread r owns row r: tcgen05.ld S, base-2 online softmax with a lazy rescale
 //                (O is only rescaled when the running max grows by more than 2^8), P -> bf16 into
 //                shared memory in the 128-byte-swizzled K-major operand layout
 //   O[128,256] += P[128,64] . V[64,256]  tcgen05.mma, V read as an MN-major operand, O in TMEM
-// Warps 0-3 are the softmax/epilogue warps (TMEM lanes 32w..32w+31); warp 4 issues TMA and MMA.
+// S is double-buffered in TMEM: S of tile j+1 is issued before the softmax of tile j is awaited, so the
+// tensor core works on S[j+1] and P.V[j-1] while the threads run the softmax of tile j. A K slot is
+// refilled as soon as its S product is done, a V slot as soon as its P.V product is done.
+// Warps 0-7 are the softmax/epilogue warps: warps w and w+4 share TMEM lanes 32w..32w+31 and each
+// thread of the pair owns half of the 64 key columns of its row (they exchange the row maximum through
+// shared memory once per tile and their partial denominators once at the end); one thread of warp 8
+// issues the MMAs and one thread of warp 9 the TMA loads, so that neither waits behind the other.
 // All waits are bounded; a wait that gives up raises the error word and the CTA drains and exits.
 #include <cuda.h>
 
@@ -32,8 +38,10 @@ constexpr uint32_t Q_KB_BYTES = 128 * 128, Q_BYTES = NKB * Q_KB_BYTES;          
 constexpr uint32_t KV_CHUNK = KT * 128, K_BYTES = NKB * KV_CHUNK, V_BYTES = K_BYTES;  // 32 KB each
 constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;                              // 64 KB
 constexpr uint32_t P_BYTES = 128 * 128;                                          // 16 KB
-constexpr uint32_t SMEM_BYTES = Q_BYTES + 2 * STAGE_BYTES + P_BYTES + 256 + 1024;
-constexpr int NUM_THREADS = 160;
+constexpr uint32_t XCH_BYTES = 2 * 256 * 4;  // row-maximum exchange, two sets of 2 x 128 floats
+constexpr uint32_t SMEM_BYTES = Q_BYTES + 2 * STAGE_BYTES + P_BYTES + XCH_BYTES + 256 + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr int ISSUER_WARP = 8, LOADER_WARP = 9;
 constexpr uint32_t O_COL = 0, S_COL = 256;
 constexpr uint32_t IDESC_QK = umma_idesc(128, KT, 0);
 constexpr uint32_t IDESC_PV = umma_idesc(128, HD, 1);
@@ -80,22 +88,27 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint32_t q_base = raw + pad;
   const uint32_t st_base = q_base + Q_BYTES;
   const uint32_t p_base = st_base + 2 * STAGE_BYTES;
-  const uint32_t bars = p_base + P_BYTES;
+  const uint32_t bars = p_base + P_BYTES + XCH_BYTES;
   uint8_t* p_ptr = smem + Q_BYTES + 2 * STAGE_BYTES;
-  uint8_t* bars_ptr = p_ptr + P_BYTES;
-  const uint32_t bar_q = bars, bar_kv0 = bars + 8, bar_s = bars + 24, bar_p = bars + 32, bar_o = bars + 40;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 48);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 52);
+  float* xch = reinterpret_cast<float*>(p_ptr + P_BYTES);
+  uint8_t* bars_ptr = p_ptr + P_BYTES + XCH_BYTES;
+  const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 64;  // bar_k/v/s: 2 each
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 72);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 76);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_kv0, 1);
-    mbar_init(bar_kv0 + 8, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_k + 8, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_v + 8, 1);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_s + 8, 1);
+    mbar_init(bar_p, 256);
     mbar_init(bar_o, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bars + 80 + 8 * i, 64);  // one per pair of softmax warps
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -109,7 +122,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  if (warp == 4) {
+  if (warp == ISSUER_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -118,50 +131,83 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 4) {
+  if (warp == LOADER_WARP) {
     if (lane == 0) {
-      // ---- TMA + MMA issuer -------------------------------------------------------------------
-      auto load_kv = [&](int j) {
+      // ---- TMA loader: Q once; K[j+2] as soon as S[j] is done, V[j+1] as soon as P.V[j-1] is done ---------------
+      auto load_k = [&](int j) {
         const int s = j & 1;
-        const uint32_t kdst = st_base + s * STAGE_BYTES, vdst = kdst + K_BYTES, bar = bar_kv0 + 8 * s;
-        mbar_expect_tx(bar, STAGE_BYTES);
+        const uint32_t kdst = st_base + s * STAGE_BYTES, bar = bar_k + 8 * s;
+        mbar_expect_tx(bar, K_BYTES);
         const bool st = j < n_st;
         const CUtensorMap* mk = st ? &tmKs : &tmKo;
+        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+#pragma unroll
+        for (int c = 0; c < NKB; ++c) tma_load_2d(kdst + c * KV_CHUNK, mk, bar, kh * HD + c * 64, row0);
+      };
+      auto load_v = [&](int j) {
+        const int s = j & 1;
+        const uint32_t vdst = st_base + s * STAGE_BYTES + K_BYTES, bar = bar_v + 8 * s;
+        mbar_expect_tx(bar, V_BYTES);
+        const bool st = j < n_st;
         const CUtensorMap* mv = st ? &tmVs : &tmVo;
         const int row0 = st ? j * KT : off + (j - n_st) * KT;
 #pragma unroll
-        for (int c = 0; c < NKB; ++c) {
-          tma_load_2d(kdst + c * KV_CHUNK, mk, bar, kh * HD + c * 64, row0);
-          tma_load_2d(vdst + c * KV_CHUNK, mv, bar, kh * HD + c * 64, row0);
-        }
+        for (int c = 0; c < NKB; ++c) tma_load_2d(vdst + c * KV_CHUNK, mv, bar, kh * HD + c * 64, row0);
       };
       mbar_expect_tx(bar_q, (uint32_t)(NKB * TT * G * 128));
 #pragma unroll
       for (int c = 0; c < NKB; ++c) tma_load_3d(q_base + c * Q_KB_BYTES, &tmQ, bar_q, c * 64, kh * G, off + t0);
-      load_kv(0);
-      if (n_tiles > 1) load_kv(1);
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      load_k(0);
+      load_v(0);
+      if (n_tiles > 1) {
+        load_k(1);
+        load_v(1);
+      }
+      bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 2 < n_tiles) {
+          if (!(ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag))) break;  // S[j] done: its K slot is free
+          load_k(j + 2);
+        }
+        if (j >= 1 && j + 1 < n_tiles) {
+          if (!(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;  // P.V of tile j-1 done: its V slot is free
+          load_v(j + 1);
+        }
+      }
+    }
+  } else if (warp == ISSUER_WARP) {
+    if (lane == 0) {
+      // ---- MMA issuer --------------------------------------------------------------------------------------------
+      auto issue_s = [&](int j) {  // S[j] = Q K[j]^T into S buffer j & 1
         const int s = j & 1;
-        if (!(ok = mbar_wait(bar_kv0 + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
-        tc_fence_after();
         const uint32_t kb_base = st_base + s * STAGE_BYTES;
 #pragma unroll
         for (int c = 0; c < NKB; ++c) {
           const uint64_t dq = umma_desc(q_base + c * Q_KB_BYTES, 16, 1024);
           const uint64_t dk = umma_desc(kb_base + c * KV_CHUNK, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f16(tmem_base + S_COL, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            umma_f16(tmem_base + S_COL + s * KT, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
         }
-        umma_commit_to(bar_s);
-        if (j >= 1) {
-          if (!(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
-          if (j + 1 < n_tiles) load_kv(j + 1);  // the stage of tile j-1 is free again
+        umma_commit_to(bar_s + 8 * s);
+      };
+      bool ok = mbar_wait(bar_q, 0, abort_flag) && mbar_wait(bar_k, 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < n_tiles) {  // S of the next tile goes to the tensor core before this tile's softmax is awaited
+          if (!(ok = mbar_wait(bar_k + 8 * (s ^ 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag))) break;
+          tc_fence_after();
+          issue_s(j + 1);
         }
         if (!(ok = mbar_wait(bar_p, (uint32_t)(j & 1), abort_flag))) break;
+        if (!(ok = mbar_wait(bar_v + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
         tc_fence_after();
         const uint64_t dp = umma_desc(p_base, 16, 1024);
-        const uint64_t dv = umma_desc(kb_base + K_BYTES, KV_CHUNK, 1024);
+        const uint64_t dv = umma_desc(st_base + s * STAGE_BYTES + K_BYTES, KV_CHUNK, 1024);
 #pragma unroll
         for (int k = 0; k < KT / 16; ++k)
           umma_f16(tmem_base + O_COL, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
@@ -169,36 +215,41 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     }
   } else {
-    // ---- softmax + epilogue: thread r owns row r of the tile --------------------------------------
-    const int r = threadIdx.x;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m_used = -INFINITY, l = 0.f;
+    // ---- softmax + epilogue: threads r and r + 128 own row r of the tile, key columns [32h, 32h + 32) each ------
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t pair_bar = bars + 80 + 8 * (warp & 3);  // mbarrier of the two warps that share these rows (bounded wait)
+    uint32_t pair_phase = 0;
+    constexpr int HK = KT / 2;                 // key columns per thread
+    float m_used = -INFINITY, l = 0.f;         // l: this thread's part of the denominator
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int valid = j < n_st ? min(KT, p.n_state - j * KT) : min(KT, L - (j - n_st) * KT);
-      ok = mbar_wait(bar_s, (uint32_t)(j & 1), abort_flag);
+      ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float x[KT];
+      float x[HK];
       {
         uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + S_COL, v);
+        tmem_ld32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * HK, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
-        tmem_ld32(tmem_base + lane_addr + S_COL + 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) x[32 + i] = __uint_as_float(v[i]);
+        for (int i = 0; i < HK; ++i) x[i] = h * HK + i < valid ? __uint_as_float(v[i]) * p.scale_log2e : -INFINITY;
       }
-      float tmax = -INFINITY;
+      float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < KT; ++i) {
-        x[i] = i < valid ? x[i] * p.scale_log2e : -INFINITY;
-        tmax = fmaxf(tmax, x[i]);
-      }
-      const bool need = tmax > m_used + RESCALE_THRESHOLD;  // also true on the first tile (m_used = -inf)
+      for (int i = 0; i < HK; ++i) t4[i & 3] = fmaxf(t4[i & 3], x[i]);
+      float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
+      float* xs = xch + (j & 1) * 256;
+      xs[h * 128 + r] = tmax;
+      mbar_arrive(pair_bar);
+      ok = mbar_wait(pair_bar, pair_phase, abort_flag);
+      pair_phase ^= 1u;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tmax = fmaxf(tmax, xs[(h ^ 1) * 128 + r]);
+      const bool need = tmax > m_used + RESCALE_THRESHOLD;  // also true on the first tile (m_used = -inf); same for the pair
       if (j >= 1) {
         ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag);  // PV of tile j-1 done: P buffer free, O stable
         ok = __all_sync(0xffffffffu, ok);
@@ -207,7 +258,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_after();
           const float f = need ? exp2f(m_used - tmax) : 1.0f;
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = h * (HD / 64); c < (h + 1) * (HD / 64); ++c) {
             uint32_t v[32];
             tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
             tmem_ld_wait();
@@ -222,28 +273,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (need) m_used = tmax;
       // P = exp2(x - m_used) rounded to bf16; the denominator sums the rounded values
       uint8_t* prow = p_ptr + r * 128;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < KT / 8; ++c) {
+      for (int c = 0; c < HK / 8; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int h2 = 0; h2 < 4; ++h2) {
           const __nv_bfloat162 pr = __floats2bfloat162_rn(exp2f(x[c * 8 + 2 * h2] - m_used), exp2f(x[c * 8 + 2 * h2 + 1] - m_used));
-          l += __low2float(pr) + __high2float(pr);
+          l4[h2] += __low2float(pr) + __high2float(pr);
           w[h2] = *reinterpret_cast<const uint32_t*>(&pr);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(prow + (((h * (HK / 8) + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(bar_p);
     }
-    // ---- epilogue: O / l, output gate, store --------------------------------------------------------
+    // ---- epilogue: O / l, output gate, store (each thread of the pair takes half of the head dims) -----------------
     if (ok) {
       ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1), abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
+      float* xs = xch + (n_tiles & 1) * 256;  // the set the last tile did not use
+      xs[h * 128 + r] = l;
+      mbar_arrive(pair_bar);
+      ok = mbar_wait(pair_bar, pair_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      float* xs = xch + (n_tiles & 1) * 256;
+      l += xs[(h ^ 1) * 128 + r];
       const int tt = r / G, g = r - tt * G;
       const bool live = tt < ntok;
       const int t = off + t0 + tt, head = kh * G + g;
@@ -251,7 +313,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bf16* orow = p.out + ((size_t)t * p.heads + head) * HD;
       const bf16* grow = p.gate_qg ? p.gate_qg + (size_t)t * p.qg_stride + (size_t)head * 2 * HD + HD : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = h * (HD / 64); c < (h + 1) * (HD / 64); ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
         tmem_ld_wait();
@@ -290,7 +352,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == ISSUER_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
