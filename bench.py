@@ -293,7 +293,7 @@ def run_ours(args):
             "states_per_s": world * args.steps / t_dev,
             "step_tflop": flops_step / 1e12, "model_tflops_per_gpu": flops_step * args.steps / t_dev / 1e12,
             "e2e": {"value": world * B * args.steps / t_e2e, "unit": UNIT, "h2d_bytes_per_step": int(4 * (S + total + B + 1)),
-                    "d2h_bytes_per_step": int(4 * B * cfg.readout_rows + 8), "p50_request_latency_ms": statistics.median(lat) * 1e3,
+                    "d2h_bytes_per_step": int(4 * B * cfg.readout_rows + 8), "p50_request_latency_ms": statistics.median(lat) * 1e3, "max_request_latency_ms": max(lat) * 1e3,
                     "logits_identical_to_device_arm": same},
             "gpu_launches": int(launches),
             "roofline": {"kernel": "gemm_bf16_tc_kernel (tcgen05, all projection/MLP GEMMs)", "bound": "tensor", "achieved": achieved, "peak": peak,

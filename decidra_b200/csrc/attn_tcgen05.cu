@@ -11,7 +11,9 @@
 // One CTA = (question, KV head, tile of 128/G tokens), G = query heads per KV head. The G heads of
 // a token share K/V, so the M=128 MMA tile is packed with (token, head) rows by a 3-D TMA box
 // {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 64 through 2-stage K and V rings:
-//   S[128,64]  = Q[128,256] . K^T        tcgen05.mma, operands in shared memory, S in TMEM
+//   S[128,64]  = Q[128,256] . K^T        tcgen05.mma, Q as the TMEM A operand (copied there once from its TMA
+//                landing buffer: re-reading a 4 KB Q slice from shared memory for every 2 KB K slice made
+//                these products shared-memory-bandwidth bound), K from shared memory, S in TMEM
 //   softmax    : thread r owns row r: tcgen05.ld S, base-2 online softmax with a lazy rescale
 //                (O is only rescaled when the running max grows by more than 2^8), P -> bf16 into
 //                shared memory in the 128-byte-swizzled K-major operand layout
@@ -42,7 +44,7 @@ constexpr uint32_t XCH_BYTES = 2 * 256 * 4;  // row-maximum exchange, two sets o
 constexpr uint32_t SMEM_BYTES = Q_BYTES + 2 * STAGE_BYTES + P_BYTES + XCH_BYTES + 256 + 1024;
 constexpr int NUM_THREADS = 320;
 constexpr int ISSUER_WARP = 8, LOADER_WARP = 9;
-constexpr uint32_t O_COL = 0, S_COL = 256;
+constexpr uint32_t O_COL = 0, S_COL = 256, Q_COL = 384;  // O 256 columns, S 2 x 64, Q 128 (bf16 pairs)
 constexpr uint32_t IDESC_QK = umma_idesc(128, KT, 0);
 constexpr uint32_t IDESC_PV = umma_idesc(128, HD, 1);
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -92,9 +94,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* p_ptr = smem + Q_BYTES + 2 * STAGE_BYTES;
   float* xch = reinterpret_cast<float*>(p_ptr + P_BYTES);
   uint8_t* bars_ptr = p_ptr + P_BYTES + XCH_BYTES;
-  const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 64;  // bar_k/v/s: 2 each
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 72);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 76);
+  const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 72;  // bar_k/v/s/p: 2 each
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 80);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 84);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -107,8 +109,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_p, 256);
+    mbar_init(bar_p + 8, 256);
     mbar_init(bar_o, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(bars + 80 + 8 * i, 64);  // one per pair of softmax warps
+    for (int i = 0; i < 4; ++i) mbar_init(bars + 88 + 8 * i, 64);  // one per pair of softmax warps
+    mbar_init(bars + 120, 256);                                    // Q copied to TMEM
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -183,15 +187,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t kb_base = st_base + s * STAGE_BYTES;
 #pragma unroll
         for (int c = 0; c < NKB; ++c) {
-          const uint64_t dq = umma_desc(q_base + c * Q_KB_BYTES, 16, 1024);
           const uint64_t dk = umma_desc(kb_base + c * KV_CHUNK, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + S_COL + s * KT, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+            umma_f16_ts(tmem_base + S_COL + s * KT, tmem_base + Q_COL + c * 32 + k * 8, dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
         }
         umma_commit_to(bar_s + 8 * s);
       };
-      bool ok = mbar_wait(bar_q, 0, abort_flag) && mbar_wait(bar_k, 0, abort_flag);
+      bool ok = mbar_wait(bars + 120, 0, abort_flag) && mbar_wait(bar_k, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -203,14 +206,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_after();
           issue_s(j + 1);
         }
-        if (!(ok = mbar_wait(bar_p, (uint32_t)(j & 1), abort_flag))) break;
+        if (!(ok = mbar_wait(bar_p + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
         if (!(ok = mbar_wait(bar_v + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
         tc_fence_after();
-        const uint64_t dp = umma_desc(p_base, 16, 1024);
         const uint64_t dv = umma_desc(st_base + s * STAGE_BYTES + K_BYTES, KV_CHUNK, 1024);
 #pragma unroll
-        for (int k = 0; k < KT / 16; ++k)
-          umma_f16(tmem_base + O_COL, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < KT / 16; ++k)  // P[j] sits over S[j]: 16 keys = 8 packed columns per step
+          umma_f16_ts(tmem_base + O_COL, tmem_base + S_COL + s * KT + k * 8, dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
         umma_commit_to(bar_o);
       }
     }
@@ -218,11 +220,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---- softmax + epilogue: threads r and r + 128 own row r of the tile, key columns [32h, 32h + 32) each ------
     const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t pair_bar = bars + 80 + 8 * (warp & 3);  // mbarrier of the two warps that share these rows (bounded wait)
+    const uint32_t pair_bar = bars + 88 + 8 * (warp & 3);  // mbarrier of the two warps that share these rows (bounded wait)
     uint32_t pair_phase = 0;
     constexpr int HK = KT / 2;                 // key columns per thread
     float m_used = -INFINITY, l = 0.f;         // l: this thread's part of the denominator
-    bool ok = true;
+    // ---- Q row r into TMEM, 128 head dims per thread of the pair (chunk i of a row sits at i ^ (r & 7)) -------------
+    bool ok = mbar_wait(bar_q, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+#pragma unroll 1
+      for (int c = 2 * h; c < 2 * h + 2; ++c) {
+        uint32_t v[32];
+        const uint8_t* qrow = smem + c * Q_KB_BYTES + r * 128;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(qrow + ((i ^ (r & 7)) << 4));
+          v[4 * i] = q4.x;
+          v[4 * i + 1] = q4.y;
+          v[4 * i + 2] = q4.z;
+          v[4 * i + 3] = q4.w;
+        }
+        tmem_st32(tmem_base + lane_addr + Q_COL + c * 32, v);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bars + 120);
+    }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int valid = j < n_st ? min(KT, p.n_state - j * KT) : min(KT, L - (j - n_st) * KT);
       ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag);
@@ -250,11 +273,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (!ok) break;
       tmax = fmaxf(tmax, xs[(h ^ 1) * 128 + r]);
       const bool need = tmax > m_used + RESCALE_THRESHOLD;  // also true on the first tile (m_used = -inf); same for the pair
-      if (j >= 1) {
-        ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag);  // PV of tile j-1 done: P buffer free, O stable
+      if (j >= 1 && __any_sync(0xffffffffu, need)) {
+        ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag);  // PV of tile j-1 done: O stable
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (__any_sync(0xffffffffu, need)) {
+        {
           tc_fence_after();
           const float f = need ? exp2f(m_used - tmax) : 1.0f;
 #pragma unroll 1
@@ -271,24 +294,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       if (need) m_used = tmax;
-      // P = exp2(x - m_used) rounded to bf16; the denominator sums the rounded values
-      uint8_t* prow = p_ptr + r * 128;
+      // P = exp2(x - m_used) rounded to bf16, packed in pairs over this thread's half of S[j] (the partner has
+      // its S values in registers since before the exchange); the denominator sums the rounded values
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t w[HK / 2];
 #pragma unroll
-      for (int c = 0; c < HK / 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int h2 = 0; h2 < 4; ++h2) {
-          const __nv_bfloat162 pr = __floats2bfloat162_rn(exp2f(x[c * 8 + 2 * h2] - m_used), exp2f(x[c * 8 + 2 * h2 + 1] - m_used));
-          l4[h2] += __low2float(pr) + __high2float(pr);
-          w[h2] = *reinterpret_cast<const uint32_t*>(&pr);
-        }
-        *reinterpret_cast<uint4*>(prow + (((h * (HK / 8) + c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < HK / 2; ++i) {
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(exp2f(x[2 * i] - m_used), exp2f(x[2 * i + 1] - m_used));
+        l4[i & 3] += __low2float(pr) + __high2float(pr);
+        w[i] = *reinterpret_cast<const uint32_t*>(&pr);
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tmem_st16(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * (HK / 2), w);
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      mbar_arrive(bar_p + 8 * (j & 1));
     }
     // ---- epilogue: O / l, output gate, store (each thread of the pair takes half of the head dims) -----------------
     if (ok) {

@@ -685,6 +685,16 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   } while (0)
 
   CRE(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream");
+  {
+    // State blocks come from the device's default stream-ordered pool. Its default release threshold (0) hands
+    // freed blocks back to the driver at the next synchronisation, so a host that frees a state and captures
+    // the next one around a blocking readout pays a fresh ~300 MB reservation each time. Keep freed blocks
+    // cached; dcd_trim_pools returns them on request (Engine::trim_pools, native/src/engine.rs:1044, has the same role).
+    cudaMemPool_t pool;
+    uint64_t keep = UINT64_MAX;
+    CRE(cudaDeviceGetDefaultMemPool(&pool, e->device), "mem pool");
+    CRE(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep), "mem pool release threshold");
+  }
   CRE(cudaEventCreate(&e->t0), "event");
   CRE(cudaEventCreate(&e->t1), "event");
   if (e->bf) CRE(tc_gemm_prepare_device(), "tcgen05 GEMM shared-memory attribute");
