@@ -24,7 +24,7 @@ def rng(seed):
 # tcgen05 GEMM
 # ---------------------------------------------------------------------------------------------
 GEMM_SHAPES = [(128, 256, 64), (128, 256, 128), (256, 512, 256), (128, 256, 1024), (300, 776, 256), (77, 48, 688), (1000, 640, 5120),
-               (2048, 5120, 1024), (640, 17408, 512)]
+               (2048, 5120, 1024), (640, 17408, 512), (2048, 16480, 256)]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
