@@ -1,0 +1,268 @@
+// C[M,N] = alpha * (Xq . Wq^T) for NVFP4 operands on the sm_100a block-scaled tensor-core path:
+// e2m1 codes (two per byte), one unsigned e4m3 scale per 16 elements along K, f32 accumulation
+// (tcgen05.mma kind::mxf4nvf4.block_scale, 16-element blocks), bf16 output.
+//
+// Replaces the cuBLASLt block-scaled FP4 GEMM of Engine::nvfp4_gemm (native/src/engine.rs:3962-4131
+// in juanqui/decidra): same operand formats (codes K-major, scales in the 128 x 4 tiled layout that
+// cuBLASLt and the reference's quantisers use: tile (row block of 128, group of 4 scales) is 512
+// bytes with scale (r, g) at (r % 32) * 16 + (r / 32) * 4 + g), alpha = 1 / (weight_global *
+// input_global) applied to the accumulator before rounding.
+//
+// Structure (one CTA per SM, persistent over 128 x 128 output tiles, K in 256-element = 128-byte blocks):
+//   warp 0: producer. Per K block two TMA tile loads (codes of X and W, 128 rows x 128 bytes, 128-byte
+//           swizzle) and two plain bulk copies of 2 KB (the four 512-byte scale tiles of each operand,
+//           contiguous in the tiled layout) into a 5-stage ring;
+//   warp 1: MMA issuer. Copies the eight scale tiles of the stage into TMEM (tcgen05.cp 32x128b.warpx4: a
+//           512-byte tile becomes 4 columns, lane r % 32 of every 32-lane quarter holding the four scales
+//           of rows r, r+32, r+64, r+96 in its four columns) and issues 4 MMAs (M128 N128 K64);
+//   warps 2-5: epilogue. tcgen05.ld, * alpha, bf16, 16-byte stores; two accumulators of 128 columns so
+//           the epilogue of a tile overlaps the main loop of the next.
+// TMEM: columns 0-255 accumulators, 256 + 32*stage: 16 columns of X scales then 16 of W scales.
+// Rows beyond M or N read the TMA zero fill for codes; their scale tiles exist (the scale buffers are
+// padded to whole 128-row blocks) and whatever they hold multiplies zeros or lands in rows/columns that
+// are not stored.
+// Every mbarrier wait is bounded: when a wait gives up the kernel raises an error word, lets in-flight
+// copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+#include "tc_common.cuh"
+
+namespace nvg {
+using namespace tcc;
+
+constexpr int BM = 128, BN = 128, BKB = 128 /* bytes of codes per row per K block = 256 elements */, STAGES = 5, ACC_STAGES = 2;
+constexpr uint32_t A_BYTES = BM * BKB, B_BYTES = BN * BKB, SF_BYTES = 2048, STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr uint32_t SF_COL = 256;
+constexpr int GROUP_M = 16;
+// block-scaled instruction descriptor: A/B format e2m1 (1) at bits 7 and 10, N>>3 at [17,23), scale format
+// UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
+constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {  // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_sf(uint32_t smem_addr) {  // 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void cp_sf(uint32_t tmem_col, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
+  const int per_group = GROUP_M * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(GROUP_M, num_m - first_m);
+  const int r = tile - g * per_group;
+  m_idx = first_m + r % gsize;
+  n_idx = r / gsize;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const uint8_t* __restrict__ sfa,
+                     const uint8_t* __restrict__ sfb, bf16* __restrict__ C, int M, int N, int K, int ldc, const float* __restrict__ alpha,
+                     int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t tiles_base = raw + pad;
+  const uint32_t bars_base = tiles_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + ACC_STAGES + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_tiles = num_m * num_n;
+  const int num_kb = K / 256;      // K blocks of 256 elements
+  const int kb64 = K / 64;         // 512-byte scale tiles per 128-row block
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < ACC_STAGES; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_idx, n_idx;
+        tile_coords(tile, num_m, num_n, m_idx, n_idx);
+        const uint8_t* sa = sfa + ((size_t)m_idx * kb64) * 512;
+        const uint8_t* sb = sfb + ((size_t)n_idx * kb64) * 512;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          const uint32_t dst = tiles_base + stage * STAGE_BYTES;
+          tma_load_2d(dst, &tmA, full_bar(stage), kb * BKB, m_idx * BM);
+          tma_load_2d(dst + A_BYTES, &tmB, full_bar(stage), kb * BKB, n_idx * BN);
+          bulk_load(dst + A_BYTES + B_BYTES, sa + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          bulk_load(dst + A_BYTES + B_BYTES + SF_BYTES, sb + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t src = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sf_tmem = tmem_base + SF_COL + (uint32_t)stage * 32u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            cp_sf(sf_tmem + 4 * k, desc_sf(src + A_BYTES + B_BYTES + 512 * k));
+            cp_sf(sf_tmem + 16 + 4 * k, desc_sf(src + A_BYTES + B_BYTES + SF_BYTES + 512 * k));
+          }
+          const uint64_t da = desc_sw128(src), db = desc_sw128(src + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 64 elements = 32 bytes of codes per instruction
+            umma_fp4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), sf_tmem + 4 * k, sf_tmem + 16 + 4 * k, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_to(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_to(tfull_bar(acc));
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    const int lane_base = 32 * (warp & 3);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const float al = alpha ? __ldg(alpha) : 1.0f;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m_idx, n_idx;
+      tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_idx * BM + lane_base + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(acc * BN);
+      bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = n_idx * BN + c * 32 + v * 8;
+            if (col + 8 <= N) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * al, __uint_as_float(r[v * 8 + 1]) * al);
+              o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * al, __uint_as_float(r[v * 8 + 3]) * al);
+              o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * al, __uint_as_float(r[v * 8 + 5]) * al);
+              o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * al, __uint_as_float(r[v * 8 + 7]) * al);
+              *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) set_err(err, DERR_GEMM_TIMEOUT);
+#pragma unroll 1
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// scales [rows, K/16] row-major -> the 128 x 4 tiled layout, padded to whole 128-row blocks (pad bytes zero)
+__global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restrict__ tiled, int rows, int groups) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int kb64 = groups / 4;
+  const size_t total = (size_t)((rows + 127) / 128) * kb64 * 512;
+  if (i >= total) return;
+  const size_t tile = i / 512;
+  const int in = (int)(i - tile * 512);
+  const int rb = (int)(tile / kb64), kc = (int)(tile - (size_t)rb * kb64);
+  const int r = rb * 128 + (in >> 4) + ((in >> 2) & 3) * 32, g = kc * 4 + (in & 3);
+  tiled[i] = r < rows ? lin[(size_t)r * groups + g] : (uint8_t)0;
+}
+
+}  // namespace nvg
+
+bool nvfp4_tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 256) == 0 && (N % 8) == 0; }
+size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 127) / 128) * (K / 64) * 512; }
+
+cudaError_t nvfp4_gemm_prepare_device() {
+  return cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::SMEM_BYTES);
+}
+cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s) {
+  const size_t total = nvfp4_sf_tiled_bytes(rows, K);
+  if (!total) return cudaSuccess;
+  nvg::sf_tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(lin, tiled, rows, K / 16);
+  return cudaGetLastError();
+}
+// tmA/tmB: tc_make_tmap_fp8_a-style byte maps over the code matrices [rows, K/2] with 128-row boxes (tc_make_tmap_u8_128).
+cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
+                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream) {
+  if (!nvfp4_tc_shape_ok(M, N, K)) return cudaErrorInvalidValue;
+  const int num_tiles = ((M + nvg::BM - 1) / nvg::BM) * ((N + nvg::BN - 1) / nvg::BN);
+  const int grid = num_tiles < sm_count ? num_tiles : sm_count;
+  nvg::gemm_nvfp4_tc_kernel<<<grid, nvg::NUM_THREADS, nvg::SMEM_BYTES, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmA),
+                                                                                  *reinterpret_cast<const CUtensorMap*>(tmB), sfa_tiled, sfb_tiled,
+                                                                                  (bf16*)C, M, N, K, ldc, alpha, err);
+  return cudaGetLastError();
+}

@@ -54,6 +54,24 @@ int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, voi
   return rc_of(launch_nvfp4_fakequant_rows((const bf16*)x, x_stride, global, (bf16*)out, rows, K, S(stream)));
 }
 
+int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K, int ldc,
+                        const float* alpha, int sm_count, int* err, void* stream) {
+  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0) return DCD_E_INVALID;
+  if (nvfp4_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap ta, tb;
+  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || tc_make_tmap_fp8_a(&tb, wq, N, K / 2)) return DCD_E_CUDA;
+  uint8_t *sa = nullptr, *sb = nullptr;  // scales re-laid in 128 x 4 tiles for the duration of the call
+  cudaStream_t st = S(stream);
+  if (cudaMallocAsync(&sa, nvfp4_sf_tiled_bytes(M, K), st) != cudaSuccess) return DCD_E_OOM;
+  if (cudaMallocAsync(&sb, nvfp4_sf_tiled_bytes(N, K), st) != cudaSuccess) { cudaFreeAsync(sa, st); return DCD_E_OOM; }
+  cudaError_t ce = launch_nvfp4_sf_tile((const uint8_t*)x_scales, sa, M, K, st);
+  if (ce == cudaSuccess) ce = launch_nvfp4_sf_tile((const uint8_t*)w_scales, sb, N, K, st);
+  if (ce == cudaSuccess) ce = nvfp4_gemm_launch(&ta, &tb, sa, sb, C, M, N, K, ldc, alpha, sm_count, err, st);
+  cudaFreeAsync(sa, st);
+  cudaFreeAsync(sb, st);
+  return rc_of(ce);
+}
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

@@ -533,3 +533,31 @@ def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
                G.devi([0, L]), 1, L, nk, nv, dk, dv, err, dtype, None)
         np.testing.assert_array_equal(G.host(o1), got[sl])
     assert int(err.item()) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 1024), (300, 776, 512), (2048, 5120, 1024), (77, 264, 5120)])
+def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K):
+    """The native block-scaled FP4 GEMM against an f32 matmul of the dequantised operands (decode(code) * decode(scale)
+    is exact in bf16, so the two differ only by the f32 summation order and the final bf16 rounding)."""
+    import torch
+    r = rng(M + 3 * N + 7 * K)
+    X = oracle.rb((r.standard_normal((M, K)) * np.exp(r.uniform(-1, 1, (M, 1)))).astype(np.float32))
+    W = oracle.rb((r.standard_normal((N, K)) * 0.05).astype(np.float32))
+    dX, dW = G.dev(X, 1), G.dev(W, 1)
+    xq = torch.zeros((M, K // 2), dtype=torch.uint8, device="cuda"); xs = torch.zeros((M, K // 16), dtype=torch.uint8, device="cuda")
+    wq = torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda"); ws = torch.zeros((N, K // 16), dtype=torch.uint8, device="cuda")
+    wglobal = 2688.0 / float(np.abs(W).max())
+    G.call("dcd_k_nvfp4_quant_rows", dX, K, C.c_float(1.0), xq, xs, M, K, None)
+    G.call("dcd_k_nvfp4_quant_rows", dW, K, C.c_float(wglobal), wq, ws, N, K, None)
+    xd = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda"); wd = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_nvfp4_dequant_rows", xq, xs, xd, M, K, None)
+    G.call("dcd_k_nvfp4_dequant_rows", wq, ws, wd, N, K, None)
+    alpha = torch.tensor([1.0 / wglobal], dtype=torch.float32, device="cuda")
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    G.call("dcd_k_gemm_nvfp4_tc", xq, xs, wq, ws, out, M, N, K, N, alpha, G.sm_count(), err, None)
+    assert int(err.item()) == 0, "a bounded wait gave up inside the kernel"
+    want = ((xd.float() @ wd.float().T) / wglobal).cpu().numpy()
+    got = G.host(out)
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2 * float(np.abs(want).max()) / 8)
