@@ -290,7 +290,7 @@ def run_ours(args):
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"bf16": "bf16", "fp8": "fp8 e4m3 GEMMs in the question pass (bf16 capture, bf16 activations elsewhere)",
                       "w4a16": "bf16 activations, int4 group-128 weights (BASELINE configs[2] format)",
-                      "nvfp4": "NVFP4 weights and activations (W4A4 semantics) computed on the bf16 tensor-core GEMM"}[args.precision],
+                      "nvfp4": "NVFP4 weights and activations (W4A4 semantics) on the block-scaled FP4 tensor-core GEMM (tcgen05 kind::mxf4nvf4)"}[args.precision],
             "data": "synthetic", "config": config_dict(args, world),
             "states_per_s": world * args.steps / t_dev,
             "step_tflop": flops_step / 1e12, "model_tflops_per_gpu": flops_step * args.steps / t_dev / 1e12,

@@ -49,7 +49,8 @@ struct LayerW {
   struct W4 { uint32_t* q = nullptr; void* scale = nullptr; int N = 0, K = 0; };
   W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
   // NVFP4 images (precision 3): e2m1 codes, e4m3 scale per 16, f32 tensor scale and GEMM alpha on the device
-  struct NV4 { uint8_t* q = nullptr; uint8_t* sf = nullptr; float* wg = nullptr; float* alpha = nullptr; int N = 0, K = 0; };
+  // codes, row-major scales, the same scales in the 128 x 4 tiled layout of the block-scaled MMA, tensor scale, 1/tensor scale
+  struct NV4 { uint8_t* q = nullptr; uint8_t* sf = nullptr; uint8_t* sft = nullptr; float* wg = nullptr; float* alpha = nullptr; int N = 0, K = 0; TcTensorMap tm; };
   NV4 n_gu, n_down, n_qkv, n_o, n_gin, n_out;
 };
 
@@ -101,6 +102,8 @@ struct dcd_engine {
   TcTensorMap tm_gdn[3];  // q/k/conv views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
   int tm_gdn_tokens = -1;
   bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
+  bool nv4_native = false;             // ... on the block-scaled FP4 tensor-core GEMM (gemm_path 0) instead of dequantise + bf16 GEMM (2)
+  uint8_t *xq = nullptr, *xsf = nullptr, *xsft = nullptr;  // activation codes, row-major scales, tiled scales
   void* xstage = nullptr;              // bf16 [Tm, max K]: activations after the NVFP4 round trip
   unsigned int* amax_tmp = nullptr;
   bool w4 = false;                     // precision 1: int4 g128 weights, dequantised per GEMM into wstage
@@ -268,8 +271,23 @@ struct Scope {
 template <typename T>
 int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
          const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi) {
+  if (e->nv4_native && epi == 0 && n4->sft && nvfp4_tc_shape_ok(M, N, K)) {
+    // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131) on the block-scaled FP4 MMA: activations are
+    // quantised per 16 elements (tensor scale 1), both scale sets are read in the 128 x 4 tiled layout, alpha =
+    // 1/(weight_global*input_global) in the epilogue.
+    {
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5625 * M * (double)K, 2);
+      CK(e, launch_nvfp4_quant_rows((const bf16*)X, (size_t)K, nullptr, 1.0f, e->xq, e->xsf, M, K, e->stream), "nvfp4 activation quantisation");
+      CK(e, launch_nvfp4_sf_tile(e->xsf, e->xsft, M, K, e->stream), "nvfp4 activation scale tiling");
+    }
+    TcTensorMap ta;
+    if (tc_make_tmap_fp8_a(&ta, e->xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
+    Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
+    CK(e, nvfp4_gemm_launch(&ta, &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream), "tcgen05 nvfp4 gemm");
+    return DCD_OK;
+  }
   if (e->nv4) {
-    // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131): both operands go through the
+    // The same product by the long route (gemm_path 2, or a shape the native kernel does not take): both operands go through the
     // e2m1/e4m3 round trip; their dequantised values are exact in bf16, so the bf16 tensor-core GEMM
     // gives the block-scaled product; alpha = 1/(weight_global*input_global) in the epilogue.
     {
@@ -326,6 +344,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
   const int nk = c.gdn_k_heads, nv = c.gdn_v_heads, dk = c.gdn_dk, dv = c.gdn_dv;
   cudaStream_t s = e->stream;
   const bool tc = e->bf && e->o.gemm_path == 0;
+  const bool fused_swiglu = tc && !e->nv4_native;  // the block-scaled FP4 kernel has the plain epilogue only
   // FP8 only in question passes with enough rows; capture and the per-row reference stay bf16
   // (native/src/engine.rs:4321-4326, fp8_min_rows :246-257)
   const bool q8 = e->fp8 && tc && p.mode == 1 && p.T >= e->o.fp8_min_rows;
@@ -439,7 +458,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       CK(e, launch_add_rmsnorm<T>((const T*)e->x, (const T*)e->mix, (const T*)w.post_norm, (T*)e->x1, (T*)e->h, T_, H, c.rms_eps, s),
          "add_rmsnorm");
     }
-    if (tc) {
+    if (fused_swiglu) {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, &w.n_gu, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
     } else {
@@ -618,7 +637,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   dcd_options o = {};
   if (opt) o = *opt;
   if (o.precision < 0 || o.precision > 3) return fail(nullptr, DCD_E_UNSUPPORTED, "precision %d unknown (0 = config dtype, 1 = w4a16 g128, 2 = fp8, 3 = nvfp4)", o.precision);
-  if (o.precision == 3 && ((c.hidden % 16) || (c.intermediate % 16) || ((c.heads * c.head_dim) % 16) || ((c.gdn_v_heads * c.gdn_dv) % 16) || o.gemm_path != 0))
+  if (o.precision == 3 && ((c.hidden % 16) || (c.intermediate % 16) || ((c.heads * c.head_dim) % 16) || ((c.gdn_v_heads * c.gdn_dv) % 16) || (o.gemm_path != 0 && o.gemm_path != 2)))
     return fail(nullptr, DCD_E_UNSUPPORTED, "nvfp4 needs every GEMM K to be a multiple of 16 and the tensor-core GEMM path");
   if (o.precision != 0 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 / fp8 precision needs a bf16 engine (dtype 1)");
   if (o.precision == 1 && ((c.hidden % 8) || (c.intermediate % 8))) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 needs K multiples of 8");
@@ -703,6 +722,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->fp8 = o.precision == 2 && o.gemm_path == 0;
   e->w4 = o.precision == 1;
   e->nv4 = o.precision == 3;
+  e->nv4_native = e->nv4 && o.gemm_path == 0;
+  if (e->nv4_native) CRE(nvfp4_gemm_prepare_device(), "nvfp4 GEMM shared-memory attribute");
   e->gdn_tc = e->bf && o.gdn_path == 0 && gdn_tc_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_tc) CRE(gdn_tc_prepare_device<bf16>(), "tcgen05 GDN shared-memory attribute");
   e->gdn_chunked = e->bf && !e->gdn_tc && (o.gdn_path == 0 || o.gdn_path == 2) && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
@@ -732,6 +753,10 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
         int rc = dev_alloc(e, reinterpret_cast<void**>(&g.q), n * k / 2, true, &e->weight_bytes);
         if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&g.sf), n * k / 16, true, &e->weight_bytes);
         if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&g.wg), 256, true, &e->weight_bytes);
+        if (!rc && e->nv4_native && (k % 256) == 0) {  // shapes the block-scaled kernel takes; others go the dequantise + bf16 route
+          rc = dev_alloc(e, reinterpret_cast<void**>(&g.sft), nvfp4_sf_tiled_bytes((int)n, (int)k), true, &e->weight_bytes);
+          if (!rc && tc_make_tmap_fp8_a(&g.tm, g.q, n, k / 2)) rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 weight operand");
+        }
         g.alpha = g.wg + 1;
         return rc;
       };
@@ -849,6 +874,11 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (e->H > e->max_k) e->max_k = e->H;
   if ((int)aw > e->max_k) e->max_k = (int)aw;
   if (e->nv4) CRA(e->xstage, Tm * (size_t)e->max_k * 2, false, ws);
+  if (e->nv4_native) {
+    CRA(e->xq, Tm * (size_t)e->max_k / 2, false, ws);
+    CRA(e->xsf, Tm * (size_t)e->max_k / 16, false, ws);
+    CRA(e->xsft, nvfp4_sf_tiled_bytes((int)Tm, (e->max_k + 63) / 64 * 64) + 512, false, ws);
+  }
   if (e->fp8) {
     CRA(e->aq, Tm * (size_t)e->max_k, false, ws);
     CRA(e->a_scale, Tm * 4, false, ws);
@@ -935,6 +965,10 @@ static int w4_stage_out(dcd_engine* e, const Loc& L) {
     CK(e, launch_absmax_bf16((const bf16*)e->wstage, (size_t)L.nv->N * L.nv->K, e->amax_tmp, e->stream), "nvfp4 absmax");
     CK(e, launch_nvfp4_global(e->amax_tmp, L.nv->wg, L.nv->alpha, 1.0f, e->stream), "nvfp4 tensor scale");
     CK(e, launch_nvfp4_quant_rows((const bf16*)e->wstage, (size_t)L.nv->K, L.nv->wg, 0.f, L.nv->q, L.nv->sf, L.nv->N, L.nv->K, e->stream), "nvfp4 stage out");
+    if (L.nv->sft) {
+      e->launches += 1;
+      CK(e, launch_nvfp4_sf_tile(L.nv->sf, L.nv->sft, L.nv->N, L.nv->K, e->stream), "nvfp4 scale tiling");
+    }
     return DCD_OK;
   }
   if (!L.w4) return DCD_OK;

@@ -72,7 +72,7 @@ typedef struct dcd_options {
   int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
   int64_t max_keys;
   int64_t max_scores;
-  int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMM (bf16 only); 1 = plain FMA GEMM (diagnostic) */
+  int32_t gemm_path;        /* 0 = tcgen05 tensor-core GEMMs (bf16 engines; precision 3 runs on the block-scaled FP4 kernel); 1 = plain FMA GEMM (diagnostic); 2 = precision 3 only: dequantise + bf16 tensor-core GEMM */
   int32_t attn_path;        /* 0 = tcgen05 attention where the shape allows (bf16, head_dim 256, 6:1 GQA); 1 = plain FMA attention */
   int32_t max_positions;    /* RoPE table length; default 65536 */
   int32_t gdn_path;         /* 0 = chunked gated delta rule on tcgen05 (bf16, dk = dv = 128), else on mma.sync (dk 128); 1 = sequential f32; 2 = mma.sync chunked */
