@@ -282,6 +282,16 @@ def run_ours(args):
             peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained: cuBLAS bf16 GEMM loop under the power cap)"
         else:
             peak, peak_src = 1400.0, "fallback (earlier sustained measurement on this pool)"
+        # No measured fp8 / fp4 tensor figure exists for this pool: those precisions are set against the measured bf16
+        # number times the nominal ratio of the dense peaks (2x, 4x), and say so.
+        kernel_name = {"bf16": "gemm_bf16_tc_kernel (tcgen05, all projection/MLP GEMMs)",
+                       "w4a16": "gemm_bf16_tc_kernel (tcgen05) on weights dequantised from int4 per call",
+                       "fp8": "gemm_bf16_tc_kernel<.,1> (tcgen05 kind::f8f6f4, e4m3 operands; capture pass in bf16)",
+                       "nvfp4": "gemm_nvfp4_tc_kernel (tcgen05 kind::mxf4nvf4 block-scaled)"}[args.precision]
+        ratio = {"bf16": 1.0, "w4a16": 1.0, "fp8": 2.0, "nvfp4": 4.0}[args.precision]
+        if ratio != 1.0:
+            peak *= ratio
+            peak_src += " x %g (nominal dense %s : bf16 ratio; no measured %s figure on this pool)" % (ratio, args.precision, args.precision)
         g = prof["gemm"]
         achieved = g["work"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else 0.0
         flops_step = cfg.capture_flops(S) + sum(cfg.question_flops(int(n), S) for n in lens)
@@ -298,8 +308,8 @@ def run_ours(args):
                     "d2h_bytes_per_step": int(4 * B * cfg.readout_rows + 8), "p50_request_latency_ms": statistics.median(lat) * 1e3, "max_request_latency_ms": max(lat) * 1e3,
                     "logits_identical_to_device_arm": same},
             "gpu_launches": int(launches),
-            "roofline": {"kernel": "gemm_bf16_tc_kernel (tcgen05, all projection/MLP GEMMs)", "bound": "tensor", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": GEMM_TRAFFIC_BYTES, "peak_source": peak_src,
+            "roofline": {"kernel": kernel_name, "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": GEMM_TRAFFIC_BYTES if args.precision == "bf16" else None, "peak_source": peak_src,
                          "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"])},
             "kernel_time_share_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
             "clocks": clock_info,
