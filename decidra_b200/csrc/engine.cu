@@ -276,9 +276,8 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     // quantised per 16 elements (tensor scale 1), both scale sets are read in the 128 x 4 tiled layout, alpha =
     // 1/(weight_global*input_global) in the epilogue.
     {
-      Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5625 * M * (double)K, 2);
-      CK(e, launch_nvfp4_quant_rows((const bf16*)X, (size_t)K, nullptr, 1.0f, e->xq, e->xsf, M, K, e->stream), "nvfp4 activation quantisation");
-      CK(e, launch_nvfp4_sf_tile(e->xsf, e->xsft, M, K, e->stream), "nvfp4 activation scale tiling");
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5625 * M * (double)K, 1);
+      CK(e, launch_nvfp4_act_quant_tiled((const bf16*)X, (size_t)K, e->xq, e->xsft, M, K, e->stream), "nvfp4 activation quantisation");
     }
     TcTensorMap ta;
     if (tc_make_tmap_fp8_a(&ta, e->xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");

@@ -24,6 +24,8 @@
 // Every mbarrier wait is bounded: when a wait gives up the kernel raises an error word, lets in-flight
 // copies land, frees its TMEM and returns.
 #include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "common.cuh"
 #include "gemm_tcgen05.h"
@@ -241,6 +243,57 @@ __global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restr
   tiled[i] = r < rows ? lin[(size_t)r * groups + g] : (uint8_t)0;
 }
 
+// Activation quantiser for the block-scaled GEMM: bf16 rows (tensor scale 1) -> e2m1 codes [rows, K/2] and e4m3 scales
+// written straight into the 128 x 4 tiled layout. Same rule as quant_nvfp4_act_bf16 / fp4_encode
+// (native/kernels/kernels.cu:222-277): sf = e4m3_satfinite(max(absmax16/6, 1e-10)), code = fp4_encode(v / decode(sf)).
+// The division is replaced by comparing |v| with threshold * decode(sf): v has an 8-bit significand, decode(sf) a 4-bit
+// one and the thresholds at most 3 bits, so the products are exact and v / decode(sf) can only round onto a threshold
+// when it equals it; both forms give the same code, including decode(sf) = 0 (every comparison true: code 7, as
+// fp4_encode gives for inf and NaN). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
+__global__ void __launch_bounds__(128) act_quant_tiled_kernel(const bf16* __restrict__ x, size_t x_stride, uint8_t* __restrict__ packed,
+                                                              uint8_t* __restrict__ tiled, int rows, int K) {
+  const int chunks = K / 64;
+  const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (size_t)rows * chunks) return;
+  const int row = (int)(t / chunks), ch = (int)(t - (size_t)row * chunks);
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * x_stride + ch * 64);
+  uint32_t codes[8];
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint4 lo = src[2 * g], hi = src[2 * g + 1];
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float v[16];
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      m = fmaxf(m, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    const float sf = fmaxf(m / 6.0f, 1e-10f);
+    const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+    const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
+    sfw |= (uint32_t)sb << (8 * g);
+    const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
+    uint32_t c0 = 0, c1 = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float a = fabsf(v[i]);
+      uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
+      e |= v[i] < 0.f ? 8u : 0u;
+      if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
+    }
+    codes[2 * g] = c0;
+    codes[2 * g + 1] = c1;
+  }
+  uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)row * (K / 2) + ch * 32);
+  dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+  *reinterpret_cast<uint32_t*>(tiled + ((size_t)(row >> 7) * chunks + ch) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4) = sfw;
+}
+
 }  // namespace nvg
 
 bool nvfp4_tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 256) == 0 && (N % 8) == 0; }
@@ -248,6 +301,13 @@ size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 127) / 12
 
 cudaError_t nvfp4_gemm_prepare_device() {
   return cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::SMEM_BYTES);
+}
+cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if ((K % 64) || (x_stride % 8)) return cudaErrorInvalidValue;
+  const size_t n = (size_t)rows * (K / 64);
+  nvg::act_quant_tiled_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(x, x_stride, packed, tiled, rows, K);
+  return cudaGetLastError();
 }
 cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s) {
   const size_t total = nvfp4_sf_tiled_bytes(rows, K);

@@ -40,5 +40,9 @@ bool nvfp4_tc_shape_ok(int M, int N, int K);
 size_t nvfp4_sf_tiled_bytes(int rows, int K);
 cudaError_t nvfp4_gemm_prepare_device();
 cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s);
+// bf16 rows (tensor scale 1) -> codes [rows, K/2] + scales in the tiled layout (rows of the last block beyond `rows` are left
+// as they are: they only meet zero-filled codes). K % 64 == 0.
+struct __nv_bfloat16;
+cudaError_t launch_nvfp4_act_quant_tiled(const __nv_bfloat16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s);
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
                               int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream);

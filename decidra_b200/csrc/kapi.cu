@@ -54,6 +54,15 @@ int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, voi
   return rc_of(launch_nvfp4_fakequant_rows((const bf16*)x, x_stride, global, (bf16*)out, rows, K, S(stream)));
 }
 
+int dcd_k_nvfp4_tile_scales(const void* scales, void* tiled, int rows, int K, void* stream) {
+  if (rows <= 0 || K <= 0 || (K % 64) != 0) return DCD_E_INVALID;
+  return rc_of(launch_nvfp4_sf_tile((const uint8_t*)scales, (uint8_t*)tiled, rows, K, S(stream)));
+}
+
+int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, void* tiled, int rows, int K, void* stream) {
+  return rc_of(launch_nvfp4_act_quant_tiled((const bf16*)x, x_stride, (uint8_t*)packed, (uint8_t*)tiled, rows, K, S(stream)));
+}
+
 int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K, int ldc,
                         const float* alpha, int sm_count, int* err, void* stream) {
   if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0) return DCD_E_INVALID;

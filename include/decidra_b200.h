@@ -271,6 +271,12 @@ DCD_API int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* 
 DCD_API int dcd_k_nvfp4_quant_rows(const void* x, size_t x_stride, float global, void* packed, void* scales, int rows, int K, void* stream);
 DCD_API int dcd_k_nvfp4_dequant_rows(const void* packed, const void* scales, void* out, int rows, int K, void* stream);
 DCD_API int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, void* out, int rows, int K, void* stream);
+/* repack_nvfp4_scales (native/src/weights.rs, layout at :35 and :634, index formula pinned at :833-847): row-major e4m3
+ * scales [rows, K/16] -> the cuBLASLt 128 x 4 tiled layout, ceil(rows/128) * (K/64) * 512 bytes, padding zero. K % 64 == 0. */
+DCD_API int dcd_k_nvfp4_tile_scales(const void* scales, void* tiled, int rows, int K, void* stream);
+/* quant_nvfp4_act_bf16 (native/kernels/kernels.cu:222-277) with tensor scale 1, writing the scales straight into the tiled
+ * layout: x bf16 rows (stride x_stride) -> packed [rows, K/2], tiled (ceil(rows/128) * (K/64) * 512 bytes). K % 64 == 0. */
+DCD_API int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, void* tiled, int rows, int K, void* stream);
 /* Block-scaled NVFP4 GEMM on tcgen05.mma kind::mxf4nvf4 (replaces the cuBLASLt FP4 GEMM of Engine::nvfp4_gemm,
  * native/src/engine.rs:3962-4131): xq [M,K/2] and wq [N,K/2] e2m1 codes, x_scales [M,K/16] and w_scales [N,K/16]
  * e4m3 bytes (row-major, as dcd_k_nvfp4_quant_rows writes them), C [M,ldc] bf16 = *alpha (device scalar, may be

@@ -274,6 +274,16 @@ def k_nvfp4_rows(x, global_scale: float = 1.0):
     return packed, scales, deq
 
 
+def nvfp4_scale_repack(scales: np.ndarray, inner: int) -> np.ndarray:
+    """Row-major e4m3 scales [outer, inner/16] -> cuBLASLt 128 x 4 tiles (uint8, padded to whole 128-row blocks)."""
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    outer = scales.shape[0]
+    out = np.zeros(((outer + 127) // 128) * (inner // 64) * 512, dtype=np.uint8)
+    u8 = C.POINTER(C.c_uint8)
+    lib().orc_nvfp4_scale_repack(scales.ctypes.data_as(u8), outer, inner, out.ctypes.data_as(u8))
+    return out
+
+
 def k_rmsnorm(x, w, eps: float, zero_centered: bool, bf16: bool) -> np.ndarray:
     x, w = _f32(x), _f32(w)
     out = np.empty_like(x)

@@ -397,6 +397,19 @@ static void nvfp4_rows(const float* x, int rows, int K, float global, uint8_t* p
       }
     }
 }
+// Scales [outer, inner/16] row-major -> the 128 x 4 tiled layout that cuBLASLt's block-scaled GEMM (and the block-scaled
+// MMA) reads: repack_nvfp4_scales, native/src/weights.rs (layout stated at :35 and :634, index formula pinned by the
+// reference's test nvfp4_scale_repack_uses_cublaslt_tiles, :833-847). Output padded to whole 128-row blocks with zeros.
+ORC_API void orc_nvfp4_scale_repack(const uint8_t* src, int outer, int inner, uint8_t* out) {
+  const int groups = inner / 16, kb64 = inner / 64, blocks = (outer + 127) / 128;
+  memset(out, 0, (size_t)blocks * kb64 * 512);
+  for (int o = 0; o < outer; ++o)
+    for (int j = 0; j < groups; ++j) {
+      const size_t base = ((size_t)(j / 4) + (size_t)(o / 128) * kb64) * 512;
+      out[base + (o % 32) * 16 + ((o % 128) / 32) * 4 + (j % 4)] = src[(size_t)o * groups + j];
+    }
+}
+
 ORC_API void orc_k_nvfp4_rows(const float* x, int rows, int K, float global, uint8_t* packed, uint8_t* scales, float* deq) {
   nvfp4_rows(x, rows, K, global, packed, scales, deq);
 }

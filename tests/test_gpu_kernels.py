@@ -561,3 +561,31 @@ def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K):
     got = G.host(out)
     assert np.isfinite(got).all()
     np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2 * float(np.abs(want).max()) / 8)
+
+
+@pytest.mark.parametrize("rows,K", [(3, 128), (300, 512), (128, 5120)])
+def test_nvfp4_scale_tiling_bit_exact(G, oracle, rows, K):
+    import torch
+    src = rng(rows + K).integers(0, 256, (rows, K // 16)).astype(np.uint8)
+    want = oracle.nvfp4_scale_repack(src, K)
+    tiled = torch.full((want.size,), 0xAA, dtype=torch.uint8, device="cuda")
+    G.call("dcd_k_nvfp4_tile_scales", torch.from_numpy(src).cuda(), tiled, rows, K, None)
+    assert np.array_equal(tiled.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("rows,K,stride", [(7, 704, 704), (300, 512, 640), (129, 5120, 5120)])
+def test_nvfp4_act_quant_tiled_matches_row_quantiser(G, oracle, rows, K, stride):
+    """The fused activation quantiser (threshold compares, tiled scales) gives the codes and scales of the oracle bit for bit."""
+    import torch
+    r = rng(rows * 3 + K)
+    xf = oracle.rb((r.standard_normal((rows, stride)) * np.exp(r.uniform(-12, 6, (rows, 1)))).astype(np.float32))
+    xf[1] = 0.0
+    xf[2, :40] = 0.0
+    xf[3] = oracle.rb(np.float32(1e-30) * r.standard_normal(stride).astype(np.float32))
+    wp, ws, _ = oracle.k_nvfp4_rows(xf[:, :K], 1.0)
+    want_tiled = oracle.nvfp4_scale_repack(ws, K)
+    packed = torch.zeros((rows, K // 2), dtype=torch.uint8, device="cuda")
+    tiled = torch.zeros((want_tiled.size,), dtype=torch.uint8, device="cuda")
+    G.call("dcd_k_nvfp4_quant_act_tiled", G.dev(xf, 1), stride, packed, tiled, rows, K, None)
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    assert np.array_equal(tiled.cpu().numpy(), want_tiled)

@@ -158,3 +158,17 @@ def test_generator_statistics(oracle):
     # streaming: a range generated from an offset equals the slice of the whole
     assert (oracle.gen_tensor(0, 3, 12, 100, bf16=True, first=1000) == oracle.gen_tensor(0, 3, 12, 1100, bf16=True)[1000:]).all()
     assert (oracle.rb(w) == np.array([oracle.lib().orc_k_rb(float(v)) for v in w[:256]] + list(oracle.rb(w)[256:]), np.float32)).all()
+
+
+def test_nvfp4_scale_repack_uses_cublaslt_tiles(oracle):
+    """The reference's own known-answer test (native/src/weights.rs:833-847): outer = 3, inner = 128, src[i] = i."""
+    outer, inner = 3, 128
+    src = np.arange(outer * inner // 16, dtype=np.uint8).reshape(outer, inner // 16)
+    got = oracle.nvfp4_scale_repack(src, inner)
+    assert got.size == (inner // 64) * 1 * 512
+    for o in range(outer):
+        for j in range(inner // 16):
+            base = ((j // 4) + (o // 128) * (inner // 64)) * 512
+            off = base + (o % 32) * 16 + ((o % 128) // 32) * 4 + (j % 4)
+            assert got[off] == src[o, j], (o, j)
+    assert int(got.astype(np.int64).sum()) == int(src.astype(np.int64).sum())   # everything else is padding
