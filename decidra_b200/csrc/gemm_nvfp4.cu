@@ -9,9 +9,10 @@
 // input_global) applied to the accumulator before rounding.
 //
 // Structure (one CTA per SM, persistent over 128 x 128 output tiles, K in 256-element = 128-byte blocks):
-//   warp 0: producer. Per K block two TMA tile loads (codes of X and W, 128 rows x 128 bytes, 128-byte
-//           swizzle) and two plain bulk copies of 2 KB (the four 512-byte scale tiles of each operand,
-//           contiguous in the tiled layout) into a 5-stage ring;
+//   warps 0, 6, 7: producers, one thread each. Per K block: the X codes tile (128 rows x 128 bytes, TMA, 128-byte
+//           swizzle), the W codes tile, and two plain bulk copies of 2 KB (the four 512-byte scale tiles of each
+//           operand, contiguous in the tiled layout) into a 5-stage ring. One thread issuing all four copies
+//           (about 100 cycles each) was slower than the four MMAs they feed;
 //   warp 1: MMA issuer. Copies the eight scale tiles of the stage into TMEM (tcgen05.cp 32x128b.warpx4: a
 //           512-byte tile becomes 4 columns, lane r % 32 of every 32-lane quarter holding the four scales
 //           of rows r, r+32, r+64, r+96 in its four columns) and issues 4 MMAs (M128 N128 K64);
@@ -36,7 +37,7 @@ using namespace tcc;
 
 constexpr int BM = 128, BN = 128, BKB = 128 /* bytes of codes per row per K block = 256 elements */, STAGES = 5, ACC_STAGES = 2;
 constexpr uint32_t A_BYTES = BM * BKB, B_BYTES = BN * BKB, SF_BYTES = 2048, STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 256;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 constexpr uint32_t SF_COL = 256;
 constexpr int GROUP_M = 16;
@@ -120,8 +121,9 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
+  if (warp == 0 || warp >= 6) {
     if (lane == 0) {
+      // warp 0: X codes (and the expected byte count of the stage); warp 6: W codes; warp 7: both scale sets
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -132,12 +134,16 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const uint8_t* sb = sfb + ((size_t)n_idx * kb64) * 512;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
-          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t dst = tiles_base + stage * STAGE_BYTES;
-          tma_load_2d(dst, &tmA, full_bar(stage), kb * BKB, m_idx * BM);
-          tma_load_2d(dst + A_BYTES, &tmB, full_bar(stage), kb * BKB, n_idx * BN);
-          bulk_load(dst + A_BYTES + B_BYTES, sa + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
-          bulk_load(dst + A_BYTES + B_BYTES + SF_BYTES, sb + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          if (warp == 0) {
+            mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+            tma_load_2d(dst, &tmA, full_bar(stage), kb * BKB, m_idx * BM);
+          } else if (warp == 6) {
+            tma_load_2d(dst + A_BYTES, &tmB, full_bar(stage), kb * BKB, n_idx * BN);
+          } else {
+            bulk_load(dst + A_BYTES + B_BYTES, sa + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+            bulk_load(dst + A_BYTES + B_BYTES + SF_BYTES, sb + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
