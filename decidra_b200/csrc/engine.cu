@@ -50,7 +50,7 @@ struct LayerW {
   W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
   // NVFP4 images (precision 3): e2m1 codes, e4m3 scale per 16, f32 tensor scale and GEMM alpha on the device
   // codes, row-major scales, the same scales in the 128 x 4 tiled layout of the block-scaled MMA, tensor scale, 1/tensor scale
-  struct NV4 { uint8_t* q = nullptr; uint8_t* sf = nullptr; uint8_t* sft = nullptr; float* wg = nullptr; float* alpha = nullptr; int N = 0, K = 0; TcTensorMap tm; };
+  struct NV4 { uint8_t* q = nullptr; uint8_t* sf = nullptr; uint8_t* sft = nullptr; float* wg = nullptr; float* alpha = nullptr; int N = 0, K = 0; TcTensorMap tm, tm256; };
   NV4 n_gu, n_down, n_qkv, n_o, n_gin, n_out;
 };
 
@@ -282,7 +282,9 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     TcTensorMap ta;
     if (tc_make_tmap_fp8_a(&ta, e->xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
     Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
-    CK(e, nvfp4_gemm_launch(&ta, &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream), "tcgen05 nvfp4 gemm");
+    const int bn = N >= 256 ? 256 : 128;
+    CK(e, nvfp4_gemm_launch(&ta, bn == 256 ? &n4->tm256 : &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream, bn),
+       "tcgen05 nvfp4 gemm");
     return DCD_OK;
   }
   if (e->nv4) {
@@ -754,7 +756,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
         if (!rc) rc = dev_alloc(e, reinterpret_cast<void**>(&g.wg), 256, true, &e->weight_bytes);
         if (!rc && e->nv4_native && (k % 256) == 0) {  // shapes the block-scaled kernel takes; others go the dequantise + bf16 route
           rc = dev_alloc(e, reinterpret_cast<void**>(&g.sft), nvfp4_sf_tiled_bytes((int)n, (int)k), true, &e->weight_bytes);
-          if (!rc && tc_make_tmap_fp8_a(&g.tm, g.q, n, k / 2)) rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 weight operand");
+          if (!rc && (tc_make_tmap_fp8_a(&g.tm, g.q, n, k / 2) || tc_make_tmap_fp8_b(&g.tm256, g.q, n, k / 2)))
+            rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 weight operand");
         }
         g.alpha = g.wg + 1;
         return rc;

@@ -35,15 +35,23 @@
 namespace nvg {
 using namespace tcc;
 
-constexpr int BM = 128, BN = 128, BKB = 128 /* bytes of codes per row per K block = 256 elements */, STAGES = 5, ACC_STAGES = 2;
-constexpr uint32_t A_BYTES = BM * BKB, B_BYTES = BN * BKB, SF_BYTES = 2048, STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+// Two tile widths: BN = 128 (5 stages, two accumulators) and BN = 256 (4 stages, one accumulator: TMEM holds 256
+// accumulator columns plus 48 scale columns per stage, so the epilogue of a tile does not overlap the next main loop,
+// but every MMA and every scale copy covers twice the columns).
+constexpr int BM = 128, BKB = 128 /* bytes of codes per row per K block = 256 elements */;
+constexpr uint32_t A_BYTES = BM * BKB, SF_BYTES = 2048;
+template <int BN> struct Cfg {
+  static constexpr int STAGES = BN == 128 ? 5 : 4, ACC_STAGES = BN == 128 ? 2 : 1, NB = BN / 128 /* 128-row scale blocks of W per tile */;
+  static constexpr uint32_t B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES + (1 + NB) * SF_BYTES;
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+  static constexpr uint32_t SF_COLS = 16 + 16 * NB;  // per stage: 16 columns of X scales, then 4 * NB per K step of W scales
+  // block-scaled instruction descriptor: A/B format e2m1 (1) at bits 7 and 10, N>>3 at [17,23), scale format
+  // UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
+  static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
 constexpr int NUM_THREADS = 256;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 constexpr uint32_t SF_COL = 256;
 constexpr int GROUP_M = 16;
-// block-scaled instruction descriptor: A/B format e2m1 (1) at bits 7 and 10, N>>3 at [17,23), scale format
-// UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
-constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {  // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
   return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
@@ -54,14 +62,14 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t smem_addr) {  // 32 rows of
 __device__ __forceinline__ void cp_sf(uint32_t tmem_col, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(sdesc) : "memory");
 }
-__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
       "}\n" ::"r"(tmem_d),
-      "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(sfa), "r"(sfb)
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -78,10 +86,14 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   n_idx = r / gsize;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const uint8_t* __restrict__ sfa,
                      const uint8_t* __restrict__ sfb, bf16* __restrict__ C, int M, int N, int K, int ldc, const float* __restrict__ alpha,
                      int* __restrict__ err) {
+  using CF = Cfg<BN>;
+  constexpr int STAGES = CF::STAGES, ACC_STAGES = CF::ACC_STAGES, NB = CF::NB;
+  constexpr uint32_t B_BYTES = CF::B_BYTES, STAGE_BYTES = CF::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
@@ -131,7 +143,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int m_idx, n_idx;
         tile_coords(tile, num_m, num_n, m_idx, n_idx);
         const uint8_t* sa = sfa + ((size_t)m_idx * kb64) * 512;
-        const uint8_t* sb = sfb + ((size_t)n_idx * kb64) * 512;
+        const uint8_t* sb = sfb + ((size_t)n_idx * NB * kb64) * 512;  // first of the NB 128-row scale blocks of this W tile
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
           const uint32_t dst = tiles_base + stage * STAGE_BYTES;
@@ -142,7 +154,9 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             tma_load_2d(dst + A_BYTES, &tmB, full_bar(stage), kb * BKB, n_idx * BN);
           } else {
             bulk_load(dst + A_BYTES + B_BYTES, sa + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
-            bulk_load(dst + A_BYTES + B_BYTES + SF_BYTES, sb + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+              bulk_load(dst + A_BYTES + B_BYTES + (1 + nb) * SF_BYTES, sb + ((size_t)nb * kb64) * 512 + (size_t)kb * SF_BYTES, SF_BYTES, full_bar(stage));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -161,16 +175,17 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
           tc_fence_after();
           const uint32_t src = tiles_base + stage * STAGE_BYTES;
-          const uint32_t sf_tmem = tmem_base + SF_COL + (uint32_t)stage * 32u;
+          const uint32_t sf_tmem = tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < 4; ++k) {  // W scales of K step k: 4 columns per 128-row block, blocks side by side
             cp_sf(sf_tmem + 4 * k, desc_sf(src + A_BYTES + B_BYTES + 512 * k));
-            cp_sf(sf_tmem + 16 + 4 * k, desc_sf(src + A_BYTES + B_BYTES + SF_BYTES + 512 * k));
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) cp_sf(sf_tmem + 16 + 4 * NB * k + 4 * nb, desc_sf(src + A_BYTES + B_BYTES + (1 + nb) * SF_BYTES + 512 * k));
           }
           const uint64_t da = desc_sw128(src), db = desc_sw128(src + A_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 64 elements = 32 bytes of codes per instruction
-            umma_fp4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), sf_tmem + 4 * k, sf_tmem + 16 + 4 * k, (kb | k) != 0 ? 1u : 0u);
+            umma_fp4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), CF::IDESC, sf_tmem + 4 * k, sf_tmem + 16 + 4 * NB * k, (kb | k) != 0 ? 1u : 0u);
           umma_commit_to(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -236,11 +251,11 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
-// scales [rows, K/16] row-major -> the 128 x 4 tiled layout, padded to whole 128-row blocks (pad bytes zero)
-__global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restrict__ tiled, int rows, int groups) {
+// scales [rows, K/16] row-major -> `blocks` 128-row blocks of the 128 x 4 tiled layout (rows beyond `rows` zero)
+__global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restrict__ tiled, int rows, int groups, int blocks) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int kb64 = groups / 4;
-  const size_t total = (size_t)((rows + 127) / 128) * kb64 * 512;
+  const size_t total = (size_t)blocks * kb64 * 512;
   if (i >= total) return;
   const size_t tile = i / 512;
   const int in = (int)(i - tile * 512);
@@ -303,10 +318,12 @@ __global__ void __launch_bounds__(128) act_quant_tiled_kernel(const bf16* __rest
 }  // namespace nvg
 
 bool nvfp4_tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && (K % 256) == 0 && (N % 8) == 0; }
-size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 127) / 128) * (K / 64) * 512; }
+size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 255) / 256) * 2 * (K / 64) * 512; }
 
 cudaError_t nvfp4_gemm_prepare_device() {
-  return cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::SMEM_BYTES);
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
+  return cudaSuccess;
 }
 cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
@@ -315,20 +332,26 @@ cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t
   nvg::act_quant_tiled_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(x, x_stride, packed, tiled, rows, K);
   return cudaGetLastError();
 }
-cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s) {
-  const size_t total = nvfp4_sf_tiled_bytes(rows, K);
+cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s, bool pad_even) {
+  // pad_even: as the GEMM wants its operands (nvfp4_sf_tiled_bytes); otherwise whole 128-row blocks only, as the reference's repack
+  const int blocks = pad_even ? (rows + 255) / 256 * 2 : (rows + 127) / 128;
+  const size_t total = (size_t)blocks * (K / 64) * 512;
   if (!total) return cudaSuccess;
-  nvg::sf_tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(lin, tiled, rows, K / 16);
+  nvg::sf_tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(lin, tiled, rows, K / 16, blocks);
   return cudaGetLastError();
 }
-// tmA/tmB: tc_make_tmap_fp8_a-style byte maps over the code matrices [rows, K/2] with 128-row boxes (tc_make_tmap_u8_128).
+// tmA: byte map over the X codes [M, K/2] with 128-row boxes (tc_make_tmap_fp8_a); tmB: the same over the W codes with bn-row boxes
+// (tc_make_tmap_fp8_a for bn 128, tc_make_tmap_fp8_b for bn 256).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
-                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream) {
-  if (!nvfp4_tc_shape_ok(M, N, K)) return cudaErrorInvalidValue;
-  const int num_tiles = ((M + nvg::BM - 1) / nvg::BM) * ((N + nvg::BN - 1) / nvg::BN);
+                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn) {
+  if (!nvfp4_tc_shape_ok(M, N, K) || (bn != 128 && bn != 256)) return cudaErrorInvalidValue;
+  const int num_tiles = ((M + nvg::BM - 1) / nvg::BM) * ((N + bn - 1) / bn);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
-  nvg::gemm_nvfp4_tc_kernel<<<grid, nvg::NUM_THREADS, nvg::SMEM_BYTES, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmA),
-                                                                                  *reinterpret_cast<const CUtensorMap*>(tmB), sfa_tiled, sfb_tiled,
-                                                                                  (bf16*)C, M, N, K, ldc, alpha, err);
+  const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
+  const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
+  if (bn == 128)
+    nvg::gemm_nvfp4_tc_kernel<128><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+  else
+    nvg::gemm_nvfp4_tc_kernel<256><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
   return cudaGetLastError();
 }

@@ -34,15 +34,16 @@ cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, v
                                const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream);
 
 // NVFP4 block-scaled GEMM (gemm_nvfp4.cu): e2m1 codes [rows, K/2] bytes (byte maps from tc_make_tmap_fp8_a, 128-row
-// boxes, for both operands), unsigned e4m3 scales per 16 elements in the 128 x 4 tiled layout padded to whole 128-row
+// boxes, for both operands), unsigned e4m3 scales per 16 elements in the 128 x 4 tiled layout padded to an even number of 128-row
 // blocks (launch_nvfp4_sf_tile converts from row-major [rows, K/16]); bf16 C = alpha * (Xq . Wq^T). K % 256 == 0.
 bool nvfp4_tc_shape_ok(int M, int N, int K);
 size_t nvfp4_sf_tiled_bytes(int rows, int K);
 cudaError_t nvfp4_gemm_prepare_device();
-cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s);
+cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s, bool pad_even = true);
 // bf16 rows (tensor scale 1) -> codes [rows, K/2] + scales in the tiled layout (rows of the last block beyond `rows` are left
 // as they are: they only meet zero-filled codes). K % 64 == 0.
 struct __nv_bfloat16;
 cudaError_t launch_nvfp4_act_quant_tiled(const __nv_bfloat16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s);
+// bn: output tile width, 128 or 256; tmB must have bn-row boxes (tc_make_tmap_fp8_a / tc_make_tmap_fp8_b over the codes).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
-                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream);
+                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn);

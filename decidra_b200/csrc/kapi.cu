@@ -56,7 +56,7 @@ int dcd_k_nvfp4_fakequant_rows(const void* x, size_t x_stride, float global, voi
 
 int dcd_k_nvfp4_tile_scales(const void* scales, void* tiled, int rows, int K, void* stream) {
   if (rows <= 0 || K <= 0 || (K % 64) != 0) return DCD_E_INVALID;
-  return rc_of(launch_nvfp4_sf_tile((const uint8_t*)scales, (uint8_t*)tiled, rows, K, S(stream)));
+  return rc_of(launch_nvfp4_sf_tile((const uint8_t*)scales, (uint8_t*)tiled, rows, K, S(stream), false));
 }
 
 int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, void* tiled, int rows, int K, void* stream) {
@@ -64,18 +64,18 @@ int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, vo
 }
 
 int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K, int ldc,
-                        const float* alpha, int sm_count, int* err, void* stream) {
-  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0) return DCD_E_INVALID;
+                        const float* alpha, int sm_count, int* err, int tile_n, void* stream) {
+  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0 || (tile_n != 128 && tile_n != 256)) return DCD_E_INVALID;
   if (nvfp4_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
   TcTensorMap ta, tb;
-  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || tc_make_tmap_fp8_a(&tb, wq, N, K / 2)) return DCD_E_CUDA;
+  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || (tile_n == 128 ? tc_make_tmap_fp8_a(&tb, wq, N, K / 2) : tc_make_tmap_fp8_b(&tb, wq, N, K / 2))) return DCD_E_CUDA;
   uint8_t *sa = nullptr, *sb = nullptr;  // scales re-laid in 128 x 4 tiles for the duration of the call
   cudaStream_t st = S(stream);
   if (cudaMallocAsync(&sa, nvfp4_sf_tiled_bytes(M, K), st) != cudaSuccess) return DCD_E_OOM;
   if (cudaMallocAsync(&sb, nvfp4_sf_tiled_bytes(N, K), st) != cudaSuccess) { cudaFreeAsync(sa, st); return DCD_E_OOM; }
   cudaError_t ce = launch_nvfp4_sf_tile((const uint8_t*)x_scales, sa, M, K, st);
   if (ce == cudaSuccess) ce = launch_nvfp4_sf_tile((const uint8_t*)w_scales, sb, N, K, st);
-  if (ce == cudaSuccess) ce = nvfp4_gemm_launch(&ta, &tb, sa, sb, C, M, N, K, ldc, alpha, sm_count, err, st);
+  if (ce == cudaSuccess) ce = nvfp4_gemm_launch(&ta, &tb, sa, sb, C, M, N, K, ldc, alpha, sm_count, err, st, tile_n);
   cudaFreeAsync(sa, st);
   cudaFreeAsync(sb, st);
   return rc_of(ce);

@@ -280,9 +280,10 @@ DCD_API int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* pa
 /* Block-scaled NVFP4 GEMM on tcgen05.mma kind::mxf4nvf4 (replaces the cuBLASLt FP4 GEMM of Engine::nvfp4_gemm,
  * native/src/engine.rs:3962-4131): xq [M,K/2] and wq [N,K/2] e2m1 codes, x_scales [M,K/16] and w_scales [N,K/16]
  * e4m3 bytes (row-major, as dcd_k_nvfp4_quant_rows writes them), C [M,ldc] bf16 = *alpha (device scalar, may be
- * NULL) * sum over 16-element blocks of scale_x * scale_w * sum(code_x * code_w). K % 256 == 0, N % 8 == 0. */
+ * NULL) * sum over 16-element blocks of scale_x * scale_w * sum(code_x * code_w). K % 256 == 0, N % 8 == 0.
+ * tile_n: output tile width, 128 or 256. */
 DCD_API int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K,
-                                int ldc, const float* alpha, int sm_count, int* err, void* stream);
+                                int ldc, const float* alpha, int sm_count, int* err, int tile_n, void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

@@ -535,8 +535,9 @@ def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
     assert int(err.item()) == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 1024), (300, 776, 512), (2048, 5120, 1024), (77, 264, 5120)])
-def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K):
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 1024), (300, 776, 512), (2048, 5120, 1024), (77, 264, 5120), (130, 392, 768)])
+def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K, tile_n):
     """The native block-scaled FP4 GEMM against an f32 matmul of the dequantised operands (decode(code) * decode(scale)
     is exact in bf16, so the two differ only by the f32 summation order and the final bf16 rounding)."""
     import torch
@@ -555,7 +556,7 @@ def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K):
     alpha = torch.tensor([1.0 / wglobal], dtype=torch.float32, device="cuda")
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    G.call("dcd_k_gemm_nvfp4_tc", xq, xs, wq, ws, out, M, N, K, N, alpha, G.sm_count(), err, None)
+    G.call("dcd_k_gemm_nvfp4_tc", xq, xs, wq, ws, out, M, N, K, N, alpha, G.sm_count(), err, tile_n, None)
     assert int(err.item()) == 0, "a bounded wait gave up inside the kernel"
     want = ((xd.float() @ wd.float().T) / wglobal).cpu().numpy()
     got = G.host(out)
