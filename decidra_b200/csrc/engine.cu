@@ -270,12 +270,12 @@ struct Scope {
 // native/src/engine.rs:4144-4296); plain FMA otherwise.
 template <typename T>
 int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
-         const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi) {
+         const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi, bool x_quantised = false) {
   if (e->nv4_native && epi == 0 && n4->sft && nvfp4_tc_shape_ok(M, N, K)) {
     // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131) on the block-scaled FP4 MMA: activations are
     // quantised per 16 elements (tensor scale 1), both scale sets are read in the 128 x 4 tiled layout, alpha =
     // 1/(weight_global*input_global) in the epilogue.
-    {
+    if (!x_quantised) {  // else the producer of X already left its codes and tiled scales in xq / xsft
       Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5625 * M * (double)K, 1);
       CK(e, launch_nvfp4_act_quant_tiled((const bf16*)X, (size_t)K, e->xq, e->xsft, M, K, e->stream), "nvfp4 activation quantisation");
     }
@@ -287,6 +287,7 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
        "tcgen05 nvfp4 gemm");
     return DCD_OK;
   }
+  if (x_quantised) return fail(e, DCD_E_INVALID, "internal: pre-quantised operand for a GEMM that does not take the block-scaled path");
   if (e->nv4) {
     // The same product by the long route (gemm_path 2, or a shape the native kernel does not take): both operands go through the
     // e2m1/e4m3 round trip; their dequantised values are exact in bf16, so the bf16 tensor-core GEMM
@@ -346,6 +347,10 @@ int run_layers(dcd_engine* e, const Pass& p) {
   cudaStream_t s = e->stream;
   const bool tc = e->bf && e->o.gemm_path == 0;
   const bool fused_swiglu = tc && !e->nv4_native;  // the block-scaled FP4 kernel has the plain epilogue only
+  // ... so SwiGLU runs as its own kernel, which then writes the down projection's operand as NVFP4 directly
+  const bool act_fused_quant = e->nv4_native && sizeof(T) == 2 && (e->I % 256) == 0 && nvfp4_tc_shape_ok(T_, H, e->I);
+  // ... and the norms that feed the q/k/v, GDN input and gate/up projections write NVFP4 instead of bf16 h
+  const bool h_fused_quant = e->nv4_native && sizeof(T) == 2 && (H % 256) == 0 && H <= 8192;
   // FP8 only in question passes with enough rows; capture and the per-row reference stay bf16
   // (native/src/engine.rs:4321-4326, fp8_min_rows :246-257)
   const bool q8 = e->fp8 && tc && p.mode == 1 && p.T >= e->o.fp8_min_rows;
@@ -360,10 +365,11 @@ int run_layers(dcd_engine* e, const Pass& p) {
     LayerW& w = e->layers[li];
     if (li == 0) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 2.0 * xbytes, 1);
-      CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
+      if (h_fused_quant) CK(e, launch_rmsnorm_nvfp4((const bf16*)e->x, (const bf16*)w.input_norm, e->xq, e->xsft, T_, H, c.rms_eps, s), "rmsnorm + nvfp4");
+      else CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)w.input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
     }
     if (w.full) {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, &w.n_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, &w.n_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0, h_fused_quant);
       if (rc) return rc;
       T* big = (T*)e->big;
       T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
@@ -405,7 +411,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, e->mix, T_, H, heads * hd, H, 0);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, &w.n_gin, e->big, T_, e->gin_n, H, e->gin_n, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, &w.n_gin, e->big, T_, e->gin_n, H, e->gin_n, 0, h_fused_quant);
       if (rc) return rc;
       T* big = (T*)e->big;
       if (p.mode == 0) {
@@ -456,24 +462,33 @@ int run_layers(dcd_engine* e, const Pass& p) {
     }
     {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      CK(e, launch_add_rmsnorm<T>((const T*)e->x, (const T*)e->mix, (const T*)w.post_norm, (T*)e->x1, (T*)e->h, T_, H, c.rms_eps, s),
-         "add_rmsnorm");
+      if (h_fused_quant)
+        CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x, (const bf16*)e->mix, (const bf16*)w.post_norm, (bf16*)e->x1, e->xq, e->xsft, T_, H, c.rms_eps, s),
+           "add_rmsnorm + nvfp4");
+      else
+        CK(e, launch_add_rmsnorm<T>((const T*)e->x, (const T*)e->mix, (const T*)w.post_norm, (T*)e->x1, (T*)e->h, T_, H, c.rms_eps, s),
+           "add_rmsnorm");
     }
     if (fused_swiglu) {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, &w.n_gu, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
     } else {
-      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, &w.n_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0);
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, &w.n_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0, h_fused_quant);
       if (rc) return rc;
       Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->I * e->esz * 3.0, 1);
-      CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
+      if (act_fused_quant) CK(e, launch_nvfp4_swiglu_quant_tiled((const bf16*)e->big, e->gu_rows, e->xq, e->xsft, T_, e->I, s), "silu_mul + nvfp4 quantisation");
+      else CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
-    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, e->mix, T_, H, e->I, H, 0);
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, e->mix, T_, H, e->I, H, 0, act_fused_quant);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      CK(e, launch_add_rmsnorm<T>((const T*)e->x1, (const T*)e->mix, (const T*)e->layers[li + 1].input_norm, (T*)e->x, (T*)e->h, T_, H,
-                                  c.rms_eps, s), "add_rmsnorm");
+      if (h_fused_quant)
+        CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x1, (const bf16*)e->mix, (const bf16*)e->layers[li + 1].input_norm, (bf16*)e->x, e->xq, e->xsft,
+                                       T_, H, c.rms_eps, s), "add_rmsnorm + nvfp4");
+      else
+        CK(e, launch_add_rmsnorm<T>((const T*)e->x1, (const T*)e->mix, (const T*)e->layers[li + 1].input_norm, (T*)e->x, (T*)e->h, T_, H,
+                                    c.rms_eps, s), "add_rmsnorm");
     } else {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 3.0 * xbytes, 1);
       CK(e, launch_add<T>((const T*)e->x1, (const T*)e->mix, (T*)e->x, (size_t)T_ * H, s), "add");

@@ -271,6 +271,42 @@ __global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restr
 // one and the thresholds at most 3 bits, so the products are exact and v / decode(sf) can only round onto a threshold
 // when it equals it; both forms give the same code, including decode(sf) = 0 (every comparison true: code 7, as
 // fp4_encode gives for inf and NaN). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
+// 16 values (already bf16-representable) -> scale byte and two words of codes
+__device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  const float sf = fmaxf(m / 6.0f, 1e-10f);
+  const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+  const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
+  sb_out = sb;
+  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
+  c0 = 0;
+  c1 = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = fabsf(v[i]);
+    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
+    e |= v[i] < 0.f ? 8u : 0u;
+    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
+  }
+}
+__device__ __forceinline__ void unpack16(const uint4& lo, const uint4& hi, float (&v)[16]) {
+  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void store_chunk64(uint8_t* packed, uint8_t* tiled, int row, int ch, int chunks, int K, const uint32_t (&codes)[8], uint32_t sfw) {
+  uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)row * (K / 2) + ch * 32);
+  dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+  *reinterpret_cast<uint32_t*>(tiled + ((size_t)(row >> 7) * chunks + ch) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4) = sfw;
+}
+
 __global__ void __launch_bounds__(128) act_quant_tiled_kernel(const bf16* __restrict__ x, size_t x_stride, uint8_t* __restrict__ packed,
                                                               uint8_t* __restrict__ tiled, int rows, int K) {
   const int chunks = K / 64;
@@ -282,37 +318,41 @@ __global__ void __launch_bounds__(128) act_quant_tiled_kernel(const bf16* __rest
   uint32_t sfw = 0;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const uint4 lo = src[2 * g], hi = src[2 * g + 1];
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     float v[16];
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-      m = fmaxf(m, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
-    }
-    const float sf = fmaxf(m / 6.0f, 1e-10f);
-    const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
-    const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
-    const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
-    sfw |= (uint32_t)sb << (8 * g);
-    const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
-    uint32_t c0 = 0, c1 = 0;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float a = fabsf(v[i]);
-      uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
-      e |= v[i] < 0.f ? 8u : 0u;
-      if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
-    }
-    codes[2 * g] = c0;
-    codes[2 * g + 1] = c1;
+    unpack16(src[2 * g], src[2 * g + 1], v);
+    uint32_t sb;
+    quant_group16(v, codes[2 * g], codes[2 * g + 1], sb);
+    sfw |= sb << (8 * g);
   }
-  uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)row * (K / 2) + ch * 32);
-  dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-  dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-  *reinterpret_cast<uint32_t*>(tiled + ((size_t)(row >> 7) * chunks + ch) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4) = sfw;
+  store_chunk64(packed, tiled, row, ch, chunks, K, codes, sfw);
+}
+
+// SwiGLU over the tile-interleaved gate/up GEMM output (each 256-column tile: 128 gate then 128 up columns), rounded as
+// silu_mul_bf16 does (native/kernels/kernels.cu:492-501: bf16(bf16(silu(g)) * u)), quantised on the spot: the bf16
+// activation matrix is never written. One thread per 64 outputs.
+__global__ void __launch_bounds__(128) swiglu_quant_tiled_kernel(const bf16* __restrict__ gu, int gu_stride, uint8_t* __restrict__ packed,
+                                                                 uint8_t* __restrict__ tiled, int rows, int I) {
+  const int chunks = I / 64;
+  const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (size_t)rows * chunks) return;
+  const int row = (int)(t / chunks), ch = (int)(t - (size_t)row * chunks);
+  const int c0 = ch * 64;
+  const uint4* gsrc = reinterpret_cast<const uint4*>(gu + (size_t)row * gu_stride + (size_t)(c0 >> 7) * 256 + (c0 & 127));
+  const uint4* usrc = gsrc + 16;  // + 128 columns
+  uint32_t codes[8];
+  uint32_t sfw = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float gv[16], uv[16], v[16];
+    unpack16(gsrc[2 * g], gsrc[2 * g + 1], gv);
+    unpack16(usrc[2 * g], usrc[2 * g + 1], uv);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = Ty<bf16>::rnd(Ty<bf16>::rnd(__fdividef(gv[i], 1.0f + __expf(-gv[i]))) * uv[i]);
+    uint32_t sb;
+    quant_group16(v, codes[2 * g], codes[2 * g + 1], sb);
+    sfw |= sb << (8 * g);
+  }
+  store_chunk64(packed, tiled, row, ch, chunks, I, codes, sfw);
 }
 
 }  // namespace nvg
@@ -330,6 +370,13 @@ cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t
   if ((K % 64) || (x_stride % 8)) return cudaErrorInvalidValue;
   const size_t n = (size_t)rows * (K / 64);
   nvg::act_quant_tiled_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(x, x_stride, packed, tiled, rows, K);
+  return cudaGetLastError();
+}
+cudaError_t launch_nvfp4_swiglu_quant_tiled(const bf16* gu, int gu_stride, uint8_t* packed, uint8_t* tiled, int rows, int I, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if ((I % 128) || (gu_stride % 8)) return cudaErrorInvalidValue;
+  const size_t n = (size_t)rows * (I / 64);
+  nvg::swiglu_quant_tiled_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(gu, gu_stride, packed, tiled, rows, I);
   return cudaGetLastError();
 }
 cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, int K, cudaStream_t s, bool pad_even) {

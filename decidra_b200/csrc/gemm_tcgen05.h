@@ -44,6 +44,9 @@ cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, i
 // as they are: they only meet zero-filled codes). K % 64 == 0.
 struct __nv_bfloat16;
 cudaError_t launch_nvfp4_act_quant_tiled(const __nv_bfloat16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s);
+// SwiGLU over the tile-interleaved gate/up GEMM output [rows, gu_stride] (256-column tiles: 128 gate, 128 up) fused with the same
+// quantiser: codes [rows, I/2] + tiled scales of the [rows, I] activation. I % 128 == 0.
+cudaError_t launch_nvfp4_swiglu_quant_tiled(const __nv_bfloat16* gu, int gu_stride, uint8_t* packed, uint8_t* tiled, int rows, int I, cudaStream_t s);
 // bn: output tile width, 128 or 256; tmB must have bn-row boxes (tc_make_tmap_fp8_a / tc_make_tmap_fp8_b over the codes).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
                               int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn);

@@ -63,6 +63,10 @@ int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, vo
   return rc_of(launch_nvfp4_act_quant_tiled((const bf16*)x, x_stride, (uint8_t*)packed, (uint8_t*)tiled, rows, K, S(stream)));
 }
 
+int dcd_k_nvfp4_swiglu_quant_tiled(const void* gu, int gu_stride, void* packed, void* tiled, int rows, int I, void* stream) {
+  return rc_of(launch_nvfp4_swiglu_quant_tiled((const bf16*)gu, gu_stride, (uint8_t*)packed, (uint8_t*)tiled, rows, I, S(stream)));
+}
+
 int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K, int ldc,
                         const float* alpha, int sm_count, int* err, int tile_n, void* stream) {
   if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0 || (tile_n != 128 && tile_n != 256)) return DCD_E_INVALID;

@@ -169,10 +169,38 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
-template <int NV, bool ADD, typename TO>
+// NVFP4 quantisation of 16 consecutive values held 8 + 8 by two neighbouring lanes (tensor scale 1; same rule as
+// quant_nvfp4_act_bf16 / fp4_encode, native/kernels/kernels.cu:222-277, with the division replaced by exact threshold
+// products as in the stand-alone activation quantiser). Returns this lane's 8 codes; *sb = the group's e4m3 scale byte.
+__device__ __forceinline__ uint32_t nvfp4_encode_half_group(const float (&y)[8], uint32_t* sb_out) {
+  float m = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(y[j]));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  const float sf = fmaxf(m / 6.0f, 1e-10f);
+  const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+  const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
+  *sb_out = sb;
+  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
+  uint32_t c = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float a = fabsf(y[j]);
+    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
+    e |= y[j] < 0.f ? 8u : 0u;
+    c |= e << (4 * j);
+  }
+  return c;
+}
+
+// QUANT: instead of the bf16 output row, write its NVFP4 image: codes to q_packed [rows, cols/2] and the e4m3 group scales
+// into the 128 x 4 tiled layout q_tiled (the operand format of the block-scaled GEMM). cols % 64 == 0.
+template <int NV, bool ADD, typename TO, bool QUANT = false>
 __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ mix, const bf16* __restrict__ w,
                                                           bf16* __restrict__ residual, TO* __restrict__ out, int cols, float eps, float wofs,
-                                                          const int32_t* __restrict__ rows_idx) {
+                                                          const int32_t* __restrict__ rows_idx, uint8_t* __restrict__ q_packed = nullptr,
+                                                          uint8_t* __restrict__ q_tiled = nullptr) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const size_t in_row = rows_idx ? (size_t)rows_idx[row] : (size_t)row;
@@ -203,7 +231,24 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const bf16* __restrict
 #pragma unroll
   for (int c = 0; c < NV; ++c) {
     const int i = threadIdx.x + c * 256;
-    if (i < n8) {
+    if constexpr (QUANT) {  // every lane takes part in the pair exchange; lanes beyond the row carry zeros and store nothing
+      float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (i < n8) {
+        float wv[8];
+        unpack8(wr[i], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = Ty<bf16>::rnd(v[c][j] * scale * (wv[j] + wofs));
+      }
+      uint32_t sb;
+      const uint32_t codes = nvfp4_encode_half_group(y, &sb);
+      if (i < n8) {
+        reinterpret_cast<uint32_t*>(q_packed + (size_t)row * (cols >> 1))[i] = codes;
+        if ((i & 1) == 0) {
+          const int g = i >> 1;  // group of 16 along the row
+          q_tiled[((size_t)(row >> 7) * (cols >> 6) + (g >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (g & 3)] = (uint8_t)sb;
+        }
+      }
+    } else if (i < n8) {
       float wv[8], y[8];
       unpack8(wr[i], wv);
 #pragma unroll
@@ -229,6 +274,18 @@ cudaError_t launch_rmsnorm(const T* x, const T* w, T* out, int rows, int cols, f
     }
   }
   rmsnorm_kernel<T, T><<<rows, 256, 0, s>>>(x, w, out, cols, eps, zero_centered ? 1.0f : 0.0f, nullptr);
+  return cudaGetLastError();
+}
+// The two norms that feed a GEMM, writing that GEMM's NVFP4 operand instead of bf16 (bf16 engines; cols % 64 == 0, cols <= 8192).
+cudaError_t launch_rmsnorm_nvfp4(const bf16* x, const bf16* w, uint8_t* q_packed, uint8_t* q_tiled, int rows, int cols, float eps, cudaStream_t s) {
+  if ((cols % 64) != 0 || !vec_norm_ok(cols)) return cudaErrorInvalidValue;
+  rmsnorm_vec_kernel<4, false, bf16, true><<<rows, 256, 0, s>>>(x, nullptr, w, nullptr, nullptr, cols, eps, 1.0f, nullptr, q_packed, q_tiled);
+  return cudaGetLastError();
+}
+cudaError_t launch_add_rmsnorm_nvfp4(const bf16* x, const bf16* mix, const bf16* w, bf16* residual, uint8_t* q_packed, uint8_t* q_tiled, int rows,
+                                     int cols, float eps, cudaStream_t s) {
+  if ((cols % 64) != 0 || !vec_norm_ok(cols)) return cudaErrorInvalidValue;
+  rmsnorm_vec_kernel<4, true, bf16, true><<<rows, 256, 0, s>>>(x, mix, w, residual, nullptr, cols, eps, 1.0f, nullptr, q_packed, q_tiled);
   return cudaGetLastError();
 }
 template <typename T>

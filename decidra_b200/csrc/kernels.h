@@ -13,6 +13,12 @@ template <typename T>
 cudaError_t launch_rmsnorm(const T* x, const T* w, T* out, int rows, int cols, float eps, bool zero_centered, cudaStream_t s);
 template <typename T>
 cudaError_t launch_add_rmsnorm(const T* x, const T* mix, const T* w, T* residual, T* out, int rows, int cols, float eps, cudaStream_t s);
+// RMSNorm(1+w) / residual add + RMSNorm(1+w) whose output row goes straight to the NVFP4 operand format of the block-scaled GEMM
+// (codes [rows, cols/2], e4m3 scales in the 128 x 4 tiled layout); the bf16 output is not written. cols % 64 == 0.
+cudaError_t launch_rmsnorm_nvfp4(const __nv_bfloat16* x, const __nv_bfloat16* w, uint8_t* q_packed, uint8_t* q_tiled, int rows, int cols, float eps,
+                                 cudaStream_t s);
+cudaError_t launch_add_rmsnorm_nvfp4(const __nv_bfloat16* x, const __nv_bfloat16* mix, const __nv_bfloat16* w, __nv_bfloat16* residual,
+                                     uint8_t* q_packed, uint8_t* q_tiled, int rows, int cols, float eps, cudaStream_t s);
 template <typename T>
 cudaError_t launch_final_norm_rows(const T* x, const T* w, float* out, const int32_t* rows_idx, int B, int cols, float eps, cudaStream_t s);
 template <typename T>

@@ -277,6 +277,10 @@ DCD_API int dcd_k_nvfp4_tile_scales(const void* scales, void* tiled, int rows, i
 /* quant_nvfp4_act_bf16 (native/kernels/kernels.cu:222-277) with tensor scale 1, writing the scales straight into the tiled
  * layout: x bf16 rows (stride x_stride) -> packed [rows, K/2], tiled (ceil(rows/128) * (K/64) * 512 bytes). K % 64 == 0. */
 DCD_API int dcd_k_nvfp4_quant_act_tiled(const void* x, size_t x_stride, void* packed, void* tiled, int rows, int K, void* stream);
+/* silu_mul_bf16 (native/kernels/kernels.cu:492-501) over the tile-interleaved gate/up GEMM output gu [rows, gu_stride] (each
+ * 256-column tile: 128 gate then 128 up columns) fused with dcd_k_nvfp4_quant_act_tiled: packed [rows, I/2] and the tiled
+ * scales of the [rows, I] activation; the bf16 activation itself is not written. I % 128 == 0. */
+DCD_API int dcd_k_nvfp4_swiglu_quant_tiled(const void* gu, int gu_stride, void* packed, void* tiled, int rows, int I, void* stream);
 /* Block-scaled NVFP4 GEMM on tcgen05.mma kind::mxf4nvf4 (replaces the cuBLASLt FP4 GEMM of Engine::nvfp4_gemm,
  * native/src/engine.rs:3962-4131): xq [M,K/2] and wq [N,K/2] e2m1 codes, x_scales [M,K/16] and w_scales [N,K/16]
  * e4m3 bytes (row-major, as dcd_k_nvfp4_quant_rows writes them), C [M,ldc] bf16 = *alpha (device scalar, may be

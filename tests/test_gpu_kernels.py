@@ -590,3 +590,33 @@ def test_nvfp4_act_quant_tiled_matches_row_quantiser(G, oracle, rows, K, stride)
     G.call("dcd_k_nvfp4_quant_act_tiled", G.dev(xf, 1), stride, packed, tiled, rows, K, None)
     assert np.array_equal(packed.cpu().numpy(), wp)
     assert np.array_equal(tiled.cpu().numpy(), want_tiled)
+
+
+@pytest.mark.parametrize("rows,I", [(5, 256), (131, 1024)])
+def test_nvfp4_swiglu_quant_tiled(G, oracle, rows, I):
+    """SwiGLU fused with the NVFP4 quantiser against the two-step oracle (bf16 SwiGLU, then quantise). The kernel uses the
+    fast exponential, so an activation may round to the neighbouring bf16 value now and then: nearly all codes and scales
+    must agree exactly, and the dequantised result must stay within one NVFP4 step of the oracle's activation."""
+    import torch
+    r = rng(rows + I)
+    gu = oracle.rb(r.standard_normal((rows, 2 * I)).astype(np.float32) * 2.0)
+    gu[1] = 0.0
+    g = gu.reshape(rows, I // 128, 2, 128)[:, :, 0].reshape(rows, I)
+    u = gu.reshape(rows, I // 128, 2, 128)[:, :, 1].reshape(rows, I)
+    act = oracle.rb(oracle.rb(g / (1 + np.exp(-g))) * u)
+    wp, ws, wd = oracle.k_nvfp4_rows(act, 1.0)
+    want_tiled = oracle.nvfp4_scale_repack(ws, I)
+    packed = torch.zeros((rows, I // 2), dtype=torch.uint8, device="cuda")
+    tiled = torch.zeros((want_tiled.size,), dtype=torch.uint8, device="cuda")
+    G.call("dcd_k_nvfp4_swiglu_quant_tiled", G.dev(gu, 1), 2 * I, packed, tiled, rows, I, None)
+    gp, gt = packed.cpu().numpy(), tiled.cpu().numpy()
+    assert (gp == wp).mean() > 0.995 and (gt == want_tiled).mean() > 0.995
+    # dequantise what the kernel wrote (scales back to row-major through the inverse of the tiling)
+    lin = np.zeros_like(ws)
+    for o in range(rows):
+        for j in range(I // 16):
+            lin[o, j] = gt[((j // 4) + (o // 128) * (I // 64)) * 512 + (o % 32) * 16 + ((o % 128) // 32) * 4 + (j % 4)]
+    out = torch.zeros((rows, I), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_nvfp4_dequant_rows", torch.from_numpy(gp).cuda(), torch.from_numpy(lin).cuda(), out, rows, I, None)
+    step = np.repeat(np.abs(act).reshape(rows, I // 16, 16).max(-1), 16, axis=1) / 6.0 + 1e-9
+    assert (np.abs(G.host(out) - act) <= 1.07 * step).all()   # half the 4..6 spacing times a scale rounded up by at most 1/16
