@@ -270,7 +270,10 @@ struct Scope {
 // native/src/engine.rs:4144-4296); plain FMA otherwise.
 template <typename T>
 int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
-         const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi, bool x_quantised = false) {
+         const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi, bool x_quantised = false,
+         const void* resid = nullptr) {  // resid: C = bf16(resid + bf16(X W^T)), tensor-core bf16 / fp8 paths only
+  if (resid && (e->nv4 || !(e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K))))
+    return fail(e, DCD_E_INVALID, "internal: fused residual on a GEMM path without that epilogue");
   if (e->nv4_native && epi == 0 && n4->sft && nvfp4_tc_shape_ok(M, N, K)) {
     // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131) on the block-scaled FP4 MMA: activations are
     // quantised per 16 elements (tensor scale 1), both scale sets are read in the 128 x 4 tiled layout, alpha =
@@ -318,12 +321,12 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     TcTensorMap ta;
     if (tc_make_tmap_fp8_a(&ta, e->aq, M, K)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an fp8 activation operand");
     Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
-    CK(e, tc_gemm_fp8_launch(&ta, &fw->tm, C, M, N, K, ldc, epi, e->a_scale, fw->scale, e->sm_count, e->d_err, e->stream), "tcgen05 fp8 gemm");
+    CK(e, tc_gemm_fp8_launch(&ta, &fw->tm, C, M, N, K, ldc, epi, e->a_scale, fw->scale, e->sm_count, e->d_err, e->stream, resid), "tcgen05 fp8 gemm");
     return DCD_OK;
   }
   Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
   if (e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K)) {
-    CK(e, tc_gemm_launch(tmA, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream), "tcgen05 gemm");
+    CK(e, tc_gemm_launch(tmA, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream, nullptr, resid), "tcgen05 gemm");
     return DCD_OK;
   }
   if (epi != 0) return fail(e, DCD_E_INVALID, "internal: fused epilogue without tensor-core path");
@@ -351,6 +354,9 @@ int run_layers(dcd_engine* e, const Pass& p) {
   const bool act_fused_quant = e->nv4_native && sizeof(T) == 2 && (e->I % 256) == 0 && nvfp4_tc_shape_ok(T_, H, e->I);
   // ... and the norms that feed the q/k/v, GDN input and gate/up projections write NVFP4 instead of bf16 h
   const bool h_fused_quant = e->nv4_native && sizeof(T) == 2 && (H % 256) == 0 && H <= 8192;
+  // bf16 / fp8 / w4a16 tensor-core GEMMs add the residual in their epilogue: the projection that closes a block writes the new
+  // residual stream itself and the norm that follows reads one tensor instead of two
+  const bool fused_resid = tc && !e->nv4 && tc_shape_ok(T_, H, H);
   // FP8 only in question passes with enough rows; capture and the per-row reference stay bf16
   // (native/src/engine.rs:4321-4326, fp8_min_rows :246-257)
   const bool q8 = e->fp8 && tc && p.mode == 1 && p.T >= e->o.fp8_min_rows;
@@ -408,7 +414,8 @@ int run_layers(dcd_engine* e, const Pass& p) {
                                    e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
         }
       }
-      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, e->mix, T_, H, heads * hd, H, 0);
+      rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, fused_resid ? e->x1 : e->mix, T_, H, heads * hd, H, 0, false,
+                   fused_resid ? e->x : nullptr);
       if (rc) return rc;
     } else {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, &w.n_gin, e->big, T_, e->gin_n, H, e->gin_n, 0, h_fused_quant);
@@ -457,12 +464,15 @@ int run_layers(dcd_engine* e, const Pass& p) {
         CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
                                       c.rms_eps, s), "rmsnorm_gated");
       }
-      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, e->mix, T_, H, e->vd, H, 0);
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, fused_resid ? e->x1 : e->mix, T_, H, e->vd, H, 0, false,
+                   fused_resid ? e->x : nullptr);
       if (rc) return rc;
     }
     {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      if (h_fused_quant)
+      if (fused_resid)
+        CK(e, launch_rmsnorm<T>((const T*)e->x1, (const T*)w.post_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
+      else if (h_fused_quant)
         CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x, (const bf16*)e->mix, (const bf16*)w.post_norm, (bf16*)e->x1, e->xq, e->xsft, T_, H, c.rms_eps, s),
            "add_rmsnorm + nvfp4");
       else
@@ -479,17 +489,20 @@ int run_layers(dcd_engine* e, const Pass& p) {
       if (act_fused_quant) CK(e, launch_nvfp4_swiglu_quant_tiled((const bf16*)e->big, e->gu_rows, e->xq, e->xsft, T_, e->I, s), "silu_mul + nvfp4 quantisation");
       else CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
-    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, e->mix, T_, H, e->I, H, 0, act_fused_quant);
+    int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, fused_resid ? e->x : e->mix, T_, H, e->I, H, 0, act_fused_quant,
+                     fused_resid ? e->x1 : nullptr);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      if (h_fused_quant)
+      if (fused_resid)
+        CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)e->layers[li + 1].input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
+      else if (h_fused_quant)
         CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x1, (const bf16*)e->mix, (const bf16*)e->layers[li + 1].input_norm, (bf16*)e->x, e->xq, e->xsft,
                                        T_, H, c.rms_eps, s), "add_rmsnorm + nvfp4");
       else
         CK(e, launch_add_rmsnorm<T>((const T*)e->x1, (const T*)e->mix, (const T*)e->layers[li + 1].input_norm, (T*)e->x, (T*)e->h, T_, H,
                                     c.rms_eps, s), "add_rmsnorm");
-    } else {
+    } else if (!fused_resid) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 3.0 * xbytes, 1);
       CK(e, launch_add<T>((const T*)e->x1, (const T*)e->mix, (T*)e->x, (size_t)T_ * H, s), "add");
     }

@@ -94,11 +94,13 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // (scale_fp8_gemm_bf16, native/kernels/kernels.cu:208-220); ESZ 2 ignores the scale pointers.
 // alpha (device scalar, may be null): the accumulator is multiplied by *alpha before rounding
 // (cuBLASLt alpha = 1/(weight_global*input_global) of the NVFP4 path, native/src/engine.rs:4108).
+// resid (EPI 0, may be null; [M, ldc] like C): C = bf16(resid + bf16(product)), the residual add of add_bf16 /
+// add_rmsnorm_bf16 (native/kernels/kernels.cu:406-426, 485-490) applied to the rounded GEMM output.
 template <int EPI, int ESZ>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
                     int M, int N, int K, int ldc, const float* __restrict__ a_scale, const float* __restrict__ w_scale,
-                    const float* __restrict__ alpha, int* __restrict__ err) {
+                    const float* __restrict__ alpha, int* __restrict__ err, const bf16* __restrict__ resid) {
   constexpr int BKE = 128 / ESZ;  // K elements per 128-byte swizzled row
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -222,6 +224,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   const float4 w1 = __ldg(reinterpret_cast<const float4*>(w_scale + col + 4));
                   f[0] = f[0] * w0.x * rs; f[1] = f[1] * w0.y * rs; f[2] = f[2] * w0.z * rs; f[3] = f[3] * w0.w * rs;
                   f[4] = f[4] * w1.x * rs; f[5] = f[5] * w1.y * rs; f[6] = f[6] * w1.z * rs; f[7] = f[7] * w1.w * rs;
+                }
+                if (resid) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(resid + (size_t)row * ldc + col);
+                  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] = Ty<bf16>::rnd(f[2 * j]) + __uint_as_float(rw[j] << 16);
+                    f[2 * j + 1] = Ty<bf16>::rnd(f[2 * j + 1]) + __uint_as_float(rw[j] & 0xffff0000u);
+                  }
                 }
                 uint4 o;
                 o.x = pack_bf16(f[0], f[1]);
@@ -387,26 +398,28 @@ cudaError_t tc_gemm_prepare_device() {
 }
 
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                           int sm_count, int* err, cudaStream_t stream, const float* alpha) {
+                           int sm_count, int* err, cudaStream_t stream, const float* alpha, const void* resid) {
+  if (resid && epi != 0) return cudaErrorInvalidValue;
   const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err);
-  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, (const bf16*)resid);
+  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, nullptr);
   return cudaGetLastError();
 }
 
 // e4m3 operands (1 byte per element; maps made with tc_make_tmap_fp8_*), bf16 output scaled by
 // w_scale[n] * a_scale[m].
 cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream) {
+                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream, const void* resid) {
+  if (resid && epi != 0) return cudaErrorInvalidValue;
   const int num_tiles = ((M + tcg::BM - 1) / tcg::BM) * ((N + tcg::BN - 1) / tcg::BN);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err);
-  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, (const bf16*)resid);
+  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, nullptr);
   return cudaGetLastError();
 }
 

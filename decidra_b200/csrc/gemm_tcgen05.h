@@ -22,8 +22,9 @@ bool tc_shape_ok(int M, int N, int K);
 cudaError_t tc_gemm_prepare_device();
 // epi 0: C[M,N] (row stride ldc). epi 1: SwiGLU over gate/up-interleaved weights, C[M,N/2].
 // alpha: optional device scalar multiplied into the accumulator before rounding.
+// resid (epi 0 only): optional bf16 [M, ldc]; C = bf16(resid + bf16(product)).
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                           int sm_count, int* err, cudaStream_t stream, const float* alpha = nullptr);
+                           int sm_count, int* err, cudaStream_t stream, const float* alpha = nullptr, const void* resid = nullptr);
 
 // e4m3 (FP8) operand form: X[M,K] and W[N,K] hold one byte per element; the f32 accumulator is
 // scaled by w_scale[n] * a_scale[m] before rounding to bf16. Needs K % 16 == 0, N % 8 == 0.
@@ -31,7 +32,7 @@ int tc_make_tmap_fp8_a(TcTensorMap* out, const void* X, uint64_t M, uint64_t K);
 int tc_make_tmap_fp8_b(TcTensorMap* out, const void* W, uint64_t N, uint64_t K);
 bool tc_fp8_shape_ok(int M, int N, int K);
 cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
-                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream);
+                               const float* a_scale, const float* w_scale, int sm_count, int* err, cudaStream_t stream, const void* resid = nullptr);
 
 // NVFP4 block-scaled GEMM (gemm_nvfp4.cu): e2m1 codes [rows, K/2] bytes (byte maps from tc_make_tmap_fp8_a, 128-row
 // boxes, for both operands), unsigned e4m3 scales per 16 elements in the 128 x 4 tiled layout padded to an even number of 128-row
