@@ -16,12 +16,12 @@
 // Everything that depends on the state is kept transposed so that TMEM lane = value column; thread
 // `ln` of each warpgroup owns lane ln, and the two warpgroups split every per-lane loop in halves
 // (with one warp per scheduler the chunk body ran at a third of an instruction per cycle, all of it
-// exposed latency). The forward substitution is sequential per column and runs on warpgroup 0.
+// exposed latency). The forward substitution is sequential per column and runs on warpgroup 0; warpgroup 1
+// meanwhile turns the query-token rows of D1 into P and writes the transposed, decay-scaled K operand.
 //   D1 [row, s]   = [K;Q] K^T            (rows 0-63 key tokens, 64-127 query tokens)
 //   D2 [vc, t]    = S^T [K;Q]^T          (columns 0-63 (K S)^T, 64-127 (Q S)^T)
 //   O2 [vc, t]    = D^T P^T
-//   RD [vc, dk]   = D^T (exp(G_C-G) K)     (B operand: a transposed, decay-scaled copy of the K tile that
-//                                          the threads write while the first two products run)
+//   RD [vc, dk]   = D^T (exp(G_C-G) K)     (B operand: a transposed, decay-scaled copy of the K tile)
 //   VR [vc, t]    = per-thread scratch: the right-hand side, then D
 // so thread vc reads (K S)[., vc] for all 64 tokens from its own TMEM lane and runs the forward
 // substitution for its column. S^T lives in shared memory as full f32 (it is both the master copy
@@ -230,22 +230,6 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       umma_commit_to(bar_mma);
     }
-    // ---- meanwhile: row dk = ln of (exp(G_C-G) K)^T, the K-major B operand of the state update (32 tokens per
-    // warpgroup) ------------------------------------------------------------------------------------------------
-    if (ok) {
-      const uint8_t* kcol = smem + KQ_OFF + (ln >> 5) * REG + (ln & 3) * 4;
-      const int c16 = (ln & 31) >> 2;
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const int c = wg * 8 + cc;
-        const float4 e4 = *reinterpret_cast<const float4*>(sE + 4 * c);
-        const float k0 = e4.x * *reinterpret_cast<const float*>(kcol + (4 * c + 0) * 128 + ((c16 ^ ((4 * c + 0) & 7)) << 4));
-        const float k1 = e4.y * *reinterpret_cast<const float*>(kcol + (4 * c + 1) * 128 + ((c16 ^ ((4 * c + 1) & 7)) << 4));
-        const float k2 = e4.z * *reinterpret_cast<const float*>(kcol + (4 * c + 2) * 128 + ((c16 ^ ((4 * c + 2) & 7)) << 4));
-        const float k3 = e4.w * *reinterpret_cast<const float*>(kcol + (4 * c + 3) * 128 + ((c16 ^ ((4 * c + 3) & 7)) << 4));
-        *reinterpret_cast<float4*>(smem + KT_OFF + (uint32_t)(c >> 3) * REG + sw_off(ln, c & 7)) = tf32x4(k0, k1, k2, k3);
-      }
-    }
     ok = ok && mbar_wait(bar_mma, mma_phase, abort_flag);
     mma_phase ^= 1u;
     if (!__syncthreads_and(ok)) { ok = false; break; }
@@ -281,9 +265,8 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     tmem_st_wait();
     tc_fence_before();  // the other warpgroup's half of the right-hand side is read by the solve below
-    if (V_TMA) __syncthreads();  // the V tile has been read by everyone: P may overwrite it
 
-    // ---- D1 rows: key-token rows give A^T, query-token rows give P -------------------------------------
+    // ---- D1 rows of the key tokens give A^T (the query-token rows, P, are taken by warpgroup 1 during the solve) ---------
     // (exponents are clamped to <= 0 and the result selected, so the loops stay branch-free)
     if (ln < 64) {
       const int t = ln;
@@ -305,32 +288,58 @@ gdn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
       }
-    } else {
-      const int t = ln - 64;
-      const float Gt = sG[t];
-#pragma unroll 1
-      for (int j = wg * 2; j < wg * 2 + 2; ++j) {
-        uint32_t v[BLK];
-        tmem_ld16(tlane + D1_COL + j * BLK, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float4 gs = *reinterpret_cast<const float4*>(sG + j * BLK + q * 4);
-          const float ge[4] = {gs.x, gs.y, gs.z, gs.w};
-          float pr[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int s = j * BLK + q * 4 + i;
-            const float e = __expf(fminf(Gt - ge[i], 0.f)) * u2f(v[q * 4 + i]);
-            pr[i] = s <= t ? e : 0.f;
-          }
-          *reinterpret_cast<float4*>(smem + P_OFF + (uint32_t)(j >> 1) * 8192 + sw_off(t, (j & 1) * 4 + q)) = tf32x4(pr[0], pr[1], pr[2], pr[3]);
-        }
-      }
     }
     __syncthreads();  // A^T complete; the right-hand sides of both warpgroups are in the scratch
 
     // ---- forward substitution, blocked 16x16, left-looking; block j ends up holding D[16j .. 16j+15] ----------
+    if (wg == 1) {
+      // ---- warpgroup 1, while warpgroup 0 runs the forward substitution: P from the query-token rows of D1 (over the V tile,
+      // which every thread has read by now), then row dk = ln of (exp(G_C-G) K)^T, the K-major B operand of the state update
+      if (ln >= 64) {
+        const int t = ln - 64;
+        const float Gt = sG[t];
+#pragma unroll 1
+        for (int j = 0; j < C / BLK; ++j) {
+          uint32_t v[BLK];
+          tmem_ld16(tlane + D1_COL + j * BLK, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 gs = *reinterpret_cast<const float4*>(sG + j * BLK + q * 4);
+            const float ge[4] = {gs.x, gs.y, gs.z, gs.w};
+            float pr[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int s = j * BLK + q * 4 + i;
+              const float e = __expf(fminf(Gt - ge[i], 0.f)) * u2f(v[q * 4 + i]);
+              pr[i] = s <= t ? e : 0.f;
+            }
+            *reinterpret_cast<float4*>(smem + P_OFF + (uint32_t)(j >> 1) * 8192 + sw_off(t, (j & 1) * 4 + q)) = tf32x4(pr[0], pr[1], pr[2], pr[3]);
+          }
+        }
+      }
+      // K^T rows: warps 4 and 5 (no P rows to do) take their own row in full and the first 32 tokens of row ln + 64; warps 6 and 7
+      // take the last 32 tokens of their own row
+      auto kt_row = [&](int r, int c_lo, int c_hi) {
+        const uint8_t* kcol = smem + KQ_OFF + (r >> 5) * REG + (r & 3) * 4;
+        const int c16 = (r & 31) >> 2;
+#pragma unroll 4
+        for (int c = c_lo; c < c_hi; ++c) {
+          const float4 e4 = *reinterpret_cast<const float4*>(sE + 4 * c);
+          const float k0 = e4.x * *reinterpret_cast<const float*>(kcol + (4 * c + 0) * 128 + ((c16 ^ ((4 * c + 0) & 7)) << 4));
+          const float k1 = e4.y * *reinterpret_cast<const float*>(kcol + (4 * c + 1) * 128 + ((c16 ^ ((4 * c + 1) & 7)) << 4));
+          const float k2 = e4.z * *reinterpret_cast<const float*>(kcol + (4 * c + 2) * 128 + ((c16 ^ ((4 * c + 2) & 7)) << 4));
+          const float k3 = e4.w * *reinterpret_cast<const float*>(kcol + (4 * c + 3) * 128 + ((c16 ^ ((4 * c + 3) & 7)) << 4));
+          *reinterpret_cast<float4*>(smem + KT_OFF + (uint32_t)(c >> 3) * REG + sw_off(r, c & 7)) = tf32x4(k0, k1, k2, k3);
+        }
+      };
+      if (ln < 64) {
+        kt_row(ln, 0, 16);
+        kt_row(ln + 64, 0, 8);
+      } else {
+        kt_row(ln, 8, 16);
+      }
+    }
     if (wg == 0) {
     tc_fence_after();
 #pragma unroll 1
