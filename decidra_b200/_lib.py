@@ -69,6 +69,7 @@ SIGNATURES = {
     "dcd_decode_answer": (I, [FP, I, F, I, FP, FP]),
     "dcd_pack": (I, [P, I32P, SZ, C.c_int32, I32P, I32P, I32P, I32P]),
     "dcd_k_gemm_bf16_tc": (I, [P, P, P, I, I, I, I, I, I, P, P]),
+    "dcd_k_gemm_bf16_tc_resid": (I, [P, P, P, P, I, I, I, I, I, P, P]),
     "dcd_k_gemm_fp8_tc": (I, [P, P, P, I, I, I, I, I, P, P, I, P, P]),
     "dcd_k_quant_fp8_rows": (I, [P, SZ, P, P, I, I, F, I, P]),
     "dcd_k_quant_w4_g128": (I, [P, P, P, I, I, P]),

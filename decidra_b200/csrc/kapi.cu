@@ -23,6 +23,15 @@ int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int 
   return rc_of(tc_gemm_launch(&ta, &tb, C, M, N, K, ldc, epi, sm_count, err, S(stream)));
 }
 
+int dcd_k_gemm_bf16_tc_resid(const void* X, const void* W, const void* resid, void* C, int M, int N, int K, int ldc, int sm_count, int* err,
+                             void* stream) {
+  if (!tc_shape_ok(M, N, K) || sm_count <= 0 || !resid) return DCD_E_INVALID;
+  TcTensorMap ta, tb;
+  if (tc_make_tmap_a(&ta, X, M, K) || tc_make_tmap_b(&tb, W, N, K)) return DCD_E_CUDA;
+  if (tc_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  return rc_of(tc_gemm_launch(&ta, &tb, C, M, N, K, ldc, 0, sm_count, err, S(stream), nullptr, resid));
+}
+
 int dcd_k_gemm_fp8_tc(const void* Xq, const void* Wq, void* C, int M, int N, int K, int ldc, int epi, const float* a_scale,
                       const float* w_scale, int sm_count, int* err, void* stream) {
   if (!tc_fp8_shape_ok(M, N, K) || sm_count <= 0 || (epi != 0 && epi != 1) || !a_scale || !w_scale) return DCD_E_INVALID;

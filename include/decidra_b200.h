@@ -248,6 +248,10 @@ DCD_API int dcd_pack(dcd_engine* e, const int32_t* lens, size_t B, int32_t pos_s
  * `err` is a device int the kernel sets non-zero when a bounded barrier wait gives up. */
 DCD_API int dcd_k_gemm_bf16_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int epi, int sm_count,
                                int* err, void* stream);
+/* The same with the residual add of a pre-norm block in the epilogue: C = bf16(resid + bf16(X . W^T)), resid bf16 [M, ldc]
+ * (add_bf16 / the add of add_rmsnorm_bf16, native/kernels/kernels.cu:406-426, 485-490, applied to the rounded product). */
+DCD_API int dcd_k_gemm_bf16_tc_resid(const void* X, const void* W, const void* resid, void* C, int M, int N, int K, int ldc,
+                                     int sm_count, int* err, void* stream);
 /* FP8 form: Xq[M,K] and Wq[N,K] are e4m3 bytes (dcd_k_quant_fp8_rows), C = bf16(acc * w_scale[n] * a_scale[m])
  * (cuBLASLt E4M3 GEMM + scale_fp8_gemm_bf16, native/src/engine.rs:4179-4296, native/kernels/kernels.cu:208-220).
  * Needs K % 16 == 0 and N % 8 == 0. epi as above (w_scale then indexes the interleaved rows). */

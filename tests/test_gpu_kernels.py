@@ -27,6 +27,24 @@ GEMM_SHAPES = [(128, 256, 64), (128, 256, 128), (256, 512, 256), (128, 256, 1024
                (2048, 5120, 1024), (640, 17408, 512), (2048, 16480, 256)]
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 776, 256), (2048, 5120, 1024)])
+def test_gemm_tc_residual_epilogue_bit_exact(G, oracle, M, N, K):
+    """C = bf16(resid + bf16(X W^T)) must equal the two-step form (GEMM, then the bf16 add) bit for bit."""
+    import torch
+    r = rng(M + N + K)
+    dX = G.dev(oracle.rb(r.standard_normal((M, K), dtype=np.float32)), 1)
+    dW = G.dev(oracle.rb(r.standard_normal((N, K), dtype=np.float32) * 0.05), 1)
+    dR = G.dev(oracle.rb(r.standard_normal((M, N), dtype=np.float32)), 1)
+    plain = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    fused = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    G.call("dcd_k_gemm_bf16_tc", dX, dW, plain, M, N, K, N, 0, G.sm_count(), err, None)
+    G.call("dcd_k_gemm_bf16_tc_resid", dX, dW, dR, fused, M, N, K, N, G.sm_count(), err, None)
+    assert int(err.item()) == 0
+    want = (dR.float() + plain.float()).to(torch.bfloat16)
+    assert torch.equal(fused, want)
+
+
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
 def test_gemm_tc_vs_fp32_matmul(G, oracle, M, N, K):
     import torch
