@@ -347,46 +347,53 @@ __global__ void rmsnorm_gated_kernel(const T* __restrict__ x, const T* __restric
     Ty<T>::st(orow + j, scaled * Ty<T>::rnd(silu_f(g)));
   }
 }
-// bf16, cols == 128: each lane owns 4 consecutive elements (8-byte loads); same arithmetic.
+// bf16, cols == 128: 8 lanes per row, 16 consecutive elements per lane (16-byte loads and stores); same arithmetic.
 __global__ void __launch_bounds__(256) rmsnorm_gated_vec128_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int z_stride,
                                                                     const bf16* __restrict__ w, bf16* __restrict__ out, int rows, int heads,
                                                                     float eps) {
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const int t = row / heads, h = row - t * heads;
-  const uint2 xv = reinterpret_cast<const uint2*>(x + (size_t)row * 128)[lane];
-  const uint2 zv = reinterpret_cast<const uint2*>(z + (size_t)t * z_stride + (size_t)h * 128)[lane];
-  const uint2 wv = reinterpret_cast<const uint2*>(w)[lane];
-  const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
-  const __nv_bfloat162* zh = reinterpret_cast<const __nv_bfloat162*>(&zv);
-  const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
-  float xf[4] = {__low2float(xh[0]), __high2float(xh[0]), __low2float(xh[1]), __high2float(xh[1])};
-  const float zf[4] = {__low2float(zh[0]), __high2float(zh[0]), __low2float(zh[1]), __high2float(zh[1])};
-  const float wf[4] = {__low2float(wh[0]), __high2float(wh[0]), __low2float(wh[1]), __high2float(wh[1])};
-  float ss = xf[0] * xf[0] + xf[1] * xf[1] + xf[2] * xf[2] + xf[3] * xf[3];
-  ss = warp_sum(ss);
-  const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
-  float y[4];
+  // 8 lanes per row, 16 consecutive elements (two 16-byte vectors) per lane: three shuffle steps per row instead of five
+  const int row = blockIdx.x * 32 + (threadIdx.x >> 3);
+  const int sub = threadIdx.x & 7;
+  const bool live = row < rows;
+  const int r = live ? row : rows - 1;  // every lane stays in the shuffles; rows past the end recompute the last row and store nothing
+  const int t = r / heads, h = r - t * heads;
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)r * 128) + sub * 2;
+  const uint4* zp = reinterpret_cast<const uint4*>(z + (size_t)t * z_stride + (size_t)h * 128) + sub * 2;
+  const uint4* wp = reinterpret_cast<const uint4*>(w) + sub * 2;
+  float xf[16], zf[16], wf[16];
+  unpack8(xp[0], *reinterpret_cast<float(*)[8]>(&xf[0]));
+  unpack8(xp[1], *reinterpret_cast<float(*)[8]>(&xf[8]));
+  unpack8(zp[0], *reinterpret_cast<float(*)[8]>(&zf[0]));
+  unpack8(zp[1], *reinterpret_cast<float(*)[8]>(&zf[8]));
+  unpack8(wp[0], *reinterpret_cast<float(*)[8]>(&wf[0]));
+  unpack8(wp[1], *reinterpret_cast<float(*)[8]>(&wf[8]));
+  float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < 16; ++j) ss += xf[j] * xf[j];
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+  float y[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
     const float normed = Ty<bf16>::rnd(xf[j] * scale);
     const float scaled = Ty<bf16>::rnd(normed * wf[j]);
     y[j] = scaled * Ty<bf16>::rnd(silu_fast(zf[j]));
   }
-  uint2 ov;
-  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
-  oh[0] = __floats2bfloat162_rn(y[0], y[1]);
-  oh[1] = __floats2bfloat162_rn(y[2], y[3]);
-  reinterpret_cast<uint2*>(out + (size_t)row * 128)[lane] = ov;
+  if (live) {
+    uint4* op = reinterpret_cast<uint4*>(out + (size_t)row * 128) + sub * 2;
+    op[0] = pack8(*reinterpret_cast<float(*)[8]>(&y[0]));
+    op[1] = pack8(*reinterpret_cast<float(*)[8]>(&y[8]));
+  }
 }
 
 template <typename T>
 cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* w, T* out, int tokens, int heads, int cols, float eps, cudaStream_t s) {
   const int rows = tokens * heads;
   if constexpr (sizeof(T) == 2) {
-    if (cols == 128 && (z_stride % 4) == 0 && (reinterpret_cast<uintptr_t>(z) % 8) == 0) {
-      rmsnorm_gated_vec128_kernel<<<(rows + 7) / 8, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, eps);
+    if (cols == 128 && rows > 0 && (z_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(z) % 16) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
+        (reinterpret_cast<uintptr_t>(w) % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
+      rmsnorm_gated_vec128_kernel<<<(rows + 31) / 32, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, eps);
       return cudaGetLastError();
     }
   }
@@ -516,12 +523,84 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qg, int qg_stride, con
   }
 }
 
+// bf16, head_dim 256: lane l owns dims 8l..8l+7 (one 16-byte load and store per lane); the rotation partner (dim +- rhalf) sits
+// rhalf/8 lanes away and comes by shuffle. Same arithmetic and rounding points as the generic kernel.
+__global__ void __launch_bounds__(256) qk_norm_rope_vec256_kernel(const bf16* __restrict__ qg, int qg_stride, const bf16* __restrict__ kraw,
+                                                                  int k_stride, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                                                                  const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t,
+                                                                  const int32_t* __restrict__ positions, int pos_base, int max_pos,
+                                                                  bf16* __restrict__ q, bf16* __restrict__ k, int k_out_stride, int tokens,
+                                                                  int heads, int kv, int rhalf, float eps, int* __restrict__ err) {
+  constexpr int HD = 256;
+  const int wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * 8 + wi;
+  const int slots = heads + kv;
+  if (idx >= tokens * slots) return;
+  const int t = idx / slots, hs = idx - t * slots;
+  const bf16* src;
+  const bf16* w;
+  bf16* dst;
+  if (hs < heads) {
+    src = qg + (size_t)t * qg_stride + (size_t)hs * 2 * HD;
+    w = qw;
+    dst = q + ((size_t)t * heads + hs) * HD;
+  } else {
+    src = kraw + (size_t)t * k_stride + (size_t)(hs - heads) * HD;
+    w = kw;
+    dst = k + (size_t)t * k_out_stride + (size_t)(hs - heads) * HD;
+  }
+  float v[8], wv[8];
+  unpack8(reinterpret_cast<const uint4*>(src)[lane], v);
+  unpack8(reinterpret_cast<const uint4*>(w)[lane], wv);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = Ty<bf16>::rnd(v[i] * scale * (wv[i] + 1.0f));
+  int pos = positions ? positions[t] : pos_base + t;
+  if (pos < 0 || pos >= max_pos) {
+    if (lane == 0) set_err(err, DERR_POSITION_RANGE);
+    pos = 0;
+  }
+  const int rl = rhalf >> 3;  // lanes per rotary half
+  const bool lo = lane < rl, rot = lane < 2 * rl;
+  const int partner = rot ? (lo ? lane + rl : lane - rl) : lane;
+  float o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = __shfl_sync(0xffffffffu, v[i], partner);
+  if (rot) {
+    float c[8], sn[8];
+    const int f0 = (lo ? lane : lane - rl) * 8;
+    unpack8(*reinterpret_cast<const uint4*>(cos_t + (size_t)pos * rhalf + f0), c);
+    unpack8(*reinterpret_cast<const uint4*>(sin_t + (size_t)pos * rhalf + f0), sn);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // first half: a = own, b = partner: a c - b s; second half: a = partner, b = own: b c + a s
+      if (lo) v[i] = Ty<bf16>::rnd(__fsub_rn(Ty<bf16>::rnd(__fmul_rn(v[i], c[i])), Ty<bf16>::rnd(__fmul_rn(o[i], sn[i]))));
+      else v[i] = Ty<bf16>::rnd(__fadd_rn(Ty<bf16>::rnd(__fmul_rn(v[i], c[i])), Ty<bf16>::rnd(__fmul_rn(o[i], sn[i]))));
+    }
+  }
+  reinterpret_cast<uint4*>(dst)[lane] = pack8(v);
+}
+
 template <typename T>
 cudaError_t launch_qk_norm_rope(const T* qg, int qg_stride, const T* kraw, int k_stride, const T* qw, const T* kw, const T* cos_t,
                                 const T* sin_t, const int32_t* positions, int pos_base, int max_pos, T* q, T* k, int k_out_stride,
                                 int tokens, int heads, int kv, int hd, int rotary_dim, float eps, int* err, cudaStream_t s) {
   const int n = tokens * (heads + kv);
   const int grid = (n + 7) / 8;
+  if constexpr (sizeof(T) == 2) {
+    const int rh = rotary_dim / 2;
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) % 16) == 0; };
+    if (hd == 256 && (rh % 8) == 0 && rh <= 128 && (qg_stride % 8) == 0 && (k_stride % 8) == 0 && (k_out_stride % 8) == 0 && al16(qg) && al16(kraw) &&
+        al16(qw) && al16(kw) && al16(cos_t) && al16(sin_t) && al16(q) && al16(k)) {
+      qk_norm_rope_vec256_kernel<<<grid, 256, 0, s>>>(qg, qg_stride, kraw, k_stride, qw, kw, cos_t, sin_t, positions, pos_base, max_pos, q, k,
+                                                      k_out_stride, tokens, heads, kv, rh, eps, err);
+      return cudaGetLastError();
+    }
+  }
 #define QK_CASE(HD_)                                                                                                     \
   case HD_:                                                                                                              \
     qk_norm_rope_kernel<T, HD_><<<grid, 256, 0, s>>>(qg, qg_stride, kraw, k_stride, qw, kw, cos_t, sin_t, positions,     \
@@ -819,6 +898,51 @@ __global__ void gdn_prepare_kernel(const T* __restrict__ conv, int conv_stride, 
     beta[(size_t)t * nv + vh] = Ty<T>::rnd(sigmoid_f(Ty<T>::ld(b + (size_t)t * ba_stride + vh)));
   }
 }
+// dk == 128, bf16: 16 lanes per (token, key head), 8 consecutive elements per lane (16-byte loads), four shuffle steps per
+// reduction, float4 stores. Same arithmetic as the generic kernel.
+__global__ void __launch_bounds__(256) gdn_prepare_vec128_kernel(const bf16* __restrict__ conv, int conv_stride, const bf16* __restrict__ b,
+                                                                 const bf16* __restrict__ a, int ba_stride, const float* __restrict__ A_log,
+                                                                 const float* __restrict__ dt_bias, float* __restrict__ qf,
+                                                                 float* __restrict__ kf, float* __restrict__ g, float* __restrict__ beta,
+                                                                 int tokens, int nk, int nv) {
+  const int pair = blockIdx.x * 16 + (threadIdx.x >> 4);
+  const int sub = threadIdx.x & 15;
+  const bool live = pair < tokens * nk;
+  const int idx = live ? pair : tokens * nk - 1;  // every lane stays in the shuffles; the tail recomputes the last pair and stores nothing
+  const int t = idx / nk, kh = idx - t * nk;
+  const bf16* row = conv + (size_t)t * conv_stride;
+  float q[8], k[8];
+  unpack8(*reinterpret_cast<const uint4*>(row + kh * 128 + sub * 8), q);
+  unpack8(*reinterpret_cast<const uint4*>(row + nk * 128 + kh * 128 + sub * 8), k);
+  float qn = 0.f, kn = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    qn += q[j] * q[j];
+    kn += k[j] * k[j];
+  }
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) {
+    qn += __shfl_xor_sync(0xffffffffu, qn, o);
+    kn += __shfl_xor_sync(0xffffffffu, kn, o);
+  }
+  if (!live) return;
+  const float qscale = (1.0f / sqrtf(qn + 1e-6f)) * (1.0f / sqrtf(128.0f));
+  const float kscale = 1.0f / sqrtf(kn + 1e-6f);
+  float4* qd = reinterpret_cast<float4*>(qf + ((size_t)t * nk + kh) * 128 + sub * 8);
+  float4* kd = reinterpret_cast<float4*>(kf + ((size_t)t * nk + kh) * 128 + sub * 8);
+  qd[0] = make_float4(q[0] * qscale, q[1] * qscale, q[2] * qscale, q[3] * qscale);
+  qd[1] = make_float4(q[4] * qscale, q[5] * qscale, q[6] * qscale, q[7] * qscale);
+  kd[0] = make_float4(k[0] * kscale, k[1] * kscale, k[2] * kscale, k[3] * kscale);
+  kd[1] = make_float4(k[4] * kscale, k[5] * kscale, k[6] * kscale, k[7] * kscale);
+  const int rep = nv / nk;
+  if (sub < rep) {
+    const int vh = kh * rep + sub;
+    const float av = __bfloat162float(a[(size_t)t * ba_stride + vh]) + dt_bias[vh];
+    const float sp = av > 20.f ? av : log1pf(expf(av));
+    g[(size_t)t * nv + vh] = -expf(A_log[vh]) * sp;
+    beta[(size_t)t * nv + vh] = Ty<bf16>::rnd(sigmoid_f(__bfloat162float(b[(size_t)t * ba_stride + vh])));
+  }
+}
 // dk == 128: one warp per (token, key head), 4 elements per lane, shuffle reductions, float4 stores.
 template <typename T>
 __global__ void __launch_bounds__(256) gdn_prepare_warp128_kernel(const T* __restrict__ conv, int conv_stride, const T* __restrict__ b,
@@ -858,6 +982,12 @@ cudaError_t launch_gdn_prepare(const T* conv, int conv_stride, const T* b, const
                                const float* dt_bias, float* qf, float* kf, float* g, float* beta, int tokens, int nk, int nv,
                                int dk, cudaStream_t s) {
   if (dk % 32 != 0 || dk > 1024 || nv / nk > dk) return cudaErrorInvalidValue;
+  if constexpr (sizeof(T) == 2) {
+    if (dk == 128 && nv / nk <= 16 && tokens > 0 && (conv_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(conv) % 16) == 0) {
+      gdn_prepare_vec128_kernel<<<(tokens * nk + 15) / 16, 256, 0, s>>>(conv, conv_stride, b, a, ba_stride, A_log, dt_bias, qf, kf, g, beta, tokens, nk, nv);
+      return cudaGetLastError();
+    }
+  }
   if (dk == 128 && nv / nk <= 32) {
     gdn_prepare_warp128_kernel<T><<<(tokens * nk + 7) / 8, 256, 0, s>>>(conv, conv_stride, b, a, ba_stride, A_log, dt_bias, qf, kf, g, beta, tokens, nk, nv);
     return cudaGetLastError();
