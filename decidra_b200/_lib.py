@@ -21,6 +21,10 @@ class Info(C.Structure):
     ]
 
 
+class TensorInfo(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_uint64 * 8), ("bytes", C.c_uint64), ("data", C.c_void_p)]
+
+
 class ProfEntry(C.Structure):
     _fields_ = [("ms", C.c_double), ("work", C.c_double), ("launches", C.c_int64)]
 
@@ -36,6 +40,14 @@ SIGNATURES = {
     "dcd_engine_init_random": (I, [P, C.c_uint64]),
     "dcd_engine_load_tensor": (I, [P, I, I, FP, SZ]),
     "dcd_engine_read_tensor": (I, [P, I, I, FP, SZ]),
+    "dcd_engine_load_tensor_typed": (I, [P, I, I, P, I, SZ]),
+    "dcd_checkpoint_open": (I, [C.c_char_p, C.POINTER(P)]),
+    "dcd_checkpoint_close": (None, [P]),
+    "dcd_checkpoint_count": (SZ, [P]),
+    "dcd_checkpoint_name": (C.c_char_p, [P, SZ]),
+    "dcd_checkpoint_tensor": (I, [P, C.c_char_p, C.POINTER(TensorInfo)]),
+    "dcd_config_from_dir": (I, [C.c_char_p, C.POINTER(ModelConfig)]),
+    "dcd_engine_load_checkpoint": (I, [P, P, C.c_char_p]),
     "dcd_rebind_blas": (I, [P]),
     "dcd_capture_state": (I, [P, U32P, SZ, P, C.POINTER(P)]),
     "dcd_readout_state_once_batch": (I, [P, P, C.POINTER(U32P), C.POINTER(SZ), SZ, FP]),

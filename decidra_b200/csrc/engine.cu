@@ -9,6 +9,7 @@
 // qkv|z|b|a), SwiGLU folded into the gate/up GEMM epilogue, no K/V concatenation copies
 // (attention reads the cached state and the question's own rows in place), no host round
 // trip before the readout, packing metadata built on the device.
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -18,6 +19,7 @@
 
 #include "../../include/decidra_b200.h"
 #include "attn_tcgen05.h"
+#include "checkpoint.h"
 #include "common.cuh"
 #include "gemm_tcgen05.h"
 #include "host_logic.h"
@@ -1114,6 +1116,361 @@ int dcd_engine_read_tensor(dcd_engine* e, int layer, int kind, float* host, size
   if (tmpT) cudaFree(tmpT);
   if (ce != cudaSuccess) return cuda_fail(e, ce, "read_tensor");
   return DCD_OK;
+}
+
+}  // extern "C"
+
+// ---- checkpoint loading ----------------------------------------------------------------
+// WeightProvider::layer / linear / final_norm (native/src/weights.rs:283-630) and the readout head
+// (HeadMatrix::load, native/src/engine.rs:747-783), re-hosted: tensors stream from the memory-mapped
+// shards through a ring of pinned buffers, and one kernel per chunk converts the stored format
+// (BF16 / F16 / F32, compressed-tensors int4, compressed-tensors NVFP4) and writes it to its place in
+// the engine's fused matrices. Quantised engines (precision 1 and 3) collect a fused matrix in the bf16
+// stage and quantise it once after its last member.
+namespace {
+
+struct Stager {
+  static constexpr int N = 6;
+  size_t cap = 0;
+  void* h[N] = {};
+  void* d[N] = {};
+  cudaEvent_t idle[N] = {};
+  int cur = 0;
+  cudaStream_t s = nullptr;
+
+  cudaError_t init(size_t cap_, cudaStream_t s_) {
+    cap = cap_;
+    s = s_;
+    for (int i = 0; i < N; ++i) {
+      cudaError_t ce = cudaMallocHost(&h[i], cap);
+      if (ce == cudaSuccess) ce = cudaMalloc(&d[i], cap);
+      if (ce == cudaSuccess) ce = cudaEventCreateWithFlags(&idle[i], cudaEventDisableTiming);
+      if (ce != cudaSuccess) return ce;
+    }
+    return cudaSuccess;
+  }
+  void destroy() {
+    for (int i = 0; i < N; ++i) {
+      if (h[i]) cudaFreeHost(h[i]);
+      if (d[i]) cudaFree(d[i]);
+      if (idle[i]) cudaEventDestroy(idle[i]);
+      h[i] = d[i] = nullptr;
+      idle[i] = nullptr;
+    }
+  }
+  // Copies `bytes` into the next slot (after the kernel that last read the slot has finished) and enqueues
+  // the H2D copy. The caller enqueues the consumer and then calls release(slot).
+  cudaError_t push(const void* src, size_t bytes, void** dev, int* slot) {
+    if (bytes > cap) return cudaErrorInvalidValue;
+    const int b = cur;
+    cur = (cur + 1) % N;
+    cudaError_t ce = cudaEventSynchronize(idle[b]);
+    if (ce != cudaSuccess) return ce;
+    memcpy(h[b], src, bytes);
+    ce = cudaMemcpyAsync(d[b], h[b], bytes, cudaMemcpyHostToDevice, s);
+    *dev = d[b];
+    *slot = b;
+    return ce;
+  }
+  cudaError_t release(int slot) { return cudaEventRecord(idle[slot], s); }
+};
+
+constexpr size_t STAGE_CHUNK = 32u << 20;
+
+int src_dt_of(int ckpt_dtype) {
+  switch (ckpt_dtype) {
+    case ckpt::F32: return 0;
+    case ckpt::F16: return 1;
+    case ckpt::BF16: return 2;
+    default: return -1;
+  }
+}
+
+template <typename F>
+int with_dst_type(dcd_engine* e, const Loc& L, F&& f) {
+  return (L.f32 || !e->bf) ? f((float*)L.base) : f((bf16*)L.base);
+}
+
+// A plain tensor of `count` values in F32 / F16 / BF16 storage -> L.
+int place_plain(dcd_engine* e, Stager& st, const char* name, const uint8_t* data, int ckpt_dtype, size_t count, const Loc& L) {
+  const int sdt = src_dt_of(ckpt_dtype);
+  if (sdt < 0) return fail(e, DCD_E_INVALID, "%s: expected F32, F16 or BF16 storage", name);
+  if (count != L.rows * L.cols) return fail(e, DCD_E_INVALID, "%s: holds %zu values, the engine expects %zu x %zu", name, count, L.rows, L.cols);
+  const size_t esz = ckpt::dtype_size(ckpt_dtype), row_bytes = L.cols * esz;
+  const size_t chunk_rows = std::max<size_t>(1, st.cap / row_bytes);
+  if (row_bytes > st.cap) return fail(e, DCD_E_INVALID, "%s: one row exceeds the staging buffer", name);
+  for (size_t r0 = 0; r0 < L.rows; r0 += chunk_rows) {
+    const size_t n = std::min(chunk_rows, L.rows - r0);
+    void* dev;
+    int slot;
+    CK(e, st.push(data + r0 * row_bytes, n * row_bytes, &dev, &slot), "checkpoint upload");
+    e->launches += 1;
+    const int rc = with_dst_type(e, L, [&](auto* dst) {
+      CK(e, launch_place_rows_cvt(dev, sdt, dst, n, (int)L.cols, r0, L.mode, L.row_offset, L.dst_stride, e->stream), "checkpoint placement");
+      return (int)DCD_OK;
+    });
+    if (rc) return rc;
+    CK(e, st.release(slot), "checkpoint staging");
+  }
+  return DCD_OK;
+}
+
+int need(dcd_engine* e, const ckpt::Store& s, const std::string& name, const ckpt::Tensor** out) {
+  *out = s.info(name);
+  if (!*out) return fail(e, DCD_E_INVALID, "tensor %s not found", name.c_str());
+  return DCD_OK;
+}
+
+int load_vector(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& name, int layer, int kind) {
+  Loc L;
+  if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  const ckpt::Tensor* t;
+  if (int rc = need(e, s, name, &t)) return rc;
+  return place_plain(e, st, name.c_str(), s.data(*t), t->dtype, t->count(), L);
+}
+
+// compressed-tensors pack-quantized int4 module -> bf16 values at L (weights.rs:292-330)
+int place_ct_w4(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& module, const Loc& L) {
+  const ckpt::Tensor *tp, *tsh, *tsc;
+  if (int rc = need(e, s, module + ".weight_packed", &tp)) return rc;
+  if (int rc = need(e, s, module + ".weight_shape", &tsh)) return rc;
+  if (int rc = need(e, s, module + ".weight_scale", &tsc)) return rc;
+  const ckpt::Tensor* tz = s.info(module + ".weight_zero_point");
+  size_t out = 0, in = 0;
+  if (tsh->count() != 2) return fail(e, DCD_E_INVALID, "%s.weight_shape: expected 2 entries", module.c_str());
+  if (tsh->dtype == ckpt::I64) { const int64_t* v = (const int64_t*)s.data(*tsh); out = (size_t)v[0]; in = (size_t)v[1]; }
+  else if (tsh->dtype == ckpt::I32) { const int32_t* v = (const int32_t*)s.data(*tsh); out = (size_t)v[0]; in = (size_t)v[1]; }
+  else return fail(e, DCD_E_INVALID, "%s.weight_shape: expected I64", module.c_str());
+  if (out != L.rows || in != L.cols) return fail(e, DCD_E_INVALID, "%s: checkpoint shape %zu x %zu, the engine expects %zu x %zu", module.c_str(), out, in, L.rows, L.cols);
+  const size_t groups = tsc->shape.empty() ? 0 : tsc->shape.back();
+  if (groups == 0 || in % groups) return fail(e, DCD_E_INVALID, "%s: in=%zu not divisible by groups=%zu", module.c_str(), in, groups);
+  const size_t gs = in / groups;
+  if (gs != 64 && gs != 128) return fail(e, DCD_E_INVALID, "%s: unsupported group size %zu", module.c_str(), gs);
+  const size_t words = (in + 7) / 8, zp_rows = (out + 7) / 8;
+  if (tp->dtype != ckpt::I32 || tp->count() != out * words) return fail(e, DCD_E_INVALID, "%s: packed has %zu words, expected %zu", module.c_str(), tp->count(), out * words);
+  if (tsc->dtype != ckpt::BF16 || tsc->count() != out * groups || (tz && (tz->dtype != ckpt::I32 || tz->count() != zp_rows * groups)))
+    return fail(e, DCD_E_INVALID, "%s: scale/zp size mismatch", module.c_str());
+  const uint8_t *pp = s.data(*tp), *ps = s.data(*tsc), *pz = tz ? s.data(*tz) : nullptr;
+  const size_t chunk_rows = std::max<size_t>(8, (st.cap / (words * 4)) & ~(size_t)7);
+  if (8 * words * 4 > st.cap) return fail(e, DCD_E_INVALID, "%s: eight rows exceed the staging buffer", module.c_str());
+  for (size_t r0 = 0; r0 < out; r0 += chunk_rows) {
+    const size_t n = std::min(chunk_rows, out - r0);
+    void *dp, *ds, *dz = nullptr;
+    int sp, ss, sz = -1;
+    CK(e, st.push(pp + r0 * words * 4, n * words * 4, &dp, &sp), "checkpoint upload");
+    CK(e, st.push(ps + r0 * groups * 2, n * groups * 2, &ds, &ss), "checkpoint upload");
+    if (pz) CK(e, st.push(pz + (r0 / 8) * groups * 4, ((n + 7) / 8) * groups * 4, &dz, &sz), "checkpoint upload");
+    e->launches += 1;
+    const int rc = with_dst_type(e, L, [&](auto* dst) {
+      CK(e, launch_dequant_ct_w4_place((const int32_t*)dp, (const bf16*)ds, (const int32_t*)dz, dst, n, (int)in, (int)gs, r0, L.mode, L.row_offset,
+                                       L.dst_stride, e->stream), "int4 checkpoint dequantisation");
+      return (int)DCD_OK;
+    });
+    if (rc) return rc;
+    CK(e, st.release(sp), "checkpoint staging");
+    CK(e, st.release(ss), "checkpoint staging");
+    if (sz >= 0) CK(e, st.release(sz), "checkpoint staging");
+  }
+  return DCD_OK;
+}
+
+// compressed-tensors nvfp4-pack-quantized module -> bf16 values at L (weights.rs:502-547)
+int place_ct_nvfp4(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& module, const Loc& L) {
+  const ckpt::Tensor *tp, *tsc, *tg;
+  if (int rc = need(e, s, module + ".weight_packed", &tp)) return rc;
+  if (int rc = need(e, s, module + ".weight_scale", &tsc)) return rc;
+  if (int rc = need(e, s, module + ".weight_global_scale", &tg)) return rc;
+  if (tp->shape.size() != 2) return fail(e, DCD_E_INVALID, "%s.weight_packed must be 2-D", module.c_str());
+  const size_t out = tp->shape[0], in = tp->shape[1] * 2;
+  if (in % 64) return fail(e, DCD_E_INVALID, "%s: K=%zu is not a multiple of 64", module.c_str(), in);
+  if (tsc->shape.size() != 2 || tsc->shape[0] != out || tsc->shape[1] != in / 16 || ckpt::dtype_size(tsc->dtype) != 1 || ckpt::dtype_size(tp->dtype) != 1)
+    return fail(e, DCD_E_INVALID, "%s: weight_scale must be [%zu, %zu] of 8-bit values", module.c_str(), out, in / 16);
+  if (out != L.rows || in != L.cols) return fail(e, DCD_E_INVALID, "%s: checkpoint shape %zu x %zu, the engine expects %zu x %zu", module.c_str(), out, in, L.rows, L.cols);
+  float global = 0.f;
+  if (tg->count() < 1) return fail(e, DCD_E_INVALID, "%s: weight_global_scale empty", module.c_str());
+  if (tg->dtype == ckpt::F32) memcpy(&global, s.data(*tg), 4);
+  else if (tg->dtype == ckpt::BF16) { uint16_t hv; memcpy(&hv, s.data(*tg), 2); const uint32_t u = (uint32_t)hv << 16; memcpy(&global, &u, 4); }
+  else return fail(e, DCD_E_INVALID, "%s.weight_global_scale: expected F32/BF16", module.c_str());
+  const uint8_t *pp = s.data(*tp), *ps = s.data(*tsc);
+  const size_t row_bytes = in / 2, chunk_rows = std::max<size_t>(1, st.cap / row_bytes);
+  if (row_bytes > st.cap) return fail(e, DCD_E_INVALID, "%s: one row exceeds the staging buffer", module.c_str());
+  for (size_t r0 = 0; r0 < out; r0 += chunk_rows) {
+    const size_t n = std::min(chunk_rows, out - r0);
+    void *dp, *ds;
+    int sp, ss;
+    CK(e, st.push(pp + r0 * row_bytes, n * row_bytes, &dp, &sp), "checkpoint upload");
+    CK(e, st.push(ps + r0 * (in / 16), n * (in / 16), &ds, &ss), "checkpoint upload");
+    e->launches += 1;
+    const int rc = with_dst_type(e, L, [&](auto* dst) {
+      CK(e, launch_dequant_ct_nvfp4_place((const uint8_t*)dp, (const uint8_t*)ds, global, dst, n, (int)in, r0, L.mode, L.row_offset, L.dst_stride,
+                                          e->stream), "nvfp4 checkpoint dequantisation");
+      return (int)DCD_OK;
+    });
+    if (rc) return rc;
+    CK(e, st.release(sp), "checkpoint staging");
+    CK(e, st.release(ss), "checkpoint staging");
+  }
+  return DCD_OK;
+}
+
+// WeightProvider::linear (weights.rs:283-499): the stored format of a module is detected by the tensors it has.
+int load_linear(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& module, const Loc& L) {
+  if (s.contains(module + ".weight_global_scale")) return place_ct_nvfp4(e, st, s, module, L);
+  if (s.contains(module + ".weight_packed")) return place_ct_w4(e, st, s, module, L);
+  const std::string wname = module + ".weight";
+  const ckpt::Tensor* t = s.info(wname);
+  if (!t) return fail(e, DCD_E_INVALID, "linear %s not found", wname.c_str());
+  if (t->shape.size() != 2) return fail(e, DCD_E_INVALID, "%s: expected 2-D weight", wname.c_str());
+  if (t->shape[0] != L.rows || t->shape[1] != L.cols)
+    return fail(e, DCD_E_INVALID, "%s: checkpoint shape %zu x %zu, the engine expects %zu x %zu", wname.c_str(), t->shape[0], t->shape[1], L.rows, L.cols);
+  return place_plain(e, st, wname.c_str(), s.data(*t), t->dtype, t->count(), L);
+}
+
+struct Member { int kind; const char* module; };
+
+// One fused engine matrix = one or more checkpoint modules.
+int load_group(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& layer_prefix, int layer, const Member* m, int count) {
+  Loc L;
+  for (int i = 0; i < count; ++i) {
+    if (!locate(e, layer, m[i].kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", m[i].kind, layer);
+    if ((L.w4 || L.nv) && i == 0) {
+      const size_t n = L.w4 ? (size_t)L.w4->N * L.w4->K : (size_t)L.nv->N * L.nv->K;
+      CK(e, cudaMemsetAsync(e->wstage, 0, n * 2, e->stream), "stage clear");
+    }
+    if (int rc = load_linear(e, st, s, layer_prefix + m[i].module, L)) return rc;
+  }
+  return w4_stage_out(e, L);
+}
+
+int load_checkpoint_impl(dcd_engine* e, Stager& st, const ckpt::Store& s, const char* readout_path) {
+  static const char* prefixes[] = {"model.language_model.", "language_model.", "model.", ""};
+  const char* prefix = nullptr;
+  for (const char* p : prefixes) if (s.contains(std::string(p) + "embed_tokens.weight")) { prefix = p; break; }
+  if (!prefix) return fail(e, DCD_E_INVALID, "could not locate embed_tokens.weight in checkpoint");
+  const std::string P = prefix;
+  int rc;
+  {
+    const ckpt::Tensor* t;
+    if ((rc = need(e, s, P + "embed_tokens.weight", &t))) return rc;
+    if (t->shape.size() != 2 || t->shape[0] != (size_t)e->c.vocab || t->shape[1] != e->H)
+      return fail(e, DCD_E_INVALID, "embed_tokens.weight: expected [%d, %zu]", e->c.vocab, e->H);
+    if ((rc = load_vector(e, st, s, P + "embed_tokens.weight", -1, DCD_T_EMBED))) return rc;
+  }
+  if ((rc = load_vector(e, st, s, P + "norm.weight", -1, DCD_T_FINAL_NORM))) return rc;
+  static const Member gate_up[] = {{DCD_T_GATE, "mlp.gate_proj"}, {DCD_T_UP, "mlp.up_proj"}};
+  static const Member down[] = {{DCD_T_DOWN, "mlp.down_proj"}};
+  static const Member qkv[] = {{DCD_T_Q, "self_attn.q_proj"}, {DCD_T_K, "self_attn.k_proj"}, {DCD_T_V, "self_attn.v_proj"}};
+  static const Member o[] = {{DCD_T_O, "self_attn.o_proj"}};
+  static const Member gin[] = {{DCD_T_IN_QKV, "linear_attn.in_proj_qkv"}, {DCD_T_IN_Z, "linear_attn.in_proj_z"}, {DCD_T_IN_B, "linear_attn.in_proj_b"},
+                               {DCD_T_IN_A, "linear_attn.in_proj_a"}};
+  static const Member gout[] = {{DCD_T_OUT, "linear_attn.out_proj"}};
+  for (int i = 0; i < e->c.num_layers; ++i) {
+    const std::string l = P + "layers." + std::to_string(i) + ".";
+    if ((rc = load_vector(e, st, s, l + "input_layernorm.weight", i, DCD_T_INPUT_NORM))) return rc;
+    if ((rc = load_vector(e, st, s, l + "post_attention_layernorm.weight", i, DCD_T_POST_NORM))) return rc;
+    if ((rc = load_group(e, st, s, l, i, gate_up, 2))) return rc;
+    if ((rc = load_group(e, st, s, l, i, down, 1))) return rc;
+    if (e->layers[i].full) {
+      if ((rc = load_group(e, st, s, l, i, qkv, 3))) return rc;
+      if ((rc = load_group(e, st, s, l, i, o, 1))) return rc;
+      if ((rc = load_vector(e, st, s, l + "self_attn.q_norm.weight", i, DCD_T_QNORM))) return rc;
+      if ((rc = load_vector(e, st, s, l + "self_attn.k_norm.weight", i, DCD_T_KNORM))) return rc;
+    } else {
+      if ((rc = load_group(e, st, s, l, i, gin, 4))) return rc;
+      if ((rc = load_group(e, st, s, l, i, gout, 1))) return rc;
+      if ((rc = load_vector(e, st, s, l + "linear_attn.conv1d.weight", i, DCD_T_CONV))) return rc;
+      if ((rc = load_vector(e, st, s, l + "linear_attn.A_log", i, DCD_T_A_LOG))) return rc;
+      if ((rc = load_vector(e, st, s, l + "linear_attn.dt_bias", i, DCD_T_DT_BIAS))) return rc;
+      if ((rc = load_vector(e, st, s, l + "linear_attn.norm.weight", i, DCD_T_GNORM))) return rc;
+    }
+  }
+  if (readout_path) {
+    ckpt::Store head;
+    std::string err;
+    if (!head.open(readout_path, &err)) return fail(e, DCD_E_INVALID, "%s", err.c_str());
+    const ckpt::Tensor* w = head.info("weight");
+    if (!w) return fail(e, DCD_E_INVALID, "readout.weight not found in %s", readout_path);
+    if (w->shape.size() != 2) return fail(e, DCD_E_INVALID, "readout.weight must be 2-D");
+    if (w->dtype != ckpt::F32 && w->dtype != ckpt::BF16) return fail(e, DCD_E_INVALID, "readout.weight dtype unsupported");
+    if (w->shape[0] != (size_t)e->c.readout_rows || w->shape[1] != e->H)
+      return fail(e, DCD_E_INVALID, "readout.weight is %zu x %zu, the engine expects %d x %zu", w->shape[0], w->shape[1], e->c.readout_rows, e->H);
+    Loc L;
+    if (!locate(e, -1, DCD_T_READOUT, &L)) return fail(e, DCD_E_INVALID, "no readout tensor");
+    if ((rc = place_plain(e, st, "readout.weight", head.data(*w), w->dtype, w->count(), L))) return rc;
+    // the mapping of `head` ends with this scope: finish the copies out of it first
+    CK(e, cudaStreamSynchronize(e->stream), "readout upload");
+  }
+  return DCD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dcd_checkpoint_open(const char* path, dcd_checkpoint** out) {
+  if (!out) return DCD_E_INVALID;
+  *out = nullptr;
+  if (!path) return fail(nullptr, DCD_E_INVALID, "null checkpoint path");
+  dcd_checkpoint* ck = new dcd_checkpoint();
+  std::string err;
+  if (!ck->store.open(path, &err)) {
+    delete ck;
+    return fail(nullptr, DCD_E_INVALID, "%s", err.c_str());
+  }
+  *out = ck;
+  return DCD_OK;
+}
+void dcd_checkpoint_close(dcd_checkpoint* ck) { delete ck; }
+size_t dcd_checkpoint_count(const dcd_checkpoint* ck) { return ck ? ck->store.size() : 0; }
+const char* dcd_checkpoint_name(const dcd_checkpoint* ck, size_t i) { return ck && i < ck->store.size() ? ck->store.name_at(i).c_str() : nullptr; }
+int dcd_checkpoint_tensor(const dcd_checkpoint* ck, const char* name, dcd_tensor_info* out) {
+  if (!ck || !name || !out) return DCD_E_INVALID;
+  const ckpt::Tensor* t = ck->store.info(name);
+  if (!t) return fail(nullptr, DCD_E_INVALID, "tensor %s not found", name);
+  memset(out, 0, sizeof *out);
+  if (t->shape.size() > 8) return fail(nullptr, DCD_E_UNSUPPORTED, "tensor %s has more than 8 dimensions", name);
+  out->dtype = t->dtype;
+  out->rank = (int32_t)t->shape.size();
+  for (size_t i = 0; i < t->shape.size(); ++i) out->shape[i] = t->shape[i];
+  out->bytes = t->end - t->start;
+  out->data = ck->store.data(*t);
+  return DCD_OK;
+}
+int dcd_config_from_dir(const char* dir, dcd_model_config* out) {
+  if (!dir || !out) return DCD_E_INVALID;
+  std::string err;
+  if (!ckpt::config_from_dir(dir, out, &err)) return fail(nullptr, DCD_E_INVALID, "%s", err.c_str());
+  return DCD_OK;
+}
+
+int dcd_engine_load_checkpoint(dcd_engine* e, const dcd_checkpoint* ck, const char* readout_path) {
+  if (!e || !ck) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  Stager st;
+  cudaError_t ce = st.init(STAGE_CHUNK, e->stream);
+  int rc = ce == cudaSuccess ? load_checkpoint_impl(e, st, ck->store, readout_path) : cuda_fail(e, ce, "checkpoint staging buffers");
+  const cudaError_t se = cudaStreamSynchronize(e->stream);
+  st.destroy();
+  if (rc == DCD_OK && se != cudaSuccess) rc = cuda_fail(e, se, "load_checkpoint");
+  if (rc == DCD_OK) { e->weights_ready = true; e->fp8_dirty = true; }
+  return rc;
+}
+
+int dcd_engine_load_tensor_typed(dcd_engine* e, int layer, int kind, const void* host, int dtype, size_t count) {
+  if (!e || !host) return DCD_E_INVALID;
+  cudaSetDevice(e->device);
+  Loc L;
+  if (!locate(e, layer, kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", kind, layer);
+  if (int rc0 = w4_stage_in(e, L)) return rc0;
+  Stager st;
+  cudaError_t ce = st.init(STAGE_CHUNK, e->stream);
+  int rc = ce == cudaSuccess ? place_plain(e, st, "tensor", (const uint8_t*)host, dtype, count, L) : cuda_fail(e, ce, "tensor staging buffers");
+  if (rc == DCD_OK) rc = w4_stage_out(e, L);
+  const cudaError_t se = cudaStreamSynchronize(e->stream);
+  st.destroy();
+  if (rc == DCD_OK && se != cudaSuccess) rc = cuda_fail(e, se, "load_tensor_typed");
+  if (rc == DCD_OK) { e->weights_ready = true; e->fp8_dirty = true; }
+  return rc;
 }
 
 // ---- hot path ---------------------------------------------------------------------

@@ -1616,3 +1616,120 @@ cudaError_t launch_nvfp4_dequant_rows(const uint8_t* packed, const uint8_t* scal
   nvfp4_dequant_rows_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, s>>>(packed, scales, global_ptr, out, groups, K);
   return cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// Checkpoint formats -> engine layout. A chunk of `n_rows` source rows (the first one is row
+// `row_start` of the logical tensor) is converted and written to its place inside the (possibly
+// fused / interleaved) engine matrix; map_row() is the same placement every other loader uses.
+//
+// place_rows_cvt: plain tensors stored as F32, F16 or BF16 (Store::bf16 / Store::f32,
+//   native/src/tensor.rs:187-215 in juanqui/decidra).
+// dequant_ct_w4_place: compressed-tensors pack-quantized int4 (LinearWeight::PackedW4A16,
+//   native/src/weights.rs:73-87): packed I32 [out, ceil(in/8)], nibble j of a word = input
+//   8*word + j; scale BF16 [out, in/group]; zero point I32 [ceil(out/8), in/group], nibble
+//   (o & 7) of word (o >> 3); symmetric checkpoints have no zero-point tensor and mean 8
+//   (weights.rs:314-320). Value = bf16((q - z) * scale), the arithmetic of dequant_w4a16_bf16
+//   (native/kernels/kernels.cu:874-892).
+// dequant_ct_nvfp4_place: compressed-tensors nvfp4-pack-quantized (nvfp4_linear,
+//   native/src/weights.rs:502-547): packed U8 [out, in/2] (low nibble = even input), scale
+//   E4M3 [out, in/16] row-major, f32 weight_global_scale; value = bf16(e2m1 * (scale / global)),
+//   the weight factor of Engine::nvfp4_gemm's alpha = 1/(weight_global*input_global)
+//   (native/src/engine.rs:4109).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void place_rows_cvt_kernel(const void* __restrict__ src, int src_dt, T* __restrict__ dst, size_t n, int cols, size_t row_start,
+                                      int mode, int row_offset, int dst_stride) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t r = i / cols, c = i - r * cols;
+  float v;
+  if (src_dt == 0) v = reinterpret_cast<const float*>(src)[i];
+  else if (src_dt == 1) v = __half2float(reinterpret_cast<const __half*>(src)[i]);
+  else v = __bfloat162float(reinterpret_cast<const bf16*>(src)[i]);
+  Ty<T>::st(dst + map_row(row_start + r, mode, row_offset) * dst_stride + c, v);
+}
+template <typename T>
+cudaError_t launch_place_rows_cvt(const void* src, int src_dt, T* dst, size_t n_rows, int cols, size_t row_start, int mode, int row_offset,
+                                  int dst_stride, cudaStream_t s) {
+  const size_t n = n_rows * cols;
+  if (n == 0) return cudaSuccess;
+  if (src_dt < 0 || src_dt > 2) return cudaErrorInvalidValue;
+  place_rows_cvt_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, src_dt, dst, n, cols, row_start, mode, row_offset, dst_stride);
+  return cudaGetLastError();
+}
+template cudaError_t launch_place_rows_cvt<float>(const void*, int, float*, size_t, int, size_t, int, int, int, cudaStream_t);
+template cudaError_t launch_place_rows_cvt<bf16>(const void*, int, bf16*, size_t, int, size_t, int, int, int, cudaStream_t);
+
+template <typename T>
+__global__ void dequant_ct_w4_place_kernel(const int32_t* __restrict__ packed, const bf16* __restrict__ scale, const int32_t* __restrict__ zp,
+                                           T* __restrict__ dst, size_t n_words, int in_dim, int group_size, size_t row_start, int mode,
+                                           int row_offset, int dst_stride) {
+  const size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (wi >= n_words) return;
+  const int words_per_row = (in_dim + 7) / 8;
+  const int groups = (in_dim + group_size - 1) / group_size;
+  const size_t o = wi / words_per_row;  // row inside the chunk; the chunk starts on a multiple of 8 rows
+  const int w = (int)(wi - o * words_per_row);
+  const uint32_t word = (uint32_t)packed[wi];
+  T* out = dst + map_row(row_start + o, mode, row_offset) * dst_stride;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = w * 8 + j;
+    if (i >= in_dim) break;
+    const int g = i / group_size;
+    const int q = (int)((word >> (4 * j)) & 0xFu);
+    const int z = zp ? (int)(((uint32_t)zp[(o >> 3) * groups + g] >> (4 * (int)(o & 7))) & 0xFu) : 8;
+    const float sc = __bfloat162float(scale[o * groups + g]);
+    Ty<T>::st(out + i, __bfloat162float(__float2bfloat16_rn((float)(q - z) * sc)));
+  }
+}
+template <typename T>
+cudaError_t launch_dequant_ct_w4_place(const int32_t* packed, const bf16* scale, const int32_t* zp, T* dst, size_t n_rows, int in_dim,
+                                       int group_size, size_t row_start, int mode, int row_offset, int dst_stride, cudaStream_t s) {
+  if (n_rows == 0) return cudaSuccess;
+  if (in_dim <= 0 || group_size <= 0 || (row_start & 7)) return cudaErrorInvalidValue;
+  const size_t n_words = n_rows * (size_t)((in_dim + 7) / 8);
+  dequant_ct_w4_place_kernel<T><<<(unsigned)((n_words + 255) / 256), 256, 0, s>>>(packed, scale, zp, dst, n_words, in_dim, group_size, row_start,
+                                                                                 mode, row_offset, dst_stride);
+  return cudaGetLastError();
+}
+template cudaError_t launch_dequant_ct_w4_place<float>(const int32_t*, const bf16*, const int32_t*, float*, size_t, int, int, size_t, int, int,
+                                                       int, cudaStream_t);
+template cudaError_t launch_dequant_ct_w4_place<bf16>(const int32_t*, const bf16*, const int32_t*, bf16*, size_t, int, int, size_t, int, int, int,
+                                                      cudaStream_t);
+
+template <typename T>
+__global__ void dequant_ct_nvfp4_place_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales, float global,
+                                              T* __restrict__ dst, size_t total_groups, int K, size_t row_start, int mode, int row_offset,
+                                              int dst_stride) {
+  const size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gi >= total_groups) return;
+  const int groups = K / 16;
+  const size_t row = gi / groups;
+  const int j = (int)(gi - row * groups);
+  float sd = e4m3_decode(scales[gi]);
+  if (global > 0.f) sd = sd / global;
+  const uint2 w = *reinterpret_cast<const uint2*>(packed + row * (size_t)(K / 2) + j * 8);
+  const uint32_t ww[2] = {w.x, w.y};
+  T* out = dst + map_row(row_start + row, mode, row_offset) * dst_stride + j * 16;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t byte = (ww[i >> 2] >> (8 * (i & 3))) & 0xff;
+    Ty<T>::st(out + 2 * i, __bfloat162float(__float2bfloat16_rn(fp4_decode((uint8_t)(byte & 0xf)) * sd)));
+    Ty<T>::st(out + 2 * i + 1, __bfloat162float(__float2bfloat16_rn(fp4_decode((uint8_t)(byte >> 4)) * sd)));
+  }
+}
+template <typename T>
+cudaError_t launch_dequant_ct_nvfp4_place(const uint8_t* packed, const uint8_t* scales, float global, T* dst, size_t n_rows, int K,
+                                          size_t row_start, int mode, int row_offset, int dst_stride, cudaStream_t s) {
+  if (n_rows == 0) return cudaSuccess;
+  if (K <= 0 || (K % 16)) return cudaErrorInvalidValue;
+  const size_t groups = n_rows * (size_t)(K / 16);
+  dequant_ct_nvfp4_place_kernel<T><<<(unsigned)((groups + 255) / 256), 256, 0, s>>>(packed, scales, global, dst, groups, K, row_start, mode,
+                                                                                   row_offset, dst_stride);
+  return cudaGetLastError();
+}
+template cudaError_t launch_dequant_ct_nvfp4_place<float>(const uint8_t*, const uint8_t*, float, float*, size_t, int, size_t, int, int, int,
+                                                          cudaStream_t);
+template cudaError_t launch_dequant_ct_nvfp4_place<bf16>(const uint8_t*, const uint8_t*, float, bf16*, size_t, int, size_t, int, int, int,
+                                                         cudaStream_t);

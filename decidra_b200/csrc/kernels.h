@@ -65,6 +65,19 @@ cudaError_t launch_gen_tensor(T* dst, uint64_t key, uint64_t first, uint64_t cou
 template <typename T>
 cudaError_t launch_place_rows(const T* src, T* dst, size_t rows, int cols, int mode, int row_offset, int dst_stride, bool inverse,
                               cudaStream_t s);
+// Checkpoint formats -> engine layout (a chunk of rows starting at row_start of the logical tensor).
+// src_dt: 0 = f32, 1 = f16, 2 = bf16.
+template <typename T>
+cudaError_t launch_place_rows_cvt(const void* src, int src_dt, T* dst, size_t n_rows, int cols, size_t row_start, int mode, int row_offset,
+                                  int dst_stride, cudaStream_t s);
+// compressed-tensors pack-quantized int4 (zp == nullptr: symmetric, zero point 8); row_start must be a multiple of 8
+template <typename T>
+cudaError_t launch_dequant_ct_w4_place(const int32_t* packed, const __nv_bfloat16* scale, const int32_t* zp, T* dst, size_t n_rows, int in_dim,
+                                       int group_size, size_t row_start, int mode, int row_offset, int dst_stride, cudaStream_t s);
+// compressed-tensors nvfp4-pack-quantized weights: e2m1 pairs, row-major e4m3 scale per 16, f32 tensor scale
+template <typename T>
+cudaError_t launch_dequant_ct_nvfp4_place(const uint8_t* packed, const uint8_t* scales, float global, T* dst, size_t n_rows, int K,
+                                          size_t row_start, int mode, int row_offset, int dst_stride, cudaStream_t s);
 
 // Chunked tensor-core form of the gated delta rule (gdn_chunked.cu); dk must be 128 and dv a multiple of 64.
 bool gdn_chunked_supported(int dk, int dv);

@@ -65,9 +65,9 @@ typedef struct dcd_options {
                                dequantised per GEMM into a shared bf16 stage (dequant_w4a16_bf16 route,
                                native/src/engine.rs:4516-4558), all passes; 3 = nvfp4 with the reference's W4A4 semantics
                                (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131): weights held as e2m1 + e4m3 scale per 16 +
-                               f32 tensor scale, activations through the same round trip per GEMM, all passes; the operands'
-                               dequantised values are exact in bf16 and feed the bf16 tensor-core GEMM (a native block-scaled
-                               FP4 MMA kernel is not built yet) */
+                               f32 tensor scale, activations quantised the same way per GEMM, all passes; gemm_path 0 multiplies the
+                               codes on the block-scaled FP4 tensor-core instruction, gemm_path 2 dequantises both operands
+                               (exact in bf16) and runs the bf16 tensor-core GEMM */
   int32_t max_pass_tokens;  /* workspace rows; also the longest state that can be captured. default 16384 */
   int32_t max_rows;         /* question-pass chunk caps; defaults 256 rows, 2^22 keys, 2^33 scores */
   int64_t max_keys;
@@ -133,6 +133,57 @@ enum {
   DCD_T_IN_QKV = 30, DCD_T_IN_Z = 31, DCD_T_IN_B = 32, DCD_T_IN_A = 33, DCD_T_OUT = 34, DCD_T_CONV = 35,
   DCD_T_A_LOG = 36, DCD_T_DT_BIAS = 37, DCD_T_GNORM = 38
 };
+
+/* Same upload from the checkpoint's own storage type (dtype = DCD_DT_F32 / DCD_DT_F16 / DCD_DT_BF16), without the
+ * f32 expansion on the host; the conversion to the engine type runs on the device. Store::bf16 / Store::f32 +
+ * clone_htod (native/src/tensor.rs:187-215, native/src/weights.rs:256-270). */
+DCD_API int dcd_engine_load_tensor_typed(dcd_engine* e, int layer, int kind, const void* host, int dtype, size_t count);
+
+/* ---- checkpoints ----------------------------------------------------------- */
+
+/* safetensors element types (DType::parse, native/src/tensor.rs:25-38). "BOOL" reads as U8,
+ * "F8_E4M3FN" as F8E4M3; anything else makes dcd_checkpoint_open fail. */
+enum { DCD_DT_F32 = 0, DCD_DT_F16 = 1, DCD_DT_BF16 = 2, DCD_DT_I32 = 3, DCD_DT_I64 = 4, DCD_DT_U8 = 5, DCD_DT_F8E4M3 = 6 };
+
+typedef struct dcd_checkpoint dcd_checkpoint; /* Store (native/src/tensor.rs:56-59): memory-mapped shards + name table */
+typedef struct dcd_tensor_info {
+  int32_t dtype; /* DCD_DT_* */
+  int32_t rank;
+  uint64_t shape[8];
+  uint64_t bytes;
+  const void* data; /* inside the mapping; valid until dcd_checkpoint_close */
+} dcd_tensor_info;
+
+/* Store::open / Store::open_file (native/src/tensor.rs:62-137,144-185). `path` is a model directory
+ * (model.safetensors; else the shards named by model.safetensors.index.json; else every *.safetensors,
+ * sorted) or one .safetensors file. Nothing is read at open time beyond the headers. No device is touched.
+ * On failure *out is NULL and dcd_last_error(NULL) describes it. */
+DCD_API int dcd_checkpoint_open(const char* path, dcd_checkpoint** out);
+DCD_API void dcd_checkpoint_close(dcd_checkpoint* ck);
+DCD_API size_t dcd_checkpoint_count(const dcd_checkpoint* ck);                 /* Store::tensor_names */
+DCD_API const char* dcd_checkpoint_name(const dcd_checkpoint* ck, size_t i);   /* NULL past the end */
+DCD_API int dcd_checkpoint_tensor(const dcd_checkpoint* ck, const char* name, dcd_tensor_info* out); /* Store::info */
+
+/* Config::from_dir (native/src/config.rs:49-172): reads <dir>/config.json (tolerant of text_config nesting, same
+ * defaults) and the attention_mode of config.json / decision_config.json, which must be prefix_bidir. Sets
+ * dtype = 1 and leaves readout_rows = 0 (the readout head is a separate file: set it before dcd_engine_create). */
+DCD_API int dcd_config_from_dir(const char* dir, dcd_model_config* out);
+
+/* WeightProvider::{layer,linear,final_norm} + Engine::preload_all + HeadMatrix::load (native/src/weights.rs:283-630,
+ * native/src/engine.rs:747-783): fills every weight of the engine from an open checkpoint. The name prefix is
+ * detected from embed_tokens.weight among "model.language_model.", "language_model.", "model.", "". Per module
+ * the stored format is detected by the tensors present:
+ *   <m>.weight (BF16; F16/F32 accepted)                              -> converted on the device;
+ *   <m>.weight_packed + weight_scale + weight_shape [+ weight_zero_point]  compressed-tensors pack-quantized int4,
+ *       group 64 or 128, asymmetric or symmetric                     -> bf16((q - z) * scale), bit-identical to
+ *       dequant_w4a16_bf16 (native/kernels/kernels.cu:874-892);
+ *   <m>.weight_packed + weight_scale + weight_global_scale            compressed-tensors NVFP4
+ *                                                                    -> bf16(e2m1 * (e4m3 scale / weight_global)).
+ * The values then take the engine's own precision route (kept as bf16, or quantised per fused matrix for
+ * precision 1 / 3; FP8 images are rebuilt lazily). Tensors stream through pinned staging buffers, so host
+ * memory use is bounded by the page cache. `readout_path` = the separate readout.safetensors ("weight",
+ * [readout_rows, hidden], F32 or BF16 widened); NULL leaves the readout head untouched. */
+DCD_API int dcd_engine_load_checkpoint(dcd_engine* e, const dcd_checkpoint* ck, const char* readout_path);
 
 /* engine.rebind_blas() (src/batch.rs:294): no vendor BLAS on this path; kept so the
  * scheduler's call compiles. Always DCD_OK. */

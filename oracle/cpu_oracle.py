@@ -426,3 +426,47 @@ def set_gemm_variant(v: int) -> None:
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+# ---- checkpoint storage formats (numpy integer arithmetic) --------------------------------------------------
+
+def ct_w4_dequant(packed, scale, zp, in_dim: int, group_size: int) -> np.ndarray:
+    """compressed-tensors pack-quantized int4 -> bf16-rounded f32 [out, in].
+
+    Restates dequant_w4a16_bf16 (native/kernels/kernels.cu:874-892): packed int32 [out, ceil(in/8)], nibble
+    (i & 7) of word (i >> 3); scale f32 values of the bf16 tensor [out, groups]; zp int32 [ceil(out/8), groups],
+    nibble (o & 7) of word (o >> 3); w = bf16((q - z) * scale). zp None = symmetric checkpoint, whose loader
+    substitutes 0x88888888 words, i.e. z = 8 (native/src/weights.rs:314-320)."""
+    packed = np.ascontiguousarray(packed).view(np.uint32)
+    out_dim = packed.shape[0]
+    i = np.arange(in_dim)
+    o = np.arange(out_dim)
+    q = ((packed[:, i >> 3] >> (4 * (i & 7)).astype(np.uint32)) & 0xF).astype(np.int32)
+    g = i // group_size
+    if zp is None:
+        z = np.full((out_dim, in_dim), 8, np.int32)
+    else:
+        zw = np.ascontiguousarray(zp).view(np.uint32)
+        z = ((zw[(o >> 3)[:, None], g[None, :]] >> (4 * (o & 7)).astype(np.uint32)[:, None]) & 0xF).astype(np.int32)
+    s = _f32(scale)[:, g]
+    return rb(((q - z).astype(np.float32) * s).astype(np.float32))
+
+
+E2M1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float32)
+
+
+def ct_nvfp4_dequant(packed, scales, weight_global: float) -> np.ndarray:
+    """compressed-tensors nvfp4-pack-quantized weight -> bf16-rounded f32 [out, in].
+
+    Layout of NvFp4Weight (native/src/weights.rs:36-45, 502-547): packed uint8 [out, in/2], low nibble = even input;
+    e4m3 scale per 16 inputs, row-major [out, in/16]; the weight's real value is e2m1 * scale / weight_global, the
+    weight factor of alpha = 1 / (weight_global * input_global) in Engine::nvfp4_gemm (native/src/engine.rs:4109)."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out_dim, half = packed.shape
+    codes = np.empty((out_dim, half * 2), dtype=np.uint8)
+    codes[:, 0::2] = packed & 0xF
+    codes[:, 1::2] = packed >> 4
+    sd = e4m3_to_f32(scales).astype(np.float32)
+    if weight_global > 0:
+        sd = (sd / np.float32(weight_global)).astype(np.float32)
+    return rb((E2M1[codes] * np.repeat(sd, 16, axis=1)).astype(np.float32))

@@ -214,3 +214,14 @@ def test_oracle_vs_reference_quantisers(ref, G, oracle):
     ref.launch("dequant_w4a16_bf16", ((n + 255) // 256,), (256,), 0,
                [torch.from_numpy(packed.view(np.int32)).cuda(), G.dev(sc, 1), zp, out, N, K, 128])
     assert G.host(out).tobytes() == oracle.k_dequant_w4(packed, sc16, K).tobytes()
+    # the checkpoint form of the same kernel: asymmetric zero points (one nibble per output row and group), groups of
+    # 64 and 128, arbitrary bf16 scales, an output count that is not a multiple of 8
+    for N, K, gs in ((21, 384, 64), (40, 640, 128)):
+        groups = K // gs
+        pk = r.integers(0, 2**32, (N, K // 8), dtype=np.uint64).astype(np.uint32).view(np.int32)
+        sc = oracle.rb(r.uniform(0.001, 0.01, (N, groups)).astype(np.float32))
+        zpw = r.integers(0, 2**32, ((N + 7) // 8, groups), dtype=np.uint64).astype(np.uint32).view(np.int32)
+        out = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+        ref.launch("dequant_w4a16_bf16", ((N * K + 255) // 256,), (256,), 0,
+                   [torch.from_numpy(pk).cuda(), G.dev(sc, 1), torch.from_numpy(zpw).cuda(), out, N, K, gs])
+        assert G.host(out).tobytes() == oracle.ct_w4_dequant(pk, sc, zpw, K, gs).tobytes()
