@@ -9,7 +9,7 @@ from .config import ModelConfig, Options
 
 LIB_PATH = Path(__file__).resolve().parent / "libdecidra_b200.so"
 
-OK, E_INVALID, E_OOM, E_UNSUPPORTED, E_CUDA, E_TIMEOUT = 0, 1, 2, 3, 4, 5
+OK, E_INVALID, E_OOM, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_OVERLOADED, E_FAILED = 0, 1, 2, 3, 4, 5, 6, 7
 PROF_NAMES = ("gemm", "attn", "gdn", "elementwise", "readout")
 
 
@@ -23,6 +23,52 @@ class Info(C.Structure):
 
 class TensorInfo(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_uint64 * 8), ("bytes", C.c_uint64), ("data", C.c_void_p)]
+
+
+class SchedOptions(C.Structure):
+    """Mirrors ``dcd_sched_options``."""
+    _fields_ = [
+        ("max_queue", C.c_int32), ("batch_requests", C.c_int32), ("batch_rows", C.c_int32), ("batch_window_us", C.c_int64),
+        ("state_cache_entries", C.c_int32), ("pin_cache", C.c_int32), ("state_cache_bytes", C.c_int64),
+        ("host_state_cache_bytes", C.c_int64), ("sched_priority", C.c_int32), ("reserved0", C.c_int32),
+        ("submit_timeout_us", C.c_int64), ("reserved", C.c_int64 * 4),
+    ]
+
+
+OP_INT_CTX = C.CFUNCTYPE(C.c_int, C.c_void_p)
+OP_CAPTURE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_void_p))
+OP_READOUT = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.POINTER(C.c_uint32)), C.POINTER(C.c_size_t), C.c_size_t,
+                         C.POINTER(C.c_float))
+OP_MOVE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p))
+OP_FREE = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+OP_MEM = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t))
+OP_ERR = C.CFUNCTYPE(C.c_void_p, C.c_void_p)  # returns the address of a NUL-terminated buffer the callee keeps alive
+OP_SIZE = C.CFUNCTYPE(C.c_size_t, C.c_void_p, C.c_size_t)
+
+
+class SchedEngineOps(C.Structure):
+    """Mirrors ``dcd_sched_engine_ops``: the engine operations the scheduler's worker calls."""
+    _fields_ = [
+        ("ctx", C.c_void_p), ("readout_rows", C.c_int32), ("reserved0", C.c_int32),
+        ("rebind_blas", OP_INT_CTX), ("capture_state", OP_CAPTURE), ("readout", OP_READOUT), ("offload", OP_MOVE), ("restore", OP_MOVE),
+        ("state_free", OP_FREE), ("host_free", OP_FREE), ("trim_pools", OP_INT_CTX), ("mem_info", OP_MEM), ("last_error", OP_ERR),
+        ("state_bytes_for", OP_SIZE), ("pass_reserve", OP_SIZE),
+    ]
+
+
+SCHED_STAT_NAMES = (
+    "submitted", "waiting", "running", "channel", "worker_alive", "requests_gpu_hit", "requests_host_hit", "requests_miss",
+    "reused_tokens", "captures", "state_tokens", "question_tokens", "questions_answered", "questions_failed", "questions_cancelled",
+    "groups_success", "groups_failed", "group_requests", "group_questions", "cancelled_queued", "cancelled_at_reply", "offloads",
+    "offload_bytes", "restores", "restore_bytes", "evict_gpu_entry_limit", "evict_gpu_byte_limit", "evict_gpu_offload_failed",
+    "evict_host_budget", "oom_retry_capture", "oom_retry_question", "fail_headroom", "fail_state_restore", "fail_state_capture",
+    "fail_state_offload", "fail_question_pass", "reject_queue_full", "reject_worker_stopped", "gpu_entries", "host_entries",
+    "gpu_bytes", "host_bytes", "gpu_free_bytes")
+
+
+class SchedStats(C.Structure):
+    """Mirrors ``dcd_sched_stats`` (all uint64)."""
+    _fields_ = [(n, C.c_uint64) for n in SCHED_STAT_NAMES]
 
 
 class ProfEntry(C.Structure):
@@ -48,6 +94,18 @@ SIGNATURES = {
     "dcd_checkpoint_tensor": (I, [P, C.c_char_p, C.POINTER(TensorInfo)]),
     "dcd_config_from_dir": (I, [C.c_char_p, C.POINTER(ModelConfig)]),
     "dcd_engine_load_checkpoint": (I, [P, P, C.c_char_p]),
+    "dcd_sched_default_options": (None, [C.POINTER(SchedOptions)]),
+    "dcd_scheduler_create": (I, [P, C.POINTER(SchedOptions), C.POINTER(P)]),
+    "dcd_scheduler_create_with_ops": (I, [C.POINTER(SchedEngineOps), C.POINTER(SchedOptions), C.POINTER(P)]),
+    "dcd_scheduler_destroy": (None, [P]),
+    "dcd_scheduler_last_error": (C.c_char_p, []),
+    "dcd_scheduler_submit": (I, [P, U32P, SZ, C.POINTER(U32P), C.POINTER(SZ), SZ, C.c_char_p, C.POINTER(P)]),
+    "dcd_ticket_wait": (I, [P, FP, SZ]),
+    "dcd_ticket_done": (I, [P]),
+    "dcd_ticket_error": (C.c_char_p, [P]),
+    "dcd_ticket_cancel": (None, [P]),
+    "dcd_ticket_free": (None, [P]),
+    "dcd_scheduler_stats": (I, [P, C.POINTER(SchedStats)]),
     "dcd_rebind_blas": (I, [P]),
     "dcd_capture_state": (I, [P, U32P, SZ, P, C.POINTER(P)]),
     "dcd_readout_state_once_batch": (I, [P, P, C.POINTER(U32P), C.POINTER(SZ), SZ, FP]),

@@ -15,6 +15,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/decidra_b200.h"
@@ -1129,6 +1130,25 @@ int dcd_engine_read_tensor(dcd_engine* e, int layer, int kind, float* host, size
 // stage and quantise it once after its last member.
 namespace {
 
+// Page cache -> pinned buffer. One thread moves about 9 GB/s, well under the host link; large chunks are split
+// over a few threads so that the staging copy keeps up with the H2D copy it overlaps with.
+void parallel_copy(void* dst, const void* src, size_t bytes) {
+  constexpr size_t MIN_PART = 4u << 20;
+  unsigned hw = std::thread::hardware_concurrency();
+  size_t parts = std::min<size_t>(std::min<size_t>(8, hw ? hw : 1), bytes / MIN_PART);
+  if (parts <= 1) { memcpy(dst, src, bytes); return; }
+  const size_t per = ((bytes / parts) + 4095) & ~(size_t)4095;
+  std::vector<std::thread> th;
+  for (size_t i = 1; i < parts; ++i) {
+    const size_t off = i * per;
+    if (off >= bytes) break;
+    const size_t n = std::min(per, bytes - off);
+    th.emplace_back([=] { memcpy((char*)dst + off, (const char*)src + off, n); });
+  }
+  memcpy(dst, src, std::min(per, bytes));
+  for (auto& t : th) t.join();
+}
+
 struct Stager {
   static constexpr int N = 6;
   size_t cap = 0;
@@ -1166,7 +1186,7 @@ struct Stager {
     cur = (cur + 1) % N;
     cudaError_t ce = cudaEventSynchronize(idle[b]);
     if (ce != cudaSuccess) return ce;
-    memcpy(h[b], src, bytes);
+    parallel_copy(h[b], src, bytes);
     ce = cudaMemcpyAsync(d[b], h[b], bytes, cudaMemcpyHostToDevice, s);
     *dev = d[b];
     *slot = b;

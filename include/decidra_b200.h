@@ -35,7 +35,9 @@ enum {
   DCD_E_OOM = 2,         /* device or host allocation failed */
   DCD_E_UNSUPPORTED = 3, /* vision, unsupported precision or shape */
   DCD_E_CUDA = 4,        /* a CUDA call failed */
-  DCD_E_TIMEOUT = 5      /* a bounded device-side wait gave up (kernel reported it, context stays usable) */
+  DCD_E_TIMEOUT = 5,     /* a bounded device-side wait gave up (kernel reported it, context stays usable) */
+  DCD_E_OVERLOADED = 6,  /* scheduler: the queue is full (EngineError::Overloaded, src/batch.rs:399-401) */
+  DCD_E_FAILED = 7       /* scheduler: the request failed in the worker or the worker stopped; the text says why */
 };
 
 /* Model description. Replaces Config::from_dir (native/src/config.rs:49-158) as a plain
@@ -138,6 +140,93 @@ enum {
  * f32 expansion on the host; the conversion to the engine type runs on the device. Store::bf16 / Store::f32 +
  * clone_htod (native/src/tensor.rs:187-215, native/src/weights.rs:256-270). */
 DCD_API int dcd_engine_load_tensor_typed(dcd_engine* e, int layer, int kind, const void* host, int dtype, size_t count);
+
+/* ---- request scheduler ------------------------------------------------------ */
+
+/* BatchHandle (src/batch.rs:32-36, 265-427): one worker thread owns the engine; requests queue up, are coalesced for
+ * a short window, grouped by exact state identity (tokens + 32-byte media digest) and served with one capture (or a
+ * cache hit) and one ragged question pass per group. Captured states stay in a device tier (entry and byte limits);
+ * when memory runs short or the tier is full they move to a pinned-host second level with its own byte budget.
+ * Defaults = src/config.rs:16-28. */
+typedef struct dcd_sched_options {
+  int32_t max_queue;              /* DECIDRA_MAX_QUEUE, 64: requests admitted (queued + running) */
+  int32_t batch_requests;         /* DECIDRA_BATCH_REQUESTS, 32: requests coalesced into one pass */
+  int32_t batch_rows;             /* DECIDRA_BATCH_ROWS, 32: sum of question rows that closes the window early */
+  int64_t batch_window_us;        /* DECIDRA_BATCH_WINDOW_US, 2000 (at most 50000) */
+  int32_t state_cache_entries;    /* DECIDRA_STATE_CACHE_ENTRIES, 16; 0 disables both tiers */
+  int32_t pin_cache;              /* DECIDRA_STATE_CACHE_PIN, 1: 0 evicts older device entries before each group */
+  int64_t state_cache_bytes;      /* DECIDRA_STATE_CACHE_BYTES, 5 GiB */
+  int64_t host_state_cache_bytes; /* DECIDRA_HOST_STATE_CACHE_BYTES, 8 GiB */
+  int32_t sched_priority;         /* DECIDRA_SCHED_PRIORITY, 0: 1 runs the cheapest group first (older than 500 ms first) */
+  int32_t reserved0;
+  int64_t submit_timeout_us;      /* 0 = wait for a queue slot like the reference's await; > 0 = give up with DCD_E_OVERLOADED */
+  int64_t reserved[4];
+} dcd_sched_options;
+DCD_API void dcd_sched_default_options(dcd_sched_options* o);
+
+/* What the worker calls on the engine. dcd_scheduler_create fills it with this library's entry points; a test
+ * double can stand in (host-made failures: an "out of memory" text, a shrinking free-memory figure).
+ * state_bytes_for / pass_reserve may be NULL: the reference's estimates are used
+ * (state_cache_bytes_for and pass_reserve, src/batch.rs:198-214). */
+typedef struct dcd_sched_engine_ops {
+  void* ctx;
+  int32_t readout_rows;
+  int32_t reserved0;
+  int (*rebind_blas)(void* ctx);                                                     /* may be NULL */
+  int (*capture_state)(void* ctx, const uint32_t* ids, size_t n, void** state_out);
+  int (*readout)(void* ctx, const void* state, const uint32_t* const* questions, const size_t* lens, size_t B, float* out);
+  int (*offload)(void* ctx, const void* state, void** host_out);
+  int (*restore)(void* ctx, const void* host, void** state_out);
+  void (*state_free)(void* ctx, void* state);
+  void (*host_free)(void* ctx, void* host);
+  int (*trim_pools)(void* ctx);
+  int (*mem_info)(void* ctx, size_t* free_bytes, size_t* total_bytes);
+  const char* (*last_error)(void* ctx);                                              /* may be NULL */
+  size_t (*state_bytes_for)(void* ctx, size_t state_len);                            /* may be NULL */
+  size_t (*pass_reserve)(void* ctx, size_t state_len);                               /* may be NULL */
+} dcd_sched_engine_ops;
+
+/* The reference's counters and gauges (docs/METRICS.md names in comments) as plain integers. */
+typedef struct dcd_sched_stats {
+  uint64_t submitted, waiting, running, channel, worker_alive;       /* decidra_engine_queue_* gauges, worker_alive */
+  uint64_t requests_gpu_hit, requests_host_hit, requests_miss;       /* decidra_state_cache_requests_total{result} */
+  uint64_t reused_tokens;                                            /* decidra_state_cache_reused_tokens_total */
+  uint64_t captures, state_tokens, question_tokens;                  /* ..._state_captures_total, ..._tokens_total{phase} */
+  uint64_t questions_answered, questions_failed, questions_cancelled; /* decidra_engine_questions_total{outcome} */
+  uint64_t groups_success, groups_failed, group_requests, group_questions;
+  uint64_t cancelled_queued, cancelled_at_reply;                     /* decidra_engine_requests_cancelled_total{stage} */
+  uint64_t offloads, offload_bytes, restores, restore_bytes;
+  uint64_t evict_gpu_entry_limit, evict_gpu_byte_limit, evict_gpu_offload_failed, evict_host_budget;
+  uint64_t oom_retry_capture, oom_retry_question;                    /* decidra_engine_oom_retries_total{stage} */
+  uint64_t fail_headroom, fail_state_restore, fail_state_capture, fail_state_offload, fail_question_pass;
+  uint64_t reject_queue_full, reject_worker_stopped;                 /* decidra_engine_admission_rejections_total{reason} */
+  uint64_t gpu_entries, host_entries, gpu_bytes, host_bytes, gpu_free_bytes;
+} dcd_sched_stats;
+
+typedef struct dcd_scheduler dcd_scheduler;
+typedef struct dcd_ticket dcd_ticket; /* the receiver half of one request's reply */
+
+/* BatchHandle::spawn (src/batch.rs:268-360). The scheduler's worker becomes the only caller of `e` until
+ * dcd_scheduler_destroy, which closes the queue, lets the worker finish what was queued, frees both cache tiers and
+ * joins the thread. opt NULL = defaults. Errors of the calls without a ticket: dcd_scheduler_last_error(). */
+DCD_API int dcd_scheduler_create(dcd_engine* e, const dcd_sched_options* opt, dcd_scheduler** out);
+DCD_API int dcd_scheduler_create_with_ops(const dcd_sched_engine_ops* ops, const dcd_sched_options* opt, dcd_scheduler** out);
+DCD_API void dcd_scheduler_destroy(dcd_scheduler* s);
+DCD_API const char* dcd_scheduler_last_error(void);
+/* BatchHandle::submit_state_once (src/batch.rs:364-426): copies the request and returns at once with a ticket.
+ * digest = 32 bytes (NULL = zeros, a text-only state). DCD_E_OVERLOADED "d3-turbo queue is full; retry shortly",
+ * DCD_E_FAILED "d3-turbo CUDA worker stopped". */
+DCD_API int dcd_scheduler_submit(dcd_scheduler* s, const uint32_t* state, size_t n_state, const uint32_t* const* questions,
+                                 const size_t* lens, size_t B, const uint8_t* digest, dcd_ticket** out);
+/* Blocks until the worker has answered. On DCD_OK logits_out holds [B, readout_rows] f32 (capacity in floats);
+ * otherwise dcd_ticket_error gives the reference's failure text ("state capture failed: ...",
+ * "insufficient GPU memory for question pass: ...", ...). */
+DCD_API int dcd_ticket_wait(dcd_ticket* t, float* logits_out, size_t capacity);
+DCD_API int dcd_ticket_done(const dcd_ticket* t);
+DCD_API const char* dcd_ticket_error(const dcd_ticket* t);
+DCD_API void dcd_ticket_cancel(dcd_ticket* t); /* the client went away: a still-queued request is skipped (src/batch.rs:437-453) */
+DCD_API void dcd_ticket_free(dcd_ticket* t);
+DCD_API int dcd_scheduler_stats(const dcd_scheduler* s, dcd_sched_stats* out);
 
 /* ---- checkpoints ----------------------------------------------------------- */
 
