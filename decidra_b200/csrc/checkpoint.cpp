@@ -226,7 +226,22 @@ bool parse_dtype(const std::string& s, int* dt) {
 }  // namespace
 
 Store::~Store() {
-  for (Shard& s : shards_) if (s.base) munmap(const_cast<uint8_t*>(s.base), s.bytes);
+  for (Shard& s : shards_) {
+    if (s.base) munmap(const_cast<uint8_t*>(s.base), s.bytes);
+    if (s.fd >= 0) ::close(s.fd);
+  }
+}
+
+bool Store::file_of(const void* p, int* fd, size_t* offset) const {
+  const uint8_t* q = (const uint8_t*)p;
+  for (const Shard& s : shards_) {
+    if (s.fd >= 0 && q >= s.base && q < s.base + s.bytes) {
+      *fd = s.fd;
+      *offset = (size_t)(q - s.base);
+      return true;
+    }
+  }
+  return false;
 }
 
 bool Store::map_file(const std::string& path, std::string* err) {
@@ -236,12 +251,12 @@ bool Store::map_file(const std::string& path, std::string* err) {
   if (fstat(fd, &st) != 0 || st.st_size < 8) { ::close(fd); *err = path + ": not a safetensors file"; return false; }
   const size_t bytes = (size_t)st.st_size;
   void* m = mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0);
-  ::close(fd);
-  if (m == MAP_FAILED) { *err = "mapping " + path + ": " + strerror(errno); return false; }
+  if (m == MAP_FAILED) { ::close(fd); *err = "mapping " + path + ": " + strerror(errno); return false; }
   Shard sh;
   sh.path = path;
   sh.base = (const uint8_t*)m;
   sh.bytes = bytes;
+  sh.fd = fd;
   const int shard = (int)shards_.size();
   shards_.push_back(sh);  // owned from here on: the destructor unmaps it whatever happens below
   uint64_t hlen = 0;

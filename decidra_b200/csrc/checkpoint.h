@@ -52,11 +52,14 @@ class Store {
   const Tensor* info(const std::string& name) const;
   bool contains(const std::string& name) const { return info(name) != nullptr; }
   const uint8_t* data(const Tensor& t) const { return shards_[t.shard].base + t.start; }
+  // The open file and offset behind a pointer into one of the mappings (false for any other pointer): bulk
+  // readers use pread on it, which copies out of the page cache without faulting the mapping in page by page.
+  bool file_of(const void* p, int* fd, size_t* offset) const;
   size_t size() const { return names_.size(); }
   const std::string& name_at(size_t i) const { return names_[i]; }
 
  private:
-  struct Shard { std::string path; const uint8_t* base = nullptr; size_t bytes = 0; };
+  struct Shard { std::string path; const uint8_t* base = nullptr; size_t bytes = 0; int fd = -1; };
   bool map_file(const std::string& path, std::string* err);
   std::vector<Shard> shards_;
   std::map<std::string, Tensor> map_;
