@@ -55,6 +55,9 @@ def parse():
     ap.add_argument("--qmin", type=int, default=48)
     ap.add_argument("--qmax", type=int, default=160)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scheduler-clients", type=int, default=0,
+                    help="extra arm: N client threads submit cold requests (a new state each) through the request scheduler; "
+                         "adds a 'scheduler' object to the JSON line (not part of the default run)")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8", "w4a16", "nvfp4"],
                     help="bf16 = BASELINE configs[1] (the headline); fp8 = e4m3 GEMMs in the question pass (extra, not the headline)")
     return ap.parse_args()
@@ -275,6 +278,44 @@ def run_ours(args):
     t_e2e = max_over_ranks(t_e2e)
     same = bool(np.array_equal(logits_host, logits_dev))
 
+    # ---- optional: the same cold requests through the request scheduler, from concurrent clients ----------------------
+    sched_info = None
+    if args.scheduler_clients > 0 and world == 1:
+        import threading
+        from decidra_b200 import scheduler
+        nc = args.scheduler_clients
+        vocab = 248320
+        per_client = []
+        for c in range(nc):
+            r = np.random.Generator(np.random.PCG64(5000 + c))
+            per_client.append([r.integers(0, vocab, S, dtype=np.uint32) for _ in range(args.steps)])  # a new state per request
+        handle = scheduler.BatchHandle(eng, state_cache_entries=0)   # no tier keeps a state: every request is cold
+        handle.submit_state_once(state, questions).result()          # warm
+        lat_s, errs = [], []
+
+        def client(c):
+            try:
+                for st_ids in per_client[c]:
+                    t = time.perf_counter()
+                    handle.submit_state_once(st_ids, questions).result()
+                    lat_s.append(time.perf_counter() - t)
+            except Exception as ex:  # noqa: BLE001
+                errs.append(repr(ex))
+
+        threads = [threading.Thread(target=client, args=(c,)) for c in range(nc)]
+        t0 = time.perf_counter()
+        for th in threads:
+            th.start()
+        for th in threads:
+            th.join()
+        t_s = time.perf_counter() - t0
+        stats = handle.stats()
+        handle.close()
+        sched_info = {"value": nc * args.steps * B / t_s, "unit": UNIT, "clients": nc, "requests": nc * args.steps,
+                      "p50_request_latency_ms": statistics.median(lat_s) * 1e3 if lat_s else None,
+                      "max_request_latency_ms": max(lat_s) * 1e3 if lat_s else None, "errors": errs,
+                      "captures": stats["captures"], "groups": stats["groups_success"], "questions_answered": stats["questions_answered"]}
+
     if rank == 0:
         peaks_path = ROOT / "MEASURED_PEAKS.json"
         if peaks_path.exists():
@@ -314,6 +355,8 @@ def run_ours(args):
             "kernel_time_share_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
             "clocks": clock_info,
         }
+        if sched_info is not None:
+            line["scheduler"] = sched_info
         if world == 1 and not args.no_cpu_baseline:
             qps, cores, desc, _ = cpu_sample(args, steps=1, warmup=0)
             line["cpu_baseline"] = {"value": qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
