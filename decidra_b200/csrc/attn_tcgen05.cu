@@ -10,21 +10,27 @@
 //
 // One CTA = (question, KV head, tile of 128/G tokens), G = query heads per KV head. The G heads of
 // a token share K/V, so the M=128 MMA tile is packed with (token, head) rows by a 3-D TMA box
-// {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 64 through 2-stage K and V rings:
-//   S[128,64]  = Q[128,256] . K^T        tcgen05.mma, Q as the TMEM A operand (copied there once from its TMA
-//                landing buffer: re-reading a 4 KB Q slice from shared memory for every 2 KB K slice made
-//                these products shared-memory-bandwidth bound), K from shared memory, S in TMEM
-//   softmax    : thread r owns row r: tcgen05.ld S, base-2 online softmax with a lazy rescale
-//                (O is only rescaled when the running max grows by more than 2^8), P -> bf16 into
-//                shared memory in the 128-byte-swizzled K-major operand layout
-//   O[128,256] += P[128,64] . V[64,256]  tcgen05.mma, V read as an MN-major operand, O in TMEM
-// S is double-buffered in TMEM: S of tile j+1 is issued before the softmax of tile j is awaited, so the
-// tensor core works on S[j+1] and P.V[j-1] while the threads run the softmax of tile j. A K slot is
-// refilled as soon as its S product is done, a V slot as soon as its P.V product is done.
-// Warps 0-7 are the softmax/epilogue warps: warps w and w+4 share TMEM lanes 32w..32w+31 and each
-// thread of the pair owns half of the 64 key columns of its row (they exchange the row maximum through
-// shared memory once per tile and their partial denominators once at the end); one thread of warp 8
-// issues the MMAs and one thread of warp 9 the TMA loads, so that neither waits behind the other.
+// {64 dims, G heads, 128/G tokens}. Keys stream in tiles of 128:
+//   S[128,128] = Q[128,256] . K^T        tcgen05.mma, Q and K from shared memory, S in TMEM. K arrives as four
+//                64-dim slabs (16 KB) through a ring of five slab slots; the products of a slab are issued as
+//                soon as it lands and the slot is handed back when they are done, so the loads run about a tile
+//                ahead of the tensor core with 80 KB of shared memory instead of two whole K tiles
+//   softmax    : threads r and r+128 own row r, 64 key columns each: tcgen05.ld S, base-2 online softmax with
+//                a lazy rescale (O is only rescaled when the running max grows by more than 2^8), P -> bf16
+//                written back over S in TMEM. The scores stay unscaled in registers: the maximum is taken on
+//                them and 1/sqrt(d)*log2(e) rides in the multiply-add in front of ex2.approx.ftz; only a
+//                partial last tile pays for the column mask (11 -> ~7 instructions per score)
+//   O[128,256] += P[128,128] . V[128,256] tcgen05.mma, P as the TMEM A operand, V (one 64 KB slot, refilled as
+//                soon as the product that read it is done) as an MN-major shared-memory operand, O in TMEM
+// S is double-buffered in TMEM (2 x 128 columns beside the 256 of O): S of tile j+1 is issued before the softmax
+// of tile j is awaited, so the tensor core works on S[j+1] and P.V[j-1] while the threads run the softmax of
+// tile j. With 128-key tiles every S instruction is 128 x 128 x 16 (the 64-wide ones ran at about a third of
+// their nominal rate) and the per-tile costs of the softmax (barrier waits, the exchange of the row maximum
+// between the two threads of a row, TMEM load/store round trips) are paid half as often.
+// Warps 0-7 are the softmax/epilogue warps: warps w and w+4 share TMEM lanes 32w..32w+31 (they exchange the row
+// maximum through shared memory once per tile and their partial denominators once at the end); one thread of
+// warp 8 issues the MMAs, one of warp 9 loads Q and the K slabs, one of warp 10 the V tiles, so that no wait
+// sits behind another.
 // All waits are bounded; a wait that gives up raises the error word and the CTA drains and exits.
 #include <cuda.h>
 
@@ -35,19 +41,26 @@
 namespace atc {
 using namespace tcc;
 
-constexpr int HD = 256, KT = 64, NKB = HD / 64;
+constexpr int HD = 256, KT = 128, NKB = HD / 64;
 constexpr uint32_t Q_KB_BYTES = 128 * 128, Q_BYTES = NKB * Q_KB_BYTES;          // 64 KB
-constexpr uint32_t KV_CHUNK = KT * 128, K_BYTES = NKB * KV_CHUNK, V_BYTES = K_BYTES;  // 32 KB each
-constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;                              // 64 KB
-constexpr uint32_t P_BYTES = 128 * 128;                                          // 16 KB
+constexpr uint32_t KV_CHUNK = KT * 128;                                         // one 64-dim slab of a K or V tile: 16 KB
+constexpr int K_SLOTS = 5;                                                       // ring of K slabs (a K tile is NKB = 4 slabs)
+constexpr uint32_t K_RING_BYTES = K_SLOTS * KV_CHUNK, V_BYTES = NKB * KV_CHUNK;  // 80 KB, 64 KB
 constexpr uint32_t XCH_BYTES = 2 * 256 * 4;  // row-maximum exchange, two sets of 2 x 128 floats
-constexpr uint32_t SMEM_BYTES = Q_BYTES + 2 * STAGE_BYTES + P_BYTES + XCH_BYTES + 256 + 1024;
-constexpr int NUM_THREADS = 320;
-constexpr int ISSUER_WARP = 8, LOADER_WARP = 9;
-constexpr uint32_t O_COL = 0, S_COL = 256, Q_COL = 384;  // O 256 columns, S 2 x 64, Q 128 (bf16 pairs)
+constexpr uint32_t SMEM_BYTES = Q_BYTES + K_RING_BYTES + V_BYTES + XCH_BYTES + 256 + 1024;
+constexpr int NUM_THREADS = 352;
+constexpr int ISSUER_WARP = 8, K_LOADER_WARP = 9, V_LOADER_WARP = 10;
+constexpr uint32_t O_COL = 0, S_COL = 256;  // O 256 columns, S 2 x 128
 constexpr uint32_t IDESC_QK = umma_idesc(128, KT, 0);
 constexpr uint32_t IDESC_PV = umma_idesc(128, HD, 1);
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+// 2^x by the special-function unit alone (inputs below -126 give 0, which is what a masked or far-away key should weigh)
+__device__ __forceinline__ float ex2_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct Params {
   const int32_t* cu;       // [B+1] packed sequence offsets
@@ -88,13 +101,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
   uint8_t* smem = smem_raw + pad;
   const uint32_t q_base = raw + pad;
-  const uint32_t st_base = q_base + Q_BYTES;
-  const uint32_t p_base = st_base + 2 * STAGE_BYTES;
-  const uint32_t bars = p_base + P_BYTES + XCH_BYTES;
-  uint8_t* p_ptr = smem + Q_BYTES + 2 * STAGE_BYTES;
-  float* xch = reinterpret_cast<float*>(p_ptr + P_BYTES);
-  uint8_t* bars_ptr = p_ptr + P_BYTES + XCH_BYTES;
-  const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 72;  // bar_k/v/s/p: 2 each
+  const uint32_t k_base = q_base + Q_BYTES;
+  const uint32_t v_base = k_base + K_RING_BYTES;
+  const uint32_t bars = v_base + V_BYTES + XCH_BYTES;
+  float* xch = reinterpret_cast<float*>(smem + Q_BYTES + K_RING_BYTES + V_BYTES);
+  uint8_t* bars_ptr = smem + Q_BYTES + K_RING_BYTES + V_BYTES + XCH_BYTES;
+  // bar_s / bar_p: two each (by tile parity); k_full / k_empty: one pair per K slab slot
+  const uint32_t bar_q = bars, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 72;
+  const uint32_t k_full = bars + 128, k_empty = bars + 128 + 8 * K_SLOTS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 80);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 84);
 
@@ -102,17 +116,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_k + 8, 1);
     mbar_init(bar_v, 1);
-    mbar_init(bar_v + 8, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_s + 8, 1);
     mbar_init(bar_p, 256);
     mbar_init(bar_p + 8, 256);
     mbar_init(bar_o, 1);
     for (int i = 0; i < 4; ++i) mbar_init(bars + 88 + 8 * i, 64);  // one per pair of softmax warps
-    mbar_init(bars + 120, 256);                                    // Q copied to TMEM
+    for (int i = 0; i < K_SLOTS; ++i) {
+      mbar_init(k_full + 8 * i, 1);
+      mbar_init(k_empty + 8 * i, 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -135,66 +149,55 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == LOADER_WARP) {
+  if (warp == K_LOADER_WARP) {
     if (lane == 0) {
-      // ---- TMA loader: Q once; K[j+2] as soon as S[j] is done, V[j+1] as soon as P.V[j-1] is done ---------------
-      auto load_k = [&](int j) {
-        const int s = j & 1;
-        const uint32_t kdst = st_base + s * STAGE_BYTES, bar = bar_k + 8 * s;
-        mbar_expect_tx(bar, K_BYTES);
-        const bool st = j < n_st;
-        const CUtensorMap* mk = st ? &tmKs : &tmKo;
-        const int row0 = st ? j * KT : off + (j - n_st) * KT;
-#pragma unroll
-        for (int c = 0; c < NKB; ++c) tma_load_2d(kdst + c * KV_CHUNK, mk, bar, kh * HD + c * 64, row0);
-      };
-      auto load_v = [&](int j) {
-        const int s = j & 1;
-        const uint32_t vdst = st_base + s * STAGE_BYTES + K_BYTES, bar = bar_v + 8 * s;
-        mbar_expect_tx(bar, V_BYTES);
-        const bool st = j < n_st;
-        const CUtensorMap* mv = st ? &tmVs : &tmVo;
-        const int row0 = st ? j * KT : off + (j - n_st) * KT;
-#pragma unroll
-        for (int c = 0; c < NKB; ++c) tma_load_2d(vdst + c * KV_CHUNK, mv, bar, kh * HD + c * 64, row0);
-      };
+      // ---- K loader: Q once, then the K slabs (tile j, 64-dim slab c) through a ring that runs ahead of the S products --
       mbar_expect_tx(bar_q, (uint32_t)(NKB * TT * G * 128));
 #pragma unroll
       for (int c = 0; c < NKB; ++c) tma_load_3d(q_base + c * Q_KB_BYTES, &tmQ, bar_q, c * 64, kh * G, off + t0);
-      load_k(0);
-      load_v(0);
-      if (n_tiles > 1) {
-        load_k(1);
-        load_v(1);
+      bool ok = true;
+      const int n_slabs = n_tiles * NKB;
+      for (int i = 0; i < n_slabs && ok; ++i) {
+        const int slot = i % K_SLOTS, use = i / K_SLOTS, j = i / NKB, c = i % NKB;
+        if (use >= 1 && !(ok = mbar_wait(k_empty + 8 * slot, (uint32_t)((use - 1) & 1), abort_flag))) break;
+        const bool st = j < n_st;
+        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+        mbar_expect_tx(k_full + 8 * slot, KV_CHUNK);
+        tma_load_2d(k_base + slot * KV_CHUNK, st ? &tmKs : &tmKo, k_full + 8 * slot, kh * HD + c * 64, row0);
       }
+    }
+  } else if (warp == V_LOADER_WARP) {
+    if (lane == 0) {
+      // ---- V loader: one tile slot, refilled as soon as the P.V product that read it is done ----------------------------
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 2 < n_tiles) {
-          if (!(ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag))) break;  // S[j] done: its K slot is free
-          load_k(j + 2);
-        }
-        if (j >= 1 && j + 1 < n_tiles) {
-          if (!(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;  // P.V of tile j-1 done: its V slot is free
-          load_v(j + 1);
-        }
+        if (j >= 1 && !(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
+        const bool st = j < n_st;
+        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+        mbar_expect_tx(bar_v, V_BYTES);
+#pragma unroll
+        for (int c = 0; c < NKB; ++c) tma_load_2d(v_base + c * KV_CHUNK, st ? &tmVs : &tmVo, bar_v, kh * HD + c * 64, row0);
       }
     }
   } else if (warp == ISSUER_WARP) {
     if (lane == 0) {
       // ---- MMA issuer --------------------------------------------------------------------------------------------
-      auto issue_s = [&](int j) {  // S[j] = Q K[j]^T into S buffer j & 1
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      auto issue_s = [&](int j) {  // S[j] = Q K[j]^T into S buffer j & 1, one 64-dim slab at a time as the slabs land
         const int s = j & 1;
-        const uint32_t kb_base = st_base + s * STAGE_BYTES;
-#pragma unroll
-        for (int c = 0; c < NKB; ++c) {
-          const uint64_t dk = umma_desc(kb_base + c * KV_CHUNK, 16, 1024);
+        for (int c = 0; c < NKB && ok; ++c) {
+          const int i = j * NKB + c, slot = i % K_SLOTS, use = i / K_SLOTS;
+          if (!(ok = mbar_wait(k_full + 8 * slot, (uint32_t)(use & 1), abort_flag))) break;
+          tc_fence_after();
+          const uint64_t dq = umma_desc(q_base + c * Q_KB_BYTES, 16, 1024);
+          const uint64_t dk = umma_desc(k_base + slot * KV_CHUNK, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ts(tmem_base + S_COL + s * KT, tmem_base + Q_COL + c * 32 + k * 8, dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_base + S_COL + s * KT, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+          umma_commit_to(k_empty + 8 * slot);  // the slab can be refilled once these products are done
         }
-        umma_commit_to(bar_s + 8 * s);
+        if (ok) umma_commit_to(bar_s + 8 * s);
       };
-      bool ok = mbar_wait(bars + 120, 0, abort_flag) && mbar_wait(bar_k, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -202,14 +205,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
         if (j + 1 < n_tiles) {  // S of the next tile goes to the tensor core before this tile's softmax is awaited
-          if (!(ok = mbar_wait(bar_k + 8 * (s ^ 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag))) break;
-          tc_fence_after();
           issue_s(j + 1);
+          if (!ok) break;
         }
         if (!(ok = mbar_wait(bar_p + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
-        if (!(ok = mbar_wait(bar_v + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
+        if (!(ok = mbar_wait(bar_v, (uint32_t)(j & 1), abort_flag))) break;
         tc_fence_after();
-        const uint64_t dv = umma_desc(st_base + s * STAGE_BYTES + K_BYTES, KV_CHUNK, 1024);
+        const uint64_t dv = umma_desc(v_base, KV_CHUNK, 1024);
 #pragma unroll
         for (int k = 0; k < KT / 16; ++k)  // P[j] sits over S[j]: 16 keys = 8 packed columns per step
           umma_f16_ts(tmem_base + O_COL, tmem_base + S_COL + s * KT + k * 8, dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
@@ -224,46 +226,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint32_t pair_phase = 0;
     constexpr int HK = KT / 2;                 // key columns per thread
     float m_used = -INFINITY, l = 0.f;         // l: this thread's part of the denominator
-    // ---- Q row r into TMEM, 128 head dims per thread of the pair (chunk i of a row sits at i ^ (r & 7)) -------------
-    bool ok = mbar_wait(bar_q, 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-#pragma unroll 1
-      for (int c = 2 * h; c < 2 * h + 2; ++c) {
-        uint32_t v[32];
-        const uint8_t* qrow = smem + c * Q_KB_BYTES + r * 128;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 q4 = *reinterpret_cast<const uint4*>(qrow + ((i ^ (r & 7)) << 4));
-          v[4 * i] = q4.x;
-          v[4 * i + 1] = q4.y;
-          v[4 * i + 2] = q4.z;
-          v[4 * i + 3] = q4.w;
-        }
-        tmem_st32(tmem_base + lane_addr + Q_COL + c * 32, v);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(bars + 120);
-    }
+    bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int valid = j < n_st ? min(KT, p.n_state - j * KT) : min(KT, L - (j - n_st) * KT);
       ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      // raw scores stay unscaled: the row maximum is taken on them (the scale is positive) and the scale is folded
+      // into the exponent's multiply-add; only a partial last tile pays for the column mask
       float x[HK];
       {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * HK, v);
+        uint32_t v[HK];
+        tmem_ld32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * HK, &v[0]);
+        tmem_ld32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * HK + 32, &v[32]);
         tmem_ld_wait();
+        if (valid == KT) {
 #pragma unroll
-        for (int i = 0; i < HK; ++i) x[i] = h * HK + i < valid ? __uint_as_float(v[i]) * p.scale_log2e : -INFINITY;
+          for (int i = 0; i < HK; ++i) x[i] = __uint_as_float(v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < HK; ++i) x[i] = h * HK + i < valid ? __uint_as_float(v[i]) : -INFINITY;
+        }
       }
       float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < HK; ++i) t4[i & 3] = fmaxf(t4[i & 3], x[i]);
-      float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
+      float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * p.scale_log2e;
       float* xs = xch + (j & 1) * 256;
       xs[h * 128 + r] = tmax;
       mbar_arrive(pair_bar);
@@ -298,14 +287,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // its S values in registers since before the exchange); the denominator sums the rounded values
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t w[HK / 2];
+      const float neg_m = -m_used;
 #pragma unroll
       for (int i = 0; i < HK / 2; ++i) {
-        const __nv_bfloat162 pr = __floats2bfloat162_rn(exp2f(x[2 * i] - m_used), exp2f(x[2 * i + 1] - m_used));
-        l4[i & 3] += __low2float(pr) + __high2float(pr);
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(ex2_ftz(fmaf(x[2 * i], p.scale_log2e, neg_m)), ex2_ftz(fmaf(x[2 * i + 1], p.scale_log2e, neg_m)));
         w[i] = *reinterpret_cast<const uint32_t*>(&pr);
+        l4[i & 3] += __uint_as_float(w[i] << 16) + __uint_as_float(w[i] & 0xffff0000u);
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      tmem_st16(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * (HK / 2), w);
+      tmem_st32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * (HK / 2), w);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_p + 8 * (j & 1));
