@@ -336,7 +336,9 @@ def test_readout_f32(G, oracle):
     np.testing.assert_allclose(G.host(out), oracle.k_gemm(x, W, False), rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("lens,S", [([1, 15, 16, 33], 70), ([130, 21, 22, 64, 65], 200), ([300], 0), ([5, 40], 64)])
+@pytest.mark.parametrize("lens,S", [([1, 15, 16, 33], 70), ([130, 21, 22, 64, 65], 200), ([300], 0), ([5, 40], 64),
+                                    # around the 128-key tile edges: full tiles only, one key short, one key over, several state tiles
+                                    ([127, 128, 129], 128), ([1, 256, 257], 255), ([40, 3], 385), ([128], 0)])
 def test_attention_tcgen05_vs_oracle(G, oracle, lens, S):
     """The tensor-core attention kernel (d3 shape: 24 query heads, 4 KV heads, head_dim 256) over
     [state || own] keys for a ragged packed batch, and as state self-attention (S = 0)."""
