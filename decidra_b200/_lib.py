@@ -106,6 +106,16 @@ SIGNATURES = {
     "dcd_ticket_cancel": (None, [P]),
     "dcd_ticket_free": (None, [P]),
     "dcd_scheduler_stats": (I, [P, C.POINTER(SchedStats)]),
+    "dcd_prompt_last_error": (C.c_char_p, []),
+    "dcd_format_float": (I, [C.c_double, P, SZ, C.POINTER(SZ)]),
+    "dcd_pyjson_dumps": (I, [C.c_char_p, SZ, P, SZ, C.POINTER(SZ)]),
+    "dcd_pyjson_repr": (I, [C.c_char_p, SZ, I, P, SZ, C.POINTER(SZ)]),
+    "dcd_pyjson_truthy": (I, [C.c_char_p, SZ, C.POINTER(C.c_int)]),
+    "dcd_d3_parse_question": (I, [C.c_char_p, SZ, P, SZ, C.POINTER(SZ)]),
+    "dcd_d3_render": (I, [C.c_char_p, SZ, C.c_char_p, SZ, C.POINTER(C.c_char_p), SZ, P, SZ, C.POINTER(SZ)]),
+    "dcd_d3_state_end_char": (I, [C.c_char_p, SZ, C.c_char_p, SZ, C.POINTER(SZ)]),
+    "dcd_d3_state_token_count": (I, [C.POINTER(SZ), SZ, SZ, C.POINTER(SZ)]),
+    "dcd_d3_contains_media": (I, [C.c_char_p, SZ, C.POINTER(C.c_int)]),
     "dcd_rebind_blas": (I, [P]),
     "dcd_capture_state": (I, [P, U32P, SZ, P, C.POINTER(P)]),
     "dcd_readout_state_once_batch": (I, [P, P, C.POINTER(U32P), C.POINTER(SZ), SZ, FP]),

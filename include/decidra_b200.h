@@ -228,6 +228,37 @@ DCD_API void dcd_ticket_cancel(dcd_ticket* t); /* the client went away: a still-
 DCD_API void dcd_ticket_free(dcd_ticket* t);
 DCD_API int dcd_scheduler_stats(const dcd_scheduler* s, dcd_sched_stats* out);
 
+/* ---- prompt contract -------------------------------------------------------- */
+
+/* Text-producing calls share one convention: `out` receives a NUL-terminated UTF-8 string when cap > length;
+ * *needed (may be NULL) is always set to the length without the NUL, so a caller can size a second call; a buffer
+ * that is too small returns DCD_E_INVALID. JSON documents are passed as UTF-8 text (object order is kept).
+ * Failure texts: dcd_prompt_last_error(). No device is touched. */
+DCD_API const char* dcd_prompt_last_error(void);
+/* pyjson::format_float (src/pyjson.rs:83-165): CPython's repr of a double. */
+DCD_API int dcd_format_float(double value, char* out, size_t cap, size_t* needed);
+/* pyjson::dumps (src/pyjson.rs:13-55): byte for byte json.dumps(value, ensure_ascii=False). */
+DCD_API int dcd_pyjson_dumps(const char* json, size_t n, char* out, size_t cap, size_t* needed);
+/* pyjson::py_repr / py_str (src/pyjson.rs:167-217): Python repr(); as_str != 0 gives str() (a top-level string verbatim). */
+DCD_API int dcd_pyjson_repr(const char* json, size_t n, int as_str, char* out, size_t cap, size_t* needed);
+/* pyjson::py_truthy (src/pyjson.rs:219-229) */
+DCD_API int dcd_pyjson_truthy(const char* json, size_t n, int* truthy);
+/* d3::parse_question (src/d3.rs:325-370) of a /v1/systemone question object; the result is the Question as JSON:
+ * {"kind": "choice"|"noul"|"score", "instructions": "...", "keys": [...], "texts": [...]}. Errors carry the reference's
+ * texts ("a choice question needs criteria", "score criteria must have 2 to 10 levels", ...). */
+DCD_API int dcd_d3_parse_question(const char* question_json, size_t n, char* out, size_t cap, size_t* needed);
+/* d3::parse_question + d3::render (src/d3.rs:85-131): the full prompt, ending where the assistant answer starts.
+ * codes = the option codes in order (the readout's code table); a question may use at most n_codes options. */
+DCD_API int dcd_d3_render(const char* state_json, size_t ns, const char* question_json, size_t nq, const char* const* codes,
+                          size_t n_codes, char* out, size_t cap, size_t* needed);
+/* d3::state_end_char (src/d3.rs:265-277): byte offset in a rendered prompt where the state segment ends. */
+DCD_API int dcd_d3_state_end_char(const char* text, size_t nt, const char* state_json, size_t ns, size_t* end);
+/* d3::state_token_count (src/d3.rs:279-292): offsets = n_tokens (start, stop) pairs from the tokenizer; the number of
+ * leading tokens that end at or before end_char = the state/question split of Engine::capture_state's input. */
+DCD_API int dcd_d3_state_token_count(const size_t* offsets, size_t n_tokens, size_t end_char, size_t* count);
+/* d3::contains_media (src/d3.rs:308-322): states with image/video content are refused by the text path. */
+DCD_API int dcd_d3_contains_media(const char* state_json, size_t ns, int* has_media);
+
 /* ---- checkpoints ----------------------------------------------------------- */
 
 /* safetensors element types (DType::parse, native/src/tensor.rs:25-38). "BOOL" reads as U8,
