@@ -121,6 +121,7 @@ SIGNATURES = {
     "dcd_readout_state_once_batch": (I, [P, P, C.POINTER(U32P), C.POINTER(SZ), SZ, FP]),
     "dcd_readout_state_once_flat": (I, [P, P, U32P, U32P, SZ, FP]),
     "dcd_readout_state_once_device": (I, [P, P, P, P, SZ, SZ, SZ, P]),
+    "dcd_readout_multi_state_batch": (I, [P, C.POINTER(P), SZ, C.POINTER(U32P), C.POINTER(SZ), U32P, SZ, FP]),
     "dcd_capture_state_device": (I, [P, P, SZ, C.POINTER(P)]),
     "dcd_decision_logits_split": (I, [P, U32P, SZ, SZ, FP]),
     "dcd_state_free": (None, [P, P]),

@@ -122,6 +122,7 @@ struct dcd_engine {
   // pinned staging
   uint32_t* h_ids = nullptr;
   int32_t* h_lens = nullptr;
+  int32_t *h_posq = nullptr, *d_posq = nullptr;  // per-question start positions of a pass over several states
   float* h_logits = nullptr;
   int* h_err = nullptr;
 
@@ -338,12 +339,25 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
   return DCD_OK;
 }
 
+// A run of consecutive questions of the packed batch that fork the same state.
+struct Group {
+  const dcd_state* st;
+  int q0, nq;      // questions [q0, q0 + nq)
+  int tok0, ntok;  // their packed tokens [tok0, tok0 + ntok)
+  int max_len;
+};
+
 struct Pass {
   int mode;  // 0 capture, 1 state-once question pass, 2 per-row reference
   int T, B, max_len;
   const dcd_state* cache = nullptr;
   dcd_state* cap = nullptr;
   int split = 0;
+  // mode 1 over several states: the token-parallel kernels (GEMMs, norms, RoPE, GDN preparation) run once over the whole
+  // batch; the kernels that read a state (attention, conv tail, recurrent seed) run once per group on its slice
+  const Group* groups = nullptr;
+  int n_groups = 0;
+  const int32_t* d_posq = nullptr;  // per-question start position (device), with groups
 };
 
 template <typename T>
@@ -371,6 +385,9 @@ int run_layers(dcd_engine* e, const Pass& p) {
       return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an activation operand");
   }
   const size_t xbytes = (size_t)T_ * H * e->esz;
+  const Group whole{p.cache, 0, p.B, 0, T_, p.max_len};
+  const Group* groups = p.n_groups > 0 ? p.groups : &whole;
+  const int n_groups = p.n_groups > 0 ? p.n_groups : 1;
   for (int li = 0; li < c.num_layers; ++li) {
     LayerW& w = e->layers[li];
     if (li == 0) {
@@ -397,25 +414,32 @@ int run_layers(dcd_engine* e, const Pass& p) {
       // Capture keeps nothing of the last layer beyond its cache entries: the reference computes the
       // rest of that layer and discards it (native/src/engine.rs:4616-4763 builds no final norm or readout).
       if (p.mode == 0 && li + 1 == c.num_layers) break;
-      {
-        const int n_state = p.mode == 1 ? (int)p.cache->state_len : 0;
+      for (int gi = 0; gi < n_groups; ++gi) {
+        const Group& g = groups[gi];
+        const int n_state = p.mode == 1 ? (int)g.st->state_len : 0;
         double keys = 0;  // sum over rows of visible keys
-        if (p.mode == 1) keys = (double)T_ * n_state + (double)T_ * p.max_len;  // upper bound on own keys
+        if (p.mode == 1) keys = (double)g.ntok * n_state + (double)g.ntok * g.max_len;  // upper bound on own keys
         else if (p.mode == 0) keys = (double)T_ * T_;
         else keys = (double)p.split * p.split + (double)(T_ - p.split) * T_;
+        const T* ks = p.mode == 1 ? (const T*)g.st->k[li] : nullptr;
+        const T* vs = p.mode == 1 ? (const T*)g.st->v[li] : nullptr;
         Scope sc(e, DCD_PROF_ATTN, 4.0 * heads * hd * keys, 1);
         if (e->attn_tc && p.mode != 2) {
-          AttnTcMaps maps;
-          if (attn_tc_make_maps(&maps, e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? p.cache->k[li] : nullptr,
-                                p.mode == 1 ? p.cache->v[li] : nullptr, n_state, T_, heads, kv, hd))
-            return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an attention operand");
           const int tt = attn_tc_tokens_per_tile(heads, kv);
-          CK(e, attn_tc_launch(&maps, e->d_cu, e->d_tile_cu, p.B, n_state, T_, (T_ + tt - 1) / tt + p.B, heads, kv, hd, big, e->qkv_n,
+          if (n_groups > 1) {  // the tile table is per launch: rebuilt for this group's sequences (same stream, so in order)
+            e->launches += 1;
+            CK(e, attn_tc_build_tiles(e->d_cu + g.q0, g.nq, tt, e->d_tile_cu, s), "attention tiles");
+          }
+          AttnTcMaps maps;
+          if (attn_tc_make_maps(&maps, e->q, kdst, kv * hd, vsrc, e->qkv_n, ks, vs, n_state, T_, heads, kv, hd))
+            return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an attention operand");
+          CK(e, attn_tc_launch(&maps, e->d_cu + g.q0, e->d_tile_cu, g.nq, n_state, T_, (g.ntok + tt - 1) / tt + g.nq, heads, kv, hd, big, e->qkv_n,
                                e->bufA, e->d_err, s), "tcgen05 attention");
         } else {
-          CK(e, launch_attn_fma<T>((const T*)e->q, kdst, kv * hd, vsrc, e->qkv_n, p.mode == 1 ? (const T*)p.cache->k[li] : nullptr,
-                                   p.mode == 1 ? (const T*)p.cache->v[li] : nullptr, n_state, big, e->qkv_n, (T*)e->bufA, e->d_cu,
-                                   e->d_tokq, T_, heads, kv, hd, p.mode == 2 ? p.split : 0, s), "attention");
+          const size_t t0 = (size_t)g.tok0;
+          CK(e, launch_attn_fma<T>((const T*)e->q + t0 * heads * hd, kdst + t0 * kv * hd, kv * hd, vsrc + t0 * e->qkv_n, e->qkv_n, ks, vs, n_state,
+                                   big + t0 * e->qkv_n, e->qkv_n, (T*)e->bufA + t0 * heads * hd, e->d_cu, e->d_tokq + t0, g.ntok, heads, kv, hd,
+                                   p.mode == 2 ? p.split : 0, s, g.tok0), "attention");
         }
       }
       rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, fused_resid ? e->x1 : e->mix, T_, H, heads * hd, H, 0, false,
@@ -435,8 +459,13 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       {
         Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->conv_dim * e->esz * 2.0, 1);
-        CK(e, launch_conv1d_silu<T>(big, e->gin_n, p.mode == 1 ? (const T*)p.cache->hist[li] : nullptr, (const T*)w.conv, (T*)e->conv,
-                                    e->d_cu, e->d_tokq, T_, e->conv_dim, s), "conv1d");
+        e->launches += n_groups - 1;
+        for (int gi = 0; gi < n_groups; ++gi) {
+          const Group& g = groups[gi];
+          const size_t t0 = (size_t)g.tok0;
+          CK(e, launch_conv1d_silu<T>(big + t0 * e->gin_n, e->gin_n, p.mode == 1 ? (const T*)g.st->hist[li] : nullptr, (const T*)w.conv,
+                                      (T*)e->conv + t0 * e->conv_dim, e->d_cu, e->d_tokq + t0, g.ntok, e->conv_dim, s, g.tok0), "conv1d");
+        }
       }
       {
         Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * nk * dk * (2.0 * e->esz + 8.0), 1);
@@ -446,21 +475,25 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       {
         Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
-        const float* seed = p.mode == 1 ? p.cache->gstate[li] : nullptr;
         float* fin = p.mode == 0 ? p.cap->gstate[li] : nullptr;
-        if (e->gdn_tc) {
-          if (e->tm_gdn_tokens != T_) {
-            if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, e->conv, e->conv_dim, e->conv_dim, (int)e->esz, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
-            e->tm_gdn_tokens = T_;
-          }
-          CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, e->d_err, s),
-             "gdn_tc");
-        } else if (e->gdn_chunked)
-          CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv, dk,
-                                      dv, p.B < 2, s), "gdn_chunked");
-        else
-          CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, e->d_cu, p.B, nk, nv,
-                                        dk, dv, p.B < 8, s), "gdn_recurrent");
+        if (e->gdn_tc && e->tm_gdn_tokens != T_) {
+          if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, e->conv, e->conv_dim, e->conv_dim, (int)e->esz, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
+          e->tm_gdn_tokens = T_;
+        }
+        e->launches += n_groups - 1;
+        for (int gi = 0; gi < n_groups; ++gi) {  // sequences index the packed buffers through cu, so a group is a slice of cu
+          const Group& g = groups[gi];
+          const float* seed = p.mode == 1 ? g.st->gstate[li] : nullptr;
+          const int32_t* cu = e->d_cu + g.q0;
+          if (e->gdn_tc)
+            CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, s), "gdn_tc");
+          else if (e->gdn_chunked)
+            CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, dk,
+                                        dv, g.nq < 2, s), "gdn_chunked");
+          else
+            CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv,
+                                          dk, dv, g.nq < 8, s), "gdn_recurrent");
+        }
       }
       if (p.mode == 0 && li + 1 == c.num_layers) break;  // last capture layer: the state and conv tail are stored
       {
@@ -525,8 +558,8 @@ int run_pass(dcd_engine* e, const Pass& p, const uint32_t* d_ids, const int32_t*
   cudaStream_t s = e->stream;
   {
     Scope sc(e, DCD_PROF_ELEMENTWISE, 12.0 * p.T, 2);
-    CK(e, launch_pack(d_lens, p.B, p.T, pos_start, e->d_cu, e->d_last, e->d_tokq, e->d_tokpos, e->d_err, s), "pack");
-    if (e->attn_tc && p.mode != 2) {
+    CK(e, launch_pack(d_lens, p.B, p.T, pos_start, e->d_cu, e->d_last, e->d_tokq, e->d_tokpos, e->d_err, s, p.d_posq), "pack");
+    if (e->attn_tc && p.mode != 2 && p.n_groups <= 1) {
       e->launches += 1;
       CK(e, attn_tc_build_tiles(e->d_cu, p.B, attn_tc_tokens_per_tile(e->c.heads, e->c.kv_heads), e->d_tile_cu, s), "attention tiles");
     }
@@ -925,6 +958,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRA(e->d_logits, (size_t)e->max_batch * c.readout_rows * 4, false, ws);
   CRA(e->d_ids, Tm * 4, false, ws);
   CRA(e->d_lens, (size_t)e->max_batch * 4, false, ws);
+  CRA(e->d_posq, (size_t)e->max_batch * 4, false, ws);
   CRA(e->d_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
   CRA(e->d_last, (size_t)e->max_batch * 4, false, ws);
   CRA(e->d_tile_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
@@ -933,6 +967,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRA(e->d_err, 256, true, ws);
   CRE(cudaMallocHost(&e->h_ids, Tm * 4), "pinned ids");
   CRE(cudaMallocHost(&e->h_lens, (size_t)e->max_batch * 4), "pinned lens");
+  CRE(cudaMallocHost(&e->h_posq, (size_t)e->max_batch * 4), "pinned positions");
   CRE(cudaMallocHost(&e->h_logits, (size_t)e->max_batch * c.readout_rows * 4), "pinned logits");
   CRE(cudaMallocHost(&e->h_err, 64), "pinned err");
   *e->h_err = 0;
@@ -950,6 +985,7 @@ void dcd_engine_destroy(dcd_engine* e) {
   for (void* p : e->allocs) cudaFree(p);
   if (e->h_ids) cudaFreeHost(e->h_ids);
   if (e->h_lens) cudaFreeHost(e->h_lens);
+  if (e->h_posq) cudaFreeHost(e->h_posq);
   if (e->h_logits) cudaFreeHost(e->h_logits);
   if (e->h_err) cudaFreeHost(e->h_err);
   for (auto& pr : e->prof.pairs) { cudaEventDestroy(pr.a); cudaEventDestroy(pr.b); }
@@ -1655,6 +1691,61 @@ int dcd_readout_state_once_flat(dcd_engine* e, const dcd_state* st, const uint32
     off += lens[i];
   }
   return dcd_readout_state_once_batch(e, st, ptrs.data(), ls.data(), B, out);
+}
+
+// One question pass over questions that fork DIFFERENT states. Questions are reordered so that those of one state are
+// consecutive (stable, states in index order); rows come back in input order.
+int dcd_readout_multi_state_batch(dcd_engine* e, const dcd_state* const* states, size_t n_states, const uint32_t* const* questions,
+                                  const size_t* lens, const uint32_t* state_of, size_t B, float* out) {
+  if (!e) return DCD_E_INVALID;
+  if (!states || n_states == 0 || !out) return fail(e, DCD_E_INVALID, "null argument");
+  if (B == 0 || !questions || !lens || !state_of) return fail(e, DCD_E_INVALID, "empty state-once question batch");
+  cudaSetDevice(e->device);
+  if (!e->weights_ready) return fail(e, DCD_E_INVALID, "weights are not loaded");
+  size_t total = 0, mx = 0;
+  for (size_t i = 0; i < B; ++i) {
+    if (lens[i] == 0 || !questions[i]) return fail(e, DCD_E_INVALID, "batch item %zu has no tokens", i);
+    if (state_of[i] >= n_states || !states[state_of[i]]) return fail(e, DCD_E_INVALID, "batch item %zu names state %u of %zu", i, state_of[i], n_states);
+    total += lens[i];
+    if (lens[i] > mx) mx = lens[i];
+  }
+  if (total > (size_t)e->Tm || B > (size_t)e->max_batch)
+    return fail(e, DCD_E_INVALID, "pass of %zu tokens in %zu questions exceeds max_pass_tokens %d: split the call", total, B, e->Tm);
+  std::vector<int32_t> order(B);
+  for (size_t i = 0; i < B; ++i) order[i] = (int32_t)i;
+  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return state_of[a] < state_of[b]; });
+  std::vector<Group> groups;
+  size_t tok = 0;
+  for (size_t n = 0; n < B; ++n) {
+    const size_t i = (size_t)order[n];
+    const dcd_state* st = states[state_of[i]];
+    if (st->pos_end + lens[i] > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "positions exceed the RoPE table");
+    if (groups.empty() || state_of[i] != state_of[(size_t)order[n - 1]]) groups.push_back(Group{st, (int)n, 0, (int)tok, 0, 0});
+    Group& g = groups.back();
+    g.nq += 1;
+    g.ntok += (int)lens[i];
+    if ((int)lens[i] > g.max_len) g.max_len = (int)lens[i];
+    memcpy(e->h_ids + tok, questions[i], lens[i] * 4);
+    e->h_lens[n] = (int32_t)lens[i];
+    e->h_posq[n] = (int32_t)st->pos_end;
+    tok += lens[i];
+  }
+  CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, total * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
+  CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, B * 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
+  CK(e, cudaMemcpyAsync(e->d_posq, e->h_posq, B * 4, cudaMemcpyHostToDevice, e->stream), "positions upload");
+  Pass p{1, (int)total, (int)B, (int)mx};
+  p.cache = groups[0].st;
+  p.groups = groups.data();
+  p.n_groups = (int)groups.size();
+  p.d_posq = e->d_posq;
+  int rc = run_pass_any(e, p, e->d_ids, e->d_lens, 0, e->d_logits);
+  if (rc) return rc;
+  const int R = e->c.readout_rows;
+  CK(e, cudaMemcpyAsync(e->h_logits, e->d_logits, B * R * 4, cudaMemcpyDeviceToHost, e->stream), "logits download");
+  rc = sync_and_check(e);
+  if (rc) return rc;
+  for (size_t n = 0; n < B; ++n) memcpy(out + (size_t)order[n] * R, e->h_logits + n * R, (size_t)R * sizeof(float));
+  return DCD_OK;
 }
 
 int dcd_decision_logits_split(dcd_engine* e, const uint32_t* ids, size_t seq, size_t split, float* out) {

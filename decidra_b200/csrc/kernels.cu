@@ -48,7 +48,7 @@ __global__ void pack_scan_kernel(const int32_t* __restrict__ lens, int B, int32_
   if (tid == nt - 1) cu[B] = part[tid];
 }
 
-__global__ void pack_fill_kernel(const int32_t* __restrict__ cu, int B, int total, int pos_start,
+__global__ void pack_fill_kernel(const int32_t* __restrict__ cu, int B, int total, int pos_start, const int32_t* __restrict__ pos_start_q,
                                  int32_t* __restrict__ tok_q, int32_t* __restrict__ tok_pos) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total) return;
@@ -58,13 +58,13 @@ __global__ void pack_fill_kernel(const int32_t* __restrict__ cu, int B, int tota
     if (cu[mid] <= t) lo = mid; else hi = mid;
   }
   tok_q[t] = lo;
-  tok_pos[t] = pos_start + (t - cu[lo]);
+  tok_pos[t] = (pos_start_q ? pos_start_q[lo] : pos_start) + (t - cu[lo]);  // per question when the batch mixes states
 }
 
 cudaError_t launch_pack(const int32_t* lens, int B, int total, int pos_start, int32_t* cu, int32_t* last_row,
-                        int32_t* tok_q, int32_t* tok_pos, int* err, cudaStream_t s) {
+                        int32_t* tok_q, int32_t* tok_pos, int* err, cudaStream_t s, const int32_t* pos_start_q) {
   pack_scan_kernel<<<1, 1024, 0, s>>>(lens, B, cu, last_row, err);
-  if (total > 0) pack_fill_kernel<<<(total + 255) / 256, 256, 0, s>>>(cu, B, total, pos_start, tok_q, tok_pos);
+  if (total > 0) pack_fill_kernel<<<(total + 255) / 256, 256, 0, s>>>(cu, B, total, pos_start, pos_start_q, tok_q, tok_pos);
   return cudaGetLastError();
 }
 
@@ -636,7 +636,7 @@ __global__ void attn_fma_kernel(const T* __restrict__ q, const T* __restrict__ k
                                 int v_stride, const T* __restrict__ k_state, const T* __restrict__ v_state, int n_state,
                                 const T* __restrict__ gate_qg, int qg_stride, T* __restrict__ out,
                                 const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int tokens, int heads, int kv,
-                                int split) {
+                                int split, int tok_base) {
   constexpr int V = HD / 32;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (idx >= tokens * heads) return;
@@ -644,8 +644,9 @@ __global__ void attn_fma_kernel(const T* __restrict__ q, const T* __restrict__ k
   const int t = idx / heads, h = idx - t * heads;
   const int kh = h / (heads / kv);
   const int qi = tok_q ? tok_q[t] : 0;
-  const int off = cu ? cu[qi] : 0;
-  int len = cu ? cu[qi + 1] - off : tokens;
+  const int off_packed = cu ? cu[qi] : 0;
+  int len = cu ? cu[qi + 1] - off_packed : tokens;
+  const int off = off_packed - tok_base;  // tok_base: packed index of row 0 when q/k/v/out/tok_q point into a larger batch
   if (split > 0 && t < split) len = split;
   const float scale = 1.0f / sqrtf((float)HD);
   float qv[V], acc[V];
@@ -719,13 +720,13 @@ __global__ void attn_fma_kernel(const T* __restrict__ q, const T* __restrict__ k
 template <typename T>
 cudaError_t launch_attn_fma(const T* q, const T* k_own, int k_stride, const T* v_own, int v_stride, const T* k_state,
                             const T* v_state, int n_state, const T* gate_qg, int qg_stride, T* out, const int32_t* cu,
-                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s) {
+                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s, int tok_base) {
   const int n = tokens * heads;
   const int grid = (n + 3) / 4;
 #define AT_CASE(HD_)                                                                                                      \
   case HD_:                                                                                                               \
     attn_fma_kernel<T, HD_><<<grid, 128, 0, s>>>(q, k_own, k_stride, v_own, v_stride, k_state, v_state, n_state, gate_qg, \
-                                                 qg_stride, out, cu, tok_q, tokens, heads, kv, split);                   \
+                                                 qg_stride, out, cu, tok_q, tokens, heads, kv, split, tok_base);         \
     break;
   switch (hd) {
     AT_CASE(64)
@@ -736,8 +737,8 @@ cudaError_t launch_attn_fma(const T* q, const T* k_own, int k_stride, const T* v
 #undef AT_CASE
   return cudaGetLastError();
 }
-template cudaError_t launch_attn_fma<float>(const float*, const float*, int, const float*, int, const float*, const float*, int, const float*, int, float*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t);
-template cudaError_t launch_attn_fma<bf16>(const bf16*, const bf16*, int, const bf16*, int, const bf16*, const bf16*, int, const bf16*, int, bf16*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t);
+template cudaError_t launch_attn_fma<float>(const float*, const float*, int, const float*, int, const float*, const float*, int, const float*, int, float*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t, int);
+template cudaError_t launch_attn_fma<bf16>(const bf16*, const bf16*, int, const bf16*, int, const bf16*, const bf16*, int, const bf16*, int, bf16*, const int32_t*, const int32_t*, int, int, int, int, int, cudaStream_t, int);
 
 // ---------------------------------------------------------------------------
 // Depthwise causal conv (4 taps) + SiLU over a packed batch; taps before a sequence start
@@ -748,11 +749,11 @@ template cudaError_t launch_attn_fma<bf16>(const bf16*, const bf16*, int, const 
 template <typename T>
 __global__ void conv1d_silu_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ hist, const T* __restrict__ w,
                                    T* __restrict__ out, const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q,
-                                   int ch) {
+                                   int ch, int tok_base) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= ch) return;
   const int t = blockIdx.y;
-  const int off = cu ? cu[tok_q[t]] : 0;
+  const int off = cu ? cu[tok_q[t]] - tok_base : 0;  // tok_base: packed index of row 0 when x/out/tok_q point into a larger batch
   const int lt = t - off;
   float xs[4];
 #pragma unroll
@@ -780,14 +781,14 @@ constexpr int CONV_TT = 8;
 __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __restrict__ x, int x_stride, const bf16* __restrict__ hist,
                                                                const bf16* __restrict__ w, bf16* __restrict__ out,
                                                                const int32_t* __restrict__ cu, const int32_t* __restrict__ tok_q, int ch,
-                                                               int tokens) {
+                                                               int tokens, int tok_base) {
   const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
   if (c8 * 8 >= ch) return;
   const int c = c8 * 8;
   const int t_begin = blockIdx.y * CONV_TT, t_end = min(t_begin + CONV_TT, tokens);
   int offs[CONV_TT];
 #pragma unroll
-  for (int i = 0; i < CONV_TT; ++i) offs[i] = cu ? cu[tok_q[min(t_begin + i, tokens - 1)]] : 0;
+  for (int i = 0; i < CONV_TT; ++i) offs[i] = cu ? cu[tok_q[min(t_begin + i, tokens - 1)]] - tok_base : 0;
   uint4 xr[CONV_TT + 3];
 #pragma unroll
   for (int k = 0; k < CONV_TT + 3; ++k) {
@@ -850,20 +851,20 @@ __global__ void __launch_bounds__(128) conv1d_silu_vec8_kernel(const bf16* __res
 
 template <typename T>
 cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T* w, T* out, const int32_t* cu,
-                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s) {
+                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s, int tok_base) {
   if constexpr (sizeof(T) == 2) {
     if ((ch % 8) == 0 && (x_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
       dim3 gridv((ch / 8 + 127) / 128, (tokens + CONV_TT - 1) / CONV_TT);
-      conv1d_silu_vec8_kernel<<<gridv, 128, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch, tokens);
+      conv1d_silu_vec8_kernel<<<gridv, 128, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch, tokens, tok_base);
       return cudaGetLastError();
     }
   }
   dim3 grid((ch + 255) / 256, tokens);
-  conv1d_silu_kernel<T><<<grid, 256, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch);
+  conv1d_silu_kernel<T><<<grid, 256, 0, s>>>(x, x_stride, hist, w, out, cu, tok_q, ch, tok_base);
   return cudaGetLastError();
 }
-template cudaError_t launch_conv1d_silu<float>(const float*, int, const float*, const float*, float*, const int32_t*, const int32_t*, int, int, cudaStream_t);
-template cudaError_t launch_conv1d_silu<bf16>(const bf16*, int, const bf16*, const bf16*, bf16*, const int32_t*, const int32_t*, int, int, cudaStream_t);
+template cudaError_t launch_conv1d_silu<float>(const float*, int, const float*, const float*, float*, const int32_t*, const int32_t*, int, int, cudaStream_t, int);
+template cudaError_t launch_conv1d_silu<bf16>(const bf16*, int, const bf16*, const bf16*, bf16*, const int32_t*, const int32_t*, int, int, cudaStream_t, int);
 
 // ---------------------------------------------------------------------------
 // GDN prepare (compact form): per (token, key head) L2-normalised q (also scaled by

@@ -6,7 +6,7 @@
 #include <stdint.h>
 
 cudaError_t launch_pack(const int32_t* lens, int B, int total, int pos_start, int32_t* cu, int32_t* last_row, int32_t* tok_q,
-                        int32_t* tok_pos, int* err, cudaStream_t s);
+                        int32_t* tok_pos, int* err, cudaStream_t s, const int32_t* pos_start_q = nullptr);
 template <typename T>
 cudaError_t launch_embed(const T* table, const uint32_t* ids, T* out, int rows, int H, int vocab, int* err, cudaStream_t s);
 template <typename T>
@@ -36,10 +36,10 @@ cudaError_t launch_qk_norm_rope(const T* qg, int qg_stride, const T* kraw, int k
 template <typename T>
 cudaError_t launch_attn_fma(const T* q, const T* k_own, int k_stride, const T* v_own, int v_stride, const T* k_state,
                             const T* v_state, int n_state, const T* gate_qg, int qg_stride, T* out, const int32_t* cu,
-                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s);
+                            const int32_t* tok_q, int tokens, int heads, int kv, int hd, int split, cudaStream_t s, int tok_base = 0);
 template <typename T>
 cudaError_t launch_conv1d_silu(const T* x, int x_stride, const T* hist, const T* w, T* out, const int32_t* cu,
-                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s);
+                               const int32_t* tok_q, int tokens, int ch, cudaStream_t s, int tok_base = 0);
 template <typename T>
 cudaError_t launch_gdn_prepare(const T* conv, int conv_stride, const T* b, const T* a, int ba_stride, const float* A_log,
                                const float* dt_bias, float* qf, float* kf, float* g, float* beta, int tokens, int nk, int nv,

@@ -179,6 +179,20 @@ class Engine:
         self._check(_lib.load().dcd_readout_state_once_batch(self._h, cache._h, ptrs, lens, B, out.ctypes.data_as(_lib.FP)))
         return out
 
+    def readout_multi_state_batch(self, caches: Sequence[StateCache], questions: Sequence[Sequence[int]], state_of: Sequence[int]) -> np.ndarray:
+        """One pass over questions of several states: ``state_of[i]`` indexes ``caches``. Rows equal those of
+        ``readout_state_once_batch`` per state, bit for bit; [B, readout_rows] f32 in input order."""
+        B = len(questions)
+        arrs = [_u32(q) for q in questions]
+        ptrs = (_lib.U32P * max(B, 1))(*[a.ctypes.data_as(_lib.U32P) for a in arrs])
+        lens = (C.c_size_t * max(B, 1))(*[a.size for a in arrs])
+        handles = (C.c_void_p * max(len(caches), 1))(*[c._h.value for c in caches])
+        sof = _u32(state_of)
+        out = np.empty((B, self.cfg.readout_rows), dtype=np.float32)
+        self._check(_lib.load().dcd_readout_multi_state_batch(self._h, handles, len(caches), ptrs, lens, sof.ctypes.data_as(_lib.U32P), B,
+                                                              out.ctypes.data_as(_lib.FP)))
+        return out
+
     def decision_logits_split(self, tokens: Sequence[int], split: int) -> np.ndarray:
         """``Engine::decision_logits_split`` (native/src/engine.rs:4585-4601): per-row reference."""
         ids = _u32(tokens)

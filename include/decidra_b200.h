@@ -333,6 +333,15 @@ DCD_API int dcd_readout_state_once_device(dcd_engine* e, const dcd_state* st, co
                                           const int32_t* d_lens, size_t B, size_t total, size_t max_len, float* d_out);
 /* Device-resident capture: d_ids[n] in HBM; no host copies; the state is valid after the
  * engine stream reaches this point. */
+/* One question pass over questions of SEVERAL states (the reference serves one state per pass and lists the cross-state
+ * pass as future work, docs/ENGINE.md:454-456; a scheduler with many small groups waiting wants it). state_of[i] names the
+ * state of question i. Every question attends to its own state's cache plus its own block and continues that state's
+ * recurrent state, conv tail and positions; rows are bit-identical to those of dcd_readout_state_once_batch called per
+ * state. The token-parallel kernels (projections, MLP, norms) run once over the whole batch; the kernels that read a state
+ * run once per state on its slice of the batch. The whole batch must fit one pass (max_pass_tokens). */
+DCD_API int dcd_readout_multi_state_batch(dcd_engine* e, const dcd_state* const* states, size_t n_states,
+                                          const uint32_t* const* questions, const size_t* lens, const uint32_t* state_of, size_t B,
+                                          float* out);
 DCD_API int dcd_capture_state_device(dcd_engine* e, const uint32_t* d_ids, size_t n, dcd_state** out);
 
 /* Engine::decision_logits_split (native/src/engine.rs:4585-4601; self-test use at

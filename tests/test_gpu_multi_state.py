@@ -1,0 +1,71 @@
+"""One question pass over questions of several states: rows must equal, bit for bit, those of one
+`readout_state_once_batch` call per state (same kernels, same per-row arithmetic; only the batching differs)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _mixed(cfg_vocab, rng, state_lens, n_questions, qlo, qhi):
+    states = [rng.integers(0, cfg_vocab, n, dtype=np.uint32) for n in state_lens]
+    state_of = rng.integers(0, len(states), n_questions).astype(np.uint32)
+    state_of[: len(states)] = np.arange(len(states))          # every state gets at least one question
+    rng.shuffle(state_of)
+    questions = [rng.integers(0, cfg_vocab, int(n), dtype=np.uint32) for n in rng.integers(qlo, qhi + 1, n_questions)]
+    return states, state_of, questions
+
+
+def _check(e, states, state_of, questions):
+    caches = [e.capture_state(s) for s in states]
+    got = e.readout_multi_state_batch(caches, questions, state_of)
+    assert got.shape == (len(questions), e.cfg.readout_rows) and np.isfinite(got).all()
+    for k, c in enumerate(caches):
+        idx = [i for i in range(len(questions)) if state_of[i] == k]
+        want = e.readout_state_once_batch(c, [questions[i] for i in idx])
+        assert got[idx].tobytes() == want.tobytes(), k
+    # the answers depend on the state: two states give different rows for the same question
+    if len(states) > 1:
+        a = e.readout_state_once_batch(caches[0], [questions[0]])
+        b = e.readout_state_once_batch(caches[1], [questions[0]])
+        assert not np.array_equal(a, b)
+    return got
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_multi_state_pass_tiny(dcd, dtype):
+    """Tiny configuration: the FMA attention, chunked / sequential GDN and scalar conv kernels on group slices."""
+    cfg = dcd.tiny_config(dtype)
+    o = dcd.Options()
+    o.max_pass_tokens = 1024
+    e = dcd.Engine(cfg, o)
+    e.init_random(0)
+    rng = np.random.default_rng(21)
+    states, state_of, questions = _mixed(cfg.vocab, rng, [128, 37, 2, 200], 19, 1, 40)
+    _check(e, states, state_of, questions)
+    # one state only, and a state that no question names
+    _check(e, states[:1], np.zeros(5, np.uint32), questions[:5])
+    caches = [e.capture_state(s) for s in states[:3]]
+    got = e.readout_multi_state_batch(caches, questions[:4], [2, 2, 0, 2])
+    want = e.readout_state_once_batch(caches[2], [questions[0], questions[1], questions[3]])
+    assert got[[0, 1, 3]].tobytes() == want.tobytes()
+    with pytest.raises(dcd.EngineError, match="names state 3 of 3"):
+        e.readout_multi_state_batch(caches, questions[:2], [0, 3])
+    with pytest.raises(dcd.EngineError, match="has no tokens"):
+        e.readout_multi_state_batch(caches, [questions[0], []], [0, 1])
+    with pytest.raises(dcd.EngineError, match="split the call"):
+        e.readout_multi_state_batch(caches, [rng.integers(0, cfg.vocab, 600, dtype=np.uint32)] * 2, [0, 1])
+    e.close()
+
+
+def test_multi_state_pass_d3_slice(dcd):
+    """d3-shaped 4-layer slice: the tcgen05 attention (per-group tile tables and state descriptors), the tcgen05 GDN
+    (per-group seed) and the vectorised conv on group slices; state lengths on both sides of the 128-key tile."""
+    cfg = dcd.d3_config(num_layers=4, vocab=4096)
+    o = dcd.Options()
+    o.max_pass_tokens = 4096
+    e = dcd.Engine(cfg, o)
+    e.init_random(3)
+    rng = np.random.default_rng(5)
+    states, state_of, questions = _mixed(cfg.vocab, rng, [300, 128, 65, 513], 24, 17, 150)
+    _check(e, states, state_of, questions)
+    e.close()
