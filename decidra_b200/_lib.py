@@ -30,7 +30,7 @@ class SchedOptions(C.Structure):
     _fields_ = [
         ("max_queue", C.c_int32), ("batch_requests", C.c_int32), ("batch_rows", C.c_int32), ("batch_window_us", C.c_int64),
         ("state_cache_entries", C.c_int32), ("pin_cache", C.c_int32), ("state_cache_bytes", C.c_int64),
-        ("host_state_cache_bytes", C.c_int64), ("sched_priority", C.c_int32), ("reserved0", C.c_int32),
+        ("host_state_cache_bytes", C.c_int64), ("sched_priority", C.c_int32), ("cross_state_pass", C.c_int32),
         ("submit_timeout_us", C.c_int64), ("reserved", C.c_int64 * 4),
     ]
 
@@ -44,6 +44,8 @@ OP_FREE = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
 OP_MEM = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t))
 OP_ERR = C.CFUNCTYPE(C.c_void_p, C.c_void_p)  # returns the address of a NUL-terminated buffer the callee keeps alive
 OP_SIZE = C.CFUNCTYPE(C.c_size_t, C.c_void_p, C.c_size_t)
+OP_READOUT_MULTI = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t, C.POINTER(C.POINTER(C.c_uint32)), C.POINTER(C.c_size_t),
+                               C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_float))
 
 
 class SchedEngineOps(C.Structure):
@@ -52,7 +54,7 @@ class SchedEngineOps(C.Structure):
         ("ctx", C.c_void_p), ("readout_rows", C.c_int32), ("reserved0", C.c_int32),
         ("rebind_blas", OP_INT_CTX), ("capture_state", OP_CAPTURE), ("readout", OP_READOUT), ("offload", OP_MOVE), ("restore", OP_MOVE),
         ("state_free", OP_FREE), ("host_free", OP_FREE), ("trim_pools", OP_INT_CTX), ("mem_info", OP_MEM), ("last_error", OP_ERR),
-        ("state_bytes_for", OP_SIZE), ("pass_reserve", OP_SIZE),
+        ("state_bytes_for", OP_SIZE), ("pass_reserve", OP_SIZE), ("readout_multi", OP_READOUT_MULTI),
     ]
 
 
@@ -63,7 +65,7 @@ SCHED_STAT_NAMES = (
     "offload_bytes", "restores", "restore_bytes", "evict_gpu_entry_limit", "evict_gpu_byte_limit", "evict_gpu_offload_failed",
     "evict_host_budget", "oom_retry_capture", "oom_retry_question", "fail_headroom", "fail_state_restore", "fail_state_capture",
     "fail_state_offload", "fail_question_pass", "reject_queue_full", "reject_worker_stopped", "gpu_entries", "host_entries",
-    "gpu_bytes", "host_bytes", "gpu_free_bytes")
+    "gpu_bytes", "host_bytes", "gpu_free_bytes", "cross_state_passes", "requests_fallback")
 
 
 class SchedStats(C.Structure):

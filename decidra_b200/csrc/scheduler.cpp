@@ -72,10 +72,16 @@ void real_host_free(void*, void* hs) { dcd_host_state_free((dcd_host_state*)hs);
 int real_trim(void* c) { return dcd_trim_pools((dcd_engine*)c); }
 int real_mem(void* c, size_t* f, size_t* t) { return dcd_mem_info((dcd_engine*)c, f, t); }
 const char* real_err(void* c) { return dcd_last_error((dcd_engine*)c); }
+int real_readout_multi(void* c, const void* const* states, size_t n, const uint32_t* const* q, const size_t* lens, const uint32_t* state_of, size_t B,
+                       float* out) {
+  return dcd_readout_multi_state_batch((dcd_engine*)c, (const dcd_state* const*)states, n, q, lens, state_of, B, out);
+}
 
 thread_local std::string g_sched_error;
 
 }  // namespace
+
+struct Acquired;
 
 struct dcd_ticket {
   std::shared_ptr<Reply> reply;
@@ -136,7 +142,12 @@ struct dcd_scheduler {
     stat([&](dcd_sched_stats& s) { s.gpu_entries = cache.size(); s.host_entries = host_cache.size(); s.gpu_bytes = gb; s.host_bytes = hb; });
   }
 
+  struct GroupJobs { std::vector<uint32_t> state; uint8_t digest[32]; std::vector<Job> jobs; };
   void host_insert(CachedState entry, size_t bytes);
+  bool acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, struct Acquired* out);
+  void release(struct Acquired& a);
+  bool pass_one(struct Acquired& a, std::vector<Job>& jobs);
+  void run_groups_together(std::vector<GroupJobs>& groups);
   bool ensure_headroom(size_t need, const char* context, std::string* message);
   void run_group(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs);
   CacheResult run_group_inner(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, bool* ok);
@@ -202,14 +213,23 @@ bool dcd_scheduler::ensure_headroom(size_t need, const char* context, std::strin
   return true;
 }
 
-// run_group_inner, src/batch.rs:571-955 (text states only: no vision encode).
-CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, bool* ok) {
-  *ok = false;
+// run_group_inner, src/batch.rs:571-955 (text states only: no vision encode), in three steps so that several groups can
+// share one question pass: acquire (cache lookup, headroom, restore or capture), the pass, release (reply bookkeeping
+// done by the caller; the state goes back to a cache tier).
+struct Acquired {
+  CachedState entry;
+  CacheResult result = Unresolved;
+  bool from_host = false;
+  size_t entry_bytes = 0, pass_need = 0;
+};
+
+bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, Acquired* out) {
   auto find_gpu = [&]() { for (size_t i = 0; i < cache.size(); ++i) if (same_identity(state, digest, cache[i].state, cache[i].digest)) return (int)i; return -1; };
   auto find_host = [&]() { for (size_t i = 0; i < host_cache.size(); ++i) if (same_identity(state, digest, host_cache[i].state, host_cache[i].digest)) return (int)i; return -1; };
   int cached = find_gpu();
   int host_cached = cached < 0 ? find_host() : -1;
   const size_t entry_bytes = state_bytes_for(state.size());
+  out->entry_bytes = entry_bytes;
   if (!opt.pin_cache) {
     // keep the hit, evict older entries down to the limits the new entry will need
     CachedState preserved{};
@@ -229,6 +249,7 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
     if (have) { cache.push_back(std::move(preserved)); cached = (int)cache.size() - 1; }
   }
   const size_t pass_need = pass_reserve(state.size());
+  out->pass_need = pass_need;
   const size_t state_need = sat_add(entry_bytes, pass_need);
   std::string message;
   if (cached < 0) {
@@ -236,18 +257,20 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
       stat([](dcd_sched_stats& s) { s.fail_headroom += 1; });
       refresh_gauges();
       fail_all(jobs, message);
-      return Unresolved;
+      out->result = Unresolved;
+      return false;
     }
     if (host_cached >= 0) host_cached = find_host();  // offloading others may have evicted it from the host tier
     refresh_gauges();
   }
   const CacheResult result = cached >= 0 ? GpuHit : host_cached >= 0 ? HostHit : Miss;
+  out->result = result;
   stat([&](dcd_sched_stats& s) {
     (result == GpuHit ? s.requests_gpu_hit : result == HostHit ? s.requests_host_hit : s.requests_miss) += jobs.size();
     if (result != Miss) s.reused_tokens += (uint64_t)state.size() * jobs.size();
   });
-  const bool from_host = host_cached >= 0;
-  CachedState entry;
+  out->from_host = host_cached >= 0;
+  CachedState& entry = out->entry;
   if (cached >= 0) {
     entry = std::move(cache[cached]);
     cache.erase(cache.begin() + cached);
@@ -256,7 +279,7 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
     if (ops.restore(ops.ctx, host_cache[host_cached].cache, &restored) != DCD_OK) {
       stat([](dcd_sched_stats& s) { s.fail_state_restore += 1; });
       fail_all(jobs, "state restore failed: " + engine_error());
-      return HostHit;
+      return false;
     }
     stat([&](dcd_sched_stats& s) { s.restores += 1; s.restore_bytes += entry_bytes; });
     entry.state = state;
@@ -277,7 +300,7 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
     if (rc != DCD_OK) {
       stat([](dcd_sched_stats& s) { s.fail_state_capture += 1; });
       fail_all(jobs, "state capture failed: " + engine_error());
-      return Miss;
+      return false;
     }
     stat([&](dcd_sched_stats& s) { s.captures += 1; s.state_tokens += state.size(); });
     entry.state = state;
@@ -285,7 +308,44 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
     entry.cache = captured;
     entry.bytes = entry_bytes;
   }
+  return true;
+}
 
+// The state goes back to the device tier if it has room, else (unless it came from there) to the host tier.
+void dcd_scheduler::release(Acquired& a) {
+  CachedState& entry = a.entry;
+  bool kept = false;
+  if (opt.state_cache_entries > 0) {
+    size_t cached_bytes = 0;
+    for (auto& c : cache) cached_bytes += c.bytes;
+    const bool has_room = cache.size() < (size_t)opt.state_cache_entries && sat_add(cached_bytes, entry.bytes) <= (size_t)opt.state_cache_bytes;
+    if (has_room) {
+      if (a.from_host) {
+        for (size_t i = 0; i < host_cache.size();) {
+          if (same_identity(entry.state, entry.digest, host_cache[i].state, host_cache[i].digest)) { ops.host_free(ops.ctx, host_cache[i].cache); host_cache.erase(host_cache.begin() + i); }
+          else ++i;
+        }
+      }
+      cache.push_back(std::move(entry));
+      kept = true;
+    } else if (!a.from_host && opt.host_state_cache_bytes > 0) {
+      host_insert(std::move(entry), a.entry_bytes);  // frees the device copy
+      kept = true;
+    }
+  }
+  if (!kept) ops.state_free(ops.ctx, entry.cache);
+}
+
+CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, bool* ok) {
+  *ok = false;
+  Acquired a;
+  if (!acquire(state, digest, jobs, &a)) return a.result;
+  *ok = pass_one(a, jobs);
+  return a.result;
+}
+
+// The question pass of one group whose state is in hand, then the replies and the state's way back to a cache tier.
+bool dcd_scheduler::pass_one(Acquired& a, std::vector<Job>& jobs) {
   std::vector<const uint32_t*> qptr;
   std::vector<size_t> qlen;
   std::vector<std::pair<size_t, size_t>> ranges;
@@ -295,56 +355,37 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
     for (auto& q : j.questions) { qptr.push_back(q.data()); qlen.push_back(q.size()); question_tokens += q.size(); }
     ranges.emplace_back(start, qptr.size());
   }
-  if (!ensure_headroom(pass_need, "question pass", &message)) {
+  std::string message;
+  if (!ensure_headroom(a.pass_need, "question pass", &message)) {
     stat([](dcd_sched_stats& s) { s.fail_headroom += 1; });
-    ops.state_free(ops.ctx, entry.cache);
+    ops.state_free(ops.ctx, a.entry.cache);
     refresh_gauges();
     fail_all(jobs, message);
-    return result;
+    return false;
   }
   refresh_gauges();
   const size_t R = (size_t)ops.readout_rows;
   std::vector<float> rows(qptr.size() * R);
-  int rc = ops.readout(ops.ctx, entry.cache, qptr.data(), qlen.data(), qptr.size(), rows.data());
+  int rc = ops.readout(ops.ctx, a.entry.cache, qptr.data(), qlen.data(), qptr.size(), rows.data());
   if (rc != DCD_OK && engine_error().find("out of memory") != std::string::npos) {
     stat([](dcd_sched_stats& s) { s.oom_retry_question += 1; });
     ops.trim_pools(ops.ctx);
     std::string ignored;
-    ensure_headroom(pass_need, "question pass retry", &ignored);
-    rc = ops.readout(ops.ctx, entry.cache, qptr.data(), qlen.data(), qptr.size(), rows.data());
+    ensure_headroom(a.pass_need, "question pass retry", &ignored);
+    rc = ops.readout(ops.ctx, a.entry.cache, qptr.data(), qlen.data(), qptr.size(), rows.data());
   }
   if (rc != DCD_OK) {
     stat([](dcd_sched_stats& s) { s.fail_question_pass += 1; });
     const std::string msg = "state-once question pass failed: " + engine_error();
-    ops.state_free(ops.ctx, entry.cache);
+    ops.state_free(ops.ctx, a.entry.cache);
     fail_all(jobs, msg);
-    return result;
+    return false;
   }
   stat([&](dcd_sched_stats& s) { s.question_tokens += question_tokens; s.questions_answered += qptr.size(); });
   for (size_t i = 0; i < jobs.size(); ++i)
     finish(jobs[i], DCD_OK, "", rows.data() + ranges[i].first * R, (ranges[i].second - ranges[i].first) * R);
-  bool kept = false;
-  if (opt.state_cache_entries > 0) {
-    size_t cached_bytes = 0;
-    for (auto& c : cache) cached_bytes += c.bytes;
-    const bool has_room = cache.size() < (size_t)opt.state_cache_entries && sat_add(cached_bytes, entry.bytes) <= (size_t)opt.state_cache_bytes;
-    if (has_room) {
-      cache.push_back(std::move(entry));
-      kept = true;
-      if (from_host) {
-        for (size_t i = 0; i < host_cache.size();) {
-          if (same_identity(state, digest, host_cache[i].state, host_cache[i].digest)) { ops.host_free(ops.ctx, host_cache[i].cache); host_cache.erase(host_cache.begin() + i); }
-          else ++i;
-        }
-      }
-    } else if (!from_host && opt.host_state_cache_bytes > 0) {
-      host_insert(std::move(entry), entry_bytes);  // frees the device copy
-      kept = true;
-    }
-  }
-  if (!kept) ops.state_free(ops.ctx, entry.cache);
-  *ok = true;
-  return result;
+  release(a);
+  return true;
 }
 
 void dcd_scheduler::run_group(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs) {
@@ -356,6 +397,67 @@ void dcd_scheduler::run_group(const std::vector<uint32_t>& state, const uint8_t*
   const CacheResult r = run_group_inner(state, digest, jobs, &ok);
   (void)r;
   stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); (ok ? s.groups_success : s.groups_failed) += 1; });
+  refresh_gauges();
+}
+
+// Several groups, one question pass (cross_state_pass; not in the reference, which lists it as future work): every group's
+// state is acquired as above, then ONE pass answers all their questions. Groups whose state cannot be acquired fail alone.
+// If the combined pass is refused or fails, the groups fall back to one pass each, so a request never fares worse than in
+// the reference's order of work.
+void dcd_scheduler::run_groups_together(std::vector<GroupJobs>& groups) {
+  struct Live { GroupJobs* g; Acquired a; };
+  std::vector<Live> live;
+  size_t n_requests = 0;
+  for (GroupJobs& g : groups) {
+    size_t questions = 0;
+    for (Job& j : g.jobs) questions += j.questions.size();
+    const size_t n = g.jobs.size();
+    n_requests += n;
+    stat([&](dcd_sched_stats& s) { s.waiting -= std::min<uint64_t>(s.waiting, n); s.running += n; s.group_requests += n; s.group_questions += questions; });
+    Live l{&g, {}};
+    if (acquire(g.state, g.digest, g.jobs, &l.a)) live.push_back(std::move(l));
+    else stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); s.groups_failed += 1; });
+  }
+  std::vector<const void*> states;
+  std::vector<const uint32_t*> qptr;
+  std::vector<size_t> qlen;
+  std::vector<uint32_t> state_of;
+  size_t question_tokens = 0, pass_need = 0;
+  for (size_t k = 0; k < live.size(); ++k) {
+    states.push_back(live[k].a.entry.cache);
+    pass_need = std::max(pass_need, live[k].a.pass_need);
+    for (Job& j : live[k].g->jobs)
+      for (auto& q : j.questions) { qptr.push_back(q.data()); qlen.push_back(q.size()); state_of.push_back((uint32_t)k); question_tokens += q.size(); }
+  }
+  const size_t R = (size_t)ops.readout_rows;
+  std::vector<float> rows(qptr.size() * R);
+  bool together = live.size() > 1;
+  std::string message;
+  if (together && !ensure_headroom(pass_need, "question pass", &message)) together = false;
+  if (together && ops.readout_multi(ops.ctx, states.data(), states.size(), qptr.data(), qlen.data(), state_of.data(), qptr.size(), rows.data()) != DCD_OK)
+    together = false;
+  if (together) {
+    stat([&](dcd_sched_stats& s) { s.cross_state_passes += 1; s.question_tokens += question_tokens; s.questions_answered += qptr.size(); });
+    size_t at = 0;
+    for (Live& l : live) {
+      for (Job& j : l.g->jobs) {
+        finish(j, DCD_OK, "", rows.data() + at * R, j.questions.size() * R);
+        at += j.questions.size();
+      }
+      release(l.a);
+      const size_t n = l.g->jobs.size();
+      stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); s.groups_success += 1; });
+    }
+  } else {
+    // one pass per group, with the states already in hand
+    for (Live& l : live) {
+      const size_t n = l.g->jobs.size();
+      if (live.size() > 1) stat([&](dcd_sched_stats& s) { s.requests_fallback += n; });
+      const bool ok = pass_one(l.a, l.g->jobs);
+      stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); (ok ? s.groups_success : s.groups_failed) += 1; });
+    }
+  }
+  (void)n_requests;
   refresh_gauges();
 }
 
@@ -376,7 +478,7 @@ void dcd_scheduler::run_jobs(std::vector<Job>& jobs) {
     }
   }
   if (live.empty()) return;
-  struct Group { std::vector<uint32_t> state; uint8_t digest[32]; std::vector<Job> jobs; };
+  using Group = GroupJobs;
   std::vector<Group> groups;
   for (Job& j : live) {
     Group* hit = nullptr;
@@ -404,6 +506,7 @@ void dcd_scheduler::run_jobs(std::vector<Job>& jobs) {
     for (auto& o : order) sorted.push_back(std::move(groups[o.second]));
     groups = std::move(sorted);
   }
+  if (opt.cross_state_pass && ops.readout_multi && groups.size() > 1) { run_groups_together(groups); return; }
   for (Group& g : groups) run_group(g.state, g.digest, g.jobs);
 }
 
@@ -514,6 +617,7 @@ int dcd_scheduler_create(dcd_engine* e, const dcd_sched_options* opt, dcd_schedu
   ops.trim_pools = real_trim;
   ops.mem_info = real_mem;
   ops.last_error = real_err;
+  ops.readout_multi = real_readout_multi;
   return dcd_scheduler_create_with_ops(&ops, opt, out);
 }
 

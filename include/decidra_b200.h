@@ -158,7 +158,8 @@ typedef struct dcd_sched_options {
   int64_t state_cache_bytes;      /* DECIDRA_STATE_CACHE_BYTES, 5 GiB */
   int64_t host_state_cache_bytes; /* DECIDRA_HOST_STATE_CACHE_BYTES, 8 GiB */
   int32_t sched_priority;         /* DECIDRA_SCHED_PRIORITY, 0: 1 runs the cheapest group first (older than 500 ms first) */
-  int32_t reserved0;
+  int32_t cross_state_pass;       /* 0 = one pass per group, as the reference; 1 = the groups of one coalesced batch share ONE
+                                     question pass (dcd_readout_multi_state_batch); falls back to a pass per group if refused */
   int64_t submit_timeout_us;      /* 0 = wait for a queue slot like the reference's await; > 0 = give up with DCD_E_OVERLOADED */
   int64_t reserved[4];
 } dcd_sched_options;
@@ -184,6 +185,8 @@ typedef struct dcd_sched_engine_ops {
   const char* (*last_error)(void* ctx);                                              /* may be NULL */
   size_t (*state_bytes_for)(void* ctx, size_t state_len);                            /* may be NULL */
   size_t (*pass_reserve)(void* ctx, size_t state_len);                               /* may be NULL */
+  int (*readout_multi)(void* ctx, const void* const* states, size_t n_states, const uint32_t* const* questions, const size_t* lens,
+                       const uint32_t* state_of, size_t B, float* out);              /* may be NULL: no cross-state pass */
 } dcd_sched_engine_ops;
 
 /* The reference's counters and gauges (docs/METRICS.md names in comments) as plain integers. */
@@ -201,6 +204,7 @@ typedef struct dcd_sched_stats {
   uint64_t fail_headroom, fail_state_restore, fail_state_capture, fail_state_offload, fail_question_pass;
   uint64_t reject_queue_full, reject_worker_stopped;                 /* decidra_engine_admission_rejections_total{reason} */
   uint64_t gpu_entries, host_entries, gpu_bytes, host_bytes, gpu_free_bytes;
+  uint64_t cross_state_passes, requests_fallback;                    /* passes shared by several groups; requests sent back to a pass per group */
 } dcd_sched_stats;
 
 typedef struct dcd_scheduler dcd_scheduler;

@@ -85,3 +85,29 @@ def test_scheduler_concurrent_clients_coalesce(dcd):
     assert s["group_requests"] == 18 and s["groups_success"] < 18      # some requests shared a pass
     h.close()
     e.close()
+
+
+def test_scheduler_cross_state_pass(dcd):
+    """cross_state_pass: requests for different states that wait together are answered by ONE question pass; the rows
+    are still those of direct per-state calls, bit for bit."""
+    from decidra_b200 import scheduler
+    e = _engine(dcd)
+    cases = _cases(4)
+    want = [e.readout_state_once_batch(e.capture_state(st), qs) for st, qs in cases]
+    h = scheduler.BatchHandle(e, batch_window_us=30000, batch_requests=16, batch_rows=64, state_cache_entries=8, cross_state_pass=1)
+    first = h.submit_state_once(*cases[0])           # keeps the worker busy (capture + pass) while the others queue up
+    tickets = [h.submit_state_once(st, qs) for st, qs in cases[1:]] + [h.submit_state_once(cases[1][0], cases[1][1][:2])]
+    assert first.result().tobytes() == want[0].tobytes()
+    for k, t in enumerate(tickets[:3]):
+        assert t.result().tobytes() == want[k + 1].tobytes()
+    assert tickets[3].result().tobytes() == want[1][:2].tobytes()
+    s = h.stats()
+    assert s["cross_state_passes"] >= 1 and s["requests_fallback"] == 0 and s["captures"] == 4 and s["questions_answered"] == 4 * 4 + 2
+    # second round: every state is a device-tier hit and they still share a pass
+    tickets = [h.submit_state_once(st, qs[::-1]) for st, qs in cases]
+    for k, t in enumerate(tickets):
+        assert t.result().tobytes() == want[k][::-1].tobytes()
+    s = h.stats()
+    assert s["captures"] == 4 and s["requests_gpu_hit"] >= 4
+    h.close()
+    e.close()

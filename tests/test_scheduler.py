@@ -26,6 +26,7 @@ class FakeEngine:
         self.log = []
         self.fail = {}                     # op -> list of messages to fail with (popped per call)
         self.errbuf = C.create_string_buffer(512)
+        self.fail_capture_of = None        # (state tokens, message): the capture of that state always fails
         self.gate = None                   # (state tuple, threading.Event): capture of that state waits for the event
         self.entered = threading.Event()
         ops = _lib.SchedEngineOps()
@@ -37,7 +38,8 @@ class FakeEngine:
             offload=_lib.OP_MOVE(self._offload), restore=_lib.OP_MOVE(self._restore),
             state_free=_lib.OP_FREE(self._state_free), host_free=_lib.OP_FREE(self._host_free),
             trim_pools=_lib.OP_INT_CTX(self._trim), mem_info=_lib.OP_MEM(self._mem), last_error=_lib.OP_ERR(lambda ctx: C.addressof(self.errbuf)),
-            state_bytes_for=_lib.OP_SIZE(lambda ctx, n: self.state_bytes(n)), pass_reserve=_lib.OP_SIZE(lambda ctx, n: self.reserve(n)))
+            state_bytes_for=_lib.OP_SIZE(lambda ctx, n: self.state_bytes(n)), pass_reserve=_lib.OP_SIZE(lambda ctx, n: self.reserve(n)),
+            readout_multi=_lib.OP_READOUT_MULTI(self._readout_multi))
         for k, v in self._cbs.items():
             setattr(ops, k, v)
         self.ops = ops
@@ -58,6 +60,9 @@ class FakeEngine:
             self.entered.set()
             assert self.gate[1].wait(20)
         self._log("capture", tokens)
+        if self.fail_capture_of is not None and tokens == tuple(self.fail_capture_of[0]):
+            self.errbuf.value = self.fail_capture_of[1].encode()
+            return 4
         if self._failing("capture"):
             return 2
         h = self.next
@@ -79,6 +84,19 @@ class FakeEngine:
             return 2
         for i, q in enumerate(questions):
             a = self.answer(self.dev[st], q)
+            for j in range(ROWS):
+                out[i * ROWS + j] = a[j]
+        return 0
+
+    def _readout_multi(self, ctx, states, n_states, qs, lens, state_of, B, out):
+        toks = [self.dev[states[k]] for k in range(n_states)]
+        questions = [tuple(qs[i][k] for k in range(lens[i])) for i in range(B)]
+        sof = tuple(state_of[i] for i in range(B))
+        self._log("readout_multi", tuple(toks), tuple(questions), sof)
+        if self._failing("readout_multi"):
+            return 1
+        for i, q in enumerate(questions):
+            a = self.answer(toks[sof[i]], q)
             for j in range(ROWS):
                 out[i * ROWS + j] = a[j]
         return 0
@@ -378,3 +396,64 @@ def test_close_finishes_queued_requests(mk):
         assert np.array_equal(t.result()[0], fake.answer([i], [i]))
     # both tiers were released
     assert fake.dev == {} and fake.host == {}
+
+
+def test_cross_state_pass_serves_several_groups_at_once(mk):
+    h, fake = mk(cross_state_pass=1, batch_requests=8, batch_rows=64)
+    pt, ev = plug(h, fake)
+    A, B = [1, 2, 3], [4, 5]
+    t1 = h.submit_state_once(A, [[10], [11, 12]])
+    t2 = h.submit_state_once(B, [[20]])
+    t3 = h.submit_state_once(A, [[30]])
+    ev.set()
+    pt.result()
+    r1, r2, r3 = t1.result(), t2.result(), t3.result()
+    multi = fake.calls("readout_multi")
+    assert multi == [("readout_multi", (tuple(A), tuple(B)), ((10,), (11, 12), (30,), (20,)), (0, 0, 0, 1))]
+    assert len(fake.calls("readout")) == 1                       # the plug's own pass only
+    assert np.array_equal(r1, np.stack([fake.answer(A, [10]), fake.answer(A, [11, 12])]))
+    assert np.array_equal(r2[0], fake.answer(B, [20])) and np.array_equal(r3[0], fake.answer(A, [30]))
+    s = h.stats()
+    assert (s["cross_state_passes"], s["requests_fallback"], s["captures"], s["groups_success"], s["questions_answered"]) == (1, 0, 3, 3, 5)
+    assert (s["gpu_entries"], s["waiting"], s["running"]) == (3, 0, 0)
+    # both states went back to the device tier; a batch with a single group takes the ordinary pass
+    assert np.array_equal(h.submit_state_once(B, [[7]]).result()[0], fake.answer(B, [7]))
+    s = h.stats()
+    assert s["requests_gpu_hit"] == 1 and s["cross_state_passes"] == 1 and len(fake.calls("readout")) == 2
+
+
+def test_cross_state_pass_falls_back_and_isolates_failures(mk):
+    h, fake = mk(cross_state_pass=1, batch_requests=8, batch_rows=64)
+    pt, ev = plug(h, fake)
+    A, B, Cc = [1, 1], [2, 2], [3, 3]
+    fake.fail["readout_multi"] = ["pass of 99999 tokens exceeds max_pass_tokens: split the call"]
+    ta, tb = h.submit_state_once(A, [[1]]), h.submit_state_once(B, [[2], [3]])
+    ev.set()
+    pt.result()
+    assert np.array_equal(ta.result()[0], fake.answer(A, [1])) and np.array_equal(tb.result()[1], fake.answer(B, [3]))
+    s = h.stats()
+    assert (s["cross_state_passes"], s["requests_fallback"], s["groups_success"], s["captures"]) == (0, 2, 3, 3)
+    assert [c[1] for c in fake.calls("readout")[1:]] == [tuple(A), tuple(B)]   # one pass per group, states captured once
+    # a group whose state cannot be captured fails alone; the other two still share a pass
+    pt, ev = plug2(h, fake)
+    fake.fail_capture_of = (Cc, "capture: device lost its mind")
+    tc_ = h.submit_state_once(Cc, [[9]])
+    ta, tb = h.submit_state_once(A, [[4]]), h.submit_state_once(B, [[5]])
+    ev.set()
+    pt.result()
+    with pytest.raises(Exception, match="state capture failed: capture: device lost its mind"):
+        tc_.result()
+    assert np.array_equal(ta.result()[0], fake.answer(A, [4])) and np.array_equal(tb.result()[0], fake.answer(B, [5]))
+    s = h.stats()
+    assert (s["cross_state_passes"], s["fail_state_capture"], s["groups_failed"]) == (1, 1, 1)
+    assert fake.calls("readout_multi")[-1][3] == (0, 1)
+
+
+def plug2(h, fake):
+    """A second plug on a scheduler whose first plug state is already cached: use a fresh state."""
+    ev = threading.Event()
+    fake.gate = ((8, 8, 8, 8), ev)
+    fake.entered.clear()
+    t = h.submit_state_once((8, 8, 8, 8), [[1]])
+    assert fake.entered.wait(20)
+    return t, ev
