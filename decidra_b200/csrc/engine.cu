@@ -1709,42 +1709,48 @@ int dcd_readout_multi_state_batch(dcd_engine* e, const dcd_state* const* states,
     total += lens[i];
     if (lens[i] > mx) mx = lens[i];
   }
-  if (total > (size_t)e->Tm || B > (size_t)e->max_batch)
-    return fail(e, DCD_E_INVALID, "pass of %zu tokens in %zu questions exceeds max_pass_tokens %d: split the call", total, B, e->Tm);
+  if (mx > (size_t)e->Tm) return fail(e, DCD_E_INVALID, "a question of %zu tokens exceeds max_pass_tokens %d", mx, e->Tm);
   std::vector<int32_t> order(B);
   for (size_t i = 0; i < B; ++i) order[i] = (int32_t)i;
   std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return state_of[a] < state_of[b]; });
-  std::vector<Group> groups;
-  size_t tok = 0;
-  for (size_t n = 0; n < B; ++n) {
-    const size_t i = (size_t)order[n];
-    const dcd_state* st = states[state_of[i]];
-    if (st->pos_end + lens[i] > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "positions exceed the RoPE table");
-    if (groups.empty() || state_of[i] != state_of[(size_t)order[n - 1]]) groups.push_back(Group{st, (int)n, 0, (int)tok, 0, 0});
-    Group& g = groups.back();
-    g.nq += 1;
-    g.ntok += (int)lens[i];
-    if ((int)lens[i] > g.max_len) g.max_len = (int)lens[i];
-    memcpy(e->h_ids + tok, questions[i], lens[i] * 4);
-    e->h_lens[n] = (int32_t)lens[i];
-    e->h_posq[n] = (int32_t)st->pos_end;
-    tok += lens[i];
-  }
-  CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, total * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
-  CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, B * 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
-  CK(e, cudaMemcpyAsync(e->d_posq, e->h_posq, B * 4, cudaMemcpyHostToDevice, e->stream), "positions upload");
-  Pass p{1, (int)total, (int)B, (int)mx};
-  p.cache = groups[0].st;
-  p.groups = groups.data();
-  p.n_groups = (int)groups.size();
-  p.d_posq = e->d_posq;
-  int rc = run_pass_any(e, p, e->d_ids, e->d_lens, 0, e->d_logits);
-  if (rc) return rc;
   const int R = e->c.readout_rows;
-  CK(e, cudaMemcpyAsync(e->h_logits, e->d_logits, B * R * 4, cudaMemcpyDeviceToHost, e->stream), "logits download");
-  rc = sync_and_check(e);
-  if (rc) return rc;
-  for (size_t n = 0; n < B; ++n) memcpy(out + (size_t)order[n] * R, e->h_logits + n * R, (size_t)R * sizeof(float));
+  // as many passes as the workspace needs: each takes the next run of (sorted) questions that fits max_pass_tokens
+  for (size_t n0 = 0; n0 < B;) {
+    std::vector<Group> groups;
+    size_t tok = 0, n = n0, pass_max = 0;
+    for (; n < B; ++n) {
+      const size_t i = (size_t)order[n];
+      if (n > n0 && (tok + lens[i] > (size_t)e->Tm || n - n0 >= (size_t)e->max_batch)) break;
+      const dcd_state* st = states[state_of[i]];
+      if (st->pos_end + lens[i] > (size_t)e->o.max_positions) return fail(e, DCD_E_INVALID, "positions exceed the RoPE table");
+      if (groups.empty() || state_of[i] != state_of[(size_t)order[n - 1]]) groups.push_back(Group{st, (int)(n - n0), 0, (int)tok, 0, 0});
+      Group& g = groups.back();
+      g.nq += 1;
+      g.ntok += (int)lens[i];
+      if ((int)lens[i] > g.max_len) g.max_len = (int)lens[i];
+      if (lens[i] > pass_max) pass_max = lens[i];
+      memcpy(e->h_ids + tok, questions[i], lens[i] * 4);
+      e->h_lens[n - n0] = (int32_t)lens[i];
+      e->h_posq[n - n0] = (int32_t)st->pos_end;
+      tok += lens[i];
+    }
+    const size_t nb = n - n0;
+    CK(e, cudaMemcpyAsync(e->d_ids, e->h_ids, tok * 4, cudaMemcpyHostToDevice, e->stream), "ids upload");
+    CK(e, cudaMemcpyAsync(e->d_lens, e->h_lens, nb * 4, cudaMemcpyHostToDevice, e->stream), "lens upload");
+    CK(e, cudaMemcpyAsync(e->d_posq, e->h_posq, nb * 4, cudaMemcpyHostToDevice, e->stream), "positions upload");
+    Pass p{1, (int)tok, (int)nb, (int)pass_max};
+    p.cache = groups[0].st;
+    p.groups = groups.data();
+    p.n_groups = (int)groups.size();
+    p.d_posq = e->d_posq;
+    int rc = run_pass_any(e, p, e->d_ids, e->d_lens, 0, e->d_logits);
+    if (rc) return rc;
+    CK(e, cudaMemcpyAsync(e->h_logits, e->d_logits, nb * R * 4, cudaMemcpyDeviceToHost, e->stream), "logits download");
+    rc = sync_and_check(e);
+    if (rc) return rc;
+    for (size_t j = 0; j < nb; ++j) memcpy(out + (size_t)order[n0 + j] * R, e->h_logits + j * R, (size_t)R * sizeof(float));
+    n0 = n;
+  }
   return DCD_OK;
 }
 

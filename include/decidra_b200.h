@@ -342,7 +342,7 @@ DCD_API int dcd_readout_state_once_device(dcd_engine* e, const dcd_state* st, co
  * state of question i. Every question attends to its own state's cache plus its own block and continues that state's
  * recurrent state, conv tail and positions; rows are bit-identical to those of dcd_readout_state_once_batch called per
  * state. The token-parallel kernels (projections, MLP, norms) run once over the whole batch; the kernels that read a state
- * run once per state on its slice of the batch. The whole batch must fit one pass (max_pass_tokens). */
+ * run once per state on its slice of the batch. A batch larger than max_pass_tokens is served in as many passes as it needs. */
 DCD_API int dcd_readout_multi_state_batch(dcd_engine* e, const dcd_state* const* states, size_t n_states,
                                           const uint32_t* const* questions, const size_t* lens, const uint32_t* state_of, size_t B,
                                           float* out);
