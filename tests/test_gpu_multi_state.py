@@ -78,3 +78,19 @@ def test_multi_state_pass_d3_slice(dcd):
     states, state_of, questions = _mixed(cfg.vocab, rng, [300, 128, 65, 513], 24, 17, 150)
     _check(e, states, state_of, questions)
     e.close()
+
+
+@pytest.mark.parametrize("precision", [1, 3])
+def test_multi_state_pass_quantised_engines(dcd, precision):
+    """W4A16 and native NVFP4 engines: weights and activations are quantised row by row (per token, per output row),
+    so a row's answer cannot depend on which other questions share the pass."""
+    cfg = dcd.d3_config(num_layers=4, vocab=4096)
+    o = dcd.Options()
+    o.max_pass_tokens = 2048
+    o.precision = precision
+    e = dcd.Engine(cfg, o)
+    e.init_random(3)
+    rng = np.random.default_rng(8)
+    states, state_of, questions = _mixed(cfg.vocab, rng, [200, 129], 10, 20, 120)
+    _check(e, states, state_of, questions)
+    e.close()
