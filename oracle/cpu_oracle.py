@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
         fp = C.POINTER(C.c_float)
         L.orc_create.restype = P
         L.orc_create.argtypes = [C.POINTER(OrcConfig), C.c_uint64]
+        L.orc_create_lazy.restype = P
+        L.orc_create_lazy.argtypes = [C.POINTER(OrcConfig), C.c_uint64]
         L.orc_destroy.argtypes = [P]
         L.orc_state_free.argtypes = [P]
         L.orc_state_len.argtypes = [P]
@@ -148,9 +150,10 @@ class OracleState:
 class Oracle:
     """CPU restatement of Engine::{capture_state, readout_state_once_batch, decision_logits_split}."""
 
-    def __init__(self, cfg: OrcConfig, seed: int = 0):
+    def __init__(self, cfg: OrcConfig, seed: int = 0, lazy: bool = False):
+        """lazy: generate the weights of a layer when a pass reaches it and drop them after it (deep models)."""
         self.cfg = cfg
-        self.h = lib().orc_create(C.byref(cfg), seed)
+        self.h = (lib().orc_create_lazy if lazy else lib().orc_create)(C.byref(cfg), seed)
 
     def __del__(self):
         if getattr(self, "h", None):

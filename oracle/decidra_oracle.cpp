@@ -623,6 +623,7 @@ struct Oracle {
   // precision 2: FP8 GEMMs in question passes of >= fp8_min_rows rows (engine.rs:4321-4326, :246-257)
   int precision = 0, fp8_min_rows = 512;
   bool q8_now = false, w4_done = false;
+  bool lazy = false;  // layer weights are generated per pass and dropped (orc_create_lazy)
   std::map<const float*, Fp8Image> fp8_cache;
   // precision 3: per GEMM weight, the NVFP4 round trip (without the tensor scale) and alpha = 1/(wg*ig)
   std::map<const float*, Nv4Image> nv4_cache;
@@ -642,46 +643,58 @@ static std::vector<float> gen(const Oracle& o, int layer, int kind, size_t n) {
   return v;
 }
 
-ORC_API Oracle* orc_create(const orc_config* cfg, uint64_t seed) {
+// All tensors of one layer from the seeded generator.
+static void fill_layer(const Oracle& o, int i, LayerW& w) {
+  const orc_config& c = o.c;
+  const size_t H = c.hidden, I = c.intermediate;
+  w.full = c.layer_is_full[i] != 0;
+  w.input_norm = gen(o, i, T_INPUT_NORM, H);
+  w.post_norm = gen(o, i, T_POST_NORM, H);
+  w.gate = gen(o, i, T_GATE, I * H);
+  w.up = gen(o, i, T_UP, I * H);
+  w.down = gen(o, i, T_DOWN, H * I);
+  if (w.full) {
+    w.q = gen(o, i, T_Q, (size_t)c.heads * 2 * c.head_dim * H);
+    w.k = gen(o, i, T_K, (size_t)c.kv_heads * c.head_dim * H);
+    w.v = gen(o, i, T_V, (size_t)c.kv_heads * c.head_dim * H);
+    w.o = gen(o, i, T_O, H * c.heads * c.head_dim);
+    w.qnorm = gen(o, i, T_QNORM, c.head_dim);
+    w.knorm = gen(o, i, T_KNORM, c.head_dim);
+  } else {
+    const size_t vd = (size_t)c.gdn_v_heads * c.gdn_dv;
+    w.in_qkv = gen(o, i, T_IN_QKV, (size_t)o.conv_dim() * H);
+    w.in_z = gen(o, i, T_IN_Z, vd * H);
+    w.in_b = gen(o, i, T_IN_B, (size_t)c.gdn_v_heads * H);
+    w.in_a = gen(o, i, T_IN_A, (size_t)c.gdn_v_heads * H);
+    w.out = gen(o, i, T_OUT, H * vd);
+    w.conv = gen(o, i, T_CONV, (size_t)o.conv_dim() * 4);
+    w.A_log = gen(o, i, T_A_LOG, c.gdn_v_heads);
+    w.dt_bias = gen(o, i, T_DT_BIAS, c.gdn_v_heads);
+    w.gnorm = gen(o, i, T_GNORM, c.gdn_dv);
+  }
+}
+
+static Oracle* create_impl(const orc_config* cfg, uint64_t seed, bool lazy) {
   Oracle* o = new Oracle();
   o->c = *cfg;
   o->seed = seed;
+  o->lazy = lazy;
   o->R = Round{cfg->dtype == 1};
   const orc_config& c = o->c;
-  const size_t H = c.hidden, I = c.intermediate;
   o->layers.resize(c.num_layers);
   for (int i = 0; i < c.num_layers; ++i) {
-    LayerW& w = o->layers[i];
-    w.full = c.layer_is_full[i] != 0;
-    w.input_norm = gen(*o, i, T_INPUT_NORM, H);
-    w.post_norm = gen(*o, i, T_POST_NORM, H);
-    w.gate = gen(*o, i, T_GATE, I * H);
-    w.up = gen(*o, i, T_UP, I * H);
-    w.down = gen(*o, i, T_DOWN, H * I);
-    if (w.full) {
-      w.q = gen(*o, i, T_Q, (size_t)c.heads * 2 * c.head_dim * H);
-      w.k = gen(*o, i, T_K, (size_t)c.kv_heads * c.head_dim * H);
-      w.v = gen(*o, i, T_V, (size_t)c.kv_heads * c.head_dim * H);
-      w.o = gen(*o, i, T_O, H * c.heads * c.head_dim);
-      w.qnorm = gen(*o, i, T_QNORM, c.head_dim);
-      w.knorm = gen(*o, i, T_KNORM, c.head_dim);
-    } else {
-      const size_t vd = (size_t)c.gdn_v_heads * c.gdn_dv;
-      w.in_qkv = gen(*o, i, T_IN_QKV, (size_t)o->conv_dim() * H);
-      w.in_z = gen(*o, i, T_IN_Z, vd * H);
-      w.in_b = gen(*o, i, T_IN_B, (size_t)c.gdn_v_heads * H);
-      w.in_a = gen(*o, i, T_IN_A, (size_t)c.gdn_v_heads * H);
-      w.out = gen(*o, i, T_OUT, H * vd);
-      w.conv = gen(*o, i, T_CONV, (size_t)o->conv_dim() * 4);
-      w.A_log = gen(*o, i, T_A_LOG, c.gdn_v_heads);
-      w.dt_bias = gen(*o, i, T_DT_BIAS, c.gdn_v_heads);
-      w.gnorm = gen(*o, i, T_GNORM, c.gdn_dv);
-    }
+    o->layers[i].full = c.layer_is_full[i] != 0;
+    if (!lazy) fill_layer(*o, i, o->layers[i]);
   }
-  o->final_norm = gen(*o, -1, T_FINAL_NORM, H);
-  o->readout = gen(*o, -1, T_READOUT, (size_t)c.readout_rows * H);
+  o->final_norm = gen(*o, -1, T_FINAL_NORM, c.hidden);
+  o->readout = gen(*o, -1, T_READOUT, (size_t)c.readout_rows * c.hidden);
   return o;
 }
+ORC_API Oracle* orc_create(const orc_config* cfg, uint64_t seed) { return create_impl(cfg, seed, false); }
+// The same model with the weights of a layer generated when a pass reaches it and dropped after it, so that a
+// model of any depth needs the host memory of one layer (a 64-layer d3-shaped model is 97 GB of f32 otherwise).
+// Precision 0 only (the quantised modes rewrite the resident weights once).
+ORC_API Oracle* orc_create_lazy(const orc_config* cfg, uint64_t seed) { return create_impl(cfg, seed, true); }
 ORC_API void orc_destroy(Oracle* o) { delete o; }
 ORC_API void orc_state_free(OrcState* s) { delete s; }
 ORC_API int orc_state_len(const OrcState* s) { return s->state_len; }
@@ -723,6 +736,7 @@ static void lin(Oracle& o, const float* X, const std::vector<float>& W, float* C
 // precision 1 (W4A16 g128): every GEMM weight is replaced once by its int4 round trip; all passes
 // (capture included) then run on the dequantised bf16 values, as the reference's W4 paths do.
 ORC_API void orc_set_precision(Oracle* o, int precision, int fp8_min_rows) {
+  if (o->lazy && precision != 0) return;  // lazy models stay at precision 0
   if (precision == 1 && !o->w4_done) {
     const orc_config& c = o->c;
     const int H = c.hidden, I = c.intermediate, hd = c.head_dim, vd = c.gdn_v_heads * c.gdn_dv;
@@ -928,7 +942,9 @@ struct LayerCtx {
 // Pre-norm residual block: Engine::run_layer_batch, native/src/engine.rs:1725-1788.
 static void run_layer(Oracle& o, int li, std::vector<float>& x, int T, const std::vector<Seg>& segs, LayerCtx& ctx) {
   const orc_config& c = o.c;
-  const LayerW& w = o.layers[li];
+  LayerW lazy_w;
+  if (o.lazy) fill_layer(o, li, lazy_w);
+  const LayerW& w = o.lazy ? lazy_w : o.layers[li];
   const int H = c.hidden;
   o.q8_now = o.precision == 2 && ctx.mode == 1 && T >= o.fp8_min_rows;
   std::vector<float> h((size_t)T * H), mix;
