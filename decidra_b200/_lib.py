@@ -146,6 +146,7 @@ SIGNATURES = {
     "dcd_profile_enable": (I, [P, I]),
     "dcd_profile_read": (I, [P, C.POINTER(ProfEntry)]),
     "dcd_launch_count": (C.c_int64, [P]),
+    "dcd_debug_bounded_wait_probe": (C.c_int, [P, C.c_int]),
     "dcd_debug_layer_outputs": (I, [P, FP, SZ]),
     "dcd_block_cascade_mask": (I, [SZ, SZ, C.POINTER(C.c_uint8)]),
     "dcd_plan_chunks": (I, [C.POINTER(SZ), SZ, SZ, SZ, SZ, SZ, I32P, I32P, I32P]),
@@ -157,6 +158,8 @@ SIGNATURES = {
     "dcd_k_quant_fp8_rows": (I, [P, SZ, P, P, I, I, F, I, P]),
     "dcd_k_quant_w4_g128": (I, [P, P, P, I, I, P]),
     "dcd_k_dequant_w4_g128": (I, [P, P, P, I, I, P]),
+    "dcd_k_w4_repack": (I, [P, P, P, P, I, I, P]),
+    "dcd_k_gemm_w4a16_tc": (I, [P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "dcd_k_nvfp4_quant_rows": (I, [P, SZ, F, P, P, I, I, P]),
     "dcd_k_nvfp4_dequant_rows": (I, [P, P, P, I, I, P]),
     "dcd_k_nvfp4_fakequant_rows": (I, [P, SZ, F, P, I, I, P]),

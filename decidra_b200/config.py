@@ -72,7 +72,9 @@ class Options(C.Structure):
         ("max_positions", C.c_int32),
         ("gdn_path", C.c_int32),
         ("fp8_min_rows", C.c_int32),
-        ("reserved", C.c_int32 * 6),
+        ("nvfp4_scale_copy", C.c_int32),
+        ("w4a16_gemm", C.c_int32),
+        ("reserved", C.c_int32 * 4),
     ]
 
 

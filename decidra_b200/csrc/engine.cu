@@ -26,8 +26,43 @@
 #include "gemm_tcgen05.h"
 #include "host_logic.h"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace {
+
+// The give-up path of the tensor-core kernels on its own, for the test that makes a bounded wait run out: one warp holds a
+// TMEM allocation (as every tcgen05 kernel here does) and waits, with the same bounded wait, on an mbarrier that nothing will
+// ever arrive at. After `polls` polls it does what the real kernels do: raise the error word, pause for work in flight (there
+// is none here), free the TMEM, return. Nothing traps, spins without limit or touches memory it does not own.
+__global__ void __launch_bounds__(32, 1) bounded_wait_probe_kernel(int* __restrict__ err, uint32_t polls, int code) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    tcc::mbar_init(tcc::smem_u32(&bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tcc::smem_u32(&tmem_holder)), "r"(32u) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  tcc::tc_fence_before();
+  __syncthreads();
+  tcc::tc_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+  bool ok = true;
+  if (threadIdx.x == 0) ok = tcc::mbar_wait_limit(tcc::smem_u32(&bar), 0, abort_flag, polls);
+  ok = __all_sync(0xffffffffu, ok);
+  tcc::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) set_err(err, code);
+    for (int i = 0; i < 20; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  tcc::tc_fence_after();
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(32u) : "memory");
+}
 
 thread_local std::string g_create_error;
 
@@ -50,7 +85,9 @@ struct LayerW {
   struct Fp8W { uint8_t* q = nullptr; float* scale = nullptr; TcTensorMap tm; };
   Fp8W f_gu, f_down, f_qkv, f_o, f_gin, f_out;
   // W4A16 group-128 images (precision 1): the only resident copy of the six GEMM weights
-  struct W4 { uint32_t* q = nullptr; void* scale = nullptr; int N = 0, K = 0; };
+  // q: words in the nibble order [k0 k2 k4 k6 k1 k3 k5 k7]; scale: fp16 [N, K/128]; scale_t: the same transposed to [K/128][N] and
+  // tm_q: TMA descriptor over q, both for the fused W4A16 GEMM (K % 128 == 0)
+  struct W4 { uint32_t* q = nullptr; void* scale = nullptr; void* scale_t = nullptr; int N = 0, K = 0; bool fused = false; TcTensorMap tm_q; };
   W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
   // NVFP4 images (precision 3): e2m1 codes, e4m3 scale per 16, f32 tensor scale and GEMM alpha on the device
   // codes, row-major scales, the same scales in the 128 x 4 tiled layout of the block-scaled MMA, tensor scale, 1/tensor scale
@@ -291,7 +328,8 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     if (tc_make_tmap_fp8_a(&ta, e->xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
     Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
     const int bn = N >= 256 ? 256 : 128;
-    CK(e, nvfp4_gemm_launch(&ta, bn == 256 ? &n4->tm256 : &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream, bn),
+    CK(e, nvfp4_gemm_launch(&ta, bn == 256 ? &n4->tm256 : &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream,
+                            bn + (e->o.nvfp4_scale_copy == 1 ? 0 : 1000)),
        "tcgen05 nvfp4 gemm");
     return DCD_OK;
   }
@@ -311,11 +349,20 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     CK(e, tc_gemm_launch(&ta, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream, n4->alpha), "tcgen05 gemm (nvfp4 operands)");
     return DCD_OK;
   }
+  if (e->w4 && g4->fused && e->o.gemm_path == 0 && e->o.w4a16_gemm != 1 && w4a16_tc_shape_ok(M, N, K) &&
+      (e->o.w4a16_gemm == 2 || w4a16_tc_prefer(M, N, e->sm_count))) {
+    // W4A16 on the fused kernel: nibbles become bf16 inside the GEMM's producer warps, no bf16 copy of W
+    // (the role of the reference's Marlin kernel, native/kernels/marlin.cu:398-408)
+    Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
+    CK(e, w4a16_gemm_launch(tmA, &g4->tm_q, g4->scale_t, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream, resid), "tcgen05 w4a16 gemm");
+    return DCD_OK;
+  }
   if (e->w4) {
-    // W4A16: int4 -> bf16 into the shared stage, then the bf16 tensor-core GEMM reads the stage
-    // (the reference's dequant_w4a16_bf16 + BF16 GEMM route, native/src/engine.rs:4516-4558)
+    // ... or, where 256-row tiles would leave the GPU half empty (or the shape is not the kernel's): int4 -> bf16 into the shared
+    // stage, then the bf16 tensor-core GEMM reads the stage (the reference's dequant_w4a16_bf16 + BF16 GEMM route,
+    // native/src/engine.rs:4516-4558)
     Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5 * N * (double)K, 1);
-    CK(e, launch_dequant_w4_g128(g4->q, g4->scale, (bf16*)e->wstage, N, K, e->stream), "w4 dequantisation");
+    CK(e, launch_dequant_w4_g128(g4->q, g4->scale, (bf16*)e->wstage, N, K, e->stream, true), "w4 dequantisation");
     W = e->wstage;
   }
   if (fw && e->bf && e->o.gemm_path == 0 && tc_fp8_shape_ok(M, N, K)) {
@@ -708,6 +755,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (o.precision != 0 && c.dtype != 1) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 / fp8 precision needs a bf16 engine (dtype 1)");
   if (o.precision == 1 && ((c.hidden % 8) || (c.intermediate % 8))) return fail(nullptr, DCD_E_UNSUPPORTED, "w4a16 needs K multiples of 8");
   if (o.fp8_min_rows <= 0) o.fp8_min_rows = 512;
+  if (o.nvfp4_scale_copy < 0 || o.nvfp4_scale_copy > 2) return fail(nullptr, DCD_E_INVALID, "nvfp4_scale_copy must be 0, 1 or 2");
+  if (o.w4a16_gemm < 0 || o.w4a16_gemm > 2) return fail(nullptr, DCD_E_INVALID, "w4a16_gemm must be 0, 1 or 2");
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -790,6 +839,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->nv4 = o.precision == 3;
   e->nv4_native = e->nv4 && o.gemm_path == 0;
   if (e->nv4_native) CRE(nvfp4_gemm_prepare_device(), "nvfp4 GEMM shared-memory attribute");
+  if (e->w4 && o.gemm_path == 0) CRE(w4a16_gemm_prepare_device(), "w4a16 GEMM shared-memory attribute");
   e->gdn_tc = e->bf && o.gdn_path == 0 && gdn_tc_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_tc) CRE(gdn_tc_prepare_device<bf16>(), "tcgen05 GDN shared-memory attribute");
   e->gdn_chunked = e->bf && !e->gdn_tc && (o.gdn_path == 0 || o.gdn_path == 2) && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
@@ -839,6 +889,11 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
         g.N = (int)n; g.K = (int)k;
         int rc = dev_alloc(e, reinterpret_cast<void**>(&g.q), n * ((k + 7) / 8) * 4, true, &e->weight_bytes);
         if (!rc) rc = dev_alloc(e, &g.scale, n * ((k + 127) / 128) * 2, true, &e->weight_bytes);
+        if (!rc && (k % 128) == 0 && o.gemm_path == 0) {  // shapes the fused W4A16 GEMM takes
+          rc = dev_alloc(e, &g.scale_t, n * (k / 128) * 2, true, &e->weight_bytes);
+          if (!rc && w4a16_make_tmap_packed(&g.tm_q, g.q, n, k)) rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an int4 weight operand");
+          g.fused = !rc;
+        }
         return rc;
       };
       int rc = mk4(w.g_gu, e->gu_rows, H);
@@ -1025,7 +1080,7 @@ static int w4_stage_in(dcd_engine* e, const Loc& L) {
   }
   if (!L.w4) return DCD_OK;
   e->launches += 1;
-  CK(e, launch_dequant_w4_g128(L.w4->q, L.w4->scale, (bf16*)e->wstage, L.w4->N, L.w4->K, e->stream), "w4 stage in");
+  CK(e, launch_dequant_w4_g128(L.w4->q, L.w4->scale, (bf16*)e->wstage, L.w4->N, L.w4->K, e->stream, true), "w4 stage in");
   return DCD_OK;
 }
 static int w4_stage_out(dcd_engine* e, const Loc& L) {
@@ -1043,7 +1098,11 @@ static int w4_stage_out(dcd_engine* e, const Loc& L) {
   }
   if (!L.w4) return DCD_OK;
   e->launches += 1;
-  CK(e, launch_quant_w4_g128((const bf16*)e->wstage, L.w4->q, L.w4->scale, L.w4->N, L.w4->K, e->stream), "w4 stage out");
+  CK(e, launch_quant_w4_g128((const bf16*)e->wstage, L.w4->q, L.w4->scale, L.w4->N, L.w4->K, e->stream, true), "w4 stage out");
+  if (L.w4->scale_t) {
+    e->launches += 1;
+    CK(e, launch_w4_scale_transpose(L.w4->scale, L.w4->scale_t, L.w4->N, (L.w4->K + 127) / 128, e->stream), "w4 scale transpose");
+  }
   return DCD_OK;
 }
 
@@ -1415,9 +1474,74 @@ int load_linear(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::stri
 
 struct Member { int kind; const char* module; };
 
+// A compressed-tensors int4 module whose codes a W4 engine can keep as they are: group 128 over the whole input width.
+// (Zero points and the fp16 exactness of the scales are checked on the device while the rows are copied.)
+bool w4_adoptable(const ckpt::Store& s, const std::string& module, const Loc& L) {
+  if (s.contains(module + ".weight_global_scale") || !s.contains(module + ".weight_packed")) return false;
+  const ckpt::Tensor *tp = s.info(module + ".weight_packed"), *tsc = s.info(module + ".weight_scale"), *tz = s.info(module + ".weight_zero_point");
+  if (!tp || !tsc || (L.cols % 128) != 0 || tsc->shape.empty()) return false;
+  const size_t groups = L.cols / 128, words = L.cols / 8;
+  if (tsc->shape.back() != groups || tsc->dtype != ckpt::BF16 || tsc->count() != L.rows * groups) return false;
+  if (tp->dtype != ckpt::I32 || tp->count() != L.rows * words) return false;
+  if (tz && (tz->dtype != ckpt::I32 || tz->count() != ((L.rows + 7) / 8) * groups)) return false;
+  return true;
+}
+
+// Copies the module's words and scales into the engine image (rows mapped like every other loader maps them).
+int adopt_ct_w4(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& module, const Loc& L, int* d_flag) {
+  const ckpt::Tensor *tp = s.info(module + ".weight_packed"), *tsc = s.info(module + ".weight_scale"), *tz = s.info(module + ".weight_zero_point");
+  const size_t groups = L.cols / 128, words = L.cols / 8, out = L.rows;
+  const uint8_t *pp = s.data(*tp), *ps = s.data(*tsc), *pz = tz ? s.data(*tz) : nullptr;
+  const size_t chunk_rows = std::max<size_t>(8, (st.cap / (words * 4)) & ~(size_t)7);
+  if (8 * words * 4 > st.cap) return fail(e, DCD_E_INVALID, "%s: eight rows exceed the staging buffer", module.c_str());
+  for (size_t r0 = 0; r0 < out; r0 += chunk_rows) {
+    const size_t n = std::min(chunk_rows, out - r0);
+    void *dp, *ds, *dz = nullptr;
+    int sp, ss, sz = -1;
+    CK(e, st.push(pp + r0 * words * 4, n * words * 4, &dp, &sp), "checkpoint upload");
+    CK(e, st.push(ps + r0 * groups * 2, n * groups * 2, &ds, &ss), "checkpoint upload");
+    if (pz) CK(e, st.push(pz + (r0 / 8) * groups * 4, ((n + 7) / 8) * groups * 4, &dz, &sz), "checkpoint upload");
+    e->launches += 1;
+    CK(e, launch_adopt_ct_w4_rows((const int32_t*)dp, (const bf16*)ds, (const int32_t*)dz, L.w4->q, L.w4->scale, n, (int)L.cols, r0, L.mode, L.row_offset,
+                                  d_flag, e->stream), "int4 checkpoint adoption");
+    CK(e, st.release(sp), "checkpoint staging");
+    CK(e, st.release(ss), "checkpoint staging");
+    if (sz >= 0) CK(e, st.release(sz), "checkpoint staging");
+  }
+  return DCD_OK;
+}
+
 // One fused engine matrix = one or more checkpoint modules.
 int load_group(dcd_engine* e, Stager& st, const ckpt::Store& s, const std::string& layer_prefix, int layer, const Member* m, int count) {
   Loc L;
+  // A W4 engine serves the checkpoint's own int4 codes and scales where it can (every member of the fused matrix symmetric, group
+  // 128, scales exact in fp16): nothing is re-quantised, so the served weights are the reference's dequant_w4a16_bf16 values bit
+  // for bit. Anything else (bf16 members, group 64, zero points, a mix) goes through the bf16 stage and is quantised again.
+  if (e->w4) {
+    bool all = true;
+    for (int i = 0; i < count && all; ++i) all = locate(e, layer, m[i].kind, &L) && L.w4 && w4_adoptable(s, layer_prefix + m[i].module, L);
+    if (all) {
+      int* d_flag = e->d_err + 8;
+      const size_t words = (size_t)L.w4->N * (L.w4->K / 8), nsc = (size_t)L.w4->N * (L.w4->K / 128);
+      CK(e, cudaMemsetAsync(d_flag, 0, sizeof(int), e->stream), "adoption flag");
+      CK(e, cudaMemsetAsync(L.w4->q, 0x88, words * 4, e->stream), "int4 image clear");   // padding rows: code 8 = 0
+      CK(e, cudaMemsetAsync(L.w4->scale, 0, nsc * 2, e->stream), "int4 scale clear");
+      for (int i = 0; i < count; ++i) {
+        locate(e, layer, m[i].kind, &L);
+        if (int rc = adopt_ct_w4(e, st, s, layer_prefix + m[i].module, L, d_flag)) return rc;
+      }
+      int flag = 0;
+      CK(e, cudaMemcpyAsync(&flag, d_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream), "adoption flag");
+      CK(e, cudaStreamSynchronize(e->stream), "adoption sync");
+      if (flag == 0) {
+        if (L.w4->scale_t) {
+          e->launches += 1;
+          CK(e, launch_w4_scale_transpose(L.w4->scale, L.w4->scale_t, L.w4->N, L.w4->K / 128, e->stream), "w4 scale transpose");
+        }
+        return DCD_OK;
+      }
+    }
+  }
   for (int i = 0; i < count; ++i) {
     if (!locate(e, layer, m[i].kind, &L)) return fail(e, DCD_E_INVALID, "no tensor kind %d in layer %d", m[i].kind, layer);
     if ((L.w4 || L.nv) && i == 0) {
@@ -1951,6 +2075,16 @@ int dcd_debug_layer_outputs(dcd_engine* e, float* host_sink, size_t capacity) {
   e->tap_sink = host_sink;
   e->tap_cap = host_sink ? capacity : 0;
   return DCD_OK;
+}
+
+int dcd_debug_bounded_wait_probe(dcd_engine* e, int polls) {
+  if (!e) return DCD_E_INVALID;
+  if (polls < 1 || polls > (1 << 20)) return fail(e, DCD_E_INVALID, "polls must be in [1, 2^20]");
+  cudaSetDevice(e->device);
+  e->launches += 1;
+  bounded_wait_probe_kernel<<<1, 32, 0, e->stream>>>(e->d_err, (uint32_t)polls, DERR_GEMM_TIMEOUT);
+  CK(e, cudaGetLastError(), "bounded-wait probe");
+  return sync_and_check(e);
 }
 
 int dcd_pack(dcd_engine* e, const int32_t* lens, size_t B, int32_t pos_start, int32_t* cu_seqlens, int32_t* positions, int32_t* tok_q,

@@ -49,7 +49,7 @@ template <int BN> struct Cfg {
   // UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
   static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
-constexpr int NUM_THREADS = 256;
+constexpr int NUM_THREADS = 288;
 constexpr uint32_t SF_COL = 256;
 constexpr int GROUP_M = 16;
 
@@ -86,7 +86,10 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   n_idx = r / gsize;
 }
 
-template <int BN>
+// SPLIT: the scale tiles are copied into TMEM by a thread of their own (warp 8) that signals the MMA issuer through one more
+// barrier per stage, so that the copies of a K block are not queued in front of that block's MMAs on the issuer's in-order
+// stream of tensor-core work.
+template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const uint8_t* __restrict__ sfa,
                      const uint8_t* __restrict__ sfb, bf16* __restrict__ C, int M, int N, int K, int ldc, const float* __restrict__ alpha,
@@ -104,7 +107,8 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   auto empty_bar = [&](int s) { return bars_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * STAGES + ACC_STAGES + a); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES));
+  auto sfull_bar = [&](int s) { return bars_base + 8u * (2 * STAGES + 2 * ACC_STAGES + s); };  // scales of the stage are in TMEM
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 2 * ACC_STAGES));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,6 +120,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(sfull_bar(s), 1);
     }
     for (int a = 0; a < ACC_STAGES; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -133,7 +138,34 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0 || warp >= 6) {
+  // the tcgen05.cp copies of one stage: X scales of K step k into 4 columns, W scales 4 columns per 128-row block, blocks side by side
+  auto copy_scales = [&](uint32_t src, uint32_t sf_tmem) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      cp_sf(sf_tmem + 4 * k, desc_sf(src + A_BYTES + B_BYTES + 512 * k));
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) cp_sf(sf_tmem + 16 + 4 * NB * k + 4 * nb, desc_sf(src + A_BYTES + B_BYTES + (1 + nb) * SF_BYTES + 512 * k));
+    }
+  };
+
+  if (warp == 8) {
+    if (SPLIT && lane == 0) {
+      // Scale copier. A stage's TMEM columns are rewritten only after the MMAs that read them have completed: the producers
+      // refill the stage after empty_bar, and this thread waits for the refill.
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
+          tc_fence_after();
+          copy_scales(tiles_base + stage * STAGE_BYTES, tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS);
+          umma_commit_to(sfull_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 0 || warp >= 6) {
     if (lane == 0) {
       // warp 0: X codes (and the expected byte count of the stage); warp 6: W codes; warp 7: both scale sets
       int stage = 0;
@@ -176,11 +208,11 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           tc_fence_after();
           const uint32_t src = tiles_base + stage * STAGE_BYTES;
           const uint32_t sf_tmem = tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {  // W scales of K step k: 4 columns per 128-row block, blocks side by side
-            cp_sf(sf_tmem + 4 * k, desc_sf(src + A_BYTES + B_BYTES + 512 * k));
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) cp_sf(sf_tmem + 16 + 4 * NB * k + 4 * nb, desc_sf(src + A_BYTES + B_BYTES + (1 + nb) * SF_BYTES + 512 * k));
+          if (SPLIT) {
+            if (!(ok = mbar_wait(sfull_bar(stage), phase, abort_flag))) break;
+            tc_fence_after();
+          } else {
+            copy_scales(src, sf_tmem);
           }
           const uint64_t da = desc_sw128(src), db = desc_sw128(src + A_BYTES);
 #pragma unroll
@@ -361,8 +393,10 @@ bool nvfp4_tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && 
 size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 255) / 256) * 2 * (K / 64) * 512; }
 
 cudaError_t nvfp4_gemm_prepare_device() {
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
   return cudaSuccess;
 }
 cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s) {
@@ -391,14 +425,20 @@ cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, i
 // (tc_make_tmap_fp8_a for bn 128, tc_make_tmap_fp8_b for bn 256).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
                               int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn) {
+  const bool split = bn >= 1000;  // bn 1128 / 1256: the variant with the scale copies on a thread of their own
+  if (split) bn -= 1000;
   if (!nvfp4_tc_shape_ok(M, N, K) || (bn != 128 && bn != 256)) return cudaErrorInvalidValue;
   const int num_tiles = ((M + nvg::BM - 1) / nvg::BM) * ((N + bn - 1) / bn);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (bn == 128)
-    nvg::gemm_nvfp4_tc_kernel<128><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+  if (bn == 128 && !split)
+    nvg::gemm_nvfp4_tc_kernel<128, false><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+  else if (bn == 128)
+    nvg::gemm_nvfp4_tc_kernel<128, true><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+  else if (!split)
+    nvg::gemm_nvfp4_tc_kernel<256, false><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
   else
-    nvg::gemm_nvfp4_tc_kernel<256><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+    nvg::gemm_nvfp4_tc_kernel<256, true><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
   return cudaGetLastError();
 }

@@ -51,3 +51,14 @@ cudaError_t launch_nvfp4_swiglu_quant_tiled(const __nv_bfloat16* gu, int gu_stri
 // bn: output tile width, 128 or 256; tmB must have bn-row boxes (tc_make_tmap_fp8_a / tc_make_tmap_fp8_b over the codes).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
                               int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn);
+
+// W4A16 GEMM without a bf16 copy of W (gemm_w4a16.cu): int4 group-128 weights in the engine's own image (words with the nibble
+// order k0 k2 k4 k6 k1 k3 k5 k7, fp16 scales transposed to [K/128][N]); bit-identical to dequantising and running the bf16 GEMM.
+bool w4a16_tc_shape_ok(int M, int N, int K);           // K % 128 == 0, N % 8 == 0
+bool w4a16_tc_prefer(int M, int N, int sm_count);       // the fused kernel is the faster route for this launch (weight-streaming-bound passes)
+cudaError_t w4a16_gemm_prepare_device();
+int w4a16_make_tmap_packed(TcTensorMap* out, const void* packed, uint64_t N, uint64_t K);
+cudaError_t launch_w4_repack(const uint32_t* packed, uint32_t* out, size_t words, cudaStream_t s);   // in place is fine
+cudaError_t launch_w4_scale_transpose(const void* scales, void* out, int N, int groups, cudaStream_t s);
+cudaError_t w4a16_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmP, const void* scale_t, void* C, int M, int N, int K, int ldc, int epi,
+                              int sm_count, int* err, cudaStream_t stream, const void* resid = nullptr);

@@ -49,6 +49,20 @@ int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, float* scale
 int dcd_k_quant_w4_g128(const void* W, void* packed, void* scales, int N, int K, void* stream) {
   return rc_of(launch_quant_w4_g128((const bf16*)W, (uint32_t*)packed, scales, N, K, S(stream)));
 }
+int dcd_k_w4_repack(const void* packed, const void* scales, void* packed_out, void* scales_t, int N, int K, void* stream) {
+  if (N <= 0 || K <= 0 || (K % 128) != 0) return DCD_E_INVALID;
+  cudaError_t ce = launch_w4_repack((const uint32_t*)packed, (uint32_t*)packed_out, (size_t)N * (K / 8), S(stream));
+  if (ce == cudaSuccess) ce = launch_w4_scale_transpose(scales, scales_t, N, K / 128, S(stream));
+  return rc_of(ce);
+}
+int dcd_k_gemm_w4a16_tc(const void* X, const void* packed, const void* scales_t, const void* resid, void* C, int M, int N, int K, int ldc, int epi,
+                        int sm_count, int* err, void* stream) {
+  if (!w4a16_tc_shape_ok(M, N, K) || sm_count <= 0 || (epi != 0 && epi != 1) || (resid && epi)) return DCD_E_INVALID;
+  if (w4a16_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap ta, tp;
+  if (tc_make_tmap_a(&ta, X, M, K) || w4a16_make_tmap_packed(&tp, packed, N, K)) return DCD_E_CUDA;
+  return rc_of(w4a16_gemm_launch(&ta, &tp, scales_t, C, M, N, K, ldc, epi, sm_count, err, S(stream), resid));
+}
 int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N, int K, void* stream) {
   return rc_of(launch_dequant_w4_g128((const uint32_t*)packed, scales, (bf16*)W, N, K, S(stream)));
 }
@@ -78,10 +92,11 @@ int dcd_k_nvfp4_swiglu_quant_tiled(const void* gu, int gu_stride, void* packed, 
 
 int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K, int ldc,
                         const float* alpha, int sm_count, int* err, int tile_n, void* stream) {
-  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0 || (tile_n != 128 && tile_n != 256)) return DCD_E_INVALID;
+  const int tile_w = tile_n >= 1000 ? tile_n - 1000 : tile_n;  // + 1000: scale copies issued by a thread of their own
+  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0 || (tile_w != 128 && tile_w != 256)) return DCD_E_INVALID;
   if (nvfp4_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
   TcTensorMap ta, tb;
-  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || (tile_n == 128 ? tc_make_tmap_fp8_a(&tb, wq, N, K / 2) : tc_make_tmap_fp8_b(&tb, wq, N, K / 2))) return DCD_E_CUDA;
+  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || (tile_w == 128 ? tc_make_tmap_fp8_a(&tb, wq, N, K / 2) : tc_make_tmap_fp8_b(&tb, wq, N, K / 2))) return DCD_E_CUDA;
   uint8_t *sa = nullptr, *sb = nullptr;  // scales re-laid in 128 x 4 tiles for the duration of the call
   cudaStream_t st = S(stream);
   if (cudaMallocAsync(&sa, nvfp4_sf_tiled_bytes(M, K), st) != cudaSuccess) return DCD_E_OOM;

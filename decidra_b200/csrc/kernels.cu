@@ -1395,8 +1395,16 @@ template cudaError_t launch_quant_fp8_rows<bf16>(const bf16*, size_t, uint8_t*, 
 //   dequant: w[o,i] = bf16(float(q - 8) * float(scale[o, i/128]))   dequant_w4a16_bf16, kernels.cu:867-892
 //   quant  : scale = fp16(absmax/7), q = clamp(rint(w/scale), -8, 7)  (round to nearest; one warp per group)
 // ---------------------------------------------------------------------------
+// perm: the engine's own word layout, nibble order [k0 k2 k4 k6 k1 k3 k5 k7] (what the fused W4A16 GEMM unpacks in two-element
+// steps); otherwise the compressed-tensors order k0..k7.
+__device__ __forceinline__ uint32_t w4_nibble_permute(uint32_t w) {
+  uint32_t o = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o |= ((w >> (4 * j)) & 0xFu) << (4 * ((j & 1) * 4 + (j >> 1)));
+  return o;
+}
 __global__ void __launch_bounds__(256) quant_w4_g128_kernel(const bf16* __restrict__ W, uint32_t* __restrict__ packed,
-                                                            __half* __restrict__ scales, int N, int K) {
+                                                            __half* __restrict__ scales, int N, int K, bool perm) {
   const int groups = (K + 127) / 128, words = (K + 7) / 8;
   const int gidx = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (gidx >= N * groups) return;
@@ -1425,12 +1433,13 @@ __global__ void __launch_bounds__(256) quant_w4_g128_kernel(const bf16* __restri
   const uint32_t other = __shfl_xor_sync(0xffffffffu, nib, 1);
   if ((lane & 1) == 0) {
     const int w = (gi * 128 + lane * 4) >> 3;
-    if (w < words) packed[(size_t)o * words + w] = nib | (other << 16);
+    const uint32_t word = nib | (other << 16);
+    if (w < words) packed[(size_t)o * words + w] = perm ? w4_nibble_permute(word) : word;
   }
 }
 
 __global__ void __launch_bounds__(256) dequant_w4_g128_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales,
-                                                              bf16* __restrict__ W, int N, int K) {
+                                                              bf16* __restrict__ W, int N, int K, bool perm) {
   const int words = (K + 7) / 8, groups = (K + 127) / 128;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)N * words) return;
@@ -1439,7 +1448,7 @@ __global__ void __launch_bounds__(256) dequant_w4_g128_kernel(const uint32_t* __
   const float sc = __half2float(scales[(size_t)o * groups + (w * 8) / 128]);
   float f[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) f[j] = (float)((int)((word >> (4 * j)) & 0xf) - 8) * sc;
+  for (int j = 0; j < 8; ++j) f[j] = (float)((int)((word >> (4 * (perm ? (j & 1) * 4 + (j >> 1) : j))) & 0xf) - 8) * sc;
   bf16* dst = W + (size_t)o * K + (size_t)w * 8;
   if (w * 8 + 8 <= K && (K % 8) == 0) {
     *reinterpret_cast<uint4*>(dst) = pack8(f);
@@ -1448,16 +1457,16 @@ __global__ void __launch_bounds__(256) dequant_w4_g128_kernel(const uint32_t* __
   }
 }
 
-cudaError_t launch_quant_w4_g128(const bf16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s) {
+cudaError_t launch_quant_w4_g128(const bf16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s, bool perm) {
   if (N <= 0 || (K % 8) != 0) return N <= 0 ? cudaSuccess : cudaErrorInvalidValue;
   const int groups = (K + 127) / 128;
-  quant_w4_g128_kernel<<<(N * groups + 7) / 8, 256, 0, s>>>(W, packed, (__half*)scales, N, K);
+  quant_w4_g128_kernel<<<(N * groups + 7) / 8, 256, 0, s>>>(W, packed, (__half*)scales, N, K, perm);
   return cudaGetLastError();
 }
-cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, bf16* W, int N, int K, cudaStream_t s) {
+cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, bf16* W, int N, int K, cudaStream_t s, bool perm) {
   if (N <= 0) return cudaSuccess;
   const size_t n = (size_t)N * ((K + 7) / 8);
-  dequant_w4_g128_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(packed, (const __half*)scales, W, N, K);
+  dequant_w4_g128_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(packed, (const __half*)scales, W, N, K, perm);
   return cudaGetLastError();
 }
 
@@ -1698,6 +1707,38 @@ template cudaError_t launch_dequant_ct_w4_place<float>(const int32_t*, const bf1
                                                        int, cudaStream_t);
 template cudaError_t launch_dequant_ct_w4_place<bf16>(const int32_t*, const bf16*, const int32_t*, bf16*, size_t, int, int, size_t, int, int, int,
                                                       cudaStream_t);
+
+// compressed-tensors int4 rows (group 128) adopted as they are by a W4 engine: the words go to their (fused / interleaved) rows in
+// the engine's nibble order, the bf16 scales become fp16. A zero point other than 8 or a scale that fp16 cannot hold exactly
+// raises *flag (the caller then takes the dequantise-and-requantise route for the whole fused matrix).
+__global__ void adopt_ct_w4_rows_kernel(const int32_t* __restrict__ packed, const bf16* __restrict__ scale, const int32_t* __restrict__ zp,
+                                        uint32_t* __restrict__ dst_q, __half* __restrict__ dst_scale, size_t n_words, int in_dim, size_t row_start,
+                                        int mode, int row_offset, int* __restrict__ flag) {
+  const size_t wi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (wi >= n_words) return;
+  const int words_per_row = in_dim / 8, groups = in_dim / 128;
+  const size_t o = wi / words_per_row;  // row inside the chunk; the chunk starts on a multiple of 8 rows
+  const int w = (int)(wi - o * words_per_row);
+  const size_t drow = map_row(row_start + o, mode, row_offset);
+  dst_q[drow * words_per_row + w] = w4_nibble_permute((uint32_t)packed[wi]);
+  if ((w & 15) == 0) {  // first word of a group: its scale and zero point
+    const int g = w >> 4;
+    const float sc = __bfloat162float(scale[o * groups + g]);
+    const __half sh = __float2half_rn(sc);
+    dst_scale[drow * groups + g] = sh;
+    const int z = zp ? (int)(((uint32_t)zp[(o >> 3) * groups + g] >> (4 * (int)(o & 7))) & 0xFu) : 8;
+    if (__half2float(sh) != sc || z != 8) atomicExch(flag, 1);
+  }
+}
+cudaError_t launch_adopt_ct_w4_rows(const int32_t* packed, const bf16* scale, const int32_t* zp, uint32_t* dst_q, void* dst_scale, size_t n_rows,
+                                    int in_dim, size_t row_start, int mode, int row_offset, int* flag, cudaStream_t s) {
+  if (n_rows == 0) return cudaSuccess;
+  if (in_dim <= 0 || (in_dim % 128) || (row_start & 7)) return cudaErrorInvalidValue;
+  const size_t n_words = n_rows * (size_t)(in_dim / 8);
+  adopt_ct_w4_rows_kernel<<<(unsigned)((n_words + 255) / 256), 256, 0, s>>>(packed, scale, zp, dst_q, (__half*)dst_scale, n_words, in_dim, row_start,
+                                                                           mode, row_offset, flag);
+  return cudaGetLastError();
+}
 
 template <typename T>
 __global__ void dequant_ct_nvfp4_place_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales, float global,

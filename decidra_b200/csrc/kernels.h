@@ -71,6 +71,10 @@ template <typename T>
 cudaError_t launch_place_rows_cvt(const void* src, int src_dt, T* dst, size_t n_rows, int cols, size_t row_start, int mode, int row_offset,
                                   int dst_stride, cudaStream_t s);
 // compressed-tensors pack-quantized int4 (zp == nullptr: symmetric, zero point 8); row_start must be a multiple of 8
+// compressed-tensors int4 group-128 rows into a W4 engine image as they are (nibble order permuted, scales bf16 -> fp16); *flag is
+// raised when a zero point is not 8 or a scale is not exact in fp16
+cudaError_t launch_adopt_ct_w4_rows(const int32_t* packed, const __nv_bfloat16* scale, const int32_t* zp, uint32_t* dst_q, void* dst_scale, size_t n_rows,
+                                    int in_dim, size_t row_start, int mode, int row_offset, int* flag, cudaStream_t s);
 template <typename T>
 cudaError_t launch_dequant_ct_w4_place(const int32_t* packed, const __nv_bfloat16* scale, const int32_t* zp, T* dst, size_t n_rows, int in_dim,
                                        int group_size, size_t row_start, int mode, int row_offset, int dst_stride, cudaStream_t s);
@@ -108,8 +112,9 @@ cudaError_t launch_quant_fp8_rows(const T* x, size_t x_stride, uint8_t* out, flo
 
 // W4A16 group-128 weights: packed [N, K/8] words (nibble k of word j = input 8j+k, zero-point 8) and
 // fp16 scales [N, ceil(K/128)]. K % 8 == 0.
-cudaError_t launch_quant_w4_g128(const __nv_bfloat16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s);
-cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, __nv_bfloat16* W, int N, int K, cudaStream_t s);
+// perm: words in the engine's nibble order [k0 k2 k4 k6 k1 k3 k5 k7] instead of the compressed-tensors order k0..k7
+cudaError_t launch_quant_w4_g128(const __nv_bfloat16* W, uint32_t* packed, void* scales, int N, int K, cudaStream_t s, bool perm = false);
+cudaError_t launch_dequant_w4_g128(const uint32_t* packed, const void* scales, __nv_bfloat16* W, int N, int K, cudaStream_t s, bool perm = false);
 
 // NVFP4 (e2m1 + e4m3 per 16 + f32 per tensor). K % 16 == 0. Scales row-major [rows, K/16].
 cudaError_t launch_absmax_bf16(const __nv_bfloat16* x, size_t n, unsigned int* out, cudaStream_t s);

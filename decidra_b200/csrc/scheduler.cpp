@@ -144,7 +144,8 @@ struct dcd_scheduler {
 
   struct GroupJobs { std::vector<uint32_t> state; uint8_t digest[32]; std::vector<Job> jobs; };
   void host_insert(CachedState entry, size_t bytes);
-  bool acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, struct Acquired* out);
+  bool acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, struct Acquired* out, bool may_retry = false,
+               int* retry = nullptr, bool count_lookup = true);
   void release(struct Acquired& a);
   bool pass_one(struct Acquired& a, std::vector<Job>& jobs);
   void run_groups_together(std::vector<GroupJobs>& groups);
@@ -223,7 +224,13 @@ struct Acquired {
   size_t entry_bytes = 0, pass_need = 0;
 };
 
-bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, Acquired* out) {
+// may_retry: other groups' states are in hand (moved out of the device tier, so ensure_headroom cannot offload them). A memory
+// failure then does not fail the requests: *retry is set and the caller runs and releases what it holds, then acquires again.
+// (*retry = 2 when the lookup counters were already updated: the second attempt passes count_lookup = false.)
+bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* digest, std::vector<Job>& jobs, Acquired* out, bool may_retry,
+                            int* retry, bool count_lookup) {
+  if (retry) *retry = 0;
+  auto oom_text = [&]() { return engine_error().find("out of memory") != std::string::npos; };
   auto find_gpu = [&]() { for (size_t i = 0; i < cache.size(); ++i) if (same_identity(state, digest, cache[i].state, cache[i].digest)) return (int)i; return -1; };
   auto find_host = [&]() { for (size_t i = 0; i < host_cache.size(); ++i) if (same_identity(state, digest, host_cache[i].state, host_cache[i].digest)) return (int)i; return -1; };
   int cached = find_gpu();
@@ -254,6 +261,7 @@ bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* d
   std::string message;
   if (cached < 0) {
     if (!ensure_headroom(state_need, "state capture/restore", &message)) {
+      if (may_retry) { *retry = 1; return false; }
       stat([](dcd_sched_stats& s) { s.fail_headroom += 1; });
       refresh_gauges();
       fail_all(jobs, message);
@@ -265,7 +273,7 @@ bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* d
   }
   const CacheResult result = cached >= 0 ? GpuHit : host_cached >= 0 ? HostHit : Miss;
   out->result = result;
-  stat([&](dcd_sched_stats& s) {
+  if (count_lookup) stat([&](dcd_sched_stats& s) {
     (result == GpuHit ? s.requests_gpu_hit : result == HostHit ? s.requests_host_hit : s.requests_miss) += jobs.size();
     if (result != Miss) s.reused_tokens += (uint64_t)state.size() * jobs.size();
   });
@@ -277,6 +285,7 @@ bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* d
   } else if (host_cached >= 0) {
     void* restored = nullptr;
     if (ops.restore(ops.ctx, host_cache[host_cached].cache, &restored) != DCD_OK) {
+      if (may_retry && oom_text()) { *retry = 2; return false; }
       stat([](dcd_sched_stats& s) { s.fail_state_restore += 1; });
       fail_all(jobs, "state restore failed: " + engine_error());
       return false;
@@ -298,6 +307,7 @@ bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* d
       rc = ops.capture_state(ops.ctx, state.data(), state.size(), &captured);
     }
     if (rc != DCD_OK) {
+      if (may_retry && oom_text()) { *retry = 2; return false; }
       stat([](dcd_sched_stats& s) { s.fail_state_capture += 1; });
       fail_all(jobs, "state capture failed: " + engine_error());
       return false;
@@ -402,62 +412,75 @@ void dcd_scheduler::run_group(const std::vector<uint32_t>& state, const uint8_t*
 
 // Several groups, one question pass (cross_state_pass; not in the reference, which lists it as future work): every group's
 // state is acquired as above, then ONE pass answers all their questions. Groups whose state cannot be acquired fail alone.
-// If the combined pass is refused or fails, the groups fall back to one pass each, so a request never fares worse than in
-// the reference's order of work.
+// If the combined pass is refused or fails, the groups fall back to one pass each; if memory runs short while states are being
+// collected, the groups in hand are served and released first and the group that did not fit is acquired again on its own. So a
+// request never fares worse than in the reference's order of work.
 void dcd_scheduler::run_groups_together(std::vector<GroupJobs>& groups) {
   struct Live { GroupJobs* g; Acquired a; };
   std::vector<Live> live;
-  size_t n_requests = 0;
+  // The question pass(es) of the groups in hand, their replies, and their states' way back to the cache tiers.
+  auto run_live = [&]() {
+    if (live.empty()) return;
+    std::vector<const void*> states;
+    std::vector<const uint32_t*> qptr;
+    std::vector<size_t> qlen;
+    std::vector<uint32_t> state_of;
+    size_t question_tokens = 0, pass_need = 0;
+    for (size_t k = 0; k < live.size(); ++k) {
+      states.push_back(live[k].a.entry.cache);
+      pass_need = std::max(pass_need, live[k].a.pass_need);
+      for (Job& j : live[k].g->jobs)
+        for (auto& q : j.questions) { qptr.push_back(q.data()); qlen.push_back(q.size()); state_of.push_back((uint32_t)k); question_tokens += q.size(); }
+    }
+    const size_t R = (size_t)ops.readout_rows;
+    std::vector<float> rows(qptr.size() * R);
+    bool together = live.size() > 1;
+    std::string message;
+    if (together && !ensure_headroom(pass_need, "question pass", &message)) together = false;
+    if (together && ops.readout_multi(ops.ctx, states.data(), states.size(), qptr.data(), qlen.data(), state_of.data(), qptr.size(), rows.data()) != DCD_OK)
+      together = false;
+    if (together) {
+      stat([&](dcd_sched_stats& s) { s.cross_state_passes += 1; s.question_tokens += question_tokens; s.questions_answered += qptr.size(); });
+      size_t at = 0;
+      for (Live& l : live) {
+        for (Job& j : l.g->jobs) {
+          finish(j, DCD_OK, "", rows.data() + at * R, j.questions.size() * R);
+          at += j.questions.size();
+        }
+        release(l.a);
+        const size_t n = l.g->jobs.size();
+        stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); s.groups_success += 1; });
+      }
+    } else {
+      // one pass per group, with the states already in hand
+      for (Live& l : live) {
+        const size_t n = l.g->jobs.size();
+        if (live.size() > 1) stat([&](dcd_sched_stats& s) { s.requests_fallback += n; });
+        const bool ok = pass_one(l.a, l.g->jobs);
+        stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); (ok ? s.groups_success : s.groups_failed) += 1; });
+      }
+    }
+    live.clear();
+  };
   for (GroupJobs& g : groups) {
     size_t questions = 0;
     for (Job& j : g.jobs) questions += j.questions.size();
     const size_t n = g.jobs.size();
-    n_requests += n;
     stat([&](dcd_sched_stats& s) { s.waiting -= std::min<uint64_t>(s.waiting, n); s.running += n; s.group_requests += n; s.group_questions += questions; });
     Live l{&g, {}};
-    if (acquire(g.state, g.digest, g.jobs, &l.a)) live.push_back(std::move(l));
+    int retry = 0;
+    bool got = acquire(g.state, g.digest, g.jobs, &l.a, !live.empty(), &retry);
+    if (!got && retry) {
+      // Memory ran short while other groups' states are in hand, where nothing can offload them: serve and release those first
+      // (the reference's one-group-at-a-time order would have done exactly that), then acquire this group with the tiers intact.
+      run_live();
+      l.a = Acquired{};
+      got = acquire(g.state, g.digest, g.jobs, &l.a, false, nullptr, retry != 2);
+    }
+    if (got) live.push_back(std::move(l));
     else stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); s.groups_failed += 1; });
   }
-  std::vector<const void*> states;
-  std::vector<const uint32_t*> qptr;
-  std::vector<size_t> qlen;
-  std::vector<uint32_t> state_of;
-  size_t question_tokens = 0, pass_need = 0;
-  for (size_t k = 0; k < live.size(); ++k) {
-    states.push_back(live[k].a.entry.cache);
-    pass_need = std::max(pass_need, live[k].a.pass_need);
-    for (Job& j : live[k].g->jobs)
-      for (auto& q : j.questions) { qptr.push_back(q.data()); qlen.push_back(q.size()); state_of.push_back((uint32_t)k); question_tokens += q.size(); }
-  }
-  const size_t R = (size_t)ops.readout_rows;
-  std::vector<float> rows(qptr.size() * R);
-  bool together = live.size() > 1;
-  std::string message;
-  if (together && !ensure_headroom(pass_need, "question pass", &message)) together = false;
-  if (together && ops.readout_multi(ops.ctx, states.data(), states.size(), qptr.data(), qlen.data(), state_of.data(), qptr.size(), rows.data()) != DCD_OK)
-    together = false;
-  if (together) {
-    stat([&](dcd_sched_stats& s) { s.cross_state_passes += 1; s.question_tokens += question_tokens; s.questions_answered += qptr.size(); });
-    size_t at = 0;
-    for (Live& l : live) {
-      for (Job& j : l.g->jobs) {
-        finish(j, DCD_OK, "", rows.data() + at * R, j.questions.size() * R);
-        at += j.questions.size();
-      }
-      release(l.a);
-      const size_t n = l.g->jobs.size();
-      stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); s.groups_success += 1; });
-    }
-  } else {
-    // one pass per group, with the states already in hand
-    for (Live& l : live) {
-      const size_t n = l.g->jobs.size();
-      if (live.size() > 1) stat([&](dcd_sched_stats& s) { s.requests_fallback += n; });
-      const bool ok = pass_one(l.a, l.g->jobs);
-      stat([&](dcd_sched_stats& s) { s.running -= std::min<uint64_t>(s.running, n); (ok ? s.groups_success : s.groups_failed) += 1; });
-    }
-  }
-  (void)n_requests;
+  run_live();
   refresh_gauges();
 }
 

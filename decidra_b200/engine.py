@@ -244,6 +244,10 @@ class Engine:
     def launch_count(self) -> int:
         return int(_lib.load().dcd_launch_count(self._h))
 
+    def bounded_wait_probe(self, polls: int = 1024) -> None:
+        """Make a bounded device-side wait run out on purpose (nothing arrives at its barrier): raises EngineError(E_TIMEOUT)."""
+        self._check(_lib.load().dcd_debug_bounded_wait_probe(self._h, polls))
+
     def debug_layer_outputs(self, sink: np.ndarray | None) -> None:
         if sink is None:
             self._check(_lib.load().dcd_debug_layer_outputs(self._h, None, 0))

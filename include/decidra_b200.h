@@ -63,9 +63,12 @@ typedef struct dcd_model_config {
 typedef struct dcd_options {
   int32_t precision;        /* 0 = the config dtype; 2 = fp8 (e4m3 GEMMs, per-token x per-output-row scales, in question passes
                                of >= fp8_min_rows rows; capture stays bf16 — Engine::fp8_gemm, native/src/engine.rs:4144-4296);
-                               1 = w4a16 group 128: the GEMM weights are held only as int4 + fp16 group scales and
-                               dequantised per GEMM into a shared bf16 stage (dequant_w4a16_bf16 route,
-                               native/src/engine.rs:4516-4558), all passes; 3 = nvfp4 with the reference's W4A4 semantics
+                               1 = w4a16 group 128: the GEMM weights are held only as int4 + fp16 group scales, all passes. Passes
+                               of up to 640 rows (bound by streaming the weights) run the GEMM that turns the nibbles into bf16
+                               inside its producer warps (the role of the reference's Marlin kernel,
+                               native/kernels/marlin.cu:398-408); larger passes, and K not a multiple of 128, dequantise into a
+                               shared bf16 stage first (dequant_w4a16_bf16 route, native/src/engine.rs:4516-4558), which is the
+                               faster route once the tensor core is the bound — both give the same bits (w4a16_gemm overrides); 3 = nvfp4 with the reference's W4A4 semantics
                                (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131): weights held as e2m1 + e4m3 scale per 16 +
                                f32 tensor scale, activations quantised the same way per GEMM, all passes; gemm_path 0 multiplies the
                                codes on the block-scaled FP4 tensor-core instruction, gemm_path 2 dequantises both operands
@@ -79,7 +82,11 @@ typedef struct dcd_options {
   int32_t max_positions;    /* RoPE table length; default 65536 */
   int32_t gdn_path;         /* 0 = chunked gated delta rule on tcgen05 (bf16, dk = dv = 128), else on mma.sync (dk 128); 1 = sequential f32; 2 = mma.sync chunked */
   int32_t fp8_min_rows;     /* fp8_min_rows() of native/src/engine.rs:246-257; default 512 */
-  int32_t reserved[6];
+  int32_t nvfp4_scale_copy; /* precision 3, block-scaled kernel: who issues the tcgen05.cp of the scale tiles. 0 = default (2); 1 = the MMA
+                               issuer, in front of each K block's MMAs; 2 = a thread of its own, signalling the issuer per stage */
+  int32_t w4a16_gemm;       /* precision 1: 0 = default (the GEMM that dequantises in its producer warps for passes of up to 640 rows),
+                               1 = always dequantise into the bf16 stage first, 2 = always the fused kernel (K % 128 == 0) */
+  int32_t reserved[4];
 } dcd_options;
 
 typedef struct dcd_info {
@@ -398,6 +405,13 @@ DCD_API int64_t dcd_launch_count(const dcd_engine* e);
  * sink is set, every layer output [T,hidden] is copied there as f32 (debug/tests). */
 DCD_API int dcd_debug_layer_outputs(dcd_engine* e, float* host_sink /* [layers*T*hidden] or NULL to disable */, size_t capacity);
 
+/* Failure-detection probe (no counterpart in the reference, whose kernels have no device-side waits): launches one warp that
+ * holds a small TMEM allocation and waits, with the same bounded wait the tensor-core kernels use, on an mbarrier nobody arrives
+ * at. After `polls` polls (1 .. 2^20; a few microseconds at 1024) it takes the kernels' give-up path: error word, short pause,
+ * TMEM freed, return. The call then reports what any pass would: DCD_E_TIMEOUT with the kernel's message, and the engine stays
+ * usable. Nothing traps or hangs. */
+DCD_API int dcd_debug_bounded_wait_probe(dcd_engine* e, int polls);
+
 /* ---- host-side integer logic (bit-exact parts) ------------------------------ */
 
 /* block_cascade_mask (native/src/engine.rs:490-504): bit q*seq+k set iff k < (q<split ? split : seq),
@@ -452,6 +466,15 @@ DCD_API int dcd_k_quant_fp8_rows(const void* x, size_t x_stride, void* out, floa
  * scale = fp16(absmax/7). W is bf16 [N,K], K % 8 == 0. */
 DCD_API int dcd_k_quant_w4_g128(const void* W, void* packed, void* scales, int N, int K, void* stream);
 DCD_API int dcd_k_dequant_w4_g128(const void* packed, const void* scales, void* W, int N, int K, void* stream);
+/* W4A16 GEMM without a bf16 copy of the weights (replaces Marlin<bf16, u4, group 128>, native/kernels/marlin.cu:398-408, and the
+ * fused fallback gemm_w4a16_bf16, native/kernels/kernels.cu:930-1230): C[M, ldc] = X[M,K] . w^T with w = bf16(float(q - 8) * float(scale))
+ * formed inside the kernel; bit-identical to dcd_k_dequant_w4_g128 followed by dcd_k_gemm_bf16_tc(_resid). Operands in the kernel's own
+ * image, made by dcd_k_w4_repack from the compressed-tensors form: every word's nibbles reordered to k0 k2 k4 k6 k1 k3 k5 k7 (so two
+ * neighbouring weights unpack with one mask), the fp16 scales transposed to [K/128][N]. K % 128 == 0, N % 8 == 0. epi as
+ * dcd_k_gemm_bf16_tc; resid (epi 0 only) may be NULL. */
+DCD_API int dcd_k_w4_repack(const void* packed, const void* scales, void* packed_out, void* scales_t, int N, int K, void* stream);
+DCD_API int dcd_k_gemm_w4a16_tc(const void* X, const void* packed, const void* scales_t, const void* resid, void* C, int M, int N, int K, int ldc,
+                                int epi, int sm_count, int* err, void* stream);
 /* NVFP4 rows (quant_nvfp4_act_bf16 / fp4_encode, native/kernels/kernels.cu:222-277): v = x*global,
  * sf = e4m3(max(absmax16(v)/6, 1e-10)), code = fp4_encode(v/decode(sf)); packed [rows, K/2] (low nibble =
  * even k), scales row-major [rows, K/16]. dequant writes decode(code)*decode(sf) as bf16 (exact);
@@ -473,7 +496,7 @@ DCD_API int dcd_k_nvfp4_swiglu_quant_tiled(const void* gu, int gu_stride, void* 
  * native/src/engine.rs:3962-4131): xq [M,K/2] and wq [N,K/2] e2m1 codes, x_scales [M,K/16] and w_scales [N,K/16]
  * e4m3 bytes (row-major, as dcd_k_nvfp4_quant_rows writes them), C [M,ldc] bf16 = *alpha (device scalar, may be
  * NULL) * sum over 16-element blocks of scale_x * scale_w * sum(code_x * code_w). K % 256 == 0, N % 8 == 0.
- * tile_n: output tile width, 128 or 256. */
+ * tile_n: output tile width, 128 or 256; + 1000 selects the variant whose scale copies are issued by a thread of their own. */
 DCD_API int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K,
                                 int ldc, const float* alpha, int sm_count, int* err, int tile_n, void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */

@@ -92,8 +92,9 @@ def _nvfp4_module(rng, out, in_dim):
 def synth_model_dir(model_dir, cfg, oracle, seed=0, prefix="model.language_model.", quant=None, shards=1,
                     partial_rotary_factor=0.25, readout_dtype="F32"):
     """Write a synthetic checkpoint of `cfg` and return {(layer, kind): f32 values} — the logical tensors a
-    loader must end up with. quant: None (all BF16), "int4" or "nvfp4" (every linear whose input width allows it;
-    the others stay BF16, as a real mixed checkpoint does)."""
+    loader must end up with. quant: None (all BF16), "int4" (groups of 64 and 128, with and without zero points), "int4_sym128"
+    (symmetric, group 128) or "nvfp4" (every linear whose input width allows it; the others stay BF16, as a real mixed checkpoint
+    does)."""
     rng = np.random.Generator(np.random.PCG64(seed))
     model_dir = Path(model_dir)
     model_dir.mkdir(parents=True, exist_ok=True)
@@ -114,7 +115,14 @@ def synth_model_dir(model_dir, cfg, oracle, seed=0, prefix="model.language_model
 
     def linear(module, layer, kind, out, in_dim, n_lin=[0]):
         n_lin[0] += 1
-        if quant == "int4" and in_dim % 64 == 0:
+        if quant == "int4_sym128" and in_dim % 128 == 0:
+            # symmetric, group 128, scales exact in fp16: the form a W4 engine can keep code for code
+            packed, scale, zp = _int4_module(rng, out, in_dim, 128, True)
+            tensors[module + ".weight_packed"] = ("I32", packed.shape, packed)
+            tensors[module + ".weight_scale"] = ("BF16", scale.shape, bf16_bits(scale))
+            tensors[module + ".weight_shape"] = ("I64", (2,), np.array([out, in_dim], dtype=np.int64))
+            logical[(layer, kind)] = oracle.ct_w4_dequant(packed, scale, None, in_dim, 128).ravel()
+        elif quant == "int4" and in_dim % 64 == 0:
             group = 64 if n_lin[0] % 2 else (128 if in_dim % 128 == 0 else 64)
             symmetric = n_lin[0] % 3 == 0
             packed, scale, zp = _int4_module(rng, out, in_dim, group, symmetric)

@@ -104,6 +104,42 @@ def test_checkpoint_into_quantised_engines(dcd, oracle, tmp_path, precision, qua
     e.close(); ref.close()
 
 
+def test_w4_engine_serves_the_checkpoints_own_int4_codes(dcd, oracle, tmp_path):
+    """A symmetric group-128 int4 checkpoint on a precision-1 engine: nothing is quantised a second time. Every adopted tensor
+    reads back as compressed-tensors dequantisation of the stored codes and scales, bit for bit (the reference serves exactly
+    those: dequant_w4a16_bf16, native/kernels/kernels.cu:867-892), including groups that contain code 0 (value -8), whose absmax
+    re-quantisation would have changed the scale. Members that cannot be adopted (down_proj: input width 688 has no group of
+    128, stored as BF16) take the quantise-once route; the answers equal those of an engine fed the same values tensor by tensor
+    only where nothing was re-quantised, so they are compared with the bf16 engine on the dequantised weights instead."""
+    from decidra_b200 import checkpoint
+    cfg = dcd.tiny_config(1)
+    H, I = cfg.hidden, cfg.intermediate
+    logical = U.synth_model_dir(tmp_path, cfg, oracle, seed=7, quant="int4_sym128")
+    e = checkpoint.engine_from_dir(tmp_path, _options(dcd, precision=1))
+    adopted = [(0, U.T_GATE, I * H), (0, U.T_UP, I * H), (1, U.T_IN_QKV, cfg.conv_dim() * H), (1, U.T_IN_Z, cfg.gdn_v_heads * cfg.gdn_dv * H),
+               (2, U.T_IN_B, cfg.gdn_v_heads * H), (2, U.T_IN_A, cfg.gdn_v_heads * H), (2, U.T_OUT, H * cfg.gdn_v_heads * cfg.gdn_dv),
+               (3, U.T_Q, cfg.heads * 2 * cfg.head_dim * H), (3, U.T_K, cfg.kv_heads * cfg.head_dim * H), (3, U.T_V, cfg.kv_heads * cfg.head_dim * H),
+               (3, U.T_O, H * cfg.heads * cfg.head_dim)]
+    has_code0 = False
+    for layer, kind, n in adopted:
+        want = logical[(layer, kind)]
+        assert e.read_tensor(layer, kind, n).tobytes() == want.tobytes(), (layer, kind)
+        has_code0 = has_code0 or bool((want < 0).any())
+    assert has_code0
+    # down_proj was stored as BF16 (688 = 5 * 128 + 48): quantised once by the engine
+    p, s = oracle.k_quant_w4(logical[(0, U.T_DOWN)].reshape(H, I))
+    assert e.read_tensor(0, U.T_DOWN, H * I).tobytes() == oracle.k_dequant_w4(p, s, I).tobytes()
+    # the same weights on a bf16 engine (down_proj through its int4 round trip) answer identically: the W4 engine only changes storage
+    vals = dict(logical)
+    for i in range(cfg.num_layers):
+        p, s = oracle.k_quant_w4(logical[(i, U.T_DOWN)].reshape(H, I))
+        vals[(i, U.T_DOWN)] = oracle.k_dequant_w4(p, s, I).ravel()
+    ref = _engine_from_logical(dcd, cfg, vals)
+    got, want = _answers(e), _answers(ref)
+    assert np.isfinite(got).all() and got.tobytes() == want.tobytes()
+    e.close(); ref.close()
+
+
 def test_typed_upload_equals_f32_upload(dcd, oracle):
     from decidra_b200 import checkpoint
     cfg = dcd.tiny_config(1)

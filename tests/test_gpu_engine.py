@@ -203,6 +203,23 @@ def test_error_behaviour_matches_reference(tiny_bf16, dcd):
     assert e.launch_count() > 0
 
 
+def test_bounded_wait_runs_out_and_engine_survives(dcd, tiny_bf16):
+    """Failure detection without a fault: a kernel waits (bounded, 1024 polls) on a barrier nothing arrives at, takes the
+    give-up path of the tensor-core kernels (error word, TMEM freed, return), the host reports DCD_E_TIMEOUT with the kernel's
+    message, and the same engine then answers exactly as before."""
+    e, o, cfg = tiny_bf16
+    state, questions = tiny_inputs(seed=3)
+    st = e.capture_state(state)
+    before = e.readout_state_once_batch(st, questions)
+    with pytest.raises(dcd.EngineError, match="bounded barrier wait gave up") as ei:
+        e.bounded_wait_probe(1024)
+    assert ei.value.code == 5  # DCD_E_TIMEOUT
+    after = e.readout_state_once_batch(st, questions)
+    assert before.tobytes() == after.tobytes()
+    with pytest.raises(dcd.EngineError, match="polls"):
+        e.bounded_wait_probe(0)
+
+
 def test_run_twice_is_deterministic(tiny_bf16):
     e, o, cfg = tiny_bf16
     state, questions = tiny_inputs(seed=9)

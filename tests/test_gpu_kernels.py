@@ -488,6 +488,54 @@ def test_w4_quant_dequant_bit_exact(G, oracle, N, K):
     assert G.host(out).tobytes() == oracle.k_dequant_w4(wp, ws, K).tobytes()
 
 
+@pytest.mark.parametrize("M,N,K,epi,with_resid", [(300, 512, 256, 0, False), (77, 96, 128, 0, False), (129, 264, 384, 0, True), (520, 1024, 5120, 1, False),
+                                                   (2048, 5120, 1024, 0, True), (1000, 16480, 640, 0, False),
+                                                   # the d3 projections at question-pass heights
+                                                   (350, 34816, 5120, 1, False), (700, 5120, 17408, 0, True), (350, 14336, 5120, 0, False),
+                                                   (700, 5120, 6144, 0, True)])
+def test_gemm_w4a16_fused_bit_identical_to_dequant_plus_bf16_gemm(G, oracle, M, N, K, epi, with_resid):
+    """The W4A16 GEMM that dequantises inside its producer warps gives the bits of the two-step route (int4 -> bf16 matrix, then the
+    bf16 tensor-core GEMM): every weight is bf16(float(q - 8) * float(scale)) as dequant_w4a16_bf16 rounds it
+    (native/kernels/kernels.cu:867-892) and each accumulator sees the same K steps in the same order. Ragged M and N, a weight
+    row of zeros, groups with tiny values, the SwiGLU and the residual epilogues."""
+    import torch
+    r = rng(M + N + K)
+    X = oracle.rb(r.standard_normal((M, K), dtype=np.float32))
+    W = oracle.rb((r.standard_normal((N, K)) * 0.02).astype(np.float32))
+    W[1] = 0.0
+    W[2, :128] *= 1e-4
+    dX, dW = G.dev(X, 1), G.dev(W, 1)
+    packed = torch.zeros((N, K // 8), dtype=torch.int32, device="cuda")
+    scales = torch.zeros((N, K // 128), dtype=torch.float16, device="cuda")
+    G.call("dcd_k_quant_w4_g128", dW, packed, scales, N, K, None)
+    Wd = torch.zeros((N, K), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_dequant_w4_g128", packed, scales, Wd, N, K, None)
+    out_w = N // 2 if epi else N
+    resid = G.dev(oracle.rb(r.standard_normal((M, out_w), dtype=np.float32)), 1) if with_resid else None
+    want = torch.full((M, out_w), float("nan"), dtype=torch.bfloat16, device="cuda")
+    err = G.devi([0])
+    if with_resid:
+        G.call("dcd_k_gemm_bf16_tc_resid", dX, Wd, resid, want, M, N, K, out_w, G.sm_count(), err, None)
+    else:
+        G.call("dcd_k_gemm_bf16_tc", dX, Wd, want, M, N, K, out_w, epi, G.sm_count(), err, None)
+    pp = torch.zeros_like(packed)
+    st = torch.zeros((K // 128, N), dtype=torch.float16, device="cuda")
+    G.call("dcd_k_w4_repack", packed, scales, pp, st, N, K, None)
+    got = torch.full((M, out_w), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_gemm_w4a16_tc", dX, pp, st, resid, got, M, N, K, out_w, epi, G.sm_count(), err, None)
+    assert int(err.item()) == 0, "a bounded wait gave up inside the kernel"
+    assert not torch.isnan(got.float()).any()
+    again = torch.full((M, out_w), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_gemm_w4a16_tc", dX, pp, st, resid, again, M, N, K, out_w, epi, G.sm_count(), err, None)
+    assert torch.equal(again, got), "two runs of the fused kernel differ"
+    same = torch.equal(got, want)
+    if not same:
+        d = (got.float() - want.float()).abs()
+        bad = (d > 0).nonzero()
+        pytest.fail(f"{bad.shape[0]} of {got.numel()} differ; max abs {float(d.max())}; first at {bad[0].tolist()}: got {float(got[tuple(bad[0])])} want {float(want[tuple(bad[0])])}; "
+                    f"rows {bad[:, 0].unique()[:16].tolist()} cols {bad[:, 1].unique()[:16].tolist()}")
+
+
 # ---------------------------------------------------------------------------------------------
 # NVFP4
 # ---------------------------------------------------------------------------------------------
@@ -555,7 +603,7 @@ def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
     assert int(err.item()) == 0
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 1128, 1256])  # + 1000: scale copies on a thread of their own
 @pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 1024), (300, 776, 512), (2048, 5120, 1024), (77, 264, 5120), (130, 392, 768)])
 def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K, tile_n):
     """The native block-scaled FP4 GEMM against an f32 matmul of the dequantised operands (decode(code) * decode(scale)

@@ -457,3 +457,29 @@ def plug2(h, fake):
     t = h.submit_state_once((8, 8, 8, 8), [[1]])
     assert fake.entered.wait(20)
     return t, ev
+
+
+@pytest.mark.parametrize("cross", [0, 1])
+def test_cross_state_pass_under_memory_pressure_answers_like_the_sequential_order(dcd, mk, cross):
+    """Three 250 MiB states on a 700 MiB device, 100 MiB reserved per pass. One group at a time, the third capture offloads the
+    oldest cached state and succeeds. With cross_state_pass the first two states are in hand (not in the device tier, so nothing
+    can offload them) when the third does not fit: the scheduler serves and releases the two it holds, then acquires the third
+    alone. Both modes answer every request."""
+    fake = FakeEngine(dcd, total=700 * MIB)
+    h, fake = mk(fake, cross_state_pass=cross, batch_requests=8, batch_rows=64)
+    pt, ev = plug(h, fake)
+    A, B, Cc = [1] * 250, [2] * 250, [3] * 250
+    ta, tb, tc_ = h.submit_state_once(A, [[1], [2]]), h.submit_state_once(B, [[3]]), h.submit_state_once(Cc, [[4], [5]])
+    ev.set()
+    pt.result()
+    ra, rb, rc = ta.result(), tb.result(), tc_.result()
+    assert np.array_equal(ra, np.stack([fake.answer(A, [1]), fake.answer(A, [2])]))
+    assert np.array_equal(rb[0], fake.answer(B, [3]))
+    assert np.array_equal(rc, np.stack([fake.answer(Cc, [4]), fake.answer(Cc, [5])]))
+    s = h.stats()
+    assert (s["groups_failed"], s["fail_headroom"], s["fail_state_capture"], s["questions_failed"]) == (0, 0, 0, 0)
+    assert s["captures"] == 4 and s["offloads"] >= 1 and s["requests_miss"] == 4
+    assert s["cross_state_passes"] == (1 if cross else 0)
+    if cross:
+        assert fake.calls("readout_multi")[0][1] == (tuple(A), tuple(B))
+        assert fake.calls("readout")[-1][1] == tuple(Cc)
