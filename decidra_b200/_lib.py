@@ -167,6 +167,7 @@ SIGNATURES = {
     "dcd_k_nvfp4_quant_act_tiled": (I, [P, SZ, P, P, I, I, P]),
     "dcd_k_nvfp4_swiglu_quant_tiled": (I, [P, I, P, P, I, I, P]),
     "dcd_k_gemm_nvfp4_tc": (I, [P, P, P, P, P, I, I, I, I, P, I, P, I, P]),
+    "dcd_k_gemm_nvfp4_tc_tiled": (I, [P, P, P, P, P, I, I, I, I, P, I, P, I, P, P, P, P]),
     "dcd_k_gemm_fma": (I, [P, P, P, I, I, I, I, P]),
     "dcd_k_rmsnorm": (I, [P, P, P, I, I, F, I, I, P]),
     "dcd_k_add_rmsnorm": (I, [P, P, P, P, P, I, I, F, I, P]),

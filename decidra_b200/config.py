@@ -74,7 +74,8 @@ class Options(C.Structure):
         ("fp8_min_rows", C.c_int32),
         ("nvfp4_scale_copy", C.c_int32),
         ("w4a16_gemm", C.c_int32),
-        ("reserved", C.c_int32 * 4),
+        ("nvfp4_fusion", C.c_int32),
+        ("reserved", C.c_int32 * 3),
     ]
 
 

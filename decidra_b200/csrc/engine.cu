@@ -145,6 +145,7 @@ struct dcd_engine {
   bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
   bool nv4_native = false;             // ... on the block-scaled FP4 tensor-core GEMM (gemm_path 0) instead of dequantise + bf16 GEMM (2)
   uint8_t *xq = nullptr, *xsf = nullptr, *xsft = nullptr;  // activation codes, row-major scales, tiled scales
+  uint8_t *aq4 = nullptr, *asft4 = nullptr;                // second set: the SwiGLU activation quantised by the gate/up GEMM's epilogue
   void* xstage = nullptr;              // bf16 [Tm, max K]: activations after the NVFP4 round trip
   unsigned int* amax_tmp = nullptr;
   bool w4 = false;                     // precision 1: int4 g128 weights, dequantised per GEMM into wstage
@@ -313,8 +314,11 @@ struct Scope {
 template <typename T>
 int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, const TcTensorMap* tmB, const LayerW::Fp8W* fw,
          const LayerW::W4* g4, const LayerW::NV4* n4, void* C, int M, int N, int K, int ldc, int epi, bool x_quantised = false,
-         const void* resid = nullptr) {  // resid: C = bf16(resid + bf16(X W^T)), tensor-core bf16 / fp8 paths only
-  if (resid && (e->nv4 || !(e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K))))
+         const void* resid = nullptr, int x_set = 0, bool act_out = false) {
+  // resid: C = bf16(resid + bf16(X W^T)) in the epilogue (tensor-core paths). x_set: which of the two NVFP4 activation buffer sets
+  // holds a pre-quantised X (0: xq / xsft, 1: aq4 / asft4). act_out (native NVFP4, gate/up projection): the epilogue applies SwiGLU
+  // and writes the NVFP4 image of the activation into set 1 instead of C.
+  if (resid && !(e->nv4_native && n4->sft && nvfp4_tc_shape_ok(M, N, K)) && (e->nv4 || !(e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K))))
     return fail(e, DCD_E_INVALID, "internal: fused residual on a GEMM path without that epilogue");
   if (e->nv4_native && epi == 0 && n4->sft && nvfp4_tc_shape_ok(M, N, K)) {
     // NVFP4 W4A4 (Engine::nvfp4_gemm, native/src/engine.rs:3962-4131) on the block-scaled FP4 MMA: activations are
@@ -324,15 +328,18 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
       Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5625 * M * (double)K, 1);
       CK(e, launch_nvfp4_act_quant_tiled((const bf16*)X, (size_t)K, e->xq, e->xsft, M, K, e->stream), "nvfp4 activation quantisation");
     }
+    const uint8_t* xq = x_set ? e->aq4 : e->xq;
+    const uint8_t* xsf = x_set ? e->asft4 : e->xsft;
     TcTensorMap ta;
-    if (tc_make_tmap_fp8_a(&ta, e->xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
+    if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2)) return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an nvfp4 activation operand");
     Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
     const int bn = N >= 256 ? 256 : 128;
-    CK(e, nvfp4_gemm_launch(&ta, bn == 256 ? &n4->tm256 : &n4->tm, e->xsft, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream,
-                            bn + (e->o.nvfp4_scale_copy == 1 ? 0 : 1000)),
+    CK(e, nvfp4_gemm_launch(&ta, bn == 256 ? &n4->tm256 : &n4->tm, xsf, n4->sft, C, M, N, K, ldc, n4->alpha, e->sm_count, e->d_err, e->stream,
+                            bn + (e->o.nvfp4_scale_copy == 1 ? 0 : 1000), resid, act_out ? e->aq4 : nullptr, act_out ? e->asft4 : nullptr),
        "tcgen05 nvfp4 gemm");
     return DCD_OK;
   }
+  if (act_out) return fail(e, DCD_E_INVALID, "internal: fused SwiGLU quantisation on a GEMM that does not take the block-scaled path");
   if (x_quantised) return fail(e, DCD_E_INVALID, "internal: pre-quantised operand for a GEMM that does not take the block-scaled path");
   if (e->nv4) {
     // The same product by the long route (gemm_path 2, or a shape the native kernel does not take): both operands go through the
@@ -421,7 +428,14 @@ int run_layers(dcd_engine* e, const Pass& p) {
   const bool h_fused_quant = e->nv4_native && sizeof(T) == 2 && (H % 256) == 0 && H <= 8192;
   // bf16 / fp8 / w4a16 tensor-core GEMMs add the residual in their epilogue: the projection that closes a block writes the new
   // residual stream itself and the norm that follows reads one tensor instead of two
-  const bool fused_resid = tc && !e->nv4 && tc_shape_ok(T_, H, H);
+  const bool fuse4 = e->nv4_native && e->o.nvfp4_fusion != 1 && sizeof(T) == 2;  // the NVFP4 epilogue / producer fusions below
+  // ... the block-scaled kernel has the residual epilogue too, where all three closing projections take it
+  const bool resid4 = fuse4 && nvfp4_tc_shape_ok(T_, H, heads * hd) && nvfp4_tc_shape_ok(T_, H, e->vd) && nvfp4_tc_shape_ok(T_, H, e->I);
+  const bool fused_resid = (tc && !e->nv4 && tc_shape_ok(T_, H, H)) || resid4;
+  // ... its gate/up epilogue can apply SwiGLU and write the down projection's NVFP4 operand itself (set 1)
+  const bool act_epi4 = fuse4 && act_fused_quant && h_fused_quant && (e->I % 128) == 0 && e->gu_rows == 2 * e->I && nvfp4_tc_shape_ok(T_, e->gu_rows, H);
+  // ... and the gated norm writes the out projection's NVFP4 operand
+  const bool gnorm4 = fuse4 && dv == 128 && (e->vd % 256) == 0 && nvfp4_tc_shape_ok(T_, H, e->vd);
   // FP8 only in question passes with enough rows; capture and the per-row reference stay bf16
   // (native/src/engine.rs:4321-4326, fp8_min_rows :246-257)
   const bool q8 = e->fp8 && tc && p.mode == 1 && p.T >= e->o.fp8_min_rows;
@@ -544,17 +558,23 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       if (p.mode == 0 && li + 1 == c.num_layers) break;  // last capture layer: the state and conv tail are stored
       {
-        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->vd * e->esz * 3.0, 1);
-        CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
-                                      c.rms_eps, s), "rmsnorm_gated");
+        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->vd * e->esz * (gnorm4 ? 2.3 : 3.0), 1);
+        if (gnorm4)
+          CK(e, launch_rmsnorm_gated_nvfp4((const bf16*)e->bufA, (const bf16*)(big + e->conv_dim), e->gin_n, (const bf16*)w.gnorm, e->xq, e->xsft, T_, nv,
+                                           c.rms_eps, s), "rmsnorm_gated + nvfp4");
+        else
+          CK(e, launch_rmsnorm_gated<T>((const T*)e->bufA, big + e->conv_dim, e->gin_n, (const T*)w.gnorm, (T*)e->bufB, T_, nv, dv,
+                                        c.rms_eps, s), "rmsnorm_gated");
       }
-      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, fused_resid ? e->x1 : e->mix, T_, H, e->vd, H, 0, false,
+      rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, fused_resid ? e->x1 : e->mix, T_, H, e->vd, H, 0, gnorm4,
                    fused_resid ? e->x : nullptr);
       if (rc) return rc;
     }
     {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      if (fused_resid)
+      if (fused_resid && h_fused_quant)
+        CK(e, launch_rmsnorm_nvfp4((const bf16*)e->x1, (const bf16*)w.post_norm, e->xq, e->xsft, T_, H, c.rms_eps, s), "rmsnorm + nvfp4");
+      else if (fused_resid)
         CK(e, launch_rmsnorm<T>((const T*)e->x1, (const T*)w.post_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
       else if (h_fused_quant)
         CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x, (const bf16*)e->mix, (const bf16*)w.post_norm, (bf16*)e->x1, e->xq, e->xsft, T_, H, c.rms_eps, s),
@@ -566,6 +586,10 @@ int run_layers(dcd_engine* e, const Pass& p) {
     if (fused_swiglu) {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, &w.n_gu, e->act, T_, e->gu_rows, H, e->I, 1);
       if (rc) return rc;
+    } else if (act_epi4) {
+      // gate/up projection whose epilogue applies SwiGLU and leaves the activation as NVFP4 in set 1 (ldc = the activation width)
+      int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, &w.n_gu, nullptr, T_, e->gu_rows, H, e->I, 0, true, nullptr, 0, true);
+      if (rc) return rc;
     } else {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, nullptr, &w.g_gu, &w.n_gu, e->big, T_, e->gu_rows, H, e->gu_rows, 0, h_fused_quant);
       if (rc) return rc;
@@ -574,11 +598,13 @@ int run_layers(dcd_engine* e, const Pass& p) {
       else CK(e, launch_silu_mul_interleaved<T>((const T*)e->big, e->gu_rows, (T*)e->act, T_, e->I, s), "silu_mul");
     }
     int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, fused_resid ? e->x : e->mix, T_, H, e->I, H, 0, act_fused_quant,
-                     fused_resid ? e->x1 : nullptr);
+                     fused_resid ? e->x1 : nullptr, act_epi4 ? 1 : 0);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
-      if (fused_resid)
+      if (fused_resid && h_fused_quant)
+        CK(e, launch_rmsnorm_nvfp4((const bf16*)e->x, (const bf16*)e->layers[li + 1].input_norm, e->xq, e->xsft, T_, H, c.rms_eps, s), "rmsnorm + nvfp4");
+      else if (fused_resid)
         CK(e, launch_rmsnorm<T>((const T*)e->x, (const T*)e->layers[li + 1].input_norm, (T*)e->h, T_, H, c.rms_eps, true, s), "rmsnorm");
       else if (h_fused_quant)
         CK(e, launch_add_rmsnorm_nvfp4((const bf16*)e->x1, (const bf16*)e->mix, (const bf16*)e->layers[li + 1].input_norm, (bf16*)e->x, e->xq, e->xsft,
@@ -757,6 +783,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (o.fp8_min_rows <= 0) o.fp8_min_rows = 512;
   if (o.nvfp4_scale_copy < 0 || o.nvfp4_scale_copy > 2) return fail(nullptr, DCD_E_INVALID, "nvfp4_scale_copy must be 0, 1 or 2");
   if (o.w4a16_gemm < 0 || o.w4a16_gemm > 2) return fail(nullptr, DCD_E_INVALID, "w4a16_gemm must be 0, 1 or 2");
+  if (o.nvfp4_fusion < 0 || o.nvfp4_fusion > 1) return fail(nullptr, DCD_E_INVALID, "nvfp4_fusion must be 0 or 1");
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -1000,6 +1027,8 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
     CRA(e->xq, Tm * (size_t)e->max_k / 2, false, ws);
     CRA(e->xsf, Tm * (size_t)e->max_k / 16, false, ws);
     CRA(e->xsft, nvfp4_sf_tiled_bytes((int)Tm, (e->max_k + 63) / 64 * 64) + 512, false, ws);
+    CRA(e->aq4, Tm * (size_t)e->I / 2, false, ws);
+    CRA(e->asft4, nvfp4_sf_tiled_bytes((int)Tm, (e->I + 63) / 64 * 64) + 512, false, ws);
   }
   if (e->fp8) {
     CRA(e->aq, Tm * (size_t)e->max_k, false, ws);

@@ -49,7 +49,10 @@ template <int BN> struct Cfg {
   // UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
   static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
-constexpr int NUM_THREADS = 288;
+constexpr int NUM_THREADS = 288;        // BN 128: warps 0 / 6 / 7 producers, 1 MMA issuer, 2-5 epilogue, 8 scale copier
+constexpr int NUM_THREADS_WIDE = 416;   // BN 256: four more epilogue warps (9-12). There is one accumulator, so the next tile's MMAs wait
+                                        // for the epilogue: eight warps first drain it into registers as bf16 pairs (32 rows x 128 columns
+                                        // each), hand it back, and only then add, activate, quantise and store, beside the next main loop
 constexpr uint32_t SF_COL = 256;
 constexpr int GROUP_M = 16;
 
@@ -86,14 +89,48 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   n_idx = r / gsize;
 }
 
+// Activation quantiser for the block-scaled GEMM: bf16 rows (tensor scale 1) -> e2m1 codes [rows, K/2] and e4m3 scales
+// written straight into the 128 x 4 tiled layout. Same rule as quant_nvfp4_act_bf16 / fp4_encode
+// (native/kernels/kernels.cu:222-277): sf = e4m3_satfinite(max(absmax16/6, 1e-10)), code = fp4_encode(v / decode(sf)).
+// The division is replaced by comparing |v| with threshold * decode(sf): v has an 8-bit significand, decode(sf) a 4-bit
+// one and the thresholds at most 3 bits, so the products are exact and v / decode(sf) can only round onto a threshold
+// when it equals it; both forms give the same code, including decode(sf) = 0 (every comparison true: code 7, as
+// fp4_encode gives for inf and NaN). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
+// 16 values (already bf16-representable) -> scale byte and two words of codes
+__device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  const float sf = fmaxf(m / 6.0f, 1e-10f);
+  const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+  const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
+  sb_out = sb;
+  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
+  c0 = 0;
+  c1 = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = fabsf(v[i]);
+    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
+    e |= v[i] < 0.f ? 8u : 0u;
+    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
+  }
+}
 // SPLIT: the scale tiles are copied into TMEM by a thread of their own (warp 8) that signals the MMA issuer through one more
 // barrier per stage, so that the copies of a K block are not queued in front of that block's MMAs on the issuer's in-order
 // stream of tensor-core work.
-template <int BN, bool SPLIT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// EPI 0: C[M, ldc] = bf16(alpha * acc), or with resid (bf16 [M, ldc]): bf16(resid + bf16(alpha * acc)), the residual add of a
+// pre-norm block (add_bf16 / add_rmsnorm_bf16, native/kernels/kernels.cu:378-404, 485-490) applied to the rounded product.
+// EPI 1 (BN = 256; W rows interleaved per tile as 128 gate rows then the matching 128 up rows): the tile's 128 activations
+// bf16(bf16(silu(bf16(gate))) * bf16(up)) (silu_mul_bf16, native/kernels/kernels.cu:492-501) are quantised to NVFP4 on the spot,
+// 16 at a time (quant_nvfp4_act_bf16's rule), as the down projection's operand: codes to q_packed [M, ldc / 2], scales into the
+// 128 x 4 tiled layout q_tiled (ldc = the activation width I). Neither the gate/up matrix nor the bf16 activation reach memory.
+template <int BN, bool SPLIT, int EPI>
+__global__ void __launch_bounds__(BN == 256 ? NUM_THREADS_WIDE : NUM_THREADS, 1)
 gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const uint8_t* __restrict__ sfa,
                      const uint8_t* __restrict__ sfb, bf16* __restrict__ C, int M, int N, int K, int ldc, const float* __restrict__ alpha,
-                     int* __restrict__ err) {
+                     int* __restrict__ err, const bf16* __restrict__ resid, uint8_t* __restrict__ q_packed, uint8_t* __restrict__ q_tiled) {
   using CF = Cfg<BN>;
   constexpr int STAGES = CF::STAGES, ACC_STAGES = CF::ACC_STAGES, NB = CF::NB;
   constexpr uint32_t B_BYTES = CF::B_BYTES, STAGE_BYTES = CF::STAGE_BYTES;
@@ -124,7 +161,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
     for (int a = 0; a < ACC_STAGES; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), ACC_STAGES == 1 ? 8 : 4);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -165,7 +202,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
       }
     }
-  } else if (warp == 0 || warp >= 6) {
+  } else if (warp == 0 || warp == 6 || warp == 7) {
     if (lane == 0) {
       // warp 0: X codes (and the expected byte count of the stage); warp 6: W codes; warp 7: both scale sets
       int stage = 0;
@@ -235,36 +272,118 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_idx, n_idx;
       tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      const int row = m_idx * BM + lane_base + lane;
       ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = m_idx * BM + lane_base + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(acc * BN);
-      bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (row < M) {
+      if constexpr (ACC_STAGES == 1) {
+        // Drain first: four 32-column chunks of this thread's row, scaled, rounded to bf16 and packed in pairs. EPI 0: the chunks
+        // of one half of the tile; EPI 1: two gate chunks and the two up chunks that go with them.
+        const int slot = warp < 9 ? 0 : 1;
+        uint32_t pk[64];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = n_idx * BN + c * 32 + v * 8;
-            if (col + 8 <= N) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * al, __uint_as_float(r[v * 8 + 1]) * al);
-              o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * al, __uint_as_float(r[v * 8 + 3]) * al);
-              o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * al, __uint_as_float(r[v * 8 + 5]) * al);
-              o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * al, __uint_as_float(r[v * 8 + 7]) * al);
-              *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
+        for (int i = 0; i < 4; ++i) {
+          const int c = EPI == 1 ? (i < 2 ? 2 * slot + i : 2 + 2 * slot + i) : 4 * slot + i;
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pk[16 * i + j] = pack_bf16(__uint_as_float(r[2 * j]) * al, __uint_as_float(r[2 * j + 1]) * al);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));  // the next tile's MMAs may overwrite the accumulator from here on
+        if constexpr (EPI == 0) {
+          if (row < M) {
+            bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = 4 * slot + i;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const int col = n_idx * BN + c * 32 + v * 8;
+                if (col + 8 <= N) {
+                  uint32_t o[4] = {pk[16 * i + 4 * v], pk[16 * i + 4 * v + 1], pk[16 * i + 4 * v + 2], pk[16 * i + 4 * v + 3]};
+                  if (resid) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(resid + (size_t)row * ldc + col);
+                    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                      o[j] = pack_bf16(__uint_as_float(o[j] << 16) + __uint_as_float(rw[j] << 16),
+                                       __uint_as_float(o[j] & 0xffff0000u) + __uint_as_float(rw[j] & 0xffff0000u));
+                  }
+                  *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+              }
+            }
+          }
+        } else {
+          // gate = columns [0,128), up = columns [128,256) of this tile -> 128 activations per row; gate chunk c and up chunk c
+          // give outputs [32 c, 32 c + 32): two scale groups = 16 bytes of codes and two bytes of the tiled scale layout
+          const int chunks = ldc / 64;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int c = 2 * slot + i;
+            uint8_t* prow = q_packed + (size_t)row * (ldc / 2) + (size_t)n_idx * (BN / 4) + c * 16;
+            uint32_t sb2 = 0u;
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t gw = pk[16 * i + 8 * grp + j], uw = pk[32 + 16 * i + 8 * grp + j];
+                const float g0 = __uint_as_float(gw << 16), g1 = __uint_as_float(gw & 0xffff0000u);
+                const float u0 = __uint_as_float(uw << 16), u1 = __uint_as_float(uw & 0xffff0000u);
+                v[2 * j] = Ty<bf16>::rnd(Ty<bf16>::rnd(__fdividef(g0, 1.0f + __expf(-g0))) * u0);
+                v[2 * j + 1] = Ty<bf16>::rnd(Ty<bf16>::rnd(__fdividef(g1, 1.0f + __expf(-g1))) * u1);
+              }
+              uint32_t c0, c1, sb;
+              quant_group16(v, c0, c1, sb);
+              if (row < M) *reinterpret_cast<uint2*>(prow + grp * 8) = make_uint2(c0, c1);
+              sb2 |= sb << (8 * grp);
+            }
+            if (row < M) {
+              uint8_t* trow = q_tiled + ((size_t)(row >> 7) * chunks + (size_t)n_idx * 2 + (c >> 1)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (c & 1) * 2;
+              *reinterpret_cast<uint16_t*>(trow) = (uint16_t)sb2;
             }
           }
         }
+      } else {
+        // two accumulators: this epilogue already runs beside the next tile's main loop
+        bf16* crow = C + (size_t)row * ldc + (size_t)n_idx * BN;
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = n_idx * BN + c * 32 + v * 8;
+              if (col + 8 <= N) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * al;
+                if (resid) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(resid + (size_t)row * ldc + col);
+                  const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] = Ty<bf16>::rnd(f[2 * j]) + __uint_as_float(rw[j] << 16);
+                    f[2 * j + 1] = Ty<bf16>::rnd(f[2 * j + 1]) + __uint_as_float(rw[j] & 0xffff0000u);
+                  }
+                }
+                *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -296,34 +415,6 @@ __global__ void sf_tile_kernel(const uint8_t* __restrict__ lin, uint8_t* __restr
   tiled[i] = r < rows ? lin[(size_t)r * groups + g] : (uint8_t)0;
 }
 
-// Activation quantiser for the block-scaled GEMM: bf16 rows (tensor scale 1) -> e2m1 codes [rows, K/2] and e4m3 scales
-// written straight into the 128 x 4 tiled layout. Same rule as quant_nvfp4_act_bf16 / fp4_encode
-// (native/kernels/kernels.cu:222-277): sf = e4m3_satfinite(max(absmax16/6, 1e-10)), code = fp4_encode(v / decode(sf)).
-// The division is replaced by comparing |v| with threshold * decode(sf): v has an 8-bit significand, decode(sf) a 4-bit
-// one and the thresholds at most 3 bits, so the products are exact and v / decode(sf) can only round onto a threshold
-// when it equals it; both forms give the same code, including decode(sf) = 0 (every comparison true: code 7, as
-// fp4_encode gives for inf and NaN). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
-// 16 values (already bf16-representable) -> scale byte and two words of codes
-__device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
-  const float sf = fmaxf(m / 6.0f, 1e-10f);
-  const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
-  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
-  const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
-  sb_out = sb;
-  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
-  c0 = 0;
-  c1 = 0;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = fabsf(v[i]);
-    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
-    e |= v[i] < 0.f ? 8u : 0u;
-    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
-  }
-}
 __device__ __forceinline__ void unpack16(const uint4& lo, const uint4& hi, float (&v)[16]) {
   const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
@@ -393,10 +484,15 @@ bool nvfp4_tc_shape_ok(int M, int N, int K) { return M > 0 && N > 0 && K > 0 && 
 size_t nvfp4_sf_tiled_bytes(int rows, int K) { return (size_t)((rows + 255) / 256) * 2 * (K / 64) * 512; }
 
 cudaError_t nvfp4_gemm_prepare_device() {
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<128>::SMEM_BYTES));
-  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<256>::SMEM_BYTES));
+#define NVG_SMEM(BN_, SP_, EPI_) \
+  CUDA_TRY(cudaFuncSetAttribute(nvg::gemm_nvfp4_tc_kernel<BN_, SP_, EPI_>, cudaFuncAttributeMaxDynamicSharedMemorySize, nvg::Cfg<BN_>::SMEM_BYTES))
+  NVG_SMEM(128, false, 0);
+  NVG_SMEM(128, true, 0);
+  NVG_SMEM(256, false, 0);
+  NVG_SMEM(256, true, 0);
+  NVG_SMEM(256, false, 1);
+  NVG_SMEM(256, true, 1);
+#undef NVG_SMEM
   return cudaSuccess;
 }
 cudaError_t launch_nvfp4_act_quant_tiled(const bf16* x, size_t x_stride, uint8_t* packed, uint8_t* tiled, int rows, int K, cudaStream_t s) {
@@ -424,21 +520,24 @@ cudaError_t launch_nvfp4_sf_tile(const uint8_t* lin, uint8_t* tiled, int rows, i
 // tmA: byte map over the X codes [M, K/2] with 128-row boxes (tc_make_tmap_fp8_a); tmB: the same over the W codes with bn-row boxes
 // (tc_make_tmap_fp8_a for bn 128, tc_make_tmap_fp8_b for bn 256).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
-                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn) {
+                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn, const void* resid,
+                              uint8_t* q_packed, uint8_t* q_tiled) {
   const bool split = bn >= 1000;  // bn 1128 / 1256: the variant with the scale copies on a thread of their own
   if (split) bn -= 1000;
+  const bool swiglu_quant = q_packed != nullptr;
   if (!nvfp4_tc_shape_ok(M, N, K) || (bn != 128 && bn != 256)) return cudaErrorInvalidValue;
+  if (swiglu_quant && (bn != 256 || resid || !q_tiled || (N % 256) || (ldc % 128) || N != 2 * ldc)) return cudaErrorInvalidValue;
   const int num_tiles = ((M + nvg::BM - 1) / nvg::BM) * ((N + bn - 1) / bn);
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (bn == 128 && !split)
-    nvg::gemm_nvfp4_tc_kernel<128, false><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
-  else if (bn == 128)
-    nvg::gemm_nvfp4_tc_kernel<128, true><<<grid, nvg::NUM_THREADS, nvg::Cfg<128>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
-  else if (!split)
-    nvg::gemm_nvfp4_tc_kernel<256, false><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
-  else
-    nvg::gemm_nvfp4_tc_kernel<256, true><<<grid, nvg::NUM_THREADS, nvg::Cfg<256>::SMEM_BYTES, stream>>>(a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err);
+  const bf16* rs = (const bf16*)resid;
+#define NVG_LAUNCH(BN_, SP_, EPI_)                                                                                                              \
+  nvg::gemm_nvfp4_tc_kernel<BN_, SP_, EPI_><<<grid, BN_ == 256 ? nvg::NUM_THREADS_WIDE : nvg::NUM_THREADS, nvg::Cfg<BN_>::SMEM_BYTES, stream>>>( \
+      a, b, sfa_tiled, sfb_tiled, (bf16*)C, M, N, K, ldc, alpha, err, rs, q_packed, q_tiled)
+  if (swiglu_quant) { if (split) NVG_LAUNCH(256, true, 1); else NVG_LAUNCH(256, false, 1); }
+  else if (bn == 128) { if (split) NVG_LAUNCH(128, true, 0); else NVG_LAUNCH(128, false, 0); }
+  else { if (split) NVG_LAUNCH(256, true, 0); else NVG_LAUNCH(256, false, 0); }
+#undef NVG_LAUNCH
   return cudaGetLastError();
 }

@@ -49,8 +49,11 @@ cudaError_t launch_nvfp4_act_quant_tiled(const __nv_bfloat16* x, size_t x_stride
 // quantiser: codes [rows, I/2] + tiled scales of the [rows, I] activation. I % 128 == 0.
 cudaError_t launch_nvfp4_swiglu_quant_tiled(const __nv_bfloat16* gu, int gu_stride, uint8_t* packed, uint8_t* tiled, int rows, int I, cudaStream_t s);
 // bn: output tile width, 128 or 256; tmB must have bn-row boxes (tc_make_tmap_fp8_a / tc_make_tmap_fp8_b over the codes).
+// resid (optional, bf16 [M, ldc]): C = bf16(resid + bf16(alpha * acc)). q_packed / q_tiled (optional, bn 256, N = 2 * ldc, W rows interleaved
+// 128 gate / 128 up per tile): instead of C, the NVFP4 image of the SwiGLU activation [M, ldc] (codes + tiled scales).
 cudaError_t nvfp4_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, const uint8_t* sfa_tiled, const uint8_t* sfb_tiled, void* C, int M,
-                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn);
+                              int N, int K, int ldc, const float* alpha, int sm_count, int* err, cudaStream_t stream, int bn,
+                              const void* resid = nullptr, uint8_t* q_packed = nullptr, uint8_t* q_tiled = nullptr);
 
 // W4A16 GEMM without a bf16 copy of W (gemm_w4a16.cu): int4 group-128 weights in the engine's own image (words with the nibble
 // order k0 k2 k4 k6 k1 k3 k5 k7, fp16 scales transposed to [K/128][N]); bit-identical to dequantising and running the bf16 GEMM.

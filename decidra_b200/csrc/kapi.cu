@@ -109,6 +109,17 @@ int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, co
   return rc_of(ce);
 }
 
+int dcd_k_gemm_nvfp4_tc_tiled(const void* xq, const void* x_tiled, const void* wq, const void* w_tiled, void* C, int M, int N, int K, int ldc,
+                              const float* alpha, int sm_count, int* err, int tile_n, const void* resid, void* q_packed, void* q_tiled, void* stream) {
+  const int tile_w = tile_n >= 1000 ? tile_n - 1000 : tile_n;
+  if (!nvfp4_tc_shape_ok(M, N, K) || sm_count <= 0 || (tile_w != 128 && tile_w != 256)) return DCD_E_INVALID;
+  if (nvfp4_gemm_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap ta, tb;
+  if (tc_make_tmap_fp8_a(&ta, xq, M, K / 2) || (tile_w == 128 ? tc_make_tmap_fp8_a(&tb, wq, N, K / 2) : tc_make_tmap_fp8_b(&tb, wq, N, K / 2))) return DCD_E_CUDA;
+  return rc_of(nvfp4_gemm_launch(&ta, &tb, (const uint8_t*)x_tiled, (const uint8_t*)w_tiled, C, M, N, K, ldc, alpha, sm_count, err, S(stream), tile_n, resid,
+                                 (uint8_t*)q_packed, (uint8_t*)q_tiled));
+}
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

@@ -347,10 +347,37 @@ __global__ void rmsnorm_gated_kernel(const T* __restrict__ x, const T* __restric
     Ty<T>::st(orow + j, scaled * Ty<T>::rnd(silu_f(g)));
   }
 }
+// 16 values (bf16-representable) -> e4m3 scale byte and 16 e2m1 codes in two words; the rule of quant_nvfp4_act_bf16 / fp4_encode
+// (native/kernels/kernels.cu:222-277) with tensor scale 1 and the division replaced by exact threshold products.
+__device__ __forceinline__ void nvfp4_encode_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  const float sf = fmaxf(m / 6.0f, 1e-10f);
+  const uint8_t sb = (uint8_t)__nv_cvt_float_to_fp8(sf, __NV_SATFINITE, __NV_E4M3);
+  const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
+  const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
+  sb_out = sb;
+  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
+  c0 = 0;
+  c1 = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = fabsf(v[i]);
+    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
+    e |= v[i] < 0.f ? 8u : 0u;
+    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
+  }
+}
+
 // bf16, cols == 128: 8 lanes per row, 16 consecutive elements per lane (16-byte loads and stores); same arithmetic.
+// QUANT: instead of the bf16 rows, their NVFP4 image as the out-projection's operand: a lane's 16 outputs are one scale group;
+// codes to q_packed [tokens, heads * 64] bytes, scale bytes into the 128 x 4 tiled layout of the [tokens, heads * 128] matrix.
+template <bool QUANT>
 __global__ void __launch_bounds__(256) rmsnorm_gated_vec128_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int z_stride,
                                                                     const bf16* __restrict__ w, bf16* __restrict__ out, int rows, int heads,
-                                                                    float eps) {
+                                                                    float eps, uint8_t* __restrict__ q_packed = nullptr,
+                                                                    uint8_t* __restrict__ q_tiled = nullptr) {
   // 8 lanes per row, 16 consecutive elements (two 16-byte vectors) per lane: three shuffle steps per row instead of five
   const int row = blockIdx.x * 32 + (threadIdx.x >> 3);
   const int sub = threadIdx.x & 7;
@@ -380,7 +407,18 @@ __global__ void __launch_bounds__(256) rmsnorm_gated_vec128_kernel(const bf16* _
     const float scaled = Ty<bf16>::rnd(normed * wf[j]);
     y[j] = scaled * Ty<bf16>::rnd(silu_fast(zf[j]));
   }
-  if (live) {
+  if constexpr (QUANT) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = Ty<bf16>::rnd(y[j]);
+    uint32_t c0, c1, sb;
+    nvfp4_encode_group16(v, c0, c1, sb);
+    if (live) {
+      const int K = heads * 128, g = h * 8 + sub;  // scale group of this lane inside the token's row
+      *reinterpret_cast<uint2*>(q_packed + (size_t)t * (K >> 1) + (size_t)g * 8) = make_uint2(c0, c1);
+      q_tiled[((size_t)(t >> 7) * (K >> 6) + (g >> 2)) * 512 + (t & 31) * 16 + ((t & 127) >> 5) * 4 + (g & 3)] = (uint8_t)sb;
+    }
+  } else if (live) {
     uint4* op = reinterpret_cast<uint4*>(out + (size_t)row * 128) + sub * 2;
     op[0] = pack8(*reinterpret_cast<float(*)[8]>(&y[0]));
     op[1] = pack8(*reinterpret_cast<float(*)[8]>(&y[8]));
@@ -393,11 +431,20 @@ cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* 
   if constexpr (sizeof(T) == 2) {
     if (cols == 128 && rows > 0 && (z_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(z) % 16) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
         (reinterpret_cast<uintptr_t>(w) % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
-      rmsnorm_gated_vec128_kernel<<<(rows + 31) / 32, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, eps);
+      rmsnorm_gated_vec128_kernel<false><<<(rows + 31) / 32, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, eps);
       return cudaGetLastError();
     }
   }
   rmsnorm_gated_kernel<T><<<(rows + 7) / 8, 256, 0, s>>>(x, z, z_stride, w, out, rows, heads, cols, eps);
+  return cudaGetLastError();
+}
+// The gated norm writing the out-projection's NVFP4 operand (bf16 inputs, value heads of 128; heads * 128 a multiple of 64).
+cudaError_t launch_rmsnorm_gated_nvfp4(const bf16* x, const bf16* z, int z_stride, const bf16* w, uint8_t* q_packed, uint8_t* q_tiled, int tokens, int heads,
+                                       float eps, cudaStream_t s) {
+  const int rows = tokens * heads;
+  if (rows <= 0) return cudaSuccess;
+  if ((z_stride % 8) || (reinterpret_cast<uintptr_t>(z) % 16) || (reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(w) % 16)) return cudaErrorInvalidValue;
+  rmsnorm_gated_vec128_kernel<true><<<(rows + 31) / 32, 256, 0, s>>>(x, z, z_stride, w, nullptr, rows, heads, eps, q_packed, q_tiled);
   return cudaGetLastError();
 }
 template cudaError_t launch_rmsnorm_gated<float>(const float*, const float*, int, const float*, float*, int, int, int, float, cudaStream_t);

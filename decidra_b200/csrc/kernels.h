@@ -21,6 +21,8 @@ cudaError_t launch_add_rmsnorm_nvfp4(const __nv_bfloat16* x, const __nv_bfloat16
                                      uint8_t* q_packed, uint8_t* q_tiled, int rows, int cols, float eps, cudaStream_t s);
 template <typename T>
 cudaError_t launch_final_norm_rows(const T* x, const T* w, float* out, const int32_t* rows_idx, int B, int cols, float eps, cudaStream_t s);
+cudaError_t launch_rmsnorm_gated_nvfp4(const __nv_bfloat16* x, const __nv_bfloat16* z, int z_stride, const __nv_bfloat16* w, uint8_t* q_packed, uint8_t* q_tiled,
+                                       int tokens, int heads, float eps, cudaStream_t s);
 template <typename T>
 cudaError_t launch_rmsnorm_gated(const T* x, const T* z, int z_stride, const T* w, T* out, int tokens, int heads, int cols, float eps, cudaStream_t s);
 template <typename T>

@@ -45,6 +45,17 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
 }
+// The same bounded wait for warps that wait long and are many (a wide epilogue waiting out a whole main loop): sleeping between polls
+// leaves the issue slots to the warps that feed the tensor core. 2^21 polls x >= 256 ns bounds the wait near the plain one's.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (WAIT_LIMIT >> 1); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(256);
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y) {
   asm volatile(

@@ -86,7 +86,10 @@ typedef struct dcd_options {
                                issuer, in front of each K block's MMAs; 2 = a thread of its own, signalling the issuer per stage */
   int32_t w4a16_gemm;       /* precision 1: 0 = default (the GEMM that dequantises in its producer warps for passes of up to 640 rows),
                                1 = always dequantise into the bf16 stage first, 2 = always the fused kernel (K % 128 == 0) */
-  int32_t reserved[4];
+  int32_t nvfp4_fusion;     /* precision 3, block-scaled kernel: 0 = default: the residual add rides in the epilogue of the projection that
+                               closes a block, the gate/up epilogue applies SwiGLU and writes the down projection's NVFP4 operand, the gated
+                               norm writes the out projection's NVFP4 operand; 1 = those steps as kernels of their own (same bits) */
+  int32_t reserved[3];
 } dcd_options;
 
 typedef struct dcd_info {
@@ -499,6 +502,17 @@ DCD_API int dcd_k_nvfp4_swiglu_quant_tiled(const void* gu, int gu_stride, void* 
  * tile_n: output tile width, 128 or 256; + 1000 selects the variant whose scale copies are issued by a thread of their own. */
 DCD_API int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void* wq, const void* w_scales, void* C, int M, int N, int K,
                                 int ldc, const float* alpha, int sm_count, int* err, int tile_n, void* stream);
+/* The same GEMM on scales already in the 128 x 4 tiled layout (dcd_k_nvfp4_tile_scales, dcd_k_nvfp4_quant_act_tiled), with the
+ * epilogues the engine's NVFP4 layers use; nothing is allocated. tile_n as above.
+ *  - resid (bf16 [M, ldc], may be NULL): C = bf16(resid + bf16(alpha * acc)), the residual add of a pre-norm block
+ *    (add_bf16, native/kernels/kernels.cu:485-490) applied to the rounded product;
+ *  - q_packed / q_tiled (both or neither; tile_n 256, N = 2 * ldc, ldc % 128 == 0, resid NULL): W holds, per 256 rows, 128 gate
+ *    rows then the matching 128 up rows; the SwiGLU activation (silu_mul_bf16, native/kernels/kernels.cu:492-501) of each
+ *    tile is quantised to NVFP4 in the epilogue: codes to q_packed [M, ldc / 2], scales to q_tiled (tiled layout of an
+ *    [M, ldc] operand); C is not written. */
+DCD_API int dcd_k_gemm_nvfp4_tc_tiled(const void* xq, const void* x_tiled, const void* wq, const void* w_tiled, void* C, int M, int N, int K,
+                                      int ldc, const float* alpha, int sm_count, int* err, int tile_n, const void* resid, void* q_packed,
+                                      void* q_tiled, void* stream);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

@@ -632,6 +632,57 @@ def test_gemm_nvfp4_block_scaled_vs_dequantised_matmul(G, oracle, M, N, K, tile_
     np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2 * float(np.abs(want).max()) / 8)
 
 
+@pytest.mark.parametrize("M,N,K,tile_n", [(300, 768, 512, 1256), (300, 768, 512, 256), (300, 776, 512, 1128), (1100, 5120, 1024, 1256), (77, 512, 5120, 1256)])
+def test_gemm_nvfp4_epilogues_bit_identical_to_the_separate_kernels(G, oracle, M, N, K, tile_n):
+    """The residual epilogue equals the plain GEMM followed by a bf16 add; the SwiGLU + quantisation epilogue (256-wide tiles)
+    equals the plain GEMM followed by dcd_k_nvfp4_swiglu_quant_tiled: same bytes of codes and of tiled scales."""
+    import torch
+    r = rng(M + N + K)
+    X = (r.standard_normal((M, K)) * np.exp(r.uniform(-1, 1, (M, 1)))).astype(np.float32)
+    W = (r.standard_normal((N, K)) * 0.05).astype(np.float32)
+    xq = torch.zeros((M, K // 2), dtype=torch.uint8, device="cuda"); xs = torch.zeros((M, K // 16), dtype=torch.uint8, device="cuda")
+    wq = torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda"); ws = torch.zeros((N, K // 16), dtype=torch.uint8, device="cuda")
+    wglobal = 2688.0 / float(np.abs(W).max())
+    G.call("dcd_k_nvfp4_quant_rows", G.dev(X, 1), K, C.c_float(1.0), xq, xs, M, K, None)
+    G.call("dcd_k_nvfp4_quant_rows", G.dev(W, 1), K, C.c_float(wglobal), wq, ws, N, K, None)
+
+    def tiled(sc, rows):
+        t = torch.zeros(((rows + 127) // 128) * (K // 64) * 512, dtype=torch.uint8, device="cuda")
+        G.call("dcd_k_nvfp4_tile_scales", sc, t, rows, K, None)
+        return t
+
+    xt, wt = tiled(xs, M), tiled(ws, N)
+    alpha = torch.tensor([1.0 / wglobal], dtype=torch.float32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plain = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_gemm_nvfp4_tc_tiled", xq, xt, wq, wt, plain, M, N, K, N, alpha, G.sm_count(), err, tile_n, None, None, None, None)
+    ref = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_gemm_nvfp4_tc", xq, xs, wq, ws, ref, M, N, K, N, alpha, G.sm_count(), err, tile_n, None)
+    assert torch.equal(plain, ref)
+    resid = torch.from_numpy(r.standard_normal((M, N)).astype(np.float32)).cuda().bfloat16()
+    fused = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_gemm_nvfp4_tc_tiled", xq, xt, wq, wt, fused, M, N, K, N, alpha, G.sm_count(), err, tile_n, resid, None, None, None)
+    assert torch.equal(fused, (resid.float() + plain.float()).bfloat16())
+    inplace = resid.clone()  # the engine adds into the residual stream in place
+    G.call("dcd_k_gemm_nvfp4_tc_tiled", xq, xt, wq, wt, inplace, M, N, K, N, alpha, G.sm_count(), err, tile_n, inplace, None, None, None)
+    assert torch.equal(inplace, fused)
+    if tile_n % 1000 == 256 and N % 256 == 0:
+        inter = N // 2
+
+        def buffers():
+            return (torch.full((M, inter // 2), 0xAA, dtype=torch.uint8, device="cuda"),
+                    torch.zeros(((M + 127) // 128) * (inter // 64) * 512, dtype=torch.uint8, device="cuda"))
+
+        want_p, want_t = buffers()
+        G.call("dcd_k_nvfp4_swiglu_quant_tiled", plain, N, want_p, want_t, M, inter, None)
+        got_p, got_t = buffers()
+        G.call("dcd_k_gemm_nvfp4_tc_tiled", xq, xt, wq, wt, None, M, N, K, inter, alpha, G.sm_count(), err, tile_n, None, got_p, got_t, None)
+        torch.cuda.synchronize()
+        assert torch.equal(got_p, want_p)
+        assert torch.equal(got_t, want_t)
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("rows,K", [(3, 128), (300, 512), (128, 5120)])
 def test_nvfp4_scale_tiling_bit_exact(G, oracle, rows, K):
     import torch
