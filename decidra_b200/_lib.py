@@ -179,6 +179,8 @@ SIGNATURES = {
     "dcd_k_gdn_recurrent": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "dcd_k_gdn_chunked": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "dcd_k_gdn_chunked_tc": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P, I, P]),
+    "dcd_k_gdn_wy_tc": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P, I, P]),
+    "dcd_k_gdn_wy_tc_phases": (I, [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P, I, P, P]),
     "dcd_k_qk_norm_rope": (I, [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F, P, I, P]),
     "dcd_k_attention": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I, P]),
     "dcd_k_attention_tc": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, P, P]),

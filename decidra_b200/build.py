@@ -13,7 +13,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libdecidra_b200.so"
-CUDA_SOURCES = ["gemm_tcgen05.cu", "gemm_nvfp4.cu", "gemm_w4a16.cu", "attn_tcgen05.cu", "attn_noalloc.cu", "gdn_chunked.cu", "gdn_tcgen05.cu", "kernels.cu", "engine.cu", "kapi.cu"]
+CUDA_SOURCES = ["gemm_tcgen05.cu", "gemm_nvfp4.cu", "gemm_w4a16.cu", "attn_tcgen05.cu", "attn_noalloc.cu", "gdn_chunked.cu", "gdn_tcgen05.cu", "gdn_wy.cu", "kernels.cu", "engine.cu", "kapi.cu"]
 CXX_SOURCES = ["host_logic.cpp", "checkpoint.cpp", "scheduler.cpp", "prompt.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -139,7 +139,7 @@ struct dcd_engine {
   float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
-  bool attn_tc = false, gdn_chunked = false, gdn_tc = false;
+  bool attn_tc = false, gdn_chunked = false, gdn_tc = false, gdn_wy = false;
   TcTensorMap tm_gdn[3];  // q/k/conv views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
   int tm_gdn_tokens = -1;
   bool nv4 = false;                    // precision 3: NVFP4 weights and NVFP4-quantised activations (W4A4 semantics)
@@ -546,7 +546,9 @@ int run_layers(dcd_engine* e, const Pass& p) {
           const Group& g = groups[gi];
           const float* seed = p.mode == 1 ? g.st->gstate[li] : nullptr;
           const int32_t* cu = e->d_cu + g.q0;
-          if (e->gdn_tc)
+          if (e->gdn_wy)
+            CK(e, launch_gdn_wy<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, s), "gdn_wy");
+          else if (e->gdn_tc)
             CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, s), "gdn_tc");
           else if (e->gdn_chunked)
             CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, dk,
@@ -867,8 +869,10 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->nv4_native = e->nv4 && o.gemm_path == 0;
   if (e->nv4_native) CRE(nvfp4_gemm_prepare_device(), "nvfp4 GEMM shared-memory attribute");
   if (e->w4 && o.gemm_path == 0) CRE(w4a16_gemm_prepare_device(), "w4a16 GEMM shared-memory attribute");
-  e->gdn_tc = e->bf && o.gdn_path == 0 && gdn_tc_supported(c.gdn_dk, c.gdn_dv);
+  e->gdn_tc = e->bf && (o.gdn_path == 0 || o.gdn_path == 3) && gdn_tc_supported(c.gdn_dk, c.gdn_dv);
+  e->gdn_wy = e->gdn_tc && o.gdn_path == 0;
   if (e->gdn_tc) CRE(gdn_tc_prepare_device<bf16>(), "tcgen05 GDN shared-memory attribute");
+  if (e->gdn_wy) CRE(gdn_wy_prepare_device<bf16>(), "tcgen05 WY GDN shared-memory attribute");
   e->gdn_chunked = e->bf && !e->gdn_tc && (o.gdn_path == 0 || o.gdn_path == 2) && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 

@@ -196,6 +196,30 @@ int dcd_k_gdn_chunked_tc(const float* qf, const float* kf, const void* conv, int
                   launch_gdn_tc<bf16>(maps, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, err, S(stream)));
 }
 
+int dcd_k_gdn_wy_tc(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                         const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens, int nk,
+                         int nv, int dk, int dv, int* err, int dtype, void* stream) {
+  if (!gdn_tc_supported(dk, dv) || total_tokens <= 0 || nk <= 0 || nv % nk != 0) return DCD_E_INVALID;
+  if ((dtype == 0 ? gdn_wy_prepare_device<float>() : gdn_wy_prepare_device<bf16>()) != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap maps[3];
+  if (gdn_tc_make_maps(maps, qf, kf, conv, conv_stride, 2 * nk * dk + nv * dv, dtype == 0 ? 4 : 2, total_tokens, nk) != 0) return DCD_E_CUDA;
+  return DISPATCH(dtype,
+                  launch_gdn_wy<float>(maps, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, err, S(stream)),
+                  launch_gdn_wy<bf16>(maps, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, err, S(stream)));
+}
+
+int dcd_k_gdn_wy_tc_phases(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                         const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens, int nk,
+                         int nv, int dk, int dv, int* err, int dtype, unsigned long long* phases, void* stream) {
+  if (!gdn_tc_supported(dk, dv) || total_tokens <= 0 || nk <= 0 || nv % nk != 0) return DCD_E_INVALID;
+  if ((dtype == 0 ? gdn_wy_prepare_device<float>() : gdn_wy_prepare_device<bf16>()) != cudaSuccess) return DCD_E_CUDA;
+  TcTensorMap maps[3];
+  if (gdn_tc_make_maps(maps, qf, kf, conv, conv_stride, 2 * nk * dk + nv * dv, dtype == 0 ? 4 : 2, total_tokens, nk) != 0) return DCD_E_CUDA;
+  return DISPATCH(dtype,
+                  launch_gdn_wy<float>(maps, (const float*)conv, conv_stride, g, beta, seed, final_state, (float*)out, cu_seqlens, B, nk, nv, err, S(stream), phases),
+                  launch_gdn_wy<bf16>(maps, (const bf16*)conv, conv_stride, g, beta, seed, final_state, (bf16*)out, cu_seqlens, B, nk, nv, err, S(stream), phases));
+}
+
 int dcd_k_qk_norm_rope(const void* qg, int qg_stride, const void* kraw, int k_stride, const void* qw, const void* kw, const void* cos_t,
                        const void* sin_t, const int32_t* positions, int max_pos, void* q, void* k, int T, int heads, int kv, int hd,
                        int rotary_dim, float eps, int* err, int dtype, void* stream) {

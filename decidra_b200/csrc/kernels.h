@@ -107,6 +107,13 @@ int gdn_tc_make_maps(TcTensorMap maps[3], const float* qf, const float* kf, cons
 template <typename T>
 cudaError_t launch_gdn_tc(const TcTensorMap maps[3], const T* conv, int conv_stride, const float* g, const float* beta, const float* seed,
                           float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int* err, cudaStream_t s);
+// The same function in WY form (gdn_wy.cu): the triangular system of a chunk is inverted blockwise once, everything else is a
+// tensor-core product. Same tensor maps, same arguments.
+template <typename T>
+cudaError_t gdn_wy_prepare_device();
+template <typename T>
+cudaError_t launch_gdn_wy(const TcTensorMap maps[3], const T* conv, int conv_stride, const float* g, const float* beta, const float* seed,
+                          float* final_state, T* out, const int32_t* cu, int B, int nk, int nv, int* err, cudaStream_t s, unsigned long long* phases = nullptr);
 
 // Per-row FP8 E4M3 quantisation: scale[row] = max(absmax*clip, 1e-10)/448, out = e4m3(x/scale).
 template <typename T>

@@ -554,6 +554,18 @@ DCD_API int dcd_k_gdn_chunked(const float* qf, const float* kf, const void* conv
 DCD_API int dcd_k_gdn_chunked_tc(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
                                  const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens,
                                  int nk, int nv, int dk, int dv, int* err, int dtype, void* stream);
+/* The same function and arguments in WY form: per chunk and head the triangular system is inverted blockwise once (T = (I+A)^-1),
+ * W = T (beta Gam K) and U = T (beta V) are tensor-core products, and only D = U - W S, the outputs and the state update depend on
+ * the state (the formulation of native/kernels/kernels.cu:1340-1352). */
+DCD_API int dcd_k_gdn_wy_tc(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                                 const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens,
+                                 int nk, int nv, int dk, int dv, int* err, int dtype, void* stream);
+/* dcd_k_gdn_wy_tc with 16 device counters that receive the clock cycles thread 0 of every CTA spent in each phase of its chunks
+ * (diagnostics; the counterpart of the reference's gdn_chunked_tc profiling variant, native/kernels/kernels.cu:1671-1690). */
+DCD_API int dcd_k_gdn_wy_tc_phases(const float* qf, const float* kf, const void* conv, int conv_stride, const float* g, const float* beta,
+                                 const float* seed, float* final_state, void* out, const int32_t* cu_seqlens, int B, int total_tokens,
+                                 int nk, int nv, int dk, int dv, int* err, int dtype,
+                                     unsigned long long* phases, void* stream);
 /* split_q_gate + q/k RMSNorm(1+w) + partial NeoX RoPE in one kernel
  * (native/kernels/kernels.cu:516-557, 406-426; tables as native/src/engine.rs:1619-1643).
  * qg [T,heads,2*hd] (row stride qg_stride), kraw [T,kv,hd] (row stride k_stride) -> q [T,heads,hd],

@@ -565,7 +565,8 @@ def test_nvfp4_rows_bit_exact(G, oracle, glob):
 
 @pytest.mark.parametrize("dtype,nk,nv,lens", [(1, 16, 48, [73, 64, 89, 1, 31, 33]), (1, 2, 6, [128, 129, 200, 63, 65, 2]), (0, 2, 6, [70, 5, 64]),
                                               (1, 2, 4, [700])])
-def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
+@pytest.mark.parametrize("entry", ["dcd_k_gdn_wy_tc", "dcd_k_gdn_chunked_tc"])  # WY form (inverse once per chunk) / substitution per column
+def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens, entry):
     """tcgen05 (kind::tf32, chunk 64) gated delta rule against the sequential oracle with the tolerances of
     the reference's chunked-vs-sequential test (native/tests/gdn_chunked.rs:109-111); lengths straddle
     the 64-token chunk, one case runs 11 chunks in a row. Also: batched == per-sequence, bit-exact."""
@@ -578,7 +579,7 @@ def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
     out = G.empty((T, nv * dv), dtype)
     fin = G.devf(np.zeros((len(lens), nv, dk, dv)))
     err = G.devi([0])
-    G.call("dcd_k_gdn_chunked_tc", G.devf(q), G.devf(k), G.dev(conv, dtype), cd, G.devf(g), G.devf(beta), G.devf(seed), fin, out, G.devi(cu), len(lens),
+    G.call(entry, G.devf(q), G.devf(k), G.dev(conv, dtype), cd, G.devf(g), G.devf(beta), G.devf(seed), fin, out, G.devi(cu), len(lens),
            T, nk, nv, dk, dv, err, dtype, None)
     assert int(err.item()) == 0
     rep = nv // nk
@@ -592,12 +593,12 @@ def test_gdn_chunked_tcgen05_vs_oracle(G, oracle, dtype, nk, nv, lens):
         d = np.abs(got[sl].reshape(L, nv, dv) - want)
         ds = np.abs(gfin[i] - wstate).max()
         worst = (max(worst[0], d.max()), max(worst[1], d.mean()), max(worst[2], ds))
-    print("gdn tcgen05 vs sequential oracle: out max %.3g mean %.3g state max %.3g" % worst)
+    print(entry, "vs sequential oracle: out max %.3g mean %.3g state max %.3g" % worst)
     assert worst[0] < 2e-2 and worst[1] < 2e-4 and worst[2] < 2e-3, worst
     for i, L in enumerate(lens[:3]):
         sl = slice(cu[i], cu[i + 1])
         o1 = G.empty((L, nv * dv), dtype)
-        G.call("dcd_k_gdn_chunked_tc", G.devf(q[sl]), G.devf(k[sl]), G.dev(conv[sl], dtype), cd, G.devf(g[sl]), G.devf(beta[sl]), G.devf(seed), None, o1,
+        G.call(entry, G.devf(q[sl]), G.devf(k[sl]), G.dev(conv[sl], dtype), cd, G.devf(g[sl]), G.devf(beta[sl]), G.devf(seed), None, o1,
                G.devi([0, L]), 1, L, nk, nv, dk, dv, err, dtype, None)
         np.testing.assert_array_equal(G.host(o1), got[sl])
     assert int(err.item()) == 0
