@@ -184,6 +184,7 @@ SIGNATURES = {
     "dcd_k_qk_norm_rope": (I, [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F, P, I, P]),
     "dcd_k_attention": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I, P]),
     "dcd_k_attention_tc": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, P, P]),
+    "dcd_k_attention_tc_split": (I, [P, P, I, P, I, P, P, I, P, I, P, P, P, I, I, I, I, I, P, I, P, C.c_size_t, P]),
     "dcd_k_attention_tc_noalloc": (I, [P, P, I, P, I, P, P, I, P, I, P, P, I, I, I, I, I, P, P, C.c_char_p, SZ]),
     "dcd_k_readout": (I, [P, P, P, I, I, I, P]),
 }

@@ -75,7 +75,8 @@ class Options(C.Structure):
         ("nvfp4_scale_copy", C.c_int32),
         ("w4a16_gemm", C.c_int32),
         ("nvfp4_fusion", C.c_int32),
-        ("reserved", C.c_int32 * 3),
+        ("attn_split", C.c_int32),
+        ("reserved", C.c_int32 * 2),
     ]
 
 

@@ -31,6 +31,11 @@
 // maximum through shared memory once per tile and their partial denominators once at the end); one thread of
 // warp 8 issues the MMAs, one of warp 9 loads Q and the K slabs, one of warp 10 the V tiles, so that no wait
 // sits behind another.
+// Few rows over a long state leave most SMs without a CTA, so the key tiles of a (token tile, KV head) can be split over
+// gridDim.z CTAs: each takes a contiguous range of tiles, leaves its unnormalised O with the maximum and denominator it is
+// relative to in a workspace, and attn_merge_kernel adds the parts up with the base-2 identity of the reference's
+// merge_attn_lse_bf16 (native/kernels/kernels.cu:461-483; the reference takes the same decision inside FlashInfer's planner,
+// native/third_party/flashinfer/fi_prefill.cu:42-86), normalises, applies the output gate and stores.
 // All waits are bounded; a wait that gives up raises the error word and the CTA drains and exits.
 #include <cuda.h>
 
@@ -71,6 +76,8 @@ struct Params {
   bf16* out;               // [T, heads, hd]
   float scale_log2e;
   int* err;
+  float* ws_o;             // gridDim.z > 1: unnormalised partial outputs [CTA][128 rows][256]
+  float2* ws_ml;           //                (maximum in log2 units, denominator) [CTA][128 rows]
 };
 
 template <int G>
@@ -94,7 +101,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int off = p.cu[b], L = p.cu[b + 1] - off;
   const int t0 = (ti - p.tile_cu[b]) * TT;
   const int ntok = min(TT, L - t0);
-  const int n_st = (p.n_state + KT - 1) / KT, n_own = (L + KT - 1) / KT, n_tiles = n_st + n_own;
+  const int n_st = (p.n_state + KT - 1) / KT, n_own = (L + KT - 1) / KT, n_all = n_st + n_own;
+  // this CTA's range of key tiles [j_lo, j_lo + n_tiles); j below counts from j_lo
+  const int per_split = (n_all + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int j_lo = (int)blockIdx.z * per_split, n_tiles = max(0, min(n_all, j_lo + per_split) - j_lo);
+  const size_t cta_lin = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  if (n_tiles == 0) {  // more parts than tiles: an empty part
+    if (gridDim.z > 1 && threadIdx.x < 128) p.ws_ml[cta_lin * 128 + threadIdx.x] = make_float2(-INFINITY, 0.f);
+    return;
+  }
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -160,8 +175,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int i = 0; i < n_slabs && ok; ++i) {
         const int slot = i % K_SLOTS, use = i / K_SLOTS, j = i / NKB, c = i % NKB;
         if (use >= 1 && !(ok = mbar_wait(k_empty + 8 * slot, (uint32_t)((use - 1) & 1), abort_flag))) break;
-        const bool st = j < n_st;
-        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+        const bool st = j_lo + j < n_st;
+        const int row0 = st ? (j_lo + j) * KT : off + (j_lo + j - n_st) * KT;
         mbar_expect_tx(k_full + 8 * slot, KV_CHUNK);
         tma_load_2d(k_base + slot * KV_CHUNK, st ? &tmKs : &tmKo, k_full + 8 * slot, kh * HD + c * 64, row0);
       }
@@ -172,8 +187,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j >= 1 && !(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
-        const bool st = j < n_st;
-        const int row0 = st ? j * KT : off + (j - n_st) * KT;
+        const bool st = j_lo + j < n_st;
+        const int row0 = st ? (j_lo + j) * KT : off + (j_lo + j - n_st) * KT;
         mbar_expect_tx(bar_v, V_BYTES);
 #pragma unroll
         for (int c = 0; c < NKB; ++c) tma_load_2d(v_base + c * KV_CHUNK, st ? &tmVs : &tmVo, bar_v, kh * HD + c * 64, row0);
@@ -228,7 +243,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float m_used = -INFINITY, l = 0.f;         // l: this thread's part of the denominator
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int valid = j < n_st ? min(KT, p.n_state - j * KT) : min(KT, L - (j - n_st) * KT);
+      const int jg = j_lo + j;
+      const int valid = jg < n_st ? min(KT, p.n_state - jg * KT) : min(KT, L - (jg - n_st) * KT);
       ok = mbar_wait(bar_s + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -313,7 +329,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ok = mbar_wait(pair_bar, pair_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok) {
+    if (ok && gridDim.z > 1) {
+      // ---- a part of a split: unnormalised O (f32) and what it is relative to ---------------------------------------------
+      float* xs = xch + (n_tiles & 1) * 256;
+      l += xs[(h ^ 1) * 128 + r];
+      if (h == 0) p.ws_ml[cta_lin * 128 + r] = make_float2(m_used, l);
+      float* orow = p.ws_o + (cta_lin * 128 + r) * HD;
+#pragma unroll 1
+      for (int c = h * (HD / 64); c < (h + 1) * (HD / 64); ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4)
+          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 4) = make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+      }
+    } else if (ok) {
       float* xs = xch + (n_tiles & 1) * 256;
       l += xs[(h ^ 1) * 128 + r];
       const int tt = r / G, g = r - tt * G;
@@ -366,6 +397,85 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
+}
+
+// Adds up the parts of a split launch: out = sum_z O_z 2^(m_z - M) / sum_z l_z 2^(m_z - M), M = max_z m_z, then the output gate.
+// One warp per row of a (token tile, KV head), eight head dims per lane; grid (token tiles, KV heads, 128 / 4 rows). The maxima and
+// denominators of all parts are fetched first, one part per lane, so that the loop over the parts has no dependent loads.
+template <int G>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const Params p, int n_split, int grid_x, int grid_y) {
+  constexpr int TT = 128 / G;
+  const int ti = blockIdx.x, kh = blockIdx.y;
+  if (ti >= p.tile_cu[p.B]) return;
+  int b = 0;
+  {
+    int lo = 0, hi = p.B;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.tile_cu[mid] <= ti) lo = mid; else hi = mid;
+    }
+    b = lo;
+  }
+  const int off = p.cu[b], L = p.cu[b + 1] - off;
+  const int t0 = (ti - p.tile_cu[b]) * TT;
+  const int ntok = min(TT, L - t0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.z * 4 + warp;
+  if (r >= ntok * G) return;
+  const int tt = r / G, g = r - tt * G;
+  const size_t part_stride = (size_t)grid_y * grid_x * 128, row0 = ((size_t)kh * grid_x + ti) * 128 + r;
+  constexpr int MAXP = 4;  // parts per lane: up to 128 parts
+  float2 ml[MAXP];
+  float M = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    const int z = lane + 32 * i;
+    ml[i] = z < n_split ? p.ws_ml[(size_t)z * part_stride + row0] : make_float2(-INFINITY, 0.f);
+    if (ml[i].y > 0.f) M = fmaxf(M, ml[i].x);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  float den = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    ml[i].x = ml[i].y > 0.f ? exp2f(ml[i].x - M) : 0.f;  // the weight of the part
+    den = fmaf(ml[i].x, ml[i].y, den);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    if (32 * i >= n_split) break;
+#pragma unroll 8
+    for (int zz = 0; zz < 32; ++zz) {
+      const int z = 32 * i + zz;
+      if (z >= n_split) break;
+      const float w = __shfl_sync(0xffffffffu, ml[i].x, zz);
+      if (w == 0.f) continue;  // an empty part wrote no output
+      const float* src = p.ws_o + ((size_t)z * part_stride + row0) * HD + lane * 8;
+      const float4 a = *reinterpret_cast<const float4*>(src);
+      const float4 c = *reinterpret_cast<const float4*>(src + 4);
+      acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
+      acc[4] = fmaf(w, c.x, acc[4]); acc[5] = fmaf(w, c.y, acc[5]); acc[6] = fmaf(w, c.z, acc[6]); acc[7] = fmaf(w, c.w, acc[7]);
+    }
+  }
+  const int t = off + t0 + tt, head = kh * G + g;
+  const float inv = 1.0f / den;
+  float o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = Ty<bf16>::rnd(acc[i] * inv);
+  if (p.gate_qg) {
+    const uint4 gv = *reinterpret_cast<const uint4*>(p.gate_qg + (size_t)t * p.qg_stride + (size_t)head * 2 * HD + HD + lane * 8);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] *= Ty<bf16>::rnd(sigmoid_f(__low2float(g2[i])));
+      o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_f(__high2float(g2[i])));
+    }
+  }
+  *reinterpret_cast<uint4*>(p.out + ((size_t)t * p.heads + head) * HD + lane * 8) =
+      make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
 }
 
 // tile_cu[b] = number of token tiles of the sequences before b (single CTA scan).
@@ -422,9 +532,22 @@ int attn_tc_make_maps(AttnTcMaps* m, const void* q, const void* k_own, int k_str
   return bad;
 }
 
+size_t attn_tc_split_workspace_bytes(int sm_count) { return (size_t)2 * sm_count * 128 * (atc::HD * sizeof(float) + sizeof(float2)); }
+
+int attn_tc_pick_split(int max_tiles, int kv, int n_state, int sm_count) {
+  const int ctas = max_tiles * kv, st_tiles = (n_state + atc::KT - 1) / atc::KT;
+  if (ctas <= 0 || 2 * ctas > sm_count || st_tiles < 8) return 1;  // enough CTAs, or too few key tiles to be worth a second pass
+  int z = (2 * sm_count) / ctas;
+  if (z > st_tiles / 2) z = st_tiles / 2;  // at least two key tiles per part
+  if (z > 128) z = 128;
+  return z < 2 ? 1 : z;
+}
+
 cudaError_t attn_tc_launch(const AttnTcMaps* m, const int32_t* cu, const int32_t* tile_cu, int B, int n_state, int T, int max_tiles,
-                           int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s) {
+                           int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s, int n_split,
+                           void* workspace) {
   if (!attn_tc_supported(heads, kv, hd)) return cudaErrorInvalidValue;
+  if (n_split < 1 || n_split > 128 || (n_split > 1 && !workspace)) return cudaErrorInvalidValue;
   atc::Params p;
   p.cu = cu;
   p.tile_cu = tile_cu;
@@ -438,10 +561,16 @@ cudaError_t attn_tc_launch(const AttnTcMaps* m, const int32_t* cu, const int32_t
   p.out = (bf16*)out;
   p.scale_log2e = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
   p.err = err;
-  dim3 grid(max_tiles, kv);
+  // workspace: the maxima and denominators of all parts, then the partial outputs
+  p.ws_ml = (float2*)workspace;
+  p.ws_o = (float*)((char*)workspace + (size_t)n_split * max_tiles * kv * 128 * sizeof(float2));
+  dim3 grid(max_tiles, kv, n_split);
   atc::attn_tc_kernel<6><<<grid, atc::NUM_THREADS, atc::SMEM_BYTES, s>>>(
       *reinterpret_cast<const CUtensorMap*>(&m->q), *reinterpret_cast<const CUtensorMap*>(&m->k_state),
       *reinterpret_cast<const CUtensorMap*>(&m->v_state), *reinterpret_cast<const CUtensorMap*>(&m->k_own),
       *reinterpret_cast<const CUtensorMap*>(&m->v_own), p);
+  cudaError_t ce = cudaGetLastError();
+  if (ce != cudaSuccess || n_split == 1) return ce;
+  atc::attn_merge_kernel<6><<<dim3(max_tiles, kv, 32), 128, 0, s>>>(p, n_split, max_tiles, kv);
   return cudaGetLastError();
 }

@@ -18,5 +18,14 @@ cudaError_t attn_tc_build_tiles(const int32_t* cu, int B, int tokens_per_tile, i
 int attn_tc_make_maps(AttnTcMaps* m, const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
                       const void* v_state, int n_state, int T, int heads, int kv, int hd);
 // max_tiles >= tile_cu[B] (e.g. ceil(T / tokens_per_tile) + B); surplus CTAs exit at once.
+// n_split > 1: the key tiles of every (token tile, KV head) are split over n_split CTAs whose parts a second kernel merges;
+// workspace then holds n_split * max_tiles * kv * 128 rows of (256 + 2) floats (attn_tc_pick_split never asks for more than
+// attn_tc_split_workspace_bytes(sm_count)).
 cudaError_t attn_tc_launch(const AttnTcMaps* m, const int32_t* cu, const int32_t* tile_cu, int B, int n_state, int T, int max_tiles,
-                           int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s);
+                           int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s, int n_split = 1,
+                           void* workspace = nullptr);
+// Parts per (token tile, KV head) for a launch of max_tiles x kv CTAs over n_state cached keys: 1 unless the launch would leave more
+// than half of the SMs idle and the state is at least eight key tiles long; then as many as bring the grid to about two CTAs per SM,
+// with at least two key tiles per part.
+int attn_tc_pick_split(int max_tiles, int kv, int n_state, int sm_count);
+size_t attn_tc_split_workspace_bytes(int sm_count);

@@ -139,6 +139,7 @@ struct dcd_engine {
   float *qf = nullptr, *kf = nullptr, *g = nullptr, *beta = nullptr, *hid = nullptr, *d_logits = nullptr, *tap_dev = nullptr;
   uint32_t* d_ids = nullptr;
   int32_t *d_lens = nullptr, *d_cu = nullptr, *d_last = nullptr, *d_tokq = nullptr, *d_tokpos = nullptr, *d_tile_cu = nullptr;
+  void* attn_ws = nullptr;  // partial outputs of split attention launches
   bool attn_tc = false, gdn_chunked = false, gdn_tc = false, gdn_wy = false;
   TcTensorMap tm_gdn[3];  // q/k/conv views for the tcgen05 GDN kernel, rebuilt when the pass's token count changes
   int tm_gdn_tokens = -1;
@@ -494,8 +495,11 @@ int run_layers(dcd_engine* e, const Pass& p) {
           AttnTcMaps maps;
           if (attn_tc_make_maps(&maps, e->q, kdst, kv * hd, vsrc, e->qkv_n, ks, vs, n_state, T_, heads, kv, hd))
             return fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an attention operand");
-          CK(e, attn_tc_launch(&maps, e->d_cu + g.q0, e->d_tile_cu, g.nq, n_state, T_, (g.ntok + tt - 1) / tt + g.nq, heads, kv, hd, big, e->qkv_n,
-                               e->bufA, e->d_err, s), "tcgen05 attention");
+          const int max_tiles = (g.ntok + tt - 1) / tt + g.nq;
+          const int n_split = e->attn_ws ? attn_tc_pick_split(max_tiles, kv, n_state, e->sm_count) : 1;
+          if (n_split > 1) e->launches += 1;  // the merge kernel
+          CK(e, attn_tc_launch(&maps, e->d_cu + g.q0, e->d_tile_cu, g.nq, n_state, T_, max_tiles, heads, kv, hd, big, e->qkv_n, e->bufA, e->d_err, s,
+                               n_split, e->attn_ws), "tcgen05 attention");
         } else {
           const size_t t0 = (size_t)g.tok0;
           CK(e, launch_attn_fma<T>((const T*)e->q + t0 * heads * hd, kdst + t0 * kv * hd, kv * hd, vsrc + t0 * e->qkv_n, e->qkv_n, ks, vs, n_state,
@@ -786,6 +790,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (o.nvfp4_scale_copy < 0 || o.nvfp4_scale_copy > 2) return fail(nullptr, DCD_E_INVALID, "nvfp4_scale_copy must be 0, 1 or 2");
   if (o.w4a16_gemm < 0 || o.w4a16_gemm > 2) return fail(nullptr, DCD_E_INVALID, "w4a16_gemm must be 0, 1 or 2");
   if (o.nvfp4_fusion < 0 || o.nvfp4_fusion > 1) return fail(nullptr, DCD_E_INVALID, "nvfp4_fusion must be 0 or 1");
+  if (o.attn_split < 0 || o.attn_split > 1) return fail(nullptr, DCD_E_INVALID, "attn_split must be 0 or 1");
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -1050,6 +1055,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   CRA(e->d_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
   CRA(e->d_last, (size_t)e->max_batch * 4, false, ws);
   CRA(e->d_tile_cu, ((size_t)e->max_batch + 1) * 4, false, ws);
+  if (e->attn_tc && o.attn_split == 0) CRA(e->attn_ws, attn_tc_split_workspace_bytes(e->sm_count), false, ws);  // parts of split launches
   CRA(e->d_tokq, Tm * 4, false, ws);
   CRA(e->d_tokpos, Tm * 4, false, ws);
   CRA(e->d_err, 256, true, ws);

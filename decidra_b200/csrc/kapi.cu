@@ -249,6 +249,26 @@ int dcd_k_attention_tc(const void* q, const void* k_own, int k_stride, const voi
   return rc_of(attn_tc_launch(&maps, cu_seqlens, tile_cu, B, n_state, T, (T + tt - 1) / tt + B, heads, kv, hd, gate_qg, qg_stride, out, err, S(stream)));
 }
 
+int dcd_k_attention_tc_split(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                             const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out, const int32_t* cu_seqlens,
+                             int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err, int n_split, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  if (!attn_tc_supported(heads, kv, hd) || B <= 0 || T <= 0 || n_split < 0) return DCD_E_INVALID;
+  if (attn_tc_prepare_device() != cudaSuccess) return DCD_E_CUDA;
+  const int tt = attn_tc_tokens_per_tile(heads, kv), max_tiles = (T + tt - 1) / tt + B;
+  if (n_split == 0) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DCD_E_CUDA;
+    n_split = attn_tc_pick_split(max_tiles, kv, n_state, sms);
+  }
+  if (n_split > 1 && (!workspace || workspace_bytes < (size_t)n_split * max_tiles * kv * 128 * 1032)) return DCD_E_INVALID;
+  AttnTcMaps maps;
+  if (attn_tc_make_maps(&maps, q, k_own, k_stride, v_own, v_stride, k_state, v_state, n_state, T, heads, kv, hd)) return DCD_E_CUDA;
+  cudaError_t ce = attn_tc_build_tiles(cu_seqlens, B, tt, tile_cu, S(stream));
+  if (ce != cudaSuccess) return rc_of(ce);
+  return rc_of(attn_tc_launch(&maps, cu_seqlens, tile_cu, B, n_state, T, max_tiles, heads, kv, hd, gate_qg, qg_stride, out, err, S(stream), n_split, workspace));
+}
+
 int dcd_k_readout(const float* x, const float* W, float* out, int B, int H, int R, void* stream) {
   return rc_of(launch_readout(x, W, out, B, H, R, S(stream)));
 }

@@ -89,7 +89,10 @@ typedef struct dcd_options {
   int32_t nvfp4_fusion;     /* precision 3, block-scaled kernel: 0 = default: the residual add rides in the epilogue of the projection that
                                closes a block, the gate/up epilogue applies SwiGLU and writes the down projection's NVFP4 operand, the gated
                                norm writes the out projection's NVFP4 operand; 1 = those steps as kernels of their own (same bits) */
-  int32_t reserved[3];
+  int32_t attn_split;       /* tcgen05 attention: 0 = default: when a launch has fewer CTAs than half the SMs and the state is at least eight
+                               key tiles long, the key tiles of each (token tile, KV head) are split over several CTAs and a second kernel
+                               merges the parts; 1 = never split */
+  int32_t reserved[2];
 } dcd_options;
 
 typedef struct dcd_info {
@@ -589,6 +592,14 @@ DCD_API int dcd_k_attention_tc(const void* q, const void* k_own, int k_stride, c
                                const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
                                const int32_t* cu_seqlens, int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err,
                                void* stream);
+/* dcd_k_attention_tc with the key tiles of every (token tile, KV head) split over n_split CTAs; each part leaves its unnormalised
+ * output with its maximum and denominator in `workspace`, and a second kernel merges the parts with the base-2 log-sum-exp identity
+ * of merge_attn_lse_bf16 (native/kernels/kernels.cu:461-483), normalises, gates and stores. n_split = 0 takes the engine's rule
+ * for this device (dcd_options.attn_split). workspace_bytes >= n_split * (ceil(T / tokens_per_tile) + B) * kv * 128 * 1032. */
+DCD_API int dcd_k_attention_tc_split(const void* q, const void* k_own, int k_stride, const void* v_own, int v_stride, const void* k_state,
+                               const void* v_state, int n_state, const void* gate_qg, int qg_stride, void* out,
+                               const int32_t* cu_seqlens, int32_t* tile_cu, int B, int T, int heads, int kv, int hd, int* err,
+                               int n_split, void* workspace, size_t workspace_bytes, void* stream);
 /* dcd_k_attention_tc for callers that cannot allocate device memory. It has no counterpart in the
  * reference; it exists for hosts that drive these kernels from a request thread where
  * cudaMalloc/cudaFree are off limits (both synchronise the whole device and would stall every other

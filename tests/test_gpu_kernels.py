@@ -380,6 +380,45 @@ def test_attention_tcgen05_vs_oracle(G, oracle, lens, S):
                     f"first got {got[t_[0], h_[0], d_[0]]} want {want[t_[0], h_[0], d_[0]]}; max abs {np.nanmax(np.abs(got - want))}")
 
 
+@pytest.mark.parametrize("lens,S,n_split", [([16], 4096, 0), ([16, 16], 4096, 0), ([16], 16384, 0), ([16, 16], 16384, 0),
+                                            ([16, 5], 1000, 3), ([40], 300, 5), ([130, 3], 2048, 2)])
+def test_attention_split_kv_vs_oracle(G, oracle, lens, S, n_split):
+    """Few rows over a long state: the key tiles of each (token tile, KV head) split over several CTAs and merged with the base-2
+    log-sum-exp identity (n_split = 0: the engine's rule for this device; 5 parts over 4 key tiles leaves one part empty), against
+    the oracle and against the unsplit kernel."""
+    import torch
+    heads, kv, hd = 24, 4, 256
+    T = sum(lens)
+    r = rng(77 + T + S)
+    R = oracle.rb
+    q = R(r.standard_normal((T, heads, hd), dtype=np.float32))
+    stride = kv * hd + 64
+    kof = R(r.standard_normal((T, stride), dtype=np.float32))
+    vof = R(r.standard_normal((T, stride), dtype=np.float32))
+    ko, vo = kof[:, :kv * hd].reshape(T, kv, hd), vof[:, :kv * hd].reshape(T, kv, hd)
+    ks = R(r.standard_normal((S, kv, hd), dtype=np.float32))
+    vs = R(r.standard_normal((S, kv, hd), dtype=np.float32))
+    qg = R(r.standard_normal((T, heads, 2 * hd), dtype=np.float32))
+    cu, pos, tq, last = oracle.pack(lens, 0)
+    err = G.devi([0])
+    tile_cu = G.devi(np.zeros(len(lens) + 1))
+    dev = (G.dev(q, 1), G.dev(kof, 1), stride, G.dev(vof, 1), stride, G.dev(ks, 1), G.dev(vs, 1), S, G.dev(qg, 1), heads * 2 * hd)
+    tail = (G.devi(cu), tile_cu, len(lens), T, heads, kv, hd, err)
+    plain = torch.full((T, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_attention_tc", *dev, plain, *tail, None)
+    ws_bytes = 2 * G.sm_count() * 128 * 1032
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    out = torch.full((T, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_attention_tc_split", *dev, out, *tail, n_split, ws, C.c_size_t(ws_bytes), None)
+    assert int(err.item()) == 0, "a bounded wait gave up inside the kernel"
+    gate = R(1 / (1 + np.exp(-qg[:, :, hd:])))
+    want = R(np.concatenate([oracle.k_attention(q[cu[i]:cu[i + 1]], ks, vs, ko[cu[i]:cu[i + 1]], vo[cu[i]:cu[i + 1]], True) for i in range(len(lens))]) * gate)
+    got, ref = G.host(out), G.host(plain)
+    assert np.isfinite(got).all()
+    assert (np.abs(got - want) <= 2e-2 * np.abs(want) + 8e-3).all(), float(np.abs(got - want).max())
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref) + 2e-3).all(), float(np.abs(got - ref).max())
+
+
 @pytest.mark.parametrize("dtype,nk,nv,dv,narrow", [(1, 16, 48, 128, 0), (1, 16, 48, 128, 1), (0, 2, 6, 64, 0), (0, 2, 6, 64, 1)])
 def test_gdn_chunked_vs_oracle(G, oracle, dtype, nk, nv, dv, narrow):
     """Chunked tensor-core gated delta rule against the sequential oracle, with the tolerances of the
