@@ -65,6 +65,11 @@ def parse():
                     help="comma list of extra workloads in the line: w4a16,nvfp4,ragged_bf16,ragged_nvfp4 | all | none")
     ap.add_argument("--ragged-states", type=int, default=6, help="states of the seeded ragged-stress list per replica")
     ap.add_argument("--c8-states", type=int, default=24, help="cold requests of the Poisson c8 run per replica")
+    ap.add_argument("--box-states", type=int, default=96,
+                    help="cold requests of the whole-box run (one process, one engine per GPU behind one router); runs on rank 0 when more than "
+                         "one GPU is used, or when --box-replicas is given; 0 = skip")
+    ap.add_argument("--box-replicas", type=int, default=0, help="single-GPU runs: this many engines on the one GPU behind the router (a functional check)")
+    ap.add_argument("--box-precision", default="nvfp4", choices=["bf16", "fp8", "w4a16", "nvfp4"])
     ap.add_argument("--scheduler-clients", type=int, default=0,
                     help="extra arm: N client threads submit cold requests (a new state each) through the request scheduler; "
                          "adds a 'scheduler' object to the JSON line (not part of the default run)")
@@ -451,6 +456,84 @@ def run_poisson_c8(eng, R, args, n_requests, precision):
             "timed": "request scheduler over the host-buffer C ABI, wall clock, max over ranks"}
 
 
+def run_box(dcd, args, devices, precision, n_states):
+    """One process, one engine and one request scheduler per device, one router in front (decidra_b200.box): cold requests (a new
+    2048-token state + 64 questions each) arrive as a Poisson stream with at most 8 in flight in the whole box; a cold state goes
+    to the replica with the fewest requests in flight. Wall clock from the first arrival to the last reply; latency is admission to
+    reply. No process group is involved: the other ranks' processes hold no engine while this runs."""
+    from decidra_b200 import box, scheduler
+    n = len(devices)
+    tm = max(args.state_len, args.questions * args.qmax)
+    engines, errs = [None] * n, []
+
+    def mk(i):
+        try:
+            engines[i] = make_engine(dcd, args, precision, tm, devices[i])[0]
+        except Exception as ex:  # noqa: BLE001
+            errs.append("replica %d: %r" % (i, ex))
+
+    t_setup = time.perf_counter()
+    ths = [threading.Thread(target=mk, args=(i,)) for i in range(n)]
+    [t.start() for t in ths]
+    [t.join() for t in ths]
+    if errs:
+        for e in engines:
+            if e is not None:
+                e.close()
+        return {"error": "; ".join(errs)}
+    handles = [scheduler.BatchHandle(e, state_cache_entries=0) for e in engines]
+    b = box.BoxRunner(handles)
+    t_setup = time.perf_counter() - t_setup
+    reqs = [headline_workload(args, 900000 + i) for i in range(n_states + 2 * n)]
+    # two requests per replica, all replicas at once: warm-up, and the service time of one request while the whole box is busy
+    t0 = time.perf_counter()
+    for rnd in range(2):
+        ts = [handles[i].submit_state_once(*reqs[rnd * n + i]) for i in range(n)]
+        [t.result() for t in ts]
+    service = (time.perf_counter() - t0) / 2
+    rng = np.random.Generator(np.random.PCG64(8800))
+    gaps = rng.exponential(service / n / 2.0, n_states)
+    sem = threading.Semaphore(8)
+    lat, failures, threads = [], [], []
+
+    def waiter(ticket, t_in):
+        try:
+            ticket.result()
+            lat.append(time.perf_counter() - t_in)
+        except Exception as ex:  # noqa: BLE001
+            failures.append(repr(ex))
+        finally:
+            sem.release()
+
+    t0 = time.perf_counter()
+    for i in range(n_states):
+        time.sleep(float(gaps[i]))
+        sem.acquire()
+        s, q = reqs[2 * n + i]
+        t_in = time.perf_counter()
+        th = threading.Thread(target=waiter, args=(b.submit_state_once(s, q), t_in))
+        th.start()
+        threads.append(th)
+    for th in threads:
+        th.join()
+    t = time.perf_counter() - t0
+    st = b.stats()
+    b.close()
+    for e in engines:
+        e.close()
+    lat.sort()
+    return {"value": n_states * args.questions / t, "unit": UNIT, "states_per_s": n_states / t, "seconds": t, "states": n_states,
+            "questions": n_states * args.questions, "replicas": n, "devices": list(devices), "precision": precision, "concurrency_cap": 8,
+            "arrivals": "Poisson, mean gap = half the box's measured service time per request (%.0f ms per request and replica)" % (service * 1e3),
+            "p50_request_latency_ms": lat[len(lat) // 2] * 1e3 if lat else None,
+            "p99_request_latency_ms": lat[min(len(lat) - 1, int(len(lat) * 0.99))] * 1e3 if lat else None,
+            "requests_per_replica": st["requests"], "stolen_per_replica": st["steals"], "captures": sum(x["captures"] for x in st["schedulers"]),
+            "errors": failures, "engine_setup_s": t_setup,
+            "sample": "%d cold requests of the 512-state workload (bounded so the default run ends in minutes)" % n_states,
+            "timed": "router + request schedulers over the host-buffer C ABI, one process, wall clock; no max over ranks: a replica "
+                     "that finishes early takes the next cold state"}
+
+
 def run_ours(args):
     import torch
 
@@ -634,6 +717,13 @@ def run_ours(args):
         e3.close()
         del e3
 
+    box_info = None
+    if args.box_states > 0 and args.precision == "bf16" and (world > 1 or args.box_replicas > 0):
+        R.barrier()  # every rank has freed its engines; rank 0 alone now drives all the GPUs from one process
+        if rank == 0:
+            box_info = run_box(dcd, args, list(range(world)) if world > 1 else [local] * args.box_replicas, args.box_precision, args.box_states)
+        R.barrier()
+
     if rank == 0:
         roof = gemm_roofline(prof, args.precision)
         roof["traffic"] = GEMM_TRAFFIC_BYTES if args.precision == "bf16" else None
@@ -658,6 +748,8 @@ def run_ours(args):
         }
         if sched_info is not None:
             line["scheduler"] = sched_info
+        if box_info is not None:
+            line["box"] = box_info
         if world == 1 and not args.no_cpu_baseline:
             qps, cores, desc, _ = cpu_sample(args, steps=1, warmup=0)
             line["cpu_baseline"] = {"value": qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}

@@ -536,7 +536,7 @@ size_t attn_tc_split_workspace_bytes(int sm_count) { return (size_t)2 * sm_count
 
 int attn_tc_pick_split(int max_tiles, int kv, int n_state, int sm_count) {
   const int ctas = max_tiles * kv, st_tiles = (n_state + atc::KT - 1) / atc::KT;
-  if (ctas <= 0 || 2 * ctas > sm_count || st_tiles < 8) return 1;  // enough CTAs, or too few key tiles to be worth a second pass
+  if (ctas <= 0 || ctas > sm_count || st_tiles < 8) return 1;  // a CTA per SM already, or too few key tiles to be worth a second pass
   int z = (2 * sm_count) / ctas;
   if (z > st_tiles / 2) z = st_tiles / 2;  // at least two key tiles per part
   if (z > 128) z = 128;

@@ -24,8 +24,8 @@ int attn_tc_make_maps(AttnTcMaps* m, const void* q, const void* k_own, int k_str
 cudaError_t attn_tc_launch(const AttnTcMaps* m, const int32_t* cu, const int32_t* tile_cu, int B, int n_state, int T, int max_tiles,
                            int heads, int kv, int hd, const void* gate_qg, int qg_stride, void* out, int* err, cudaStream_t s, int n_split = 1,
                            void* workspace = nullptr);
-// Parts per (token tile, KV head) for a launch of max_tiles x kv CTAs over n_state cached keys: 1 unless the launch would leave more
-// than half of the SMs idle and the state is at least eight key tiles long; then as many as bring the grid to about two CTAs per SM,
-// with at least two key tiles per part.
+// Parts per (token tile, KV head) for a launch of max_tiles x kv CTAs over n_state cached keys: 1 unless the launch has no more CTAs
+// than there are SMs and the state is at least eight key tiles long; then as many as bring the grid to about two CTAs per SM, with
+// at least two key tiles per part.
 int attn_tc_pick_split(int max_tiles, int kv, int n_state, int sm_count);
 size_t attn_tc_split_workspace_bytes(int sm_count);

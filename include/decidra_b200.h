@@ -89,7 +89,7 @@ typedef struct dcd_options {
   int32_t nvfp4_fusion;     /* precision 3, block-scaled kernel: 0 = default: the residual add rides in the epilogue of the projection that
                                closes a block, the gate/up epilogue applies SwiGLU and writes the down projection's NVFP4 operand, the gated
                                norm writes the out projection's NVFP4 operand; 1 = those steps as kernels of their own (same bits) */
-  int32_t attn_split;       /* tcgen05 attention: 0 = default: when a launch has fewer CTAs than half the SMs and the state is at least eight
+  int32_t attn_split;       /* tcgen05 attention: 0 = default: when a launch has no more CTAs than there are SMs and the state is at least eight
                                key tiles long, the key tiles of each (token tile, KV head) are split over several CTAs and a second kernel
                                merges the parts; 1 = never split */
   int32_t reserved[2];
