@@ -309,12 +309,20 @@ class Ranks:
             os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
             self.dist = dist
+            self.host_group = dist.new_group(backend="gloo")  # barriers that must not put a kernel on any GPU
 
     def barrier(self):
         self.torch.cuda.synchronize()
         if self.dist:
             self.dist.barrier()
         self.torch.cuda.synchronize()
+
+    def host_barrier(self):
+        """A barrier on the host alone. An NCCL barrier is a kernel that spins on the GPUs of the ranks that arrived first; while
+        rank 0 drives every GPU of the box from its own process, those kernels would hold SMs that the persistent GEMMs expect."""
+        self.torch.cuda.synchronize()
+        if self.dist:
+            self.dist.barrier(group=self.host_group)
 
     def _reduce(self, x, op):
         if not self.dist:
@@ -720,9 +728,10 @@ def run_ours(args):
     box_info = None
     if args.box_states > 0 and args.precision == "bf16" and (world > 1 or args.box_replicas > 0):
         R.barrier()  # every rank has freed its engines; rank 0 alone now drives all the GPUs from one process
+        R.host_barrier()
         if rank == 0:
             box_info = run_box(dcd, args, list(range(world)) if world > 1 else [local] * args.box_replicas, args.box_precision, args.box_states)
-        R.barrier()
+        R.host_barrier()
 
     if rank == 0:
         roof = gemm_roofline(prof, args.precision)
