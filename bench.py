@@ -46,7 +46,7 @@ VOCAB = 248320
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up (SwiGLU epilogue) GEMM launch of the question pass
 # (M = 6835 rows, K = 5120, N = 34816), from an ncu capture of a 4-layer slice of the same model
 # (algorithmic bytes of that launch: 2*(M*K + N*K + M*N/2) = 664.5 MB).
-GEMM_TRAFFIC_BYTES = None
+GEMM_TRAFFIC_BYTES = 1747872224  # 1513.6 MB read + 234.3 MB written: the weight panel comes from DRAM about four times
 
 
 def parse():

@@ -409,3 +409,37 @@ def test_nvfp4_precision(dcd, oracle):
     info16 = make_engine(dcd, cfg, max_pass_tokens=512)
     assert e.info().weight_bytes < 0.7 * info16.info().weight_bytes
     info16.close(); e.close()
+
+
+@pytest.mark.parametrize("precision,name", [(1, "w4a16"), (2, "fp8"), (3, "nvfp4")])
+def test_quantised_engines_on_a_d3_shaped_slice(dcd, oracle, precision, name):
+    """The quantised engines where the tensor-core kernels run (the tiny model takes the plain-FMA paths): a 2-layer [GDN, full]
+    model at d3 width (hidden 5120, 24/4 heads of 256, GDN 16/48 heads of 128, SwiGLU 17408), a 160-token state and 4 questions,
+    against the CPU oracle in the same precision mode. The bar scales with what the quantisation itself does to the logits
+    (oracle in that mode against the oracle in bf16): the engine has to sit much closer to its own oracle than the two modes
+    sit to each other."""
+    cfg = dcd.d3_config(num_layers=2, dtype=1, vocab=4096)
+    cfg.layer_is_full[0], cfg.layer_is_full[1] = 0, 1
+    state, questions = tiny_inputs(seed=31, vocab=4096, state_len=160, qlens=(20, 33, 24, 40))
+    ob = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    base = ob.readout_state_once_batch(ob.capture_state(state), questions)
+    del ob
+    oq = oracle.Oracle(orc_cfg(oracle, cfg), 0)
+    oq.set_precision(precision, 16) if precision == 2 else oq.set_precision(precision)
+    want = oq.readout_state_once_batch(oq.capture_state(state), questions)
+    del oq
+    effect = float(np.abs(want - base).max())
+    opt = dict(max_pass_tokens=512, precision=precision)
+    if precision == 2:
+        opt["fp8_min_rows"] = 16
+    e = make_engine(dcd, cfg, **opt)
+    e.profile_enable(True)
+    got = e.readout_state_once_batch(e.capture_state(state), questions)
+    prof = e.profile_read()
+    e.close()
+    err = float(np.abs(got - want).max())
+    bar = max(0.75 * effect, 0.12)
+    print(f"d3-shaped slice, {name}: max abs vs oracle in the same mode {err:.3g} (bar {bar:.3g}; the mode itself moves the logits by {effect:.3g}); "
+          f"gemm launches {prof['gemm']['launches']}")
+    assert np.isfinite(got).all() and err < bar, (name, err, bar)
+    assert (np.argmax(got, 1) == np.argmax(want, 1)).mean() >= 0.75
