@@ -130,6 +130,8 @@ SIGNATURES = {
     "dcd_state_tokens": (SZ, [P]),
     "dcd_state_pos_end": (SZ, [P]),
     "dcd_state_bytes": (SZ, [P]),
+    "dcd_state_bytes_for": (SZ, [P, SZ]),
+    "dcd_pass_reserve_bytes": (SZ, [P, SZ]),
     "dcd_state_offload": (I, [P, P, C.POINTER(P)]),
     "dcd_state_restore": (I, [P, P, C.POINTER(P)]),
     "dcd_host_state_free": (None, [P]),

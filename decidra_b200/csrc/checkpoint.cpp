@@ -1,5 +1,6 @@
 // safetensors store + config.json reader. Plain C++ over POSIX mmap; see checkpoint.h.
 #include "checkpoint.h"
+#include <stdint.h>
 
 #include <dirent.h>
 #include <fcntl.h>
@@ -279,7 +280,21 @@ bool Store::map_file(const std::string& path, std::string* err) {
     if (!jd || jd->kind != Json::String) { *err = path + ": " + m2.first + ": dtype"; return false; }
     if (!parse_dtype(jd->text, &ti.dtype)) { *err = "unsupported safetensors dtype " + jd->text; return false; }
     if (!js || js->kind != Json::Array) { *err = path + ": " + m2.first + ": shape"; return false; }
-    for (const Json& d : js->items) { uint64_t v = 0; d.as_u64(&v); ti.shape.push_back((size_t)v); }
+    // every dimension an unsigned integer, and the element count (times the element size) without wrap-around: a shape that
+    // overflows could otherwise still "match" its byte range
+    uint64_t elems = 1;
+    bool shape_ok = true;
+    for (const Json& d : js->items) {
+      uint64_t v = 0;
+      if (!d.as_u64(&v)) { shape_ok = false; break; }
+      if (v != 0 && elems > UINT64_MAX / v) { shape_ok = false; break; }
+      elems *= v;
+      ti.shape.push_back((size_t)v);
+    }
+    if (!shape_ok || (elems != 0 && dtype_size(ti.dtype) > UINT64_MAX / elems)) {
+      *err = path + ": " + m2.first + ": shape is not a list of unsigned integers whose product fits 64 bits";
+      return false;
+    }
     uint64_t o0 = 0, o1 = 0;
     if (!jo || jo->kind != Json::Array || jo->items.size() != 2 || !jo->items[0].as_u64(&o0) || !jo->items[1].as_u64(&o1) || o1 < o0 ||
         o1 > bytes - data_start) {
@@ -367,6 +382,19 @@ bool config_from_dir(const std::string& dir, dcd_model_config* out, std::string*
   if (!get_usize(c, "intermediate_size", &inter)) { *err = "config missing intermediate_size"; return false; }
   if (!get_usize(c, "vocab_size", &vocab)) { *err = "config missing vocab_size"; return false; }
   if (layers == 0 || layers > 256) { *err = "num_hidden_layers outside 1..256"; return false; }
+  // everything below is narrowed to int32 and multiplied into buffer sizes
+  {
+    const struct { const char* name; uint64_t v, lo, hi; } lim[] = {
+        {"hidden_size", hidden, 1, 1u << 20},          {"num_attention_heads", heads, 1, 1u << 12}, {"num_key_value_heads", kv, 1, 1u << 12},
+        {"head_dim", hd, 1, 1u << 12},                 {"intermediate_size", inter, 1, 1u << 22},   {"vocab_size", vocab, 1, 1u << 26},
+        {"linear_num_key_heads", usize_or(c, "linear_num_key_heads", 16), 1, 1u << 12},
+        {"linear_num_value_heads", usize_or(c, "linear_num_value_heads", 48), 1, 1u << 12},
+        {"linear_key_head_dim", usize_or(c, "linear_key_head_dim", 128), 1, 1u << 12},
+        {"linear_value_head_dim", usize_or(c, "linear_value_head_dim", 128), 1, 1u << 12}};
+    for (const auto& l : lim)
+      if (l.v < l.lo || l.v > l.hi) { *err = std::string("config ") + l.name + " outside " + std::to_string(l.lo) + ".." + std::to_string(l.hi); return false; }
+    if (heads % kv != 0) { *err = "config num_attention_heads is not a multiple of num_key_value_heads"; return false; }
+  }
   double eps = 1e-6;
   if (const Json* e = c.get("rms_norm_eps")) e->as_f64(&eps);
   const Json* lt = c.get("layer_types");

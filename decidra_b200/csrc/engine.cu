@@ -1951,6 +1951,13 @@ void dcd_state_free(dcd_engine* e, dcd_state* st) {
 size_t dcd_state_tokens(const dcd_state* st) { return st ? st->state_len : 0; }
 size_t dcd_state_pos_end(const dcd_state* st) { return st ? st->pos_end : 0; }
 size_t dcd_state_bytes(const dcd_state* st) { return st ? st->bytes : 0; }
+size_t dcd_state_bytes_for(const dcd_engine* e, size_t state_len) { return e ? state_bytes_for(e, state_len) : 0; }
+// Every working buffer of a pass is sized at engine creation (max_pass_tokens); a pass allocates nothing beyond the state
+// itself, so what has to stay free besides a state is the stream-ordered pool's granularity and the CUDA context's own needs.
+size_t dcd_pass_reserve_bytes(const dcd_engine* e, size_t state_len) {
+  (void)state_len;
+  return e ? (size_t)256 << 20 : 0;
+}
 
 int dcd_state_offload(dcd_engine* e, const dcd_state* st, dcd_host_state** out) {
   if (!e || !st || !out) return DCD_E_INVALID;

@@ -72,6 +72,8 @@ void real_host_free(void*, void* hs) { dcd_host_state_free((dcd_host_state*)hs);
 int real_trim(void* c) { return dcd_trim_pools((dcd_engine*)c); }
 int real_mem(void* c, size_t* f, size_t* t) { return dcd_mem_info((dcd_engine*)c, f, t); }
 const char* real_err(void* c) { return dcd_last_error((dcd_engine*)c); }
+size_t real_state_bytes_for(void* c, size_t n) { return dcd_state_bytes_for((const dcd_engine*)c, n); }
+size_t real_pass_reserve(void* c, size_t n) { return dcd_pass_reserve_bytes((const dcd_engine*)c, n); }
 int real_readout_multi(void* c, const void* const* states, size_t n, const uint32_t* const* q, const size_t* lens, const uint32_t* state_of, size_t B,
                        float* out) {
   return dcd_readout_multi_state_batch((dcd_engine*)c, (const dcd_state* const*)states, n, q, lens, state_of, B, out);
@@ -641,6 +643,8 @@ int dcd_scheduler_create(dcd_engine* e, const dcd_sched_options* opt, dcd_schedu
   ops.mem_info = real_mem;
   ops.last_error = real_err;
   ops.readout_multi = real_readout_multi;
+  ops.state_bytes_for = real_state_bytes_for;
+  ops.pass_reserve = real_pass_reserve;
   return dcd_scheduler_create_with_ops(&ops, opt, out);
 }
 

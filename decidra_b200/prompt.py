@@ -94,8 +94,19 @@ def state_end_char(text: str, state) -> int:
     return out.value
 
 
+def char_to_byte_offsets(text: str, offsets: Sequence[tuple]) -> list:
+    """Character offsets (what HF ``tokenizers`` reports in Python) -> UTF-8 byte offsets (what the Rust tokenizer of the
+    reference reports and what ``state_end_char`` / ``state_token_count`` work in). Identity for ASCII text."""
+    at = [0]
+    for ch in text:
+        at.append(at[-1] + len(ch.encode("utf-8")))
+    return [(at[a], at[b]) for a, b in offsets]
+
+
 def state_token_count(offsets: Sequence[tuple], end_char: int) -> int:
-    """``d3::state_token_count``: the state/question split from tokenizer offsets."""
+    """``d3::state_token_count``: the state/question split from tokenizer offsets. ``offsets`` and ``end_char`` are UTF-8 BYTE
+    offsets into the prompt, as in the reference (Rust ``tokenizers`` offsets index the ``&str`` bytes); offsets from a Python
+    tokenizer are character offsets and go through ``char_to_byte_offsets`` first."""
     flat = (C.c_size_t * max(2 * len(offsets), 1))(*[v for pair in offsets for v in pair])
     out = C.c_size_t()
     rc = _lib.load().dcd_d3_state_token_count(flat, len(offsets), end_char, C.byref(out))

@@ -181,7 +181,8 @@ DCD_API void dcd_sched_default_options(dcd_sched_options* o);
 /* What the worker calls on the engine. dcd_scheduler_create fills it with this library's entry points; a test
  * double can stand in (host-made failures: an "out of memory" text, a shrinking free-memory figure).
  * state_bytes_for / pass_reserve may be NULL: the reference's estimates are used
- * (state_cache_bytes_for and pass_reserve, src/batch.rs:198-214). */
+ * (state_cache_bytes_for and pass_reserve, src/batch.rs:198-214); dcd_scheduler_create sets them to
+ * dcd_state_bytes_for / dcd_pass_reserve_bytes. */
 typedef struct dcd_sched_engine_ops {
   void* ctx;
   int32_t readout_rows;
@@ -371,6 +372,12 @@ DCD_API void dcd_state_free(dcd_engine* e, dcd_state* st);
 DCD_API size_t dcd_state_tokens(const dcd_state* st);   /* StateCache::state_tokens */
 DCD_API size_t dcd_state_pos_end(const dcd_state* st);
 DCD_API size_t dcd_state_bytes(const dcd_state* st);    /* state_cache_bytes_for, src/batch.rs:212-214 */
+/* The exact device bytes a captured state of state_len tokens takes in this engine (its model config and storage type), and the
+ * memory that has to stay free beside it for a pass (pass_reserve, src/batch.rs:198-210: there an estimate of FlashInfer's and
+ * cuBLAS's transient needs; here a constant, every working buffer being allocated at engine creation). dcd_scheduler_create
+ * budgets with these instead of the reference's 64 KiB/token + 160 MiB constants. */
+DCD_API size_t dcd_state_bytes_for(const dcd_engine* e, size_t state_len);
+DCD_API size_t dcd_pass_reserve_bytes(const dcd_engine* e, size_t state_len);
 /* StateCache::offload / restore (native/src/engine.rs:559-648; src/batch.rs:683,1034). */
 DCD_API int dcd_state_offload(dcd_engine* e, const dcd_state* st, dcd_host_state** out);
 DCD_API int dcd_state_restore(dcd_engine* e, const dcd_host_state* hs, dcd_state** out);

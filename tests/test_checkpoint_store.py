@@ -136,6 +136,13 @@ def test_malformed_files_are_rejected(ck, tmp_path):
         p.write_bytes(struct.pack("<Q", len(h)) + h + b"\0" * 8)
         with pytest.raises(Exception, match=what):
             ck.Store(p)
+    # a dimension that is not an unsigned integer, and a shape whose element count wraps 64 bits and would then "match" its range
+    for shape, tag in (([2.5], "frac"), ([-2], "neg"), (["2"], "str"), ([1 << 62, 4, 2], "wrap"), ([1 << 63, 2], "wrap2")):
+        h = json.dumps({"t": {"dtype": "F32", "shape": shape, "data_offsets": [0, 8]}}).encode()
+        p = tmp_path / f"shape_{tag}.safetensors"
+        p.write_bytes(struct.pack("<Q", len(h)) + h + b"\0" * 8)
+        with pytest.raises(Exception, match="shape is not a list of unsigned integers"):
+            ck.Store(p)
     write_safetensors(tmp_path / "ok.safetensors", good)
     assert ck.Store(tmp_path / "ok.safetensors").array("t").tolist() == [1.0, 2.0]
 
@@ -205,6 +212,14 @@ def test_config_fails_closed(ck, tmp_path):
     _write_cfg(tmp_path / "missing", missing, {"attention_mode": "prefix_bidir"})
     with pytest.raises(Exception, match="config missing vocab_size"):
         ck.config_from_dir(tmp_path / "missing")
+    # integers that would not survive the narrowing to the engine's 32-bit fields, or make no model
+    for key, value, what in (("hidden_size", 1 << 33, "hidden_size outside"), ("vocab_size", 1 << 40, "vocab_size outside"),
+                             ("intermediate_size", 0, "intermediate_size outside"), ("num_attention_heads", 1 << 20, "num_attention_heads outside"),
+                             ("num_key_value_heads", 3, "not a multiple")):
+        bad = {"text_config": dict(MINIMAL["text_config"], **{key: value})}
+        _write_cfg(tmp_path / ("bad_" + key), bad, {"attention_mode": "prefix_bidir"})
+        with pytest.raises(Exception, match=what):
+            ck.config_from_dir(tmp_path / ("bad_" + key))
     (tmp_path / "empty").mkdir()
     with pytest.raises(Exception, match="config.json"):
         ck.config_from_dir(tmp_path / "empty")

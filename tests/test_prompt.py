@@ -159,3 +159,19 @@ _json_plain = st.recursive(
 def test_repr_is_cpython_repr_on_quote_free_strings(P, value):
     assert P.py_repr(value) == repr(value)
     assert P.py_str(value) == str(value)
+
+
+def test_state_split_on_non_ascii_text_needs_byte_offsets(P):
+    """``state_end_char`` is a UTF-8 byte offset (as in the reference); a Python tokenizer's character offsets have to be converted,
+    or the split lands too late for every multi-byte character in the state."""
+    state = "caf\u00e9 \u2014 na\u00efve r\u00e9sum\u00e9 \u6771\u4eac"
+    text = P.render(state, {"type": "choice", "instructions": "Pick", "criteria": {"yes": None, "no": None}}, ["A", "B"])
+    end = P.state_end_char(text, state)
+    assert text.encode()[:end].decode().endswith(state) and end > text.index(state) + len(state)   # bytes, not characters
+    # a toy tokenizer: one token per character, character offsets as a Python tokenizer reports them
+    chars = [(i, i + 1) for i in range(len(text))]
+    end_char_index = len(text.encode()[:end].decode())
+    want = sum(1 for a, b in chars if b <= end_char_index)
+    assert P.state_token_count(P.char_to_byte_offsets(text, chars), end) == want
+    assert P.state_token_count(chars, end) > want           # character offsets against a byte boundary: too many tokens in the state
+    assert P.char_to_byte_offsets("abc", [(0, 1), (1, 3)]) == [(0, 1), (1, 3)]
