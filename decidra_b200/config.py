@@ -1,4 +1,4 @@
-"""Model and option structs of the C ABI, plus the two BASELINE presets.
+"""Model and option structs of the C ABI, plus the two benchmark presets (the tiny CPU-runnable hybrid and the d3-turbo shape).
 
 ``ModelConfig`` mirrors ``dcd_model_config`` (include/decidra_b200.h), the plain-struct form of
 juanqui/decidra's ``Config`` (native/src/config.rs:49-158).
@@ -96,14 +96,14 @@ def make_config(*, num_layers, hidden, heads, kv_heads, head_dim, rotary_dim, ro
 
 
 def tiny_config(dtype: int = 0) -> ModelConfig:
-    """BASELINE config 1: 4 layers [GDN,GDN,GDN,full], hidden 256, 4q/1kv heads of 64, GDN 2k/4v heads of
+    """The tiny hybrid the reference can run on its CPU scalar path: 4 layers [GDN,GDN,GDN,full], hidden 256, 4q/1kv heads of 64, GDN 2k/4v heads of
     64, SwiGLU 688, vocab 4096, readout [255,256]. partial_rotary_factor 0.25 (as d3-turbo) → rotary_dim 16."""
     return make_config(num_layers=4, hidden=256, heads=4, kv_heads=1, head_dim=64, rotary_dim=16, rope_theta=1e7,
                        gdn_k_heads=2, gdn_v_heads=4, gdn_dk=64, gdn_dv=64, intermediate=688, vocab=4096, dtype=dtype)
 
 
 def d3_config(num_layers: int = 64, dtype: int = 1, vocab: int = 248320) -> ModelConfig:
-    """BASELINE configs 2-5 (d3-turbo shape): 3 GDN : 1 full, hidden 5120, 24q/4kv heads of 256 (rotary 64),
+    """The d3-turbo shape of the headline benchmark and of the quantised and ragged-stress workloads: 3 GDN : 1 full, hidden 5120, 24q/4kv heads of 256 (rotary 64),
     GDN 16k/48v heads of 128, SwiGLU 17408, vocab 248320, readout [255,5120]."""
     return make_config(num_layers=num_layers, hidden=5120, heads=24, kv_heads=4, head_dim=256, rotary_dim=64, rope_theta=1e7,
                        gdn_k_heads=16, gdn_v_heads=48, gdn_dk=128, gdn_dv=128, intermediate=17408, vocab=vocab, dtype=dtype)

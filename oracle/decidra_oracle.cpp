@@ -19,10 +19,13 @@
 //    norm, SwiGLU, sigmoid gate, FP8 quantiser, W4 dequantiser): the reference's own kernels.cu
 //    compiled for sm_100a (oracle/Makefile `ref`) and run on the GPU next to this restatement,
 //    tests/test_gpu_reference_kernels.py;
-//  * GEMM and attention arithmetic lives in third-party code of the reference (cuBLAS via
-//    cudarc 0.19.10; FlashInfer 0.7.0.post1 templates) and the model-level goldens need its
-//    checkpoint: there parity is unpinned and rests on the published algorithms
-//    (f32-accumulated GEMM; softmax(QK^T/sqrt(d))V with bf16 probabilities).
+//  * GEMM, attention, the chunked tensor-core GDN, the NVFP4 activation quantiser and the model-level
+//    results (layer outputs, logits, argmax): the reference's own CUDA run on the GPU, oracle/ref_gpu.py:
+//    its kernels.cu cubin, its FlashInfer 0.7.0.post1 shim (fi_prefill.cu) compiled for sm_100a and
+//    cuBLAS (through torch.matmul; the reference reaches it through cudarc 0.19.10), driven in the launch
+//    order of native/src/engine.rs; compared three ways (product, reference kernels, this file) in
+//    tests/test_gpu_oracle_a.py. The reference's checkpoint is not available, so model-level
+//    comparisons use the seeded generator both sides share.
 //
 // Build: see oracle/Makefile (g++ -O3 -mavx2 -ffp-contract=off -fopenmp).
 
@@ -89,7 +92,7 @@ struct Round {
 
 // ---------------------------------------------------------------------------
 // Seeded weight generator. Not from the reference (it loads a checkpoint that is
-// not available); BASELINE asks for "random-init N(0,0.02), seed 0". The
+// not available); the benchmark workloads are defined on "random-init N(0,0.02), seed 0". The
 // generator is integer-only up to one float multiply so that CPU and GPU
 // produce bit-identical tensors:
 //   key = mix64(mix64(seed) ^ tensor_id)
@@ -285,12 +288,12 @@ ORC_API void orc_k_quant_fp8_rows(const float* x, int rows, int cols, float clip
 ORC_API float orc_k_e4m3_to_f32(uint8_t c) { return e4m3_to_f32(c); }
 
 // ---------------------------------------------------------------------------
-// W4A16, group 128 (BASELINE config 3: "int4 symmetric, group 128, fp16 scales, quantised from seeded
+// W4A16, group 128 (the W4A16 benchmark workload: "int4 symmetric, group 128, fp16 scales, quantised from seeded
 // random BF16"). Packing and dequantisation follow compressed-tensors pack-quantized as the reference
 // reads it (native/src/weights.rs:292-330; dequant_w4a16_bf16, native/kernels/kernels.cu:867-892):
 // nibble k of word packed[o, i>>3] holds input 8*(i>>3)+k, symmetric zero-point 8,
-// w[o,i] = bf16(float(q - 8) * float(scale[o, i/128])). The reference stores bf16 scales; BASELINE
-// asks for fp16. Round-to-nearest quantiser (the reference's checkpoints come from GPTQ, which is
+// w[o,i] = bf16(float(q - 8) * float(scale[o, i/128])). The reference stores bf16 scales; the W4A16
+// benchmark workload asks for fp16. Round-to-nearest quantiser (the reference's checkpoints come from GPTQ, which is
 // offline tooling and out of scope): scale = fp16(absmax/7), q = clamp(rint(w/scale), -8, 7).
 // ---------------------------------------------------------------------------
 static inline uint16_t f32_to_f16(float x) {  // round-to-nearest-even, host twin of __float2half_rn

@@ -1,6 +1,6 @@
 """Generates the committed oracle fixtures.
 
-tests/golden/tiny_oracle.npz: logits of the CPU oracle on BASELINE config 1 (tiny hybrid,
+tests/golden/tiny_oracle.npz: logits of the CPU oracle on the tiny CPU-runnable benchmark model (tiny hybrid,
 seed 0, one 128-token state, questions of 16/20/24/32 tokens; ids from PCG64(0)), in f32 and bf16 modes.
 
 tests/golden/d3_slice_oracle.npz (``--d3``, a few minutes of CPU): a 4-layer [GDN,GDN,GDN,full] slice at

@@ -301,7 +301,7 @@ def test_fp8_precision_tiny(dcd, oracle):
 
 
 def test_w4a16_precision(dcd, oracle):
-    """precision = 1 (BASELINE config 3): GEMM weights held as int4 group-128 + fp16 scales, dequantised per
+    """precision = 1 (the W4A16 benchmark workload): GEMM weights held as int4 group-128 + fp16 scales, dequantised per
     GEMM; all passes. Against the oracle with the same round-to-nearest quantiser: the dequantised weights
     are bit-identical, so the bars are those of the bf16 engine."""
     cfg = dcd.tiny_config(1)
@@ -339,7 +339,7 @@ def test_w4a16_precision(dcd, oracle):
 
 
 def test_ragged_stress_shapes_tiny(dcd, oracle):
-    """BASELINE config 5 in miniature (seed 7): a long state, many questions with lengths uniform in
+    """The ragged-stress benchmark workload in miniature (seed 7): a long state, many questions with lengths uniform in
     [16,512], more tokens than one pass holds, so the planner splits by tokens and rows come back in
     input order. Checked against the oracle question by question."""
     cfg = dcd.tiny_config(1)

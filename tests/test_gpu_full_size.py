@@ -1,4 +1,4 @@
-"""The full 64-layer d3-shaped model at BASELINE configs[4] sizes (ragged stress: long states, many questions of
+"""The full 64-layer d3-shaped model at the sizes of the ragged-stress benchmark workload ( long states, many questions of
 16-512 tokens), where the CPU oracle is out of reach: size-independent properties instead. A permuted batch must
 give the same rows (the chunk planner sorts and cuts the batch, rows go back to input order), a state that went
 through pinned host memory must answer identically, and one pass over several states must equal a pass per state.
