@@ -149,6 +149,7 @@ SIGNATURES = {
     "dcd_profile_read": (I, [P, C.POINTER(ProfEntry)]),
     "dcd_launch_count": (C.c_int64, [P]),
     "dcd_debug_bounded_wait_probe": (C.c_int, [P, C.c_int]),
+    "dcd_debug_set_gemm_group_m": (None, [I]),
     "dcd_debug_layer_outputs": (I, [P, FP, SZ]),
     "dcd_block_cascade_mask": (I, [SZ, SZ, C.POINTER(C.c_uint8)]),
     "dcd_plan_chunks": (I, [C.POINTER(SZ), SZ, SZ, SZ, SZ, SZ, I32P, I32P, I32P]),

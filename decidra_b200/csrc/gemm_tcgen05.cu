@@ -29,7 +29,7 @@ constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
-constexpr int GROUP_M = 16;  // rasterisation: 16 M-tiles share each W tile while it is hot in L2
+constexpr int GROUP_M = 16;  // default rasterisation: 16 M-tiles share each W tile while it is hot in L2 (see pick_group_m)
 
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
 // 8-row groups 1024 bytes apart. Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused
@@ -77,11 +77,11 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_idx, int& n_idx) {
-  const int per_group = GROUP_M * num_n;
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int& m_idx, int& n_idx) {
+  const int per_group = group_m * num_n;
   const int g = tile / per_group;
-  const int first_m = g * GROUP_M;
-  const int gsize = min(GROUP_M, num_m - first_m);
+  const int first_m = g * group_m;
+  const int gsize = min(group_m, num_m - first_m);
   const int r = tile - g * per_group;
   m_idx = first_m + r % gsize;
   n_idx = r / gsize;
@@ -100,7 +100,7 @@ template <int EPI, int ESZ>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
                     int M, int N, int K, int ldc, const float* __restrict__ a_scale, const float* __restrict__ w_scale,
-                    const float* __restrict__ alpha, int* __restrict__ err, const bf16* __restrict__ resid) {
+                    const float* __restrict__ alpha, int* __restrict__ err, const bf16* __restrict__ resid, int group_m) {
   constexpr int BKE = 128 / ESZ;  // K elements per 128-byte swizzled row
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -149,7 +149,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_idx, n_idx;
-        tile_coords(tile, num_m, num_n, m_idx, n_idx);
+        tile_coords(tile, num_m, num_n, group_m, m_idx, n_idx);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -195,7 +195,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_idx, n_idx;
-      tile_coords(tile, num_m, num_n, m_idx, n_idx);
+      tile_coords(tile, num_m, num_n, group_m, m_idx, n_idx);
       ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -397,6 +397,17 @@ cudaError_t tc_gemm_prepare_device() {
   return cudaSuccess;
 }
 
+// M tiles per rasterisation group. A group sweeps all N tiles with its M tiles innermost, so the W panel streams from DRAM once
+// per group while the group's rows of X stay in L2: fewer, larger groups re-read W less. The override is for measurements.
+static int g_group_m_override = 0;
+void tc_gemm_set_group_m(int group_m) { g_group_m_override = group_m; }
+static int pick_group_m(int M, int K, int esz) {
+  (void)K; (void)esz;
+  const int num_m = (M + tcg::BM - 1) / tcg::BM;
+  int g = g_group_m_override > 0 ? g_group_m_override : tcg::GROUP_M;
+  return g < num_m ? g : (num_m > 0 ? num_m : 1);
+}
+
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
                            int sm_count, int* err, cudaStream_t stream, const float* alpha, const void* resid) {
   if (resid && epi != 0) return cudaErrorInvalidValue;
@@ -404,8 +415,8 @@ cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void*
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, (const bf16*)resid);
-  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, nullptr);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, (const bf16*)resid, pick_group_m(M, K, 2));
+  else tcg::gemm_bf16_tc_kernel<1, 2><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, nullptr, nullptr, alpha, err, nullptr, pick_group_m(M, K, 2));
   return cudaGetLastError();
 }
 
@@ -418,8 +429,8 @@ cudaError_t tc_gemm_fp8_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, v
   const int grid = num_tiles < sm_count ? num_tiles : sm_count;
   const CUtensorMap& a = *reinterpret_cast<const CUtensorMap*>(tmA);
   const CUtensorMap& b = *reinterpret_cast<const CUtensorMap*>(tmB);
-  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, (const bf16*)resid);
-  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, nullptr);
+  if (epi == 0) tcg::gemm_bf16_tc_kernel<0, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, (const bf16*)resid, pick_group_m(M, K, 1));
+  else tcg::gemm_bf16_tc_kernel<1, 1><<<grid, tcg::NUM_THREADS, tcg::SMEM_BYTES, stream>>>(a, b, (bf16*)C, M, N, K, ldc, a_scale, w_scale, nullptr, err, nullptr, pick_group_m(M, K, 1));
   return cudaGetLastError();
 }
 

@@ -23,6 +23,8 @@ cudaError_t tc_gemm_prepare_device();
 // epi 0: C[M,N] (row stride ldc). epi 1: SwiGLU over gate/up-interleaved weights, C[M,N/2].
 // alpha: optional device scalar multiplied into the accumulator before rounding.
 // resid (epi 0 only): optional bf16 [M, ldc]; C = bf16(resid + bf16(product)).
+// M tiles per rasterisation group of the bf16 / e4m3 GEMM (0 = the built-in choice); for measurements.
+void tc_gemm_set_group_m(int group_m);
 cudaError_t tc_gemm_launch(const TcTensorMap* tmA, const TcTensorMap* tmB, void* C, int M, int N, int K, int ldc, int epi,
                            int sm_count, int* err, cudaStream_t stream, const float* alpha = nullptr, const void* resid = nullptr);
 

@@ -120,6 +120,8 @@ int dcd_k_gemm_nvfp4_tc_tiled(const void* xq, const void* x_tiled, const void* w
                                  (uint8_t*)q_packed, (uint8_t*)q_tiled));
 }
 
+void dcd_debug_set_gemm_group_m(int group_m) { tc_gemm_set_group_m(group_m); }
+
 int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream) {
   return DISPATCH(dtype, launch_gemm_fma<float>((const float*)X, (const float*)W, (float*)C, M, N, K, N, S(stream)),
                   launch_gemm_fma<bf16>((const bf16*)X, (const bf16*)W, (bf16*)C, M, N, K, N, S(stream)));

@@ -523,6 +523,9 @@ DCD_API int dcd_k_gemm_nvfp4_tc(const void* xq, const void* x_scales, const void
 DCD_API int dcd_k_gemm_nvfp4_tc_tiled(const void* xq, const void* x_tiled, const void* wq, const void* w_tiled, void* C, int M, int N, int K,
                                       int ldc, const float* alpha, int sm_count, int* err, int tile_n, const void* resid, void* q_packed,
                                       void* q_tiled, void* stream);
+/* M tiles per rasterisation group of the bf16 / e4m3 tcgen05 GEMM, process-wide (0 = the library's choice): a group sweeps all N
+ * tiles with its M tiles innermost, so the weight panel streams from DRAM once per group. For measurements. */
+DCD_API void dcd_debug_set_gemm_group_m(int group_m);
 /* The same contraction with plain FMA; T in, T out, f32 accumulate (f32 engine, diagnostics). */
 DCD_API int dcd_k_gemm_fma(const void* X, const void* W, void* C, int M, int N, int K, int dtype, void* stream);
 /* rmsnorm_bf16 / add_rmsnorm_bf16 (native/kernels/kernels.cu:378-426). */

@@ -442,4 +442,5 @@ def test_quantised_engines_on_a_d3_shaped_slice(dcd, oracle, precision, name):
     print(f"d3-shaped slice, {name}: max abs vs oracle in the same mode {err:.3g} (bar {bar:.3g}; the mode itself moves the logits by {effect:.3g}); "
           f"gemm launches {prof['gemm']['launches']}")
     assert np.isfinite(got).all() and err < bar, (name, err, bar)
-    assert (np.argmax(got, 1) == np.argmax(want, 1)).mean() >= 0.75
+    if precision == 1:   # same codes, same scales, same dequantised weights on both sides: only bf16 accumulation noise is left
+        assert err < 0.12 and (np.argmax(got, 1) == np.argmax(want, 1)).all()

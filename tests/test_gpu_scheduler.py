@@ -37,7 +37,7 @@ def test_scheduler_replies_equal_direct_calls(dcd):
     # the cache's byte ledger holds what the state really takes in this engine (its config and storage type), not the
     # reference's 64 KiB per token
     st0 = e.capture_state(cases[0][0])
-    assert h.stats()["gpu_bytes"] == st0.nbytes() > 0 and st0.nbytes() != len(cases[0][0]) * 65536
+    assert h.stats()["gpu_bytes"] == st0.nbytes > 0 and st0.nbytes != len(cases[0][0]) * 65536
     st0.free()
     # device hit with a subset of the questions
     got = h.submit_state_once(cases[0][0], cases[0][1][1:3]).result()
