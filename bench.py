@@ -730,7 +730,10 @@ def run_ours(args):
         R.barrier()  # every rank has freed its engines; rank 0 alone now drives all the GPUs from one process
         R.host_barrier()
         if rank == 0:
-            box_info = run_box(dcd, args, list(range(world)) if world > 1 else [local] * args.box_replicas, args.box_precision, args.box_states)
+            try:
+                box_info = run_box(dcd, args, list(range(world)) if world > 1 else [local] * args.box_replicas, args.box_precision, args.box_states)
+            except Exception as ex:  # noqa: BLE001  (the line of the per-rank arms must survive a failure of this extra arm)
+                box_info = {"error": repr(ex)}
         R.host_barrier()
 
     if rank == 0:
