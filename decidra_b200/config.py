@@ -76,7 +76,8 @@ class Options(C.Structure):
         ("w4a16_gemm", C.c_int32),
         ("nvfp4_fusion", C.c_int32),
         ("attn_split", C.c_int32),
-        ("reserved", C.c_int32 * 2),
+        ("w4a16_prefetch", C.c_int32),
+        ("reserved", C.c_int32 * 1),
     ]
 
 

@@ -87,7 +87,8 @@ struct LayerW {
   // W4A16 group-128 images (precision 1): the only resident copy of the six GEMM weights
   // q: words in the nibble order [k0 k2 k4 k6 k1 k3 k5 k7]; scale: fp16 [N, K/128]; scale_t: the same transposed to [K/128][N] and
   // tm_q: TMA descriptor over q, both for the fused W4A16 GEMM (K % 128 == 0)
-  struct W4 { uint32_t* q = nullptr; void* scale = nullptr; void* scale_t = nullptr; int N = 0, K = 0; bool fused = false; TcTensorMap tm_q; };
+  struct W4 { uint32_t* q = nullptr; void* scale = nullptr; void* scale_t = nullptr; int N = 0, K = 0; bool fused = false; TcTensorMap tm_q;
+              TcTensorMap tm_stage[2]; };  // this weight's [N, K] bf16 image in either of the two dequantisation stages
   W4 g_gu, g_down, g_qkv, g_o, g_gin, g_out;
   // NVFP4 images (precision 3): e2m1 codes, e4m3 scale per 16, f32 tensor scale and GEMM alpha on the device
   // codes, row-major scales, the same scales in the 128 x 4 tiled layout of the block-scaled MMA, tensor scale, 1/tensor scale
@@ -151,6 +152,15 @@ struct dcd_engine {
   unsigned int* amax_tmp = nullptr;
   bool w4 = false;                     // precision 1: int4 g128 weights, dequantised per GEMM into wstage
   void* wstage = nullptr;              // bf16 [max N*K] stage shared by all W4 GEMMs
+  // precision 1, staged route, w4a16_prefetch = 1: a second stage and a second stream, so that the weight of the NEXT projection is
+  // dequantised while the tensor cores run the current one. Off by default: under the power cap the GEMM slows by more than the
+  // dequantisation it hides (8 layers: 54.96 ms per step with it, 53.56 without; identical results)
+  void* wstage2 = nullptr;
+  cudaStream_t stream2 = nullptr;
+  cudaEvent_t w4_free[2] = {nullptr, nullptr}, w4_ready[2] = {nullptr, nullptr};  // stage b: last GEMM that read it launched / image complete
+  const void* w4_holds[2] = {nullptr, nullptr};                                    // the W4 whose image stage b holds or is being given
+  bool w4_pending[2] = {false, false};                                             // written on stream2, not yet awaited by the main stream
+  int w4_cur = 0;                                                                  // stage read by the last staged GEMM
   bool fp8 = false, fp8_dirty = true;  // precision 2: e4m3 GEMMs in question passes of >= fp8_min_rows rows
   uint8_t* aq = nullptr;               // [Tm, max K] quantised activations
   float* a_scale = nullptr;            // [Tm] per-token scales
@@ -319,6 +329,7 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
   // resid: C = bf16(resid + bf16(X W^T)) in the epilogue (tensor-core paths). x_set: which of the two NVFP4 activation buffer sets
   // holds a pre-quantised X (0: xq / xsft, 1: aq4 / asft4). act_out (native NVFP4, gate/up projection): the epilogue applies SwiGLU
   // and writes the NVFP4 image of the activation into set 1 instead of C.
+  int w4_stage_used = -1;
   if (resid && !(e->nv4_native && n4->sft && nvfp4_tc_shape_ok(M, N, K)) && (e->nv4 || !(e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K))))
     return fail(e, DCD_E_INVALID, "internal: fused residual on a GEMM path without that epilogue");
   if (e->nv4_native && epi == 0 && n4->sft && nvfp4_tc_shape_ok(M, N, K)) {
@@ -369,9 +380,26 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
     // ... or, where 256-row tiles would leave the GPU half empty (or the shape is not the kernel's): int4 -> bf16 into the shared
     // stage, then the bf16 tensor-core GEMM reads the stage (the reference's dequant_w4a16_bf16 + BF16 GEMM route,
     // native/src/engine.rs:4516-4558)
-    Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5 * N * (double)K, 1);
-    CK(e, launch_dequant_w4_g128(g4->q, g4->scale, (bf16*)e->wstage, N, K, e->stream, true), "w4 dequantisation");
-    W = e->wstage;
+    int b = -1;
+    for (int i = 0; i < 2; ++i)
+      if (e->wstage2 && e->w4_pending[i] && e->w4_holds[i] == g4) b = i;
+    if (b >= 0) {  // dequantised ahead on the second stream (w4_prefetch)
+      CK(e, cudaStreamWaitEvent(e->stream, e->w4_ready[b], 0), "w4 stage ready");
+      e->w4_pending[b] = false;
+    } else {
+      b = e->wstage2 ? e->w4_cur ^ 1 : 0;
+      if (e->w4_pending[b]) {  // a prefetch nobody asked for after all: let it finish before the stage is rewritten
+        CK(e, cudaStreamWaitEvent(e->stream, e->w4_ready[b], 0), "w4 stage ready");
+        e->w4_pending[b] = false;
+      }
+      Scope sc(e, DCD_PROF_ELEMENTWISE, 2.5 * N * (double)K, 1);
+      CK(e, launch_dequant_w4_g128(g4->q, g4->scale, (bf16*)(b ? e->wstage2 : e->wstage), N, K, e->stream, true), "w4 dequantisation");
+      e->w4_holds[b] = g4;
+    }
+    W = b ? e->wstage2 : e->wstage;
+    tmB = &g4->tm_stage[b];
+    e->w4_cur = b;
+    w4_stage_used = b;
   }
   if (fw && e->bf && e->o.gemm_path == 0 && tc_fp8_shape_ok(M, N, K)) {
     {
@@ -387,10 +415,33 @@ int gemm(dcd_engine* e, const void* X, const TcTensorMap* tmA, const void* W, co
   Scope sc(e, DCD_PROF_GEMM, 2.0 * M * (double)N * K, 1);
   if (e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, N, K)) {
     CK(e, tc_gemm_launch(tmA, tmB, C, M, N, K, ldc, epi, e->sm_count, e->d_err, e->stream, nullptr, resid), "tcgen05 gemm");
+    if (w4_stage_used >= 0 && e->wstage2) CK(e, cudaEventRecord(e->w4_free[w4_stage_used], e->stream), "w4 stage free");
     return DCD_OK;
   }
   if (epi != 0) return fail(e, DCD_E_INVALID, "internal: fused epilogue without tensor-core path");
   CK(e, launch_gemm_fma<T>((const T*)X, (const T*)W, (T*)C, M, N, K, ldc, e->stream), "fma gemm");
+  return DCD_OK;
+}
+
+// Staged W4A16 route: would gemm() dequantise this weight into a stage for a pass of M rows?
+bool w4_takes_stage(const dcd_engine* e, const LayerW::W4* g4, int M) {
+  if (!e->w4 || !g4 || !g4->q) return false;
+  const bool fused = g4->fused && e->o.gemm_path == 0 && e->o.w4a16_gemm != 1 && w4a16_tc_shape_ok(M, g4->N, g4->K) &&
+                     (e->o.w4a16_gemm == 2 || w4a16_tc_prefer(M, g4->N, e->sm_count));
+  return !fused;
+}
+// Start dequantising the weight of the NEXT projection on the second stream into the stage the GEMM launched last does not read.
+// That stage was last read by the GEMM before it, whose completion event the second stream awaits first.
+int w4_prefetch(dcd_engine* e, const LayerW::W4* next, int M) {
+  if (!e->wstage2 || !w4_takes_stage(e, next, M) || !(e->bf && e->o.gemm_path == 0 && tc_shape_ok(M, next->N, next->K))) return DCD_OK;
+  const int b = e->w4_cur ^ 1;
+  if (e->w4_pending[b]) return DCD_OK;  // still holds an image nobody consumed
+  CK(e, cudaStreamWaitEvent(e->stream2, e->w4_free[b], 0), "w4 stage free");
+  CK(e, launch_dequant_w4_g128(next->q, next->scale, (bf16*)(b ? e->wstage2 : e->wstage), next->N, next->K, e->stream2, true), "w4 dequantisation ahead");
+  CK(e, cudaEventRecord(e->w4_ready[b], e->stream2), "w4 stage ready");
+  e->w4_holds[b] = next;
+  e->w4_pending[b] = true;
+  e->launches += 1;
   return DCD_OK;
 }
 
@@ -459,6 +510,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
     }
     if (w.full) {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_qkv, &w.tm_qkv, q8 ? &w.f_qkv : nullptr, &w.g_qkv, &w.n_qkv, e->big, T_, e->qkv_n, H, e->qkv_n, 0, h_fused_quant);
+      if (!rc) rc = w4_prefetch(e, &w.g_o, T_);
       if (rc) return rc;
       T* big = (T*)e->big;
       T* kdst = p.mode == 0 ? (T*)p.cap->k[li] : (T*)e->kown;
@@ -509,9 +561,11 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       rc = gemm<T>(e, e->bufA, &tm_A, w.w_o, &w.tm_o, q8 ? &w.f_o : nullptr, &w.g_o, &w.n_o, fused_resid ? e->x1 : e->mix, T_, H, heads * hd, H, 0, false,
                    fused_resid ? e->x : nullptr);
+      if (!rc) rc = w4_prefetch(e, &w.g_gu, T_);
       if (rc) return rc;
     } else {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gin, &w.tm_gin, q8 ? &w.f_gin : nullptr, &w.g_gin, &w.n_gin, e->big, T_, e->gin_n, H, e->gin_n, 0, h_fused_quant);
+      if (!rc) rc = w4_prefetch(e, &w.g_out, T_);
       if (rc) return rc;
       T* big = (T*)e->big;
       if (p.mode == 0) {
@@ -574,6 +628,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
       }
       rc = gemm<T>(e, e->bufB, &tm_B, w.w_out, &w.tm_out, q8 ? &w.f_out : nullptr, &w.g_out, &w.n_out, fused_resid ? e->x1 : e->mix, T_, H, e->vd, H, 0, gnorm4,
                    fused_resid ? e->x : nullptr);
+      if (!rc) rc = w4_prefetch(e, &w.g_gu, T_);
       if (rc) return rc;
     }
     {
@@ -591,6 +646,7 @@ int run_layers(dcd_engine* e, const Pass& p) {
     }
     if (fused_swiglu) {
       int rc = gemm<T>(e, e->h, &tm_h, w.w_gu, &w.tm_gu, q8 ? &w.f_gu : nullptr, &w.g_gu, &w.n_gu, e->act, T_, e->gu_rows, H, e->I, 1);
+      if (!rc) rc = w4_prefetch(e, &w.g_down, T_);
       if (rc) return rc;
     } else if (act_epi4) {
       // gate/up projection whose epilogue applies SwiGLU and leaves the activation as NVFP4 in set 1 (ldc = the activation width)
@@ -605,6 +661,8 @@ int run_layers(dcd_engine* e, const Pass& p) {
     }
     int rc = gemm<T>(e, e->act, &tm_act, w.w_down, &w.tm_down, q8 ? &w.f_down : nullptr, &w.g_down, &w.n_down, fused_resid ? e->x : e->mix, T_, H, e->I, H, 0, act_fused_quant,
                      fused_resid ? e->x1 : nullptr, act_epi4 ? 1 : 0);
+    if (!rc && li + 1 < c.num_layers)
+      rc = w4_prefetch(e, e->layers[li + 1].full ? &e->layers[li + 1].g_qkv : &e->layers[li + 1].g_gin, T_);
     if (rc) return rc;
     if (li + 1 < c.num_layers) {
       Scope sc(e, DCD_PROF_ELEMENTWISE, 4.0 * xbytes, 1);
@@ -791,6 +849,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (o.w4a16_gemm < 0 || o.w4a16_gemm > 2) return fail(nullptr, DCD_E_INVALID, "w4a16_gemm must be 0, 1 or 2");
   if (o.nvfp4_fusion < 0 || o.nvfp4_fusion > 1) return fail(nullptr, DCD_E_INVALID, "nvfp4_fusion must be 0 or 1");
   if (o.attn_split < 0 || o.attn_split > 1) return fail(nullptr, DCD_E_INVALID, "attn_split must be 0 or 1");
+  if (o.w4a16_prefetch < 0 || o.w4a16_prefetch > 1) return fail(nullptr, DCD_E_INVALID, "w4a16_prefetch must be 0 or 1");
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -890,6 +949,14 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
     up(H * (size_t)e->I); up((size_t)e->qkv_n * H); up(H * (size_t)c.heads * c.head_dim); up((size_t)e->gin_n * H); up(H * (size_t)e->vd);
     CRA(e->wstage, mx * 2, true, &e->weight_bytes);
     if (e->nv4) CRA(e->amax_tmp, 256, true, &e->weight_bytes);
+    if (e->w4 && e->bf && o.w4a16_prefetch == 1) {
+      CRA(e->wstage2, mx * 2, true, &e->weight_bytes);
+      CRE(cudaStreamCreateWithFlags(&e->stream2, cudaStreamNonBlocking), "second stream");
+      for (int i = 0; i < 2; ++i) {
+        CRE(cudaEventCreateWithFlags(&e->w4_free[i], cudaEventDisableTiming), "event");
+        CRE(cudaEventCreateWithFlags(&e->w4_ready[i], cudaEventDisableTiming), "event");
+      }
+    }
   }
   CRA(e->embed, (size_t)c.vocab * H * es, false, &e->weight_bytes);
   CRA(e->final_norm, H * es, true, &e->weight_bytes);
@@ -929,6 +996,10 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
           rc = dev_alloc(e, &g.scale_t, n * (k / 128) * 2, true, &e->weight_bytes);
           if (!rc && w4a16_make_tmap_packed(&g.tm_q, g.q, n, k)) rc = fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for an int4 weight operand");
           g.fused = !rc;
+        }
+        if (!rc && e->bf && o.gemm_path == 0) {  // the weight's image in either dequantisation stage, as a GEMM operand
+          if (tc_make_tmap_b(&g.tm_stage[0], e->wstage, n, k) || (e->wstage2 && tc_make_tmap_b(&g.tm_stage[1], e->wstage2, n, k)))
+            rc = tc_shape_ok(128, (int)n, (int)k) ? fail(e, DCD_E_CUDA, "cuTensorMapEncodeTiled failed for a staged weight operand") : DCD_OK;
         }
         return rc;
       };
@@ -1086,6 +1157,11 @@ void dcd_engine_destroy(dcd_engine* e) {
   for (auto ev : e->prof.pool) cudaEventDestroy(ev);
   if (e->t0) cudaEventDestroy(e->t0);
   if (e->t1) cudaEventDestroy(e->t1);
+  if (e->stream2) { cudaStreamSynchronize(e->stream2); cudaStreamDestroy(e->stream2); }
+  for (int i = 0; i < 2; ++i) {
+    if (e->w4_free[i]) cudaEventDestroy(e->w4_free[i]);
+    if (e->w4_ready[i]) cudaEventDestroy(e->w4_ready[i]);
+  }
   if (e->stream) cudaStreamDestroy(e->stream);
   delete e;
 }

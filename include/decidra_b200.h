@@ -92,7 +92,10 @@ typedef struct dcd_options {
   int32_t attn_split;       /* tcgen05 attention: 0 = default: when a launch has no more CTAs than there are SMs and the state is at least eight
                                key tiles long, the key tiles of each (token tile, KV head) are split over several CTAs and a second kernel
                                merges the parts; 1 = never split */
-  int32_t reserved[2];
+  int32_t w4a16_prefetch;   /* precision 1, staged route: 0 = default: one stage, dequantise then multiply; 1 = the next projection's weight is
+                               dequantised on a second stream into a second stage while the tensor cores run the current projection (same
+                               results; measured slower under the power cap, kept for boxes that are not power-limited) */
+  int32_t reserved[1];
 } dcd_options;
 
 typedef struct dcd_info {
