@@ -45,7 +45,8 @@ UNIT = "questions/s"
 VOCAB = 248320
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up (SwiGLU epilogue) GEMM launch of the question pass
 # (M = 6835 rows, K = 5120, N = 34816), from an ncu capture of a 4-layer slice of the same model
-# (algorithmic bytes of that launch: 2*(M*K + N*K + M*N/2) = 664.5 MB).
+# (algorithmic bytes of that launch: 2*(M*K + N*K + M*N/2) = 664.5 MB). Captured in the two-pass order; the one-pass cold request's launch
+# has 8883 rows (the state's 2048 ride along) and proportionally more activation traffic.
 GEMM_TRAFFIC_BYTES = 1747872224  # 1513.6 MB read + 234.3 MB written: the weight panel comes from DRAM about four times
 
 
@@ -65,6 +66,9 @@ def parse():
                     help="comma list of extra workloads in the line: w4a16,nvfp4,ragged_bf16,ragged_nvfp4 | all | none")
     ap.add_argument("--ragged-states", type=int, default=6, help="states of the seeded ragged-stress list per replica")
     ap.add_argument("--c8-states", type=int, default=24, help="cold requests of the Poisson c8 run per replica")
+    ap.add_argument("--two-pass", action="store_true",
+                    help="serve a cold request as the reference does, capture then question pass, instead of the one-pass call "
+                         "(dcd_capture_and_readout: same bits, the weights stream once per layer for the whole request)")
     ap.add_argument("--box-states", type=int, default=96,
                     help="cold requests of the whole-box run (one process, one engine per GPU behind one router); runs on rank 0 when more than "
                          "one GPU is used, or when --box-replicas is given; 0 = skip")
@@ -126,6 +130,8 @@ def config_dict(args, n_gpus):
         "parallelism": "replicas sharded by state (dp%d), no collective on the data path" % n_gpus,
         "l2": "inputs larger than L2: 48.7 GB of weights are streamed from HBM every step",
         "seed": 0,
+        "cold_request": "capture then question pass (two passes)" if getattr(args, "two_pass", False) or args.precision == "fp8"
+                        else "state and questions in one pass over the layers (dcd_capture_and_readout; bit-identical to capture + question pass)",
     }
 
 
@@ -373,13 +379,20 @@ def gemm_roofline(prof, precision):
             "peak_source": src, "launches": g["launches"], "avg_launch_ms": g["ms"] / max(1, g["launches"])}
 
 
-def run_requests(eng, R, requests, warm=1):
-    """Serve `requests` (list of (state ids, questions)) through the host-buffer C ABI, one cold request after the other.
+def run_requests(eng, R, requests, warm=1, two_pass=False):
+    """Serve `requests` (list of (state ids, questions)) through the host-buffer C ABI, one cold request after the other
+    (dcd_capture_and_readout, which takes the two-pass order by itself where one pass cannot hold the request).
     Returns a dict of whole-job figures (sums over ranks, time = max over ranks)."""
-    for st_ids, qs in requests[:warm]:
-        st = eng.capture_state(st_ids)
-        eng.readout_state_once_batch(st, qs)
+    def serve(st_ids, qs):
+        if two_pass:
+            st = eng.capture_state(st_ids)
+            eng.readout_state_once_batch(st, qs)
+        else:
+            st, _ = eng.capture_and_readout(st_ids, qs)
         st.free()
+
+    for st_ids, qs in requests[:warm]:
+        serve(st_ids, qs)
     eng.sync()
     eng.profile_read()
     eng.profile_enable(True)
@@ -388,9 +401,7 @@ def run_requests(eng, R, requests, warm=1):
     t0 = time.perf_counter()
     for st_ids, qs in requests:
         s0 = time.perf_counter()
-        st = eng.capture_state(st_ids)
-        eng.readout_state_once_batch(st, qs)
-        st.free()
+        serve(st_ids, qs)
         lat.append(time.perf_counter() - s0)
     eng.sync()
     t = time.perf_counter() - t0
@@ -417,7 +428,7 @@ def run_poisson_c8(eng, R, args, n_requests, precision):
     at 8, served through the request scheduler (one worker thread owns the engine). The arrival rate is twice the
     service rate measured on the first requests, so the replica stays saturated; latency is admission to reply."""
     from decidra_b200 import scheduler
-    handle = scheduler.BatchHandle(eng, state_cache_entries=0)
+    handle = scheduler.BatchHandle(eng, state_cache_entries=0, cold_one_pass=0 if args.two_pass else 1)
     reqs = [headline_workload(args, 500000 + R.rank * 100000 + i) for i in range(n_requests + 2)]
     t0 = time.perf_counter()
     for s, q in reqs[:2]:
@@ -471,7 +482,7 @@ def run_box(dcd, args, devices, precision, n_states):
     reply. No process group is involved: the other ranks' processes hold no engine while this runs."""
     from decidra_b200 import box, scheduler
     n = len(devices)
-    tm = max(args.state_len, args.questions * args.qmax)
+    tm = args.state_len + args.questions * args.qmax   # room for a cold request in one pass
     engines, errs = [None] * n, []
 
     def mk(i):
@@ -489,7 +500,7 @@ def run_box(dcd, args, devices, precision, n_states):
             if e is not None:
                 e.close()
         return {"error": "; ".join(errs)}
-    handles = [scheduler.BatchHandle(e, state_cache_entries=0) for e in engines]
+    handles = [scheduler.BatchHandle(e, state_cache_entries=0, cold_one_pass=0 if args.two_pass else 1) for e in engines]
     b = box.BoxRunner(handles)
     t_setup = time.perf_counter() - t_setup
     reqs = [headline_workload(args, 900000 + i) for i in range(2 * n_states + 2 * n)]
@@ -563,6 +574,8 @@ def run_ours(args):
     want = {"w4a16", "nvfp4", "ragged_bf16", "ragged_nvfp4"} if args.configs == "all" else set(c for c in args.configs.split(",") if c and c != "none")
     need_ragged_bf16 = "ragged_bf16" in want and args.precision == "bf16"
     tm = max(args.state_len, args.questions * args.qmax)
+    if not args.two_pass:  # room for the state and its questions in one pass
+        tm = args.state_len + args.questions * args.qmax
     if need_ragged_bf16:
         tm = max(tm, 16384)
     if args.scheduler_cross_state:  # room for one pass over the requests of all clients
@@ -575,23 +588,35 @@ def run_ours(args):
     mine = replicas.shard_states(costs, world, rank)
     reqs = [headline_workload(args, int(i)) for i in mine]
     dev = []
+    B, S = args.questions, args.state_len
+    one_pass = not args.two_pass and args.precision != "fp8" and S + args.questions * args.qmax <= tm
     for state, questions in reqs:
         lens = np.array([len(q) for q in questions], dtype=np.int32)
         flat = np.concatenate(questions)
+        if one_pass:  # the state is the first sequence of the packed batch
+            lens = np.concatenate([[S], lens]).astype(np.int32)
+            flat = np.concatenate([state, flat])
         dev.append((torch.from_numpy(state.astype(np.int64)).to(torch.int32).cuda(),  # same 32-bit patterns as uint32 ids
-                    torch.from_numpy(flat.astype(np.int64)).to(torch.int32).cuda(), torch.from_numpy(lens).cuda(), int(lens.sum()), int(lens.max())))
-    B, S = args.questions, args.state_len
-    d_out = torch.empty(B * cfg.readout_rows, dtype=torch.float32, device="cuda")
+                    torch.from_numpy(flat.astype(np.int64)).to(torch.int32).cuda(), torch.from_numpy(lens).cuda(), int(lens.sum()),
+                    int(lens[1:].max() if one_pass else lens.max())))
+    d_out_all = torch.empty((B + 1) * cfg.readout_rows, dtype=torch.float32, device="cuda")
+    d_out = d_out_all[cfg.readout_rows:] if one_pass else d_out_all[:B * cfg.readout_rows]   # one pass: row 0 is the state's own last token
 
     def step_device(i):
         d_state, d_flat, d_lens, total, max_len = dev[i]
-        st = eng.capture_state_device(d_state.data_ptr(), S)
-        eng.readout_state_once_device(st, d_flat.data_ptr(), d_lens.data_ptr(), B, total, max_len, d_out.data_ptr())
+        if one_pass:
+            st = eng.capture_and_readout_device(d_flat.data_ptr(), d_lens.data_ptr(), S, B, total, max_len, d_out_all.data_ptr())
+        else:
+            st = eng.capture_state_device(d_state.data_ptr(), S)
+            eng.readout_state_once_device(st, d_flat.data_ptr(), d_lens.data_ptr(), B, total, max_len, d_out.data_ptr())
         st.free()
 
     def step_host(i):
-        st = eng.capture_state(reqs[i][0])
-        out = eng.readout_state_once_batch(st, reqs[i][1])
+        if one_pass:
+            st, out = eng.capture_and_readout(reqs[i][0], reqs[i][1])
+        else:
+            st = eng.capture_state(reqs[i][0])
+            out = eng.readout_state_once_batch(st, reqs[i][1])
         st.free()
         return out
 
@@ -634,7 +659,7 @@ def run_ours(args):
     R.barrier()
     t_e2e = R.max(t_e2e)
     same = bool(np.array_equal(logits_host, logits_dev))
-    total_last = dev[-1][3]
+    total_last = dev[-1][3] - (S if one_pass else 0)
     flops_step = sum(cfg.capture_flops(S) + sum(cfg.question_flops(len(q), S) for q in qs) for _, qs in reqs[args.warmup:]) / args.steps
 
     # ---- optional: the same cold requests through the request scheduler, from concurrent clients ----------------------
@@ -702,17 +727,17 @@ def run_ours(args):
 
     if need_ragged_bf16:
         rq, n = ragged_requests()
-        obj, p = run_requests(eng, R, rq, warm=1)
+        obj, p = run_requests(eng, R, rq, warm=1, two_pass=args.two_pass)
         obj["sample"] = "first %d states of the seeded 2048-state list (S ~ logU[256,16384], 1-256 questions of 16-512 tokens, seed 7), routed to replicas by predicted FLOPs" % n
         configs["ragged_stress_bf16"] = add_roofline(obj, p, "bf16")
     eng.close()
     del eng
 
     if "w4a16" in want and args.precision == "bf16":
-        e2, _ = make_engine(dcd, args, "w4a16", max(args.state_len, args.questions * args.qmax), local)
+        e2, _ = make_engine(dcd, args, "w4a16", tm, local)
         own = replicas.shard_states(np.ones(8), world, rank)       # 8 states in all, whatever the number of replicas
         rq = [headline_workload(args, 200000 + int(i)) for i in own]
-        obj, p = run_requests(e2, R, rq, warm=1)                   # a replica without a state idles but joins the barriers and reductions
+        obj, p = run_requests(e2, R, rq, warm=1, two_pass=args.two_pass)                   # a replica without a state idles but joins the barriers and reductions
         obj["sample"] = "8 states x (2048 tokens + 64 questions of 48-160 tokens) in all, int4 group-128 weights with fp16 scales"
         configs["w4a16_8states"] = add_roofline(obj, p, "w4a16")
         e2.close()
@@ -723,13 +748,13 @@ def run_ours(args):
         if "nvfp4" in want:
             # device-timed steps first (the kernel view of this precision), then the Poisson c8 run through the scheduler
             rq = [headline_workload(args, 300000 + rank * 1000 + i) for i in range(4)]
-            obj, p = run_requests(e3, R, rq, warm=1)
+            obj, p = run_requests(e3, R, rq, warm=1, two_pass=args.two_pass)
             c8 = run_poisson_c8(e3, R, args, args.c8_states, "nvfp4")
             c8["sequential_cold_requests"] = {k: obj[k] for k in ("value", "states_per_s", "seconds", "states", "p50_request_latency_ms", "kernel_time_share_ms")}
             configs["nvfp4_c8"] = add_roofline(c8, p, "nvfp4")
         if "ragged_nvfp4" in want:
             rq, n = ragged_requests()
-            obj, p = run_requests(e3, R, rq, warm=1)
+            obj, p = run_requests(e3, R, rq, warm=1, two_pass=args.two_pass)
             obj["sample"] = "first %d states of the seeded 2048-state list (as ragged_stress_bf16), NVFP4 weights and activations" % n
             configs["ragged_stress_nvfp4"] = add_roofline(obj, p, "nvfp4")
         e3.close()

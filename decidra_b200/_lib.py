@@ -31,7 +31,7 @@ class SchedOptions(C.Structure):
         ("max_queue", C.c_int32), ("batch_requests", C.c_int32), ("batch_rows", C.c_int32), ("batch_window_us", C.c_int64),
         ("state_cache_entries", C.c_int32), ("pin_cache", C.c_int32), ("state_cache_bytes", C.c_int64),
         ("host_state_cache_bytes", C.c_int64), ("sched_priority", C.c_int32), ("cross_state_pass", C.c_int32),
-        ("submit_timeout_us", C.c_int64), ("reserved", C.c_int64 * 4),
+        ("submit_timeout_us", C.c_int64), ("cold_one_pass", C.c_int64), ("reserved", C.c_int64 * 3),
     ]
 
 
@@ -44,6 +44,8 @@ OP_FREE = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
 OP_MEM = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t))
 OP_ERR = C.CFUNCTYPE(C.c_void_p, C.c_void_p)  # returns the address of a NUL-terminated buffer the callee keeps alive
 OP_SIZE = C.CFUNCTYPE(C.c_size_t, C.c_void_p, C.c_size_t)
+OP_CAPTURE_READOUT = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.POINTER(C.c_uint32)), C.POINTER(C.c_size_t),
+                                 C.c_size_t, C.POINTER(C.c_void_p), C.POINTER(C.c_float))
 OP_READOUT_MULTI = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t, C.POINTER(C.POINTER(C.c_uint32)), C.POINTER(C.c_size_t),
                                C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_float))
 
@@ -54,7 +56,7 @@ class SchedEngineOps(C.Structure):
         ("ctx", C.c_void_p), ("readout_rows", C.c_int32), ("reserved0", C.c_int32),
         ("rebind_blas", OP_INT_CTX), ("capture_state", OP_CAPTURE), ("readout", OP_READOUT), ("offload", OP_MOVE), ("restore", OP_MOVE),
         ("state_free", OP_FREE), ("host_free", OP_FREE), ("trim_pools", OP_INT_CTX), ("mem_info", OP_MEM), ("last_error", OP_ERR),
-        ("state_bytes_for", OP_SIZE), ("pass_reserve", OP_SIZE), ("readout_multi", OP_READOUT_MULTI),
+        ("state_bytes_for", OP_SIZE), ("pass_reserve", OP_SIZE), ("readout_multi", OP_READOUT_MULTI), ("capture_readout", OP_CAPTURE_READOUT),
     ]
 
 
@@ -125,6 +127,8 @@ SIGNATURES = {
     "dcd_readout_state_once_device": (I, [P, P, P, P, SZ, SZ, SZ, P]),
     "dcd_readout_multi_state_batch": (I, [P, C.POINTER(P), SZ, C.POINTER(U32P), C.POINTER(SZ), U32P, SZ, FP]),
     "dcd_capture_state_device": (I, [P, P, SZ, C.POINTER(P)]),
+    "dcd_capture_and_readout": (I, [P, U32P, SZ, C.POINTER(U32P), C.POINTER(SZ), SZ, C.POINTER(P), FP]),
+    "dcd_capture_and_readout_device": (I, [P, P, P, SZ, SZ, SZ, SZ, C.POINTER(P), P]),
     "dcd_decision_logits_split": (I, [P, U32P, SZ, SZ, FP]),
     "dcd_state_free": (None, [P, P]),
     "dcd_state_tokens": (SZ, [P]),

@@ -74,6 +74,9 @@ int real_mem(void* c, size_t* f, size_t* t) { return dcd_mem_info((dcd_engine*)c
 const char* real_err(void* c) { return dcd_last_error((dcd_engine*)c); }
 size_t real_state_bytes_for(void* c, size_t n) { return dcd_state_bytes_for((const dcd_engine*)c, n); }
 size_t real_pass_reserve(void* c, size_t n) { return dcd_pass_reserve_bytes((const dcd_engine*)c, n); }
+int real_capture_readout(void* c, const uint32_t* ids, size_t n, const uint32_t* const* q, const size_t* lens, size_t B, void** st, float* out) {
+  return dcd_capture_and_readout((dcd_engine*)c, ids, n, q, lens, B, (dcd_state**)st, out);
+}
 int real_readout_multi(void* c, const void* const* states, size_t n, const uint32_t* const* q, const size_t* lens, const uint32_t* state_of, size_t B,
                        float* out) {
   return dcd_readout_multi_state_batch((dcd_engine*)c, (const dcd_state* const*)states, n, q, lens, state_of, B, out);
@@ -223,6 +226,7 @@ struct Acquired {
   CachedState entry;
   CacheResult result = Unresolved;
   bool from_host = false;
+  bool answered = false;  // a miss served by the one-pass call: the jobs have their rows already
   size_t entry_bytes = 0, pass_need = 0;
 };
 
@@ -299,6 +303,43 @@ bool dcd_scheduler::acquire(const std::vector<uint32_t>& state, const uint8_t* d
     entry.bytes = entry_bytes;
   } else {
     void* captured = nullptr;
+    if (opt.cold_one_pass && ops.capture_readout && !may_retry) {
+      // the state and its questions in one engine call (headroom for both was secured above); anything but success or a memory
+      // failure that a retry cures leaves the group to the two steps below, whose failure texts are the reference's
+      std::vector<const uint32_t*> qptr;
+      std::vector<size_t> qlen;
+      size_t question_tokens = 0;
+      for (Job& j : jobs)
+        for (auto& q : j.questions) { qptr.push_back(q.data()); qlen.push_back(q.size()); question_tokens += q.size(); }
+      const size_t R = (size_t)ops.readout_rows;
+      std::vector<float> rows(qptr.size() * R);
+      int rc1 = ops.capture_readout(ops.ctx, state.data(), state.size(), qptr.data(), qlen.data(), qptr.size(), &captured, rows.data());
+      if (rc1 != DCD_OK && oom_text()) {
+        stat([](dcd_sched_stats& s) { s.oom_retry_capture += 1; });
+        ops.trim_pools(ops.ctx);
+        std::string ignored;
+        ensure_headroom(state_need, "state capture retry", &ignored);
+        captured = nullptr;
+        rc1 = ops.capture_readout(ops.ctx, state.data(), state.size(), qptr.data(), qlen.data(), qptr.size(), &captured, rows.data());
+      }
+      if (rc1 == DCD_OK) {
+        stat([&](dcd_sched_stats& s) {
+          s.captures += 1; s.state_tokens += state.size(); s.question_tokens += question_tokens; s.questions_answered += qptr.size();
+        });
+        size_t at = 0;
+        for (Job& j : jobs) {
+          finish(j, DCD_OK, "", rows.data() + at * R, j.questions.size() * R);
+          at += j.questions.size();
+        }
+        entry.state = state;
+        memcpy(entry.digest, digest, 32);
+        entry.cache = captured;
+        entry.bytes = entry_bytes;
+        out->answered = true;
+        return true;
+      }
+      captured = nullptr;
+    }
     int rc = ops.capture_state(ops.ctx, state.data(), state.size(), &captured);
     if (rc != DCD_OK && engine_error().find("out of memory") != std::string::npos) {
       // a long state can exceed the estimate: drop what can be dropped and retry once
@@ -352,7 +393,8 @@ CacheResult dcd_scheduler::run_group_inner(const std::vector<uint32_t>& state, c
   *ok = false;
   Acquired a;
   if (!acquire(state, digest, jobs, &a)) return a.result;
-  *ok = pass_one(a, jobs);
+  if (a.answered) { release(a); *ok = true; }
+  else *ok = pass_one(a, jobs);
   return a.result;
 }
 
@@ -645,6 +687,7 @@ int dcd_scheduler_create(dcd_engine* e, const dcd_sched_options* opt, dcd_schedu
   ops.readout_multi = real_readout_multi;
   ops.state_bytes_for = real_state_bytes_for;
   ops.pass_reserve = real_pass_reserve;
+  ops.capture_readout = real_capture_readout;
   return dcd_scheduler_create_with_ops(&ops, opt, out);
 }
 

@@ -179,6 +179,21 @@ class Engine:
         self._check(_lib.load().dcd_readout_state_once_batch(self._h, cache._h, ptrs, lens, B, out.ctypes.data_as(_lib.FP)))
         return out
 
+    def capture_and_readout(self, state: Sequence[int], questions: Sequence[Sequence[int]]):
+        """A cold request in one pass (``dcd_capture_and_readout``): returns ``(StateCache, logits [B, readout_rows])``, bit-identical
+        to ``capture_state`` followed by ``readout_state_once_batch``; the library falls back to that order when one pass cannot
+        hold the request."""
+        ids = _u32(state)
+        B = len(questions)
+        arrs = [_u32(q) for q in questions]
+        ptrs = (_lib.U32P * max(B, 1))(*[a.ctypes.data_as(_lib.U32P) for a in arrs])
+        lens = (C.c_size_t * max(B, 1))(*[a.size for a in arrs])
+        out = np.empty((B, self.cfg.readout_rows), dtype=np.float32)
+        st = C.c_void_p()
+        self._check(_lib.load().dcd_capture_and_readout(self._h, ids.ctypes.data_as(_lib.U32P), ids.size, ptrs, lens, B, C.byref(st),
+                                                        out.ctypes.data_as(_lib.FP)))
+        return StateCache(self, st), out
+
     def readout_multi_state_batch(self, caches: Sequence[StateCache], questions: Sequence[Sequence[int]], state_of: Sequence[int]) -> np.ndarray:
         """One pass over questions of several states: ``state_of[i]`` indexes ``caches``. Rows equal those of
         ``readout_state_once_batch`` per state, bit for bit; [B, readout_rows] f32 in input order."""
@@ -204,6 +219,11 @@ class Engine:
     def capture_state_device(self, d_ids: int, n: int) -> StateCache:
         out = C.c_void_p()
         self._check(_lib.load().dcd_capture_state_device(self._h, d_ids, n, C.byref(out)))
+        return StateCache(self, out)
+
+    def capture_and_readout_device(self, d_ids: int, d_lens: int, n_state: int, B: int, total: int, max_len: int, d_out: int) -> StateCache:
+        out = C.c_void_p()
+        self._check(_lib.load().dcd_capture_and_readout_device(self._h, d_ids, d_lens, n_state, B, total, max_len, C.byref(out), d_out))
         return StateCache(self, out)
 
     def readout_state_once_device(self, cache: StateCache, d_ids: int, d_lens: int, B: int, total: int, max_len: int, d_out: int) -> None:

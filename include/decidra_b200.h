@@ -177,7 +177,10 @@ typedef struct dcd_sched_options {
   int32_t cross_state_pass;       /* 0 = one pass per group, as the reference; 1 = the groups of one coalesced batch share ONE
                                      question pass (dcd_readout_multi_state_batch); falls back to a pass per group if refused */
   int64_t submit_timeout_us;      /* 0 = wait for a queue slot like the reference's await; > 0 = give up with DCD_E_OVERLOADED */
-  int64_t reserved[4];
+  int64_t cold_one_pass;          /* 0 = a miss is captured, then its questions are answered, as the reference; 1 = a miss is served by ONE
+                                     engine call (dcd_capture_and_readout: same cache, same rows); if that call fails for anything but
+                                     memory the group goes through the two steps, so the failure texts stay the reference's */
+  int64_t reserved[3];
 } dcd_sched_options;
 DCD_API void dcd_sched_default_options(dcd_sched_options* o);
 
@@ -204,6 +207,8 @@ typedef struct dcd_sched_engine_ops {
   size_t (*pass_reserve)(void* ctx, size_t state_len);                               /* may be NULL */
   int (*readout_multi)(void* ctx, const void* const* states, size_t n_states, const uint32_t* const* questions, const size_t* lens,
                        const uint32_t* state_of, size_t B, float* out);              /* may be NULL: no cross-state pass */
+  int (*capture_readout)(void* ctx, const uint32_t* ids, size_t n, const uint32_t* const* questions, const size_t* lens, size_t B,
+                         void** state_out, float* out);                               /* may be NULL: no one-pass miss */
 } dcd_sched_engine_ops;
 
 /* The reference's counters and gauges (docs/METRICS.md names in comments) as plain integers. */
@@ -364,6 +369,20 @@ DCD_API int dcd_readout_multi_state_batch(dcd_engine* e, const dcd_state* const*
                                           const uint32_t* const* questions, const size_t* lens, const uint32_t* state_of, size_t B,
                                           float* out);
 DCD_API int dcd_capture_state_device(dcd_engine* e, const uint32_t* d_ids, size_t n, dcd_state** out);
+/* A cold request in ONE pass: the capture of a state and the question pass over it as one sweep over the layers (the reference
+ * captures, then runs the question pass, src/batch.rs:752-905). The state is one more sequence of the packed batch: it attends
+ * to itself only and its K/V, conv tail and recurrent state are kept, layer by layer, where the questions' kernels of the same
+ * layer read them. Every row goes through the same kernels as in the two-pass order, so *out_state and the logits are
+ * bit-identical to dcd_capture_state + dcd_readout_state_once_batch; the weights stream once per layer for the whole request.
+ * Falls back to the two-pass order by itself when state + questions exceed max_pass_tokens, when the reference's chunk planner
+ * would cut the questions into several passes, or on an FP8 engine (whose capture stays bf16). out: B x readout_rows. */
+DCD_API int dcd_capture_and_readout(dcd_engine* e, const uint32_t* state_ids, size_t n_state, const uint32_t* const* questions,
+                                    const size_t* lens, size_t B, dcd_state** out_state, float* out);
+/* Device-resident form, no fallback: d_ids = the state's n_state ids followed by the questions' (total in all), d_lens[B + 1] =
+ * n_state then the question lengths, d_out[(B + 1) x readout_rows] (row 0 belongs to the state's own last token; the questions'
+ * rows follow in input order). Enqueues on the engine stream. DCD_E_INVALID when the request does not fit one pass. */
+DCD_API int dcd_capture_and_readout_device(dcd_engine* e, const uint32_t* d_ids, const int32_t* d_lens, size_t n_state, size_t B,
+                                           size_t total, size_t max_len, dcd_state** out_state, float* d_out);
 
 /* Engine::decision_logits_split (native/src/engine.rs:4585-4601; self-test use at
  * src/native_backend.rs:251-253): per-row reference formulation over [state || question]

@@ -94,3 +94,48 @@ def test_multi_state_pass_quantised_engines(dcd, precision):
     states, state_of, questions = _mixed(cfg.vocab, rng, [200, 129], 10, 20, 120)
     _check(e, states, state_of, questions)
     e.close()
+
+
+@pytest.mark.parametrize("which", ["tiny_f32", "tiny_bf16", "d3_slice", "d3_slice_nvfp4", "d3_slice_w4a16"])
+def test_cold_request_in_one_pass_is_bit_identical_to_capture_then_readout(dcd, which):
+    """dcd_capture_and_readout: the state rides in the same pass as its questions. Logits and every tensor of the returned cache
+    must equal those of capture_state + readout_state_once_batch bit for bit, on the fallback kernels (tiny model) and on the
+    tensor-core kernels (d3-shaped slice, also with NVFP4 and W4A16 weights); the cache must serve a later warm request."""
+    if which.startswith("tiny"):
+        cfg = dcd.tiny_config(0 if which == "tiny_f32" else 1)
+        vocab, cases = cfg.vocab, [(128, (16, 20, 24, 32)), (2, (1,)), (67, (5, 64, 3))]
+    else:
+        cfg = dcd.d3_config(num_layers=4, dtype=1, vocab=4096)
+        vocab, cases = 4096, [(160, (20, 33, 24, 40)), (300, (130, 7)), (64, (64,))]
+    opt = dcd.Options()
+    opt.max_pass_tokens = 1024
+    opt.precision = {"d3_slice_nvfp4": 3, "d3_slice_w4a16": 1}.get(which, 0)
+    e = dcd.Engine(cfg, opt)
+    e.init_random(0)
+    rng = np.random.Generator(np.random.PCG64(11))
+    for S, qlens in cases:
+        state = rng.integers(0, vocab, S, dtype=np.uint32)
+        qs = [rng.integers(0, vocab, n, dtype=np.uint32) for n in qlens]
+        st_a = e.capture_state(state)
+        want = e.readout_state_once_batch(st_a, qs)
+        st_b, got = e.capture_and_readout(state, qs)
+        assert got.tobytes() == want.tobytes(), (which, S, qlens, float(np.abs(got - want).max()))
+        assert st_b.state_len == S and st_b.nbytes == st_a.nbytes
+        for li in range(cfg.num_layers):
+            for kind in range(4):
+                a, b = st_a.tensor(li, kind), st_b.tensor(li, kind)
+                assert (a is None) == (b is None)
+                if a is not None:
+                    assert a.tobytes() == b.tobytes(), (which, S, li, kind)
+        warm = e.readout_state_once_batch(st_b, qs[:1])
+        assert warm.tobytes() == want[:1].tobytes()
+        st_a.free()
+        st_b.free()
+    # a request that does not fit one pass takes the two-pass order by itself
+    state = rng.integers(0, vocab, 900, dtype=np.uint32)
+    qs = [rng.integers(0, vocab, 100, dtype=np.uint32) for _ in range(3)]
+    st_a = e.capture_state(state)
+    want = e.readout_state_once_batch(st_a, qs)
+    st_b, got = e.capture_and_readout(state, qs)
+    assert got.tobytes() == want.tobytes()
+    e.close()

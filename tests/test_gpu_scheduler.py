@@ -116,3 +116,24 @@ def test_scheduler_cross_state_pass(dcd):
     assert s["captures"] == 4 and s["requests_gpu_hit"] >= 4
     h.close()
     e.close()
+
+
+def test_cold_one_pass_through_the_scheduler_equals_direct_calls(dcd):
+    """cold_one_pass = 1 on the real engine: a miss served by dcd_capture_and_readout gives the rows of capture + readout bit for bit,
+    leaves the state in the device tier for the next request, and a bad question still fails with the reference's text."""
+    from decidra_b200 import scheduler
+    e = _engine(dcd)
+    cases = _cases()
+    want = [e.readout_state_once_batch(e.capture_state(st), qs) for st, qs in cases]
+    h = scheduler.BatchHandle(e, batch_window_us=0, cold_one_pass=1)
+    for (st, qs), w in zip(cases, want):
+        assert h.submit_state_once(st, qs).result().tobytes() == w.tobytes()
+    assert h.submit_state_once(cases[1][0], cases[1][1][:2]).result().tobytes() == want[1][:2].tobytes()
+    s = h.stats()
+    assert (s["requests_miss"], s["requests_gpu_hit"], s["captures"], s["gpu_entries"]) == (3, 1, 3, 3)
+    bad = [np.array([1, 2, 999999], dtype=np.uint32)]
+    fresh = np.arange(50, dtype=np.uint32)
+    with pytest.raises(dcd.EngineError, match="state-once question pass failed"):
+        h.submit_state_once(fresh, bad).result()
+    h.close()
+    e.close()

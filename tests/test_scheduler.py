@@ -39,7 +39,7 @@ class FakeEngine:
             state_free=_lib.OP_FREE(self._state_free), host_free=_lib.OP_FREE(self._host_free),
             trim_pools=_lib.OP_INT_CTX(self._trim), mem_info=_lib.OP_MEM(self._mem), last_error=_lib.OP_ERR(lambda ctx: C.addressof(self.errbuf)),
             state_bytes_for=_lib.OP_SIZE(lambda ctx, n: self.state_bytes(n)), pass_reserve=_lib.OP_SIZE(lambda ctx, n: self.reserve(n)),
-            readout_multi=_lib.OP_READOUT_MULTI(self._readout_multi))
+            readout_multi=_lib.OP_READOUT_MULTI(self._readout_multi), capture_readout=_lib.OP_CAPTURE_READOUT(self._capture_readout))
         for k, v in self._cbs.items():
             setattr(ops, k, v)
         self.ops = ops
@@ -97,6 +97,23 @@ class FakeEngine:
             return 1
         for i, q in enumerate(questions):
             a = self.answer(toks[sof[i]], q)
+            for j in range(ROWS):
+                out[i * ROWS + j] = a[j]
+        return 0
+
+    def _capture_readout(self, ctx, ids, n, qs, lens, B, st_out, out):
+        tokens = tuple(ids[i] for i in range(n))
+        questions = [tuple(qs[i][k] for k in range(lens[i])) for i in range(B)]
+        self._log("capture_readout", tokens, tuple(questions))
+        if self._failing("capture_readout"):
+            return 2
+        h = self.next
+        self.next += 1
+        self.dev[h] = tokens
+        self.used += self.state_bytes(n)
+        st_out[0] = h
+        for i, q in enumerate(questions):
+            a = self.answer(tokens, q)
             for j in range(ROWS):
                 out[i * ROWS + j] = a[j]
         return 0
@@ -483,3 +500,34 @@ def test_cross_state_pass_under_memory_pressure_answers_like_the_sequential_orde
     if cross:
         assert fake.calls("readout_multi")[0][1] == (tuple(A), tuple(B))
         assert fake.calls("readout")[-1][1] == tuple(Cc)
+
+
+def test_cold_one_pass_serves_a_miss_with_one_engine_call(mk):
+    """cold_one_pass = 1: a miss is one capture_readout call (state kept in the cache as after a capture); a hit is a plain readout;
+    a memory failure is retried once; any other failure of the one-pass call sends the group through capture + readout, so the
+    failure texts stay the reference's."""
+    h, fake = mk(cold_one_pass=1)
+    A, qs = [3, 1, 4], [[2, 7], [1, 8]]
+    got = h.submit_state_once(A, qs).result()
+    assert np.array_equal(got, np.stack([fake.answer(A, q) for q in qs]))
+    assert len(fake.calls("capture_readout")) == 1 and not fake.calls("capture") and not fake.calls("readout")
+    s = h.stats()
+    assert (s["requests_miss"], s["captures"], s["state_tokens"], s["questions_answered"], s["question_tokens"], s["gpu_entries"]) == (1, 1, 3, 2, 4, 1)
+    # the state is cached: the next request is a hit served by a plain readout
+    assert np.array_equal(h.submit_state_once(A, [[5]]).result()[0], fake.answer(A, [5]))
+    assert len(fake.calls("capture_readout")) == 1 and len(fake.calls("readout")) == 1
+    # a memory failure: trimmed and retried once, same call
+    fake.fail["capture_readout"] = ["CUDA error: out of memory"]
+    B = [9, 9, 1]
+    assert np.array_equal(h.submit_state_once(B, [[4]]).result()[0], fake.answer(B, [4]))
+    assert len(fake.calls("capture_readout")) == 3 and h.stats()["oom_retry_capture"] == 1
+    # another failure: the two steps, and their messages
+    fake.fail["capture_readout"] = ["token id out of range"]
+    fake.fail["readout"] = ["token id out of range"]
+    with pytest.raises(Exception, match="state-once question pass failed: token id out of range"):
+        h.submit_state_once([7, 7, 7], [[1]]).result()
+    assert fake.calls("capture")[-1] == ("capture", (7, 7, 7))
+    # and with the option off nothing changes
+    h2, fake2 = mk()
+    h2.submit_state_once(A, qs).result()
+    assert not fake2.calls("capture_readout") and len(fake2.calls("capture")) == 1
