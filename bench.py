@@ -43,11 +43,11 @@ sys.path.insert(0, str(ROOT))
 METRIC = "questions/sec (whole box) at 64 q/state, 2048-tok state"
 UNIT = "questions/s"
 VOCAB = 248320
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up (SwiGLU epilogue) GEMM launch of the question pass
-# (M = 6835 rows, K = 5120, N = 34816), from an ncu capture of a 4-layer slice of the same model
-# (algorithmic bytes of that launch: 2*(M*K + N*K + M*N/2) = 664.5 MB). Captured in the two-pass order; the one-pass cold request's launch
-# has 8883 rows (the state's 2048 ride along) and proportionally more activation traffic.
-GEMM_TRAFFIC_BYTES = 1747872224  # 1513.6 MB read + 234.3 MB written: the weight panel comes from DRAM about four times
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up (SwiGLU epilogue) GEMM launch, the largest of the step (K = 5120, N = 34816), from
+# ncu captures of a 4-layer slice of the same model: with the cold request in one pass the launch has M = 8883 rows (state + questions;
+# algorithmic bytes 2*(M*K + N*K + M*N/2) = 756.8 MB), in the two-pass order the question pass's launch has M = 6835 (664.5 MB). The weight
+# panel comes from DRAM once per group of 16 M tiles, about four to five times.
+GEMM_TRAFFIC_BYTES = {"one_pass": 2180447136, "two_pass": 1747872224}
 
 
 def parse():
@@ -773,7 +773,7 @@ def run_ours(args):
 
     if rank == 0:
         roof = gemm_roofline(prof, args.precision)
-        roof["traffic"] = GEMM_TRAFFIC_BYTES if args.precision == "bf16" else None
+        roof["traffic"] = GEMM_TRAFFIC_BYTES["one_pass" if one_pass else "two_pass"] if args.precision == "bf16" else None
         line = {
             "metric": METRIC, "value": world * B * args.steps / t_dev, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
