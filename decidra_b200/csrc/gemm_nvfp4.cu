@@ -49,10 +49,15 @@ template <int BN> struct Cfg {
   // UE4M3 (0) at bit 23, M>>4 at [24,29), K = 64 (bit 31 = 0), scale-factor ids 0
   static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
-constexpr int NUM_THREADS = 288;        // BN 128: warps 0 / 6 / 7 producers, 1 MMA issuer, 2-5 epilogue, 8 scale copier
-constexpr int NUM_THREADS_WIDE = 416;   // BN 256: four more epilogue warps (9-12). There is one accumulator, so the next tile's MMAs wait
-                                        // for the epilogue: eight warps first drain it into registers as bf16 pairs (32 rows x 128 columns
-                                        // each), hand it back, and only then add, activate, quantise and store, beside the next main loop
+constexpr int NUM_THREADS = 320;        // BN 128: warps 0 / 6 / 7 producers, 1 MMA issuer, 2-5 epilogue, 8 and 9 scale copiers
+constexpr int NUM_THREADS_WIDE = 480;   // BN 256: four more epilogue warps (9-12) and scale copiers 8, 13, 14. There is one accumulator, so
+                                        // the next tile's MMAs wait for the epilogue: eight warps first drain it into registers as bf16
+                                        // pairs (32 rows x 128 columns each), hand it back, and only then add, activate, quantise and
+                                        // store, beside the next main loop
+// A thread issues one tcgen05.cp every 57 cycles (measured; the instruction itself completes faster: three threads of three warps
+// issue three in 57). A stage needs 4 + 4 NB of them and its four MMAs run for 256 (BN 128) or 512 cycles (BN 256), so one copier
+// (12 x 57 = 684 cycles per stage at BN 256) holds the tensor core back; the copies are therefore spread over 1 + NB threads, one
+// for the X scales and one per 128-row block of W scales, each committing to the stage's barrier (count 1 + NB).
 constexpr uint32_t SF_COL = 256;
 constexpr int GROUP_M = 16;
 
@@ -117,8 +122,8 @@ __device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0
     if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
   }
 }
-// SPLIT: the scale tiles are copied into TMEM by a thread of their own (warp 8) that signals the MMA issuer through one more
-// barrier per stage, so that the copies of a K block are not queued in front of that block's MMAs on the issuer's in-order
+// SPLIT: the scale tiles are copied into TMEM by threads of their own (one per 2 KB scale set of the stage, each in a warp of
+// its own) that signal the MMA issuer through one more barrier per stage, so that the copies of a K block are not queued in front of that block's MMAs on the issuer's in-order
 // stream of tensor-core work.
 // EPI 0: C[M, ldc] = bf16(alpha * acc), or with resid (bf16 [M, ldc]): bf16(resid + bf16(alpha * acc)), the residual add of a
 // pre-norm block (add_bf16 / add_rmsnorm_bf16, native/kernels/kernels.cu:378-404, 485-490) applied to the rounded product.
@@ -148,7 +153,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 2 * ACC_STAGES));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
   const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_tiles = num_m * num_n;
   const int num_kb = K / 256;      // K blocks of 256 elements
   const int kb64 = K / 64;         // 512-byte scale tiles per 128-row block
@@ -157,7 +162,7 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(sfull_bar(s), 1);
+      mbar_init(sfull_bar(s), SPLIT ? 1 + NB : 1);
     }
     for (int a = 0; a < ACC_STAGES; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -185,25 +190,35 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   };
 
-  if (warp == 8) {
-    if (SPLIT && lane == 0) {
-      // Scale copier. A stage's TMEM columns are rewritten only after the MMAs that read them have completed: the producers
-      // refill the stage after empty_bar, and this thread waits for the refill.
+  constexpr int COPIER1 = BN == 256 ? 13 : 9;  // warp of the second copier; the first is warp 8
+  const int copier = warp == 8 ? 0 : (warp >= COPIER1 && warp < COPIER1 + NB) ? warp - COPIER1 + 1 : -1;
+  if (copier >= 0) {
+    if (SPLIT) {
+      // Scale copiers: number 0 takes the X scales, number 1 + nb the W scales of 128-row block nb. A stage's TMEM columns are
+      // rewritten only after the MMAs that read them have completed: the producers refill the stage after empty_bar, and these
+      // warps wait for the refill. (Every role below: the whole warp runs the loop, the elected lane issues.)
+      const bool el = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
+          if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag))) break;
           tc_fence_after();
-          copy_scales(tiles_base + stage * STAGE_BYTES, tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS);
-          umma_commit_to(sfull_bar(stage));
+          const uint32_t src = tiles_base + stage * STAGE_BYTES + A_BYTES + B_BYTES + (uint32_t)copier * SF_BYTES;
+          const uint32_t col = tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS + (copier == 0 ? 0u : 16u + 4u * (uint32_t)(copier - 1));
+          if (el) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) cp_sf(col + (copier == 0 ? 4 : 4 * NB) * k, desc_sf(src + 512 * k));
+            umma_commit_to(sfull_bar(stage));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 0 || warp == 6 || warp == 7) {
-    if (lane == 0) {
+    {
+      const bool el = elect_one();
       // warp 0: X codes (and the expected byte count of the stage); warp 6: W codes; warp 7: both scale sets
       int stage = 0;
       uint32_t phase = 0;
@@ -214,9 +229,10 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const uint8_t* sa = sfa + ((size_t)m_idx * kb64) * 512;
         const uint8_t* sb = sfb + ((size_t)n_idx * NB * kb64) * 512;  // first of the NB 128-row scale blocks of this W tile
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) break;
+          if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag))) break;
           const uint32_t dst = tiles_base + stage * STAGE_BYTES;
-          if (warp == 0) {
+          if (!el) {
+          } else if (warp == 0) {
             mbar_expect_tx(full_bar(stage), STAGE_BYTES);
             tma_load_2d(dst, &tmA, full_bar(stage), kb * BKB, m_idx * BM);
           } else if (warp == 6) {
@@ -232,34 +248,40 @@ gemm_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      const bool el = elect_one();
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) break;
+        if (!(ok = mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag))) break;
-          tc_fence_after();
           const uint32_t src = tiles_base + stage * STAGE_BYTES;
           const uint32_t sf_tmem = tmem_base + SF_COL + (uint32_t)stage * CF::SF_COLS;
           if (SPLIT) {
-            if (!(ok = mbar_wait(sfull_bar(stage), phase, abort_flag))) break;
+            // the copiers commit to sfull_bar after they have seen full_bar (codes and scales of the stage, one byte count),
+            // so this one wait covers both; a second wait only lengthens this thread's stream of about 57 cycles per tcgen05
+            // instruction, which is what the tensor core waits for (measured: 548 -> 623 us on the gate/up shape)
+            if (!(ok = mbar_wait_warp(sfull_bar(stage), phase, abort_flag))) break;
             tc_fence_after();
           } else {
-            copy_scales(src, sf_tmem);
+            if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag))) break;
+            tc_fence_after();
+            if (el) copy_scales(src, sf_tmem);
           }
           const uint64_t da = desc_sw128(src), db = desc_sw128(src + A_BYTES);
+          if (el) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // 64 elements = 32 bytes of codes per instruction
-            umma_fp4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), CF::IDESC, sf_tmem + 4 * k, sf_tmem + 16 + 4 * NB * k, (kb | k) != 0 ? 1u : 0u);
-          umma_commit_to(empty_bar(stage));
+            for (int k = 0; k < 4; ++k)  // 64 elements = 32 bytes of codes per instruction
+              umma_fp4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), CF::IDESC, sf_tmem + 4 * k, sf_tmem + 16 + 4 * NB * k, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_to(empty_bar(stage));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit_to(tfull_bar(acc));
+        if (el) umma_commit_to(tfull_bar(acc));
         if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
       }
     }

@@ -45,6 +45,28 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
 }
+// The tcgen05 / TMA issuing roles run as WHOLE warps with uniform control flow and let one elected lane execute the asynchronous
+// instructions: measured on sm_100a, a lone lane inside an `if (lane == 0)` branch issues one tcgen05.cp or tcgen05.mma every
+// 50-57 cycles (its descriptors and addresses live in per-thread registers and are moved to the uniform datapath one by one),
+// the elected lane of a warp whose loop is uniform issues one every 21. elect.sync picks the same lane every time for a given
+// member mask, so tcgen05.commit (which tracks the executing thread's earlier instructions) stays with the issuing lane.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+// Bounded wait by a whole converged warp; the vote makes the result provably the same in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+// The warp index as a value the compiler knows to be the same in every lane of the warp.
+__device__ __forceinline__ int uniform_warp_idx() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
 // The same bounded wait for warps that wait long and are many (a wide epilogue waiting out a whole main loop): sleeping between polls
 // leaves the issue slots to the warps that feed the tensor core. 2^21 polls x >= 256 ns bounds the wait near the plain one's.
 __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
