@@ -67,6 +67,13 @@ __device__ __forceinline__ float ex2_ftz(float x) {
   return y;
 }
 
+// the same, kept in program order behind the barrier arrive that precedes it (so that the work stays between an arrive and its wait)
+__device__ __forceinline__ float ex2_ftz_ordered(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Params {
   const int32_t* cu;       // [B+1] packed sequence offsets
   const int32_t* tile_cu;  // [B+1] prefix sum of token tiles per sequence
@@ -127,7 +134,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 80);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 84);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
@@ -164,54 +171,66 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  // The three roles below run as whole warps with uniform control flow; the elected lane executes the asynchronous instructions.
   if (warp == K_LOADER_WARP) {
-    if (lane == 0) {
+    {
       // ---- K loader: Q once, then the K slabs (tile j, 64-dim slab c) through a ring that runs ahead of the S products --
-      mbar_expect_tx(bar_q, (uint32_t)(NKB * TT * G * 128));
+      const bool el = elect_one();
+      if (el) {
+        mbar_expect_tx(bar_q, (uint32_t)(NKB * TT * G * 128));
 #pragma unroll
-      for (int c = 0; c < NKB; ++c) tma_load_3d(q_base + c * Q_KB_BYTES, &tmQ, bar_q, c * 64, kh * G, off + t0);
+        for (int c = 0; c < NKB; ++c) tma_load_3d(q_base + c * Q_KB_BYTES, &tmQ, bar_q, c * 64, kh * G, off + t0);
+      }
       bool ok = true;
       const int n_slabs = n_tiles * NKB;
       for (int i = 0; i < n_slabs && ok; ++i) {
         const int slot = i % K_SLOTS, use = i / K_SLOTS, j = i / NKB, c = i % NKB;
-        if (use >= 1 && !(ok = mbar_wait(k_empty + 8 * slot, (uint32_t)((use - 1) & 1), abort_flag))) break;
+        if (use >= 1 && !(ok = mbar_wait_warp(k_empty + 8 * slot, (uint32_t)((use - 1) & 1), abort_flag))) break;
         const bool st = j_lo + j < n_st;
         const int row0 = st ? (j_lo + j) * KT : off + (j_lo + j - n_st) * KT;
-        mbar_expect_tx(k_full + 8 * slot, KV_CHUNK);
-        tma_load_2d(k_base + slot * KV_CHUNK, st ? &tmKs : &tmKo, k_full + 8 * slot, kh * HD + c * 64, row0);
+        if (el) {
+          mbar_expect_tx(k_full + 8 * slot, KV_CHUNK);
+          tma_load_2d(k_base + slot * KV_CHUNK, st ? &tmKs : &tmKo, k_full + 8 * slot, kh * HD + c * 64, row0);
+        }
       }
     }
   } else if (warp == V_LOADER_WARP) {
-    if (lane == 0) {
+    {
       // ---- V loader: one tile slot, refilled as soon as the P.V product that read it is done ----------------------------
+      const bool el = elect_one();
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j >= 1 && !(ok = mbar_wait(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
+        if (j >= 1 && !(ok = mbar_wait_warp(bar_o, (uint32_t)((j - 1) & 1), abort_flag))) break;
         const bool st = j_lo + j < n_st;
         const int row0 = st ? (j_lo + j) * KT : off + (j_lo + j - n_st) * KT;
-        mbar_expect_tx(bar_v, V_BYTES);
+        if (el) {
+          mbar_expect_tx(bar_v, V_BYTES);
 #pragma unroll
-        for (int c = 0; c < NKB; ++c) tma_load_2d(v_base + c * KV_CHUNK, st ? &tmVs : &tmVo, bar_v, kh * HD + c * 64, row0);
+          for (int c = 0; c < NKB; ++c) tma_load_2d(v_base + c * KV_CHUNK, st ? &tmVs : &tmVo, bar_v, kh * HD + c * 64, row0);
+        }
       }
     }
   } else if (warp == ISSUER_WARP) {
-    if (lane == 0) {
+    {
       // ---- MMA issuer --------------------------------------------------------------------------------------------
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      const bool el = elect_one();
+      bool ok = mbar_wait_warp(bar_q, 0, abort_flag);
       auto issue_s = [&](int j) {  // S[j] = Q K[j]^T into S buffer j & 1, one 64-dim slab at a time as the slabs land
         const int s = j & 1;
         for (int c = 0; c < NKB && ok; ++c) {
           const int i = j * NKB + c, slot = i % K_SLOTS, use = i / K_SLOTS;
-          if (!(ok = mbar_wait(k_full + 8 * slot, (uint32_t)(use & 1), abort_flag))) break;
+          if (!(ok = mbar_wait_warp(k_full + 8 * slot, (uint32_t)(use & 1), abort_flag))) break;
           tc_fence_after();
           const uint64_t dq = umma_desc(q_base + c * Q_KB_BYTES, 16, 1024);
           const uint64_t dk = umma_desc(k_base + slot * KV_CHUNK, 16, 1024);
+          if (el) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + S_COL + s * KT, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
-          umma_commit_to(k_empty + 8 * slot);  // the slab can be refilled once these products are done
+            for (int k = 0; k < 4; ++k)
+              umma_f16(tmem_base + S_COL + s * KT, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), IDESC_QK, (c | k) != 0 ? 1u : 0u);
+            umma_commit_to(k_empty + 8 * slot);  // the slab can be refilled once these products are done
+          }
         }
-        if (ok) umma_commit_to(bar_s + 8 * s);
+        if (ok && el) umma_commit_to(bar_s + 8 * s);
       };
       if (ok) {
         tc_fence_after();
@@ -223,14 +242,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           issue_s(j + 1);
           if (!ok) break;
         }
-        if (!(ok = mbar_wait(bar_p + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
-        if (!(ok = mbar_wait(bar_v, (uint32_t)(j & 1), abort_flag))) break;
+        if (!(ok = mbar_wait_warp(bar_p + 8 * s, (uint32_t)((j >> 1) & 1), abort_flag))) break;
+        if (!(ok = mbar_wait_warp(bar_v, (uint32_t)(j & 1), abort_flag))) break;
         tc_fence_after();
         const uint64_t dv = umma_desc(v_base, KV_CHUNK, 1024);
+        if (el) {
 #pragma unroll
-        for (int k = 0; k < KT / 16; ++k)  // P[j] sits over S[j]: 16 keys = 8 packed columns per step
-          umma_f16_ts(tmem_base + O_COL, tmem_base + S_COL + s * KT + k * 8, dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
-        umma_commit_to(bar_o);
+          for (int k = 0; k < KT / 16; ++k)  // P[j] sits over S[j]: 16 keys = 8 packed columns per step
+            umma_f16_ts(tmem_base + O_COL, tmem_base + S_COL + s * KT + k * 8, dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
+          umma_commit_to(bar_o);
+        }
       }
     }
   } else {
@@ -265,13 +286,45 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int i = 0; i < HK; ++i) x[i] = h * HK + i < valid ? __uint_as_float(v[i]) : -INFINITY;
         }
       }
-      float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int i = 0; i < HK; ++i) t4[i & 3] = fmaxf(t4[i & 3], x[i]);
-      float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * p.scale_log2e;
+      // P = exp2(x * scale - m_used) rounded to bf16, packed in pairs over this thread's half of S[j]; the denominator sums the
+      // rounded values. From the second tile on the exponentials are taken against the maximum in use BEFORE this tile's own
+      // maximum is known (it only changes when a row's maximum grows by more than 2^8, which is rare after the first tiles):
+      // the maximum is folded into the first half of the loop, handed to the partner thread at the midpoint, and the partner's
+      // value is read after the second half, so that neither the 64 max instructions nor the exchange sit in front of the
+      // special-function unit. A row whose maximum did grow takes the exponentials again against the new one.
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t w[HK / 2];
+      auto pair = [&](int i, float neg_m, bool ordered) {
+        const float a0 = fmaf(x[2 * i], p.scale_log2e, neg_m), a1 = fmaf(x[2 * i + 1], p.scale_log2e, neg_m);
+        const __nv_bfloat162 pr = ordered ? __floats2bfloat162_rn(ex2_ftz_ordered(a0), ex2_ftz_ordered(a1)) : __floats2bfloat162_rn(ex2_ftz(a0), ex2_ftz(a1));
+        w[i] = *reinterpret_cast<const uint32_t*>(&pr);
+        l4[i & 3] += __uint_as_float(w[i] << 16) + __uint_as_float(w[i] & 0xffff0000u);
+      };
       float* xs = xch + (j & 1) * 256;
+      float tmax;
+      {
+        float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (j >= 1) {
+          const float neg_m = -m_used;
+#pragma unroll
+          for (int i = 0; i < HK / 4; ++i) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) t4[q4] = fmaxf(t4[q4], x[4 * i + q4]);
+            pair(i, neg_m, false);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < HK; ++i) t4[i & 3] = fmaxf(t4[i & 3], x[i]);
+        }
+        tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * p.scale_log2e;
+      }
       xs[h * 128 + r] = tmax;
       mbar_arrive(pair_bar);
+      if (j >= 1) {
+        const float neg_m = -m_used;
+#pragma unroll
+        for (int i = HK / 4; i < HK / 2; ++i) pair(i, neg_m, true);
+      }
       ok = mbar_wait(pair_bar, pair_phase, abort_flag);
       pair_phase ^= 1u;
       ok = __all_sync(0xffffffffu, ok);
@@ -298,17 +351,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           l *= f;
         }
       }
-      if (need) m_used = tmax;
-      // P = exp2(x - m_used) rounded to bf16, packed in pairs over this thread's half of S[j] (the partner has
-      // its S values in registers since before the exchange); the denominator sums the rounded values
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t w[HK / 2];
-      const float neg_m = -m_used;
+      if (need) {  // the first tile, or a row whose maximum grew: the exponentials against the new maximum
+        m_used = tmax;
+        const float neg_m = -m_used;
+        l4[0] = l4[1] = l4[2] = l4[3] = 0.f;
 #pragma unroll
-      for (int i = 0; i < HK / 2; ++i) {
-        const __nv_bfloat162 pr = __floats2bfloat162_rn(ex2_ftz(fmaf(x[2 * i], p.scale_log2e, neg_m)), ex2_ftz(fmaf(x[2 * i + 1], p.scale_log2e, neg_m)));
-        w[i] = *reinterpret_cast<const uint32_t*>(&pr);
-        l4[i & 3] += __uint_as_float(w[i] << 16) + __uint_as_float(w[i] & 0xffff0000u);
+        for (int i = 0; i < HK / 2; ++i) pair(i, neg_m, false);
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_st32(tmem_base + lane_addr + S_COL + (j & 1) * KT + h * (HK / 2), w);

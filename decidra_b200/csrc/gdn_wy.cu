@@ -176,7 +176,11 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
   const int off = cu[b], len = cu[b + 1] - off;
   const int kh = head / (nv / nk);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
+  // The tensor-core and TMA instructions are issued by the elected lane of a warp that runs the surrounding code as a whole: operands
+  // built by the whole warp sit in uniform registers, and the instructions then issue every ~21 cycles instead of every ~57 from
+  // a lone thread inside a divergent branch.
+  const bool el = elect_one();
   const int wg = warp >> 2, ln = tid & 127;  // warpgroup; TMEM lane / operand row owned by this thread
   const int vcol0 = 2 * nk * DK + head * DV;
 
@@ -217,16 +221,16 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tlane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
   constexpr bool V_TMA = sizeof(T) == 2;  // a 16-bit conv output: the chunk's V tile comes by TMA
-  auto load_kq = [&](int t0) {  // one elected thread; K/Q tiles and (16-bit storage) the V tile of the chunk at t0
-    mbar_expect_tx(bar_kq, 4 * REG + (V_TMA ? REG : 0));
+  auto load_kq = [&](int t0) {  // called by a whole warp; K/Q tiles and (16-bit storage) the V tile of the chunk at t0
+    if (el) mbar_expect_tx(bar_kq, 4 * REG + (V_TMA ? REG : 0));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      tma_load_2d(sbase + KQ_OFF + j * REG, &tmK, bar_kq, kh * DK + j * 32, off + t0);
-      tma_load_2d(sbase + KQ_OFF + j * REG + 8192, &tmQ, bar_kq, kh * DK + j * 32, off + t0);
+      if (el) tma_load_2d(sbase + KQ_OFF + j * REG, &tmK, bar_kq, kh * DK + j * 32, off + t0);
+      if (el) tma_load_2d(sbase + KQ_OFF + j * REG + 8192, &tmQ, bar_kq, kh * DK + j * 32, off + t0);
     }
     if (V_TMA) {
-      tma_load_2d(sbase + V_OFF, &tmV, bar_kq, vcol0, off + t0);
-      tma_load_2d(sbase + V_OFF + 8192, &tmV, bar_kq, vcol0 + 64, off + t0);
+      if (el) tma_load_2d(sbase + V_OFF, &tmV, bar_kq, vcol0, off + t0);
+      if (el) tma_load_2d(sbase + V_OFF + 8192, &tmV, bar_kq, vcol0 + 64, off + t0);
     }
   };
   // Scalars of the chunk at t0 into set `set` (warp 6: decays, warp 7: beta). A set is rewritten two chunks later, after every thread
@@ -256,7 +260,7 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   };
 
-  if (tid == 0) load_kq(0);
+  if (warp == 0) load_kq(0);
   scalars(0, 0);
   // ---- the blocks of T above the diagonal stay zero for the whole kernel ------------------------------------------
 #pragma unroll
@@ -293,14 +297,14 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     // ---- D1 = [K;Q] K^T ---------------------------------------------------------------------------------------------------------
     ok = mbar_wait(bar_kq, (uint32_t)(ci & 1), abort_flag);  // every thread reads the K tile below
     GWY_PH(0);
-    if (tid == 0 && ok) {
+    if (warp == 0 && ok) {
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) {
         const uint64_t o = (uint64_t)(((kk >> 2) * REG + (kk & 3) * 32) >> 4);
-        umma_tf32(tmem_base + D1_COL, d_kq + o, d_kq + o, IDESC_N64, kk != 0 ? 1u : 0u);
+        if (el) umma_tf32(tmem_base + D1_COL, d_kq + o, d_kq + o, IDESC_N64, kk != 0 ? 1u : 0u);
       }
-      umma_commit_to(bar_a);
+      if (el) umma_commit_to(bar_a);
     }
     // ---- (exp(G_C-G) K)^T: row dk = ln, 16 tokens per warpgroup, a K-major tf32 operand (while D1 runs) --------------------------------
     if (ok) {
@@ -380,16 +384,16 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       float* Xb = M1 + (bb * BLK) * LDM + bb * BLK + j;
 #pragma unroll
       for (int i = 0; i < BLK; ++i) Xb[i * LDM] = x[i];
-    } else if (tid == 384) {
+    } else if (warp == 12) {
       // ---- meanwhile D2 = S^T [K;Q]^T, not needed before R: issued from a warp that has nothing to do until T is stored (the issuing
       //      thread is held while the tensor core's queue is full) ---------------------------------------------------------------------
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) {
         const uint64_t o = (uint64_t)(((kk >> 2) * REG + (kk & 3) * 32) >> 4);
-        umma_tf32_ts(tmem_base + D2_COL, tmem_base + ST_COL + kk * 8, d_kq + o, IDESC_N128, kk != 0 ? 1u : 0u);
+        if (el) umma_tf32_ts(tmem_base + D2_COL, tmem_base + ST_COL + kk * 8, d_kq + o, IDESC_N128, kk != 0 ? 1u : 0u);
       }
-      umma_commit_to(bar_q);
+      if (el) umma_commit_to(bar_q);
     }
     __syncthreads();
     GWY_PH(3);
@@ -499,15 +503,15 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     GWY_PH(7);
 
     // ---- DR = R^T T^T; the K/Q/V tiles are free: request the next chunk's -----------------------------------------------------------
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         const uint64_t ob = (uint64_t)(((kk >> 2) * 8192 + (kk & 3) * 32) >> 4);
-        umma_tf32_ts(tmem_base + D1_COL, tmem_base + VT_COL + kk * 8, d_t + ob, IDESC_N64, kk != 0 ? 1u : 0u);
+        if (el) umma_tf32_ts(tmem_base + D1_COL, tmem_base + VT_COL + kk * 8, d_t + ob, IDESC_N64, kk != 0 ? 1u : 0u);
       }
-      umma_commit_to(bar_a);
-    } else if (tid == 416 && !last) {
+      if (el) umma_commit_to(bar_a);
+    } else if (warp == 13 && !last) {
       load_kq(t0 + C);
     }
     ok = mbar_wait(bar_a, ph_a, abort_flag);
@@ -530,20 +534,20 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     GWY_PH(9);
 
     // ---- RD = D^T (exp(G_C-G) K), O2 = D^T P^T ---------------------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp == 0) {
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         const uint64_t ob = (uint64_t)(((kk >> 2) * REG + (kk & 3) * 32) >> 4);
-        umma_tf32_ts(tmem_base + RD_COL, tmem_base + VT_COL + kk * 8, d_ke + ob, IDESC_N128, kk != 0 ? 1u : 0u);
+        if (el) umma_tf32_ts(tmem_base + RD_COL, tmem_base + VT_COL + kk * 8, d_ke + ob, IDESC_N128, kk != 0 ? 1u : 0u);
       }
-      umma_commit_to(bar_a);
+      if (el) umma_commit_to(bar_a);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         const uint64_t op = (uint64_t)(((kk >> 2) * 8192 + (kk & 3) * 32) >> 4);
-        umma_tf32_ts(tmem_base + D1_COL, tmem_base + VT_COL + kk * 8, d_p + op, IDESC_N64, kk != 0 ? 1u : 0u);
+        if (el) umma_tf32_ts(tmem_base + D1_COL, tmem_base + VT_COL + kk * 8, d_p + op, IDESC_N64, kk != 0 ? 1u : 0u);
       }
-      umma_commit_to(bar_o);
+      if (el) umma_commit_to(bar_o);
     }
     if (!last) scalars(t0 + C, (ci + 1) & 1);  // meanwhile (warps 6 and 7): scalars of the next chunk
     ok = mbar_wait(bar_a, ph_a, abort_flag);

@@ -61,7 +61,9 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
-// Bounded wait by a whole converged warp; the vote makes the result provably the same in every lane.
+// Bounded wait by a whole converged warp: every lane polls, and the vote makes the result provably the same in every lane.
+// (Polling from the elected lane alone, the others parked at the vote, was tried: launches then failed or ran into the wait
+// limit now and then, for a reason not found by reading; this form has run clean.)
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
 }
