@@ -97,10 +97,8 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // Activation quantiser for the block-scaled GEMM: bf16 rows (tensor scale 1) -> e2m1 codes [rows, K/2] and e4m3 scales
 // written straight into the 128 x 4 tiled layout. Same rule as quant_nvfp4_act_bf16 / fp4_encode
 // (native/kernels/kernels.cu:222-277): sf = e4m3_satfinite(max(absmax16/6, 1e-10)), code = fp4_encode(v / decode(sf)).
-// The division is replaced by comparing |v| with threshold * decode(sf): v has an 8-bit significand, decode(sf) a 4-bit
-// one and the thresholds at most 3 bits, so the products are exact and v / decode(sf) can only round onto a threshold
-// when it equals it; both forms give the same code, including decode(sf) = 0 (every comparison true: code 7, as
-// fp4_encode gives for inf and NaN). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
+// The codes come from the e2m1 conversion instruction, steered onto fp4_encode's rule on exact ties, -0 and decode(sf) = 0
+// (nvfp4_codes8 in common.cuh says how). One thread per 64 elements (four scale groups = one 32-bit word of a tile).
 // 16 values (already bf16-representable) -> scale byte and two words of codes
 __device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
   float m = 0.f;
@@ -111,16 +109,8 @@ __device__ __forceinline__ void quant_group16(const float (&v)[16], uint32_t& c0
   const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
   const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
   sb_out = sb;
-  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
-  c0 = 0;
-  c1 = 0;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = fabsf(v[i]);
-    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
-    e |= v[i] < 0.f ? 8u : 0u;
-    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
-  }
+  c0 = nvfp4_codes8(&v[0], sd);
+  c1 = nvfp4_codes8(&v[8], sd);
 }
 // SPLIT: the scale tiles are copied into TMEM by threads of their own (one per 2 KB scale set of the stage, each in a warp of
 // its own) that signal the MMA issuer through one more barrier per stage, so that the copies of a K block are not queued in front of that block's MMAs on the issuer's in-order

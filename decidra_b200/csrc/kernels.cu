@@ -170,8 +170,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // NVFP4 quantisation of 16 consecutive values held 8 + 8 by two neighbouring lanes (tensor scale 1; same rule as
-// quant_nvfp4_act_bf16 / fp4_encode, native/kernels/kernels.cu:222-277, with the division replaced by exact threshold
-// products as in the stand-alone activation quantiser). Returns this lane's 8 codes; *sb = the group's e4m3 scale byte.
+// quant_nvfp4_act_bf16 / fp4_encode, native/kernels/kernels.cu:222-277, the codes by nvfp4_codes8). Returns this lane's 8 codes; *sb = the group's e4m3 scale byte.
 __device__ __forceinline__ uint32_t nvfp4_encode_half_group(const float (&y)[8], uint32_t* sb_out) {
   float m = 0.f;
 #pragma unroll
@@ -182,16 +181,7 @@ __device__ __forceinline__ uint32_t nvfp4_encode_half_group(const float (&y)[8],
   const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
   const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
   *sb_out = sb;
-  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
-  uint32_t c = 0;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float a = fabsf(y[j]);
-    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
-    e |= y[j] < 0.f ? 8u : 0u;
-    c |= e << (4 * j);
-  }
-  return c;
+  return nvfp4_codes8(y, sd);
 }
 
 // QUANT: instead of the bf16 output row, write its NVFP4 image: codes to q_packed [rows, cols/2] and the e4m3 group scales
@@ -348,7 +338,7 @@ __global__ void rmsnorm_gated_kernel(const T* __restrict__ x, const T* __restric
   }
 }
 // 16 values (bf16-representable) -> e4m3 scale byte and 16 e2m1 codes in two words; the rule of quant_nvfp4_act_bf16 / fp4_encode
-// (native/kernels/kernels.cu:222-277) with tensor scale 1 and the division replaced by exact threshold products.
+// (native/kernels/kernels.cu:222-277) with tensor scale 1; the codes by nvfp4_codes8.
 __device__ __forceinline__ void nvfp4_encode_group16(const float (&v)[16], uint32_t& c0, uint32_t& c1, uint32_t& sb_out) {
   float m = 0.f;
 #pragma unroll
@@ -358,16 +348,8 @@ __device__ __forceinline__ void nvfp4_encode_group16(const float (&v)[16], uint3
   const __half_raw hr = __nv_cvt_fp8_to_halfraw(sb, __NV_E4M3);
   const float sd = __half2float(*reinterpret_cast<const __half*>(&hr));
   sb_out = sb;
-  const float t0 = 0.25f * sd, t1 = 0.75f * sd, t2 = 1.25f * sd, t3 = 1.75f * sd, t4 = 2.5f * sd, t5 = 3.5f * sd, t6 = 5.0f * sd;
-  c0 = 0;
-  c1 = 0;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = fabsf(v[i]);
-    uint32_t e = (a >= t0) + (a >= t1) + (a >= t2) + (a >= t3) + (a >= t4) + (a >= t5) + (a >= t6);
-    e |= v[i] < 0.f ? 8u : 0u;
-    if (i < 8) c0 |= e << (4 * i); else c1 |= e << (4 * (i - 8));
-  }
+  c0 = nvfp4_codes8(&v[0], sd);
+  c1 = nvfp4_codes8(&v[8], sd);
 }
 
 // bf16, cols == 128: 8 lanes per row, 16 consecutive elements per lane (16-byte loads and stores); same arithmetic.

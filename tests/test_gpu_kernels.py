@@ -751,6 +751,43 @@ def test_nvfp4_act_quant_tiled_matches_row_quantiser(G, oracle, rows, K, stride)
     assert np.array_equal(tiled.cpu().numpy(), want_tiled)
 
 
+def test_nvfp4_act_quant_on_ties_negative_zero_and_empty_groups(G, oracle):
+    """The activation quantiser takes its codes from the e2m1 conversion instruction (round to nearest even); the reference's rule
+    rounds a tie up and gives -0 no sign bit. Groups built to sit on every tie (c * scale for the seven midpoints, both signs), on
+    the bf16 neighbours of the ties, on -0, and groups so small that their scale decodes to zero, bit for bit against the oracle."""
+    import torch
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    scales = [2.0 ** -9, 2.0 ** -7 * 1.125, 0.4375, 1.0, 1.875, 52.0, 448.0 / 8]  # e4m3 values (subnormal, odd mantissas, large)
+
+    def bf16_step(v, up):  # the neighbouring bf16 value
+        bits = (np.float32(v).view(np.uint32) >> 16).astype(np.int64)
+        return ((bits + (1 if up else -1)).astype(np.uint32) << 16).view(np.float32)
+
+    groups = []
+    for sc in scales:
+        t = (ties * np.float32(sc)).astype(np.float32)
+        assert oracle.rb(t).tobytes() == t.tobytes()  # the ties are bf16 values
+        groups.append(np.concatenate([[6 * sc], t, [-0.0], -t]).astype(np.float32))
+        groups.append(np.concatenate([[-6 * sc], bf16_step(t, True), [0.0], bf16_step(t, False)]).astype(np.float32))
+        groups.append(np.concatenate([[6 * sc], -bf16_step(t, True), [-0.0], -bf16_step(t, False)]).astype(np.float32))
+    tiny = np.float32(2.0 ** -12)
+    groups.append(np.array([0.0, -0.0, tiny, -tiny] * 4, dtype=np.float32))          # scale decodes to zero: code 7 throughout
+    groups.append(np.zeros(16, dtype=np.float32))
+    groups.append(np.full(16, -0.0, dtype=np.float32))
+    while len(groups) % 4:
+        groups.append(np.arange(16, dtype=np.float32) - 7.5)
+    xf = oracle.rb(np.concatenate(groups).reshape(-1, 64))
+    rows, K = xf.shape
+    wp, ws, _ = oracle.k_nvfp4_rows(xf, 1.0)
+    want_tiled = oracle.nvfp4_scale_repack(ws, K)
+    packed = torch.zeros((rows, K // 2), dtype=torch.uint8, device="cuda")
+    tiled = torch.zeros((want_tiled.size,), dtype=torch.uint8, device="cuda")
+    G.call("dcd_k_nvfp4_quant_act_tiled", G.dev(xf, 1), K, packed, tiled, rows, K, None)
+    assert np.array_equal(tiled.cpu().numpy(), want_tiled)
+    got = packed.cpu().numpy()
+    assert np.array_equal(got, wp), f"first differing bytes at {np.argwhere(got != wp)[:8].tolist()}"
+
+
 @pytest.mark.parametrize("rows,I", [(5, 256), (131, 1024)])
 def test_nvfp4_swiglu_quant_tiled(G, oracle, rows, I):
     """SwiGLU fused with the NVFP4 quantiser against the two-step oracle (bf16 SwiGLU, then quantise). The kernel uses the
