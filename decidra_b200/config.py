@@ -77,7 +77,7 @@ class Options(C.Structure):
         ("nvfp4_fusion", C.c_int32),
         ("attn_split", C.c_int32),
         ("w4a16_prefetch", C.c_int32),
-        ("reserved", C.c_int32 * 1),
+        ("gdn_overlap", C.c_int32),
     ]
 
 

@@ -157,6 +157,9 @@ struct dcd_engine {
   // dequantisation it hides (8 layers: 54.96 ms per step with it, 53.56 without; identical results)
   void* wstage2 = nullptr;
   cudaStream_t stream2 = nullptr;
+  // gdn_overlap = 0: the state's delta rule of a one-pass cold request runs here while the questions' conv and preparation run on `stream`
+  cudaStream_t stream_gdn = nullptr;
+  cudaEvent_t gdn_fork = nullptr, gdn_join = nullptr;
   cudaEvent_t w4_free[2] = {nullptr, nullptr}, w4_ready[2] = {nullptr, nullptr};  // stage b: last GEMM that read it launched / image complete
   const void* w4_holds[2] = {nullptr, nullptr};                                    // the W4 whose image stage b holds or is being given
   bool w4_pending[2] = {false, false};                                             // written on stream2, not yet awaited by the main stream
@@ -597,45 +600,73 @@ int run_layers(dcd_engine* e, const Pass& p) {
         CK(e, launch_copy_rows<T>(big + (size_t)(g.tok0 + g.ntok - keep) * e->gin_n, e->gin_n, (T*)g.cap->hist[li] + (size_t)(3 - keep) * e->conv_dim,
                                   e->conv_dim, keep, e->conv_dim, s), "copy conv tail");
       }
-      {
-        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->conv_dim * e->esz * 2.0, 1);
-        e->launches += n_groups - 1;
-        for (int gi = 0; gi < n_groups; ++gi) {
-          const Group& g = groups[gi];
-          const size_t t0 = (size_t)g.tok0;
-          CK(e, launch_conv1d_silu<T>(big + t0 * e->gin_n, e->gin_n, p.mode == 1 && g.st ? (const T*)g.st->hist[li] : nullptr, (const T*)w.conv,
-                                      (T*)e->conv + t0 * e->conv_dim, e->d_cu, e->d_tokq + t0, g.ntok, e->conv_dim, s, g.tok0), "conv1d");
-        }
+      // A cold request in one pass = the state (group 0, rows [0, n)) and its questions (group 1). The state's delta rule occupies one
+      // CTA per value head (48 of the SMs) for 32 chunks in a row and the questions' needs its final state, so with gdn_overlap = 0
+      // it runs on a stream of its own while the conv and the preparation of the questions' rows run here; same kernels, same bits.
+      const bool overlap = e->stream_gdn && e->gdn_wy && p.mode == 1 && n_groups == 2 && groups[0].cap && groups[0].tok0 == 0 &&
+                           groups[1].tok0 == groups[0].ntok && groups[1].st == groups[0].cap;
+      auto conv_group = [&](const Group& g) {
+        const size_t t0 = (size_t)g.tok0;
+        return launch_conv1d_silu<T>(big + t0 * e->gin_n, e->gin_n, p.mode == 1 && g.st ? (const T*)g.st->hist[li] : nullptr, (const T*)w.conv,
+                                     (T*)e->conv + t0 * e->conv_dim, e->d_cu, e->d_tokq + t0, g.ntok, e->conv_dim, s, g.tok0);
+      };
+      auto prepare_rows = [&](size_t t0, int rows) {
+        const T* bsrc = big + t0 * e->gin_n + e->conv_dim + e->vd;
+        return launch_gdn_prepare<T>((const T*)e->conv + t0 * e->conv_dim, e->conv_dim, bsrc, bsrc + nv, e->gin_n, w.A_log, w.dt_bias,
+                                     e->qf + t0 * nk * dk, e->kf + t0 * nk * dk, e->g + t0 * nv, e->beta + t0 * nv, rows, nk, nv, dk, s);
+      };
+      auto gdn_group = [&](const Group& g, float* fin0, cudaStream_t gs) -> cudaError_t {  // sequences index the packed buffers through cu, so a group is a slice of cu
+        const float* seed = p.mode == 1 && g.st ? g.st->gstate[li] : nullptr;
+        float* fin = g.cap ? g.cap->gstate[li] : fin0;
+        const int32_t* cu = e->d_cu + g.q0;
+        if (e->gdn_wy) return launch_gdn_wy<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, gs);
+        if (e->gdn_tc) return launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, gs);
+        if (e->gdn_chunked)
+          return launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, dk, dv, g.nq < 2, gs);
+        return launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, dk, dv, g.nq < 8, gs);
+      };
+      if (e->gdn_tc && e->tm_gdn_tokens != T_) {
+        if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, e->conv, e->conv_dim, e->conv_dim, (int)e->esz, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
+        e->tm_gdn_tokens = T_;
       }
-      {
-        Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * nk * dk * (2.0 * e->esz + 8.0), 1);
-        const T* bsrc = big + e->conv_dim + e->vd;
-        CK(e, launch_gdn_prepare<T>((const T*)e->conv, e->conv_dim, bsrc, bsrc + nv, e->gin_n, w.A_log, w.dt_bias, e->qf, e->kf, e->g,
-                                    e->beta, T_, nk, nv, dk, s), "gdn_prepare");
-      }
-      {
-        Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
-        float* fin0 = p.mode == 0 ? p.cap->gstate[li] : nullptr;
-        if (e->gdn_tc && e->tm_gdn_tokens != T_) {
-          if (gdn_tc_make_maps(e->tm_gdn, e->qf, e->kf, e->conv, e->conv_dim, e->conv_dim, (int)e->esz, T_, nk) != 0) return fail(e, DCD_E_CUDA, "GDN q/k tensor maps");
-          e->tm_gdn_tokens = T_;
+      if (overlap) {
+        {
+          Scope sc(e, DCD_PROF_ELEMENTWISE, (double)groups[0].ntok * (e->conv_dim * e->esz * 2.0 + nk * dk * (2.0 * e->esz + 8.0)), 1);
+          e->launches += 1;
+          CK(e, conv_group(groups[0]), "conv1d");
+          CK(e, prepare_rows(0, groups[0].ntok), "gdn_prepare");
         }
-        e->launches += n_groups - 1;
-        for (int gi = 0; gi < n_groups; ++gi) {  // sequences index the packed buffers through cu, so a group is a slice of cu
-          const Group& g = groups[gi];
-          const float* seed = p.mode == 1 && g.st ? g.st->gstate[li] : nullptr;
-          float* fin = g.cap ? g.cap->gstate[li] : fin0;
-          const int32_t* cu = e->d_cu + g.q0;
-          if (e->gdn_wy)
-            CK(e, launch_gdn_wy<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, s), "gdn_wy");
-          else if (e->gdn_tc)
-            CK(e, launch_gdn_tc<T>(e->tm_gdn, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, e->d_err, s), "gdn_tc");
-          else if (e->gdn_chunked)
-            CK(e, launch_gdn_chunked<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv, dk,
-                                        dv, g.nq < 2, s), "gdn_chunked");
-          else
-            CK(e, launch_gdn_recurrent<T>(e->qf, e->kf, (const T*)e->conv, e->conv_dim, e->g, e->beta, seed, fin, (T*)e->bufA, cu, g.nq, nk, nv,
-                                          dk, dv, g.nq < 8, s), "gdn_recurrent");
+        CK(e, cudaEventRecord(e->gdn_fork, s), "GDN fork");
+        CK(e, cudaStreamWaitEvent(e->stream_gdn, e->gdn_fork, 0), "GDN fork");
+        CK(e, gdn_group(groups[0], nullptr, e->stream_gdn), "gdn_wy");
+        CK(e, cudaEventRecord(e->gdn_join, e->stream_gdn), "GDN join");
+        {
+          Scope sc(e, DCD_PROF_ELEMENTWISE, (double)groups[1].ntok * (e->conv_dim * e->esz * 2.0 + nk * dk * (2.0 * e->esz + 8.0)), 1);
+          e->launches += 1;
+          CK(e, conv_group(groups[1]), "conv1d");
+          CK(e, prepare_rows((size_t)groups[1].tok0, groups[1].ntok), "gdn_prepare");
+        }
+        {
+          Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
+          e->launches += 1;
+          CK(e, cudaStreamWaitEvent(s, e->gdn_join, 0), "GDN join");
+          CK(e, gdn_group(groups[1], nullptr, s), "gdn_wy");
+        }
+      } else {
+        {
+          Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * e->conv_dim * e->esz * 2.0, 1);
+          e->launches += n_groups - 1;
+          for (int gi = 0; gi < n_groups; ++gi) CK(e, conv_group(groups[gi]), "conv1d");
+        }
+        {
+          Scope sc(e, DCD_PROF_ELEMENTWISE, (double)T_ * nk * dk * (2.0 * e->esz + 8.0), 1);
+          CK(e, prepare_rows(0, T_), "gdn_prepare");
+        }
+        {
+          Scope sc(e, DCD_PROF_GDN, 6.0 * dk * dv * (double)T_ * nv, 1);
+          float* fin0 = p.mode == 0 ? p.cap->gstate[li] : nullptr;
+          e->launches += n_groups - 1;
+          for (int gi = 0; gi < n_groups; ++gi) CK(e, gdn_group(groups[gi], fin0, s), "gdn");
         }
       }
       if (p.mode == 0 && li + 1 == c.num_layers) break;  // last capture layer: the state and conv tail are stored
@@ -872,6 +903,7 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   if (o.nvfp4_fusion < 0 || o.nvfp4_fusion > 1) return fail(nullptr, DCD_E_INVALID, "nvfp4_fusion must be 0 or 1");
   if (o.attn_split < 0 || o.attn_split > 1) return fail(nullptr, DCD_E_INVALID, "attn_split must be 0 or 1");
   if (o.w4a16_prefetch < 0 || o.w4a16_prefetch > 1) return fail(nullptr, DCD_E_INVALID, "w4a16_prefetch must be 0 or 1");
+  if (o.gdn_overlap < 0 || o.gdn_overlap > 1) return fail(nullptr, DCD_E_INVALID, "gdn_overlap must be 0 or 1");
   if (o.max_pass_tokens <= 0) o.max_pass_tokens = 16384;
   if (o.max_rows <= 0) o.max_rows = 256;
   if (o.max_keys <= 0) o.max_keys = (int64_t)1 << 22;
@@ -959,6 +991,11 @@ int dcd_engine_create(const dcd_model_config* cfg, const dcd_options* opt, int d
   e->gdn_wy = e->gdn_tc && o.gdn_path == 0;
   if (e->gdn_tc) CRE(gdn_tc_prepare_device<bf16>(), "tcgen05 GDN shared-memory attribute");
   if (e->gdn_wy) CRE(gdn_wy_prepare_device<bf16>(), "tcgen05 WY GDN shared-memory attribute");
+  if (e->gdn_wy && o.gdn_overlap == 0) {
+    CRE(cudaStreamCreateWithFlags(&e->stream_gdn, cudaStreamNonBlocking), "GDN stream");
+    CRE(cudaEventCreateWithFlags(&e->gdn_fork, cudaEventDisableTiming), "event");
+    CRE(cudaEventCreateWithFlags(&e->gdn_join, cudaEventDisableTiming), "event");
+  }
   e->gdn_chunked = e->bf && !e->gdn_tc && (o.gdn_path == 0 || o.gdn_path == 2) && gdn_chunked_supported(c.gdn_dk, c.gdn_dv);
   if (e->gdn_chunked) CRE(gdn_chunked_prepare_device<bf16>(), "chunked GDN shared-memory attribute");
 
@@ -1180,6 +1217,9 @@ void dcd_engine_destroy(dcd_engine* e) {
   if (e->t0) cudaEventDestroy(e->t0);
   if (e->t1) cudaEventDestroy(e->t1);
   if (e->stream2) { cudaStreamSynchronize(e->stream2); cudaStreamDestroy(e->stream2); }
+  if (e->stream_gdn) { cudaStreamSynchronize(e->stream_gdn); cudaStreamDestroy(e->stream_gdn); }
+  if (e->gdn_fork) cudaEventDestroy(e->gdn_fork);
+  if (e->gdn_join) cudaEventDestroy(e->gdn_join);
   for (int i = 0; i < 2; ++i) {
     if (e->w4_free[i]) cudaEventDestroy(e->w4_free[i]);
     if (e->w4_ready[i]) cudaEventDestroy(e->w4_ready[i]);

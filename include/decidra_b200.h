@@ -95,7 +95,9 @@ typedef struct dcd_options {
   int32_t w4a16_prefetch;   /* precision 1, staged route: 0 = default: one stage, dequantise then multiply; 1 = the next projection's weight is
                                dequantised on a second stream into a second stage while the tensor cores run the current projection (same
                                results; measured slower under the power cap, kept for boxes that are not power-limited) */
-  int32_t reserved[1];
+  int32_t gdn_overlap;      /* the cold request in one pass, GDN layers: 0 = default: the state's delta rule (one CTA per value head, 48 of the
+                               SMs) runs on a second stream while the causal conv and the q/k/g/beta preparation of the questions' rows run on
+                               the first; the questions' delta rule waits for it (same results); 1 = everything in stream order */
 } dcd_options;
 
 typedef struct dcd_info {
