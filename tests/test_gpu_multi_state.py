@@ -96,11 +96,14 @@ def test_multi_state_pass_quantised_engines(dcd, precision):
     e.close()
 
 
-@pytest.mark.parametrize("which", ["tiny_f32", "tiny_bf16", "d3_slice", "d3_slice_nvfp4", "d3_slice_w4a16"])
+@pytest.mark.parametrize("which", ["tiny_f32", "tiny_bf16", "d3_slice", "d3_slice_stream_order", "d3_slice_nvfp4", "d3_slice_w4a16"])
 def test_cold_request_in_one_pass_is_bit_identical_to_capture_then_readout(dcd, which):
     """dcd_capture_and_readout: the state rides in the same pass as its questions. Logits and every tensor of the returned cache
     must equal those of capture_state + readout_state_once_batch bit for bit, on the fallback kernels (tiny model) and on the
-    tensor-core kernels (d3-shaped slice, also with NVFP4 and W4A16 weights); the cache must serve a later warm request."""
+    tensor-core kernels (d3-shaped slice, also with NVFP4 and W4A16 weights); the cache must serve a later warm request. On the
+    d3-shaped slice the state's delta rule runs on a second stream beside the questions' conv and preparation (state lengths that
+    are not a multiple of the 64-token chunk make its last chunk read rows the other stream is writing, masked in the kernel);
+    "stream_order" switches that off (gdn_overlap = 1)."""
     if which.startswith("tiny"):
         cfg = dcd.tiny_config(0 if which == "tiny_f32" else 1)
         vocab, cases = cfg.vocab, [(128, (16, 20, 24, 32)), (2, (1,)), (67, (5, 64, 3))]
@@ -110,6 +113,7 @@ def test_cold_request_in_one_pass_is_bit_identical_to_capture_then_readout(dcd, 
     opt = dcd.Options()
     opt.max_pass_tokens = 1024
     opt.precision = {"d3_slice_nvfp4": 3, "d3_slice_w4a16": 1}.get(which, 0)
+    opt.gdn_overlap = 1 if which == "d3_slice_stream_order" else 0
     e = dcd.Engine(cfg, opt)
     e.init_random(0)
     rng = np.random.Generator(np.random.PCG64(11))
@@ -129,6 +133,12 @@ def test_cold_request_in_one_pass_is_bit_identical_to_capture_then_readout(dcd, 
                     assert a.tobytes() == b.tobytes(), (which, S, li, kind)
         warm = e.readout_state_once_batch(st_b, qs[:1])
         assert warm.tobytes() == want[:1].tobytes()
+        if which == "d3_slice" and S % 64:  # the two streams race on nothing: the same bits every time
+            for _ in range(8):
+                st_c, again = e.capture_and_readout(state, qs)
+                assert again.tobytes() == want.tobytes()
+                assert all(st_c.tensor(li, 2).tobytes() == st_a.tensor(li, 2).tobytes() for li in range(cfg.num_layers) if st_a.tensor(li, 2) is not None)
+                st_c.free()
         st_a.free()
         st_b.free()
     # a request that does not fit one pass takes the two-pass order by itself
