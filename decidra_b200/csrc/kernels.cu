@@ -606,9 +606,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_vec256_kernel(const bf16* __
     unpack8(*reinterpret_cast<const uint4*>(sin_t + (size_t)pos * rhalf + f0), sn);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      // first half: a = own, b = partner: a c - b s; second half: a = partner, b = own: b c + a s
-      if (lo) v[i] = Ty<bf16>::rnd(__fsub_rn(Ty<bf16>::rnd(__fmul_rn(v[i], c[i])), Ty<bf16>::rnd(__fmul_rn(o[i], sn[i]))));
-      else v[i] = Ty<bf16>::rnd(__fadd_rn(Ty<bf16>::rnd(__fmul_rn(v[i], c[i])), Ty<bf16>::rnd(__fmul_rn(o[i], sn[i]))));
+      // first half: a = own, b = partner: a c - b s; second half: a = partner, b = own: b c + a s. Both are own * c -/+ partner * s;
+      // a - b and a + (-b) are the same sum, so the halves share one instruction stream instead of diverging
+      const float bs = Ty<bf16>::rnd(__fmul_rn(o[i], sn[i]));
+      v[i] = Ty<bf16>::rnd(__fadd_rn(Ty<bf16>::rnd(__fmul_rn(v[i], c[i])), lo ? -bs : bs));
     }
   }
   reinterpret_cast<uint4*>(dst)[lane] = pack8(v);
