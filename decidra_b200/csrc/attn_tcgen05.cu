@@ -74,6 +74,12 @@ __device__ __forceinline__ float ex2_ftz_ordered(float x) {
   return y;
 }
 
+// The output gate: sigmoid with the hardware exponential and reciprocal approximations (about 2 ulp in f32). Its result is rounded to
+// bf16 straight away (sigmoid_gate_bf16, native/kernels/kernels.cu:504-512, rounds there too), which hides the difference except on
+// rare rounding ties; the accurate expf and division cost about 25 instructions per element, 128 elements per thread, and made the
+// epilogue a third of a CTA's time at 2048 keys (30 k of 93 k cycles).
+__device__ __forceinline__ float sigmoid_gate(float g) { return __fdividef(1.0f, 1.0f + __expf(-g)); }
+
 struct Params {
   const int32_t* cu;       // [B+1] packed sequence offsets
   const int32_t* tile_cu;  // [B+1] prefix sum of token tiles per sequence
@@ -131,6 +137,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   // bar_s / bar_p: two each (by tile parity); k_full / k_empty: one pair per K slab slot
   const uint32_t bar_q = bars, bar_v = bars + 24, bar_s = bars + 40, bar_p = bars + 56, bar_o = bars + 72;
   const uint32_t k_full = bars + 128, k_empty = bars + 128 + 8 * K_SLOTS;
+  // bar_o counts one phase per tile and its waiters test a phase PARITY, which is only sound while the barrier is at most one
+  // phase behind what they wait for. That holds for the V loader (in lockstep) and for the rescale (S[j] done implies P.V[j-2]
+  // done: the tensor core runs the issuer's instructions in order), but not for the epilogue: the softmax can finish the last
+  // tile while P.V of the tile before it still waits for its V tile, and the parity of the last phase then reads as complete.
+  // The end of the last product therefore has a barrier of its own, used once.
+  const uint32_t bar_done = k_empty + 8 * K_SLOTS;
+  static_assert(128 + 16 * K_SLOTS + 8 <= 256, "barrier area");
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars_ptr + 80);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 84);
 
@@ -144,6 +157,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar_p, 256);
     mbar_init(bar_p + 8, 256);
     mbar_init(bar_o, 1);
+    mbar_init(bar_done, 1);
     for (int i = 0; i < 4; ++i) mbar_init(bars + 88 + 8 * i, 64);  // one per pair of softmax warps
     for (int i = 0; i < K_SLOTS; ++i) {
       mbar_init(k_full + 8 * i, 1);
@@ -251,6 +265,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int k = 0; k < KT / 16; ++k)  // P[j] sits over S[j]: 16 keys = 8 packed columns per step
             umma_f16_ts(tmem_base + O_COL, tmem_base + S_COL + s * KT + k * 8, dv + (uint64_t)(k * (16 * 128 / 16)), IDESC_PV, (j | k) != 0 ? 1u : 0u);
           umma_commit_to(bar_o);
+          if (j + 1 == n_tiles) umma_commit_to(bar_done);
         }
       }
     }
@@ -366,7 +381,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     // ---- epilogue: O / l, output gate, store (each thread of the pair takes half of the head dims) -----------------
     if (ok) {
-      ok = mbar_wait(bar_o, (uint32_t)((n_tiles - 1) & 1), abort_flag);
+      ok = mbar_wait(bar_done, 0, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -400,11 +415,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const int t = off + t0 + tt, head = kh * G + g;
       const float inv = 1.0f / l;
       bf16* orow = p.out + ((size_t)t * p.heads + head) * HD;
-      const bf16* grow = p.gate_qg ? p.gate_qg + (size_t)t * p.qg_stride + (size_t)head * 2 * HD + HD : nullptr;
+      const bf16* grow = p.gate_qg && live ? p.gate_qg + (size_t)t * p.qg_stride + (size_t)head * 2 * HD + HD : nullptr;
+      // the gate values of a 32-column chunk are requested before the chunk's accumulator is read from TMEM, those of the next chunk
+      // while this one is worked on, so that no load latency sits between the chunks
+      uint4 gv[4], gn[4];
+      const int c_lo = h * (HD / 64), c_hi = (h + 1) * (HD / 64);
+      if (grow) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) gv[q4] = __ldg(reinterpret_cast<const uint4*>(grow + c_lo * 32 + q4 * 8));
+      }
 #pragma unroll 1
-      for (int c = h * (HD / 64); c < (h + 1) * (HD / 64); ++c) {
+      for (int c = c_lo; c < c_hi; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_base + lane_addr + O_COL + c * 32, v);
+        if (grow && c + 1 < c_hi) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) gn[q4] = __ldg(reinterpret_cast<const uint4*>(grow + (c + 1) * 32 + q4 * 8));
+        }
         tmem_ld_wait();
         if (live) {
 #pragma unroll
@@ -413,12 +440,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = Ty<bf16>::rnd(__uint_as_float(v[q4 * 8 + i]) * inv);
             if (grow) {
-              const uint4 gv = *reinterpret_cast<const uint4*>(grow + c * 32 + q4 * 8);
-              const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+              const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv[q4]);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                o[2 * i] *= Ty<bf16>::rnd(sigmoid_f(__low2float(g2[i])));
-                o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_f(__high2float(g2[i])));
+                o[2 * i] *= Ty<bf16>::rnd(sigmoid_gate(__low2float(g2[i])));
+                o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_gate(__high2float(g2[i])));
               }
             }
             uint4 ov;
@@ -429,6 +455,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = ov;
           }
         }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) gv[q4] = gn[q4];
       }
     }
   }
@@ -518,8 +546,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const Params p, int n_s
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      o[2 * i] *= Ty<bf16>::rnd(sigmoid_f(__low2float(g2[i])));
-      o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_f(__high2float(g2[i])));
+      o[2 * i] *= Ty<bf16>::rnd(sigmoid_gate(__low2float(g2[i])));
+      o[2 * i + 1] *= Ty<bf16>::rnd(sigmoid_gate(__high2float(g2[i])));
     }
   }
   *reinterpret_cast<uint4*>(p.out + ((size_t)t * p.heads + head) * HD + lane * 8) =

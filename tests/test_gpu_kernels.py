@@ -419,6 +419,47 @@ def test_attention_split_kv_vs_oracle(G, oracle, lens, S, n_split):
     assert (np.abs(got - ref) <= 2e-2 * np.abs(ref) + 2e-3).all(), float(np.abs(got - ref).max())
 
 
+@pytest.mark.parametrize("n_split", [16, 0])
+def test_attention_split_kv_same_bits_every_run(G, n_split):
+    """The parts of a split launch run two to four key tiles each, their K/V comes cold from HBM, and the softmax warps reach the
+    epilogue while the product of the tile before the last still waits for its V tile: the end of the LAST product has a barrier
+    of its own (a phase-parity wait on the per-tile barrier read as complete one product early and left whole tiles out of the
+    partial outputs). Repeated with whatever the workspace held before and with the caches flushed: the same bits every time,
+    and the unsplit kernel's result within rounding."""
+    import torch
+    heads, kv, hd, S, T = 24, 4, 256, 16384, 16
+    torch.manual_seed(5)
+    q = torch.randn(T, heads, hd, device="cuda").bfloat16()
+    ko = torch.randn(T, kv * hd, device="cuda").bfloat16()
+    vo = torch.randn(T, kv * hd, device="cuda").bfloat16()
+    ks = torch.randn(S, kv, hd, device="cuda").bfloat16()
+    vs = torch.randn(S, kv, hd, device="cuda").bfloat16()
+    qg = torch.randn(T, heads, 2 * hd, device="cuda").bfloat16()
+    cu = G.devi(np.array([0, T]))
+    tile_cu = G.devi(np.zeros(2))
+    err = G.devi([0])
+    dev = (q, ko, kv * hd, vo, kv * hd, ks, vs, S, qg, heads * 2 * hd)
+    tail = (cu, tile_cu, 1, T, heads, kv, hd, err)
+    plain = torch.full((T, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.call("dcd_k_attention_tc", *dev, plain, *tail, None)
+    ws_bytes = 2 * G.sm_count() * 128 * 1032
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    first = None
+    for _ in range(12):
+        ws.random_(0, 256)
+        flush.zero_()
+        out = torch.full((T, heads, hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.call("dcd_k_attention_tc_split", *dev, out, *tail, n_split, ws, C.c_size_t(ws_bytes), None)
+        torch.cuda.synchronize()
+        if first is None:
+            first = out.clone()
+            assert float((first.float() - plain.float()).abs().max()) < 1e-3
+        else:
+            assert torch.equal(out.view(torch.int16), first.view(torch.int16))
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("dtype,nk,nv,dv,narrow", [(1, 16, 48, 128, 0), (1, 16, 48, 128, 1), (0, 2, 6, 64, 0), (0, 2, 6, 64, 1)])
 def test_gdn_chunked_vs_oracle(G, oracle, dtype, nk, nv, dv, narrow):
     """Chunked tensor-core gated delta rule against the sequential oracle, with the tolerances of the
