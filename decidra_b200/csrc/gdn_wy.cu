@@ -170,6 +170,7 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int head = blockIdx.x, b = blockIdx.y;
   unsigned long long pacc[PROF ? 16 : 1];
   long long plast = 0;
+  const long long t_entry = PROF ? clock64() : 0;  // phase 13: kernel entry to the first chunk (allocation, seed, first tiles)
   if (PROF) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) pacc[i] = 0;
@@ -292,7 +293,10 @@ gdn_wy_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const float* sE = sG + 128;
     const float* sGam = sG + 192;
     __syncthreads();  // scalars visible; S^T of the previous chunk written and fenced by every thread
-    if (PROF && tid == 0 && ci == 0) plast = clock64();
+    if (PROF && tid == 0 && ci == 0) {
+      plast = clock64();
+      pacc[13] += (unsigned long long)(plast - t_entry);
+    }
 
     // ---- D1 = [K;Q] K^T ---------------------------------------------------------------------------------------------------------
     ok = mbar_wait(bar_kq, (uint32_t)(ci & 1), abort_flag);  // every thread reads the K tile below
