@@ -149,3 +149,39 @@ def test_cold_request_in_one_pass_is_bit_identical_to_capture_then_readout(dcd, 
     st_b, got = e.capture_and_readout(state, qs)
     assert got.tobytes() == want.tobytes()
     e.close()
+
+
+@pytest.mark.parametrize("precision", [0, 3])
+def test_cold_request_same_bits_with_flushed_caches(dcd, precision):
+    """A cold request repeated with every cache line evicted in between (different arrival times of every tile, the state's delta
+    rule on its own stream): logits and cache tensors identical run after run, one-pass equal to capture + question pass; the
+    second case has so few question rows that the attention splits its key range over CTAs."""
+    import torch
+    cfg = dcd.d3_config(num_layers=4, dtype=1, vocab=4096)
+    opt = dcd.Options()
+    opt.max_pass_tokens = 6144
+    opt.precision = precision
+    e = dcd.Engine(cfg, opt)
+    e.init_random(0)
+    rng = np.random.Generator(np.random.PCG64(21))
+    flush = torch.empty(300 << 20, dtype=torch.uint8, device="cuda")
+    for S, lens in ((1100, rng.integers(16, 161, 12)), (4096, [16, 20])):
+        state = rng.integers(0, 4096, S, dtype=np.uint32)
+        qs = [rng.integers(0, 4096, int(n), dtype=np.uint32) for n in lens]
+        first = None
+        for _ in range(5):
+            flush.random_(0, 256)
+            torch.cuda.synchronize()
+            st, out = e.capture_and_readout(state, qs)
+            sig = [st.tensor(li, k).tobytes() for li in range(cfg.num_layers) for k in range(4) if st.tensor(li, k) is not None]
+            st.free()
+            if first is None:
+                first = (out.tobytes(), sig)
+            else:
+                assert out.tobytes() == first[0] and sig == first[1]
+        st = e.capture_state(state)
+        two = e.readout_state_once_batch(st, qs)
+        st.free()
+        assert two.tobytes() == first[0]
+    e.close()
+
